@@ -1,0 +1,7 @@
+from .manager import CacheGroup, CacheLayout, CacheManager, FixedState, PagedKV, RequestCache
+from .pages import BlockTable, CacheAccountingError, OutOfPages, PagePool, StateSlots
+
+__all__ = [
+    "CacheGroup", "CacheLayout", "CacheManager", "FixedState", "PagedKV", "RequestCache", "BlockTable",
+    "CacheAccountingError", "OutOfPages", "PagePool", "StateSlots",
+]

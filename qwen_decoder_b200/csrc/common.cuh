@@ -1,0 +1,54 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions.
+//
+// Every launcher is `extern "C"`, takes raw device pointers and a stream, launches
+// on that stream and returns the `cudaGetLastError()` code (0 = success).  Element
+// types are passed as a code: 0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define QD_F32 0
+#define QD_BF16 1
+
+// Returned by launchers for arguments a kernel refuses (never a wrong result).
+#define QD_ERR_UNSUPPORTED 10001
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; the order of additions depends only on
+// the block size, so a row's result does not depend on what else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int qd_last_error() { return (int)cudaGetLastError(); }

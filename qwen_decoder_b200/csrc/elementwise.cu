@@ -1,0 +1,223 @@
+// Row-wise kernels of the decoder step: embedding gather, residual add + RMSNorm,
+// rotary position encoding fused with the write of K and V into cache pages, and
+// the SwiGLU gate.  One template per kernel serves the float32 path and the
+// bfloat16 path; all arithmetic is float32.
+//
+// What each replaces in the reference: embedding_kernel (gpu_kernels.cu:18-29),
+// residual_kernel + rmsnorm_kernel (gpu_kernels.cu:136-146, 32-67), rope_kernel +
+// kvcache_write_kernel (gpu_kernels.cu:82-133), swiglu_kernel (gpu_kernels.cu:149-160).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// x[t, :] = table[tokens[t], :]; the residual stream x is float32 in both paths.
+template <typename TW>
+__global__ void embedding_kernel(float* __restrict__ x, const TW* __restrict__ table,
+                                 const int* __restrict__ tokens, int D) {
+  int t = blockIdx.x;
+  const TW* row = table + (size_t)tokens[t] * D;
+  float* out = x + (size_t)t * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+extern "C" int qd_embedding(float* x, const void* table, int table_dtype, const int* tokens,
+                            int T, int D, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (table_dtype == QD_F32)
+    embedding_kernel<float><<<T, 256, 0, stream>>>(x, (const float*)table, tokens, D);
+  else if (table_dtype == QD_BF16)
+    embedding_kernel<bf16><<<T, 256, 0, stream>>>(x, (const bf16*)table, tokens, D);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// ------------------------------------------------- residual add + RMSNorm
+// For output row r (source row s = rows ? rows[r] : r):
+//   v = x[s] + delta[s]            (float32; delta may be absent)
+//   x[s] = v                       (if write_back)
+//   out[r] = v / sqrt(mean(v^2) + eps) * w
+// The sum of squares is taken in a fixed order that depends only on D.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                   const float* __restrict__ w, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int D, float eps, int write_back) {
+  extern __shared__ float sm[];  // D values + 33 scratch
+  float* v = sm;
+  float* scratch = sm + D;
+  int r = blockIdx.x;
+  size_t s = rows ? (size_t)rows[r] : (size_t)r;
+  float* xr = x + s * D;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float a = xr[i];
+    if (delta) a += to_float(delta[s * D + i]);
+    v[i] = a;
+    if (write_back && delta) xr[i] = a;
+    ss += a * a;
+  }
+  ss = block_sum(ss, scratch);
+  float inv = 1.0f / sqrtf(ss / (float)D + eps);
+  TO* o = out + (size_t)r * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_float<TO>(v[i] * inv * w[i]);
+}
+
+extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* w, void* out,
+                              int out_dtype, const int* rows, int n_rows, int D, float eps,
+                              int write_back, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  size_t smem = (size_t)(D + 40) * sizeof(float);
+  if (smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
+#define LAUNCH(TD, TO)                                                                          \
+  do {                                                                                          \
+    if (smem > 48 * 1024)                                                                       \
+      cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           (int)smem);                                                          \
+    add_rmsnorm_kernel<TD, TO><<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, w, (TO*)out, rows, \
+                                                              D, eps, write_back);              \
+  } while (0)
+  bool dbf = delta && delta_dtype == QD_BF16;
+  if (delta && delta_dtype != QD_BF16 && delta_dtype != QD_F32) return QD_ERR_UNSUPPORTED;
+  if (out_dtype == QD_F32) {
+    if (dbf) LAUNCH(bf16, float); else LAUNCH(float, float);
+  } else if (out_dtype == QD_BF16) {
+    if (dbf) LAUNCH(bf16, bf16); else LAUNCH(float, bf16);
+  } else {
+    return QD_ERR_UNSUPPORTED;
+  }
+#undef LAUNCH
+  return qd_last_error();
+}
+
+// x[t] += delta[t] with no norm after it (used when a residual is left pending at
+// the end of a schedule that does not finish with a norm).
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += to_float(delta[i]);
+}
+
+extern "C" int qd_residual_add(float* x, const void* delta, int delta_dtype, long long n,
+                               cudaStream_t stream) {
+  if (n <= 0) return 0;
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  if (delta_dtype == QD_F32)
+    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
+  else if (delta_dtype == QD_BF16)
+    residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, (size_t)n);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// -------------------------------------------- rotary + K/V write into pages
+// qkv row t = [ q (H*d) | k (G*d) | v (G*d) ].  q and k are rotated by the angle
+// table row of positions[t]; q stays in place, k and v go to the token's slot of the
+// layer's cache, laid out [page][K or V][kv head][offset in page][d].
+// Pairing 0 rotates elements (2p, 2p+1) (the reference's rope_kernel,
+// gpu_kernels.cu:94-100); pairing 1 rotates (p, p + rotary_dim/2).
+// cos/sin are float32 tables [positions, rotary_dim/2]; a null table means "no rotation".
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, int H, int G, int d, int rotary_dim,
+                                     int pairing, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t,
+                                     const int* __restrict__ positions, T* __restrict__ kv,
+                                     const int* __restrict__ slot_map, int page_size, int write_kv) {
+  int t = blockIdx.x;
+  int row_w = (H + 2 * G) * d;
+  T* row = qkv + (size_t)t * row_w;
+  int half = rotary_dim >> 1;
+  const float* c = cos_t ? cos_t + (size_t)positions[t] * half : nullptr;
+  const float* s = cos_t ? sin_t + (size_t)positions[t] * half : nullptr;
+  size_t kbase = 0, vbase = 0;
+  int off = 0;
+  if (write_kv) {
+    int slot = slot_map[t];
+    int page = slot / page_size;
+    off = slot - page * page_size;
+    kbase = (size_t)page * 2 * G * page_size * d;
+    vbase = kbase + (size_t)G * page_size * d;
+  }
+  // One work item = one (head, pair) of q or k, or one (head, element pair) of v.
+  int pairs_per_head = d >> 1;
+  int n_qk = (H + G) * pairs_per_head;
+  for (int w = threadIdx.x; w < n_qk; w += blockDim.x) {
+    int head = w / pairs_per_head, p = w - head * pairs_per_head;
+    T* hp = row + (size_t)head * d;  // q heads then k heads are contiguous in the row
+    int i0, i1;
+    bool rot = p < half;
+    if (pairing == 0) { i0 = 2 * p; i1 = 2 * p + 1; }
+    else if (rot)     { i0 = p; i1 = p + half; }
+    else              { // elements beyond the rotated width pass through, two at a time
+      int j = 2 * (p - half) + rotary_dim; i0 = j; i1 = j + 1; }
+    if (pairing == 0) rot = (2 * p + 1) < rotary_dim;
+    float a = to_float(hp[i0]), b = to_float(hp[i1]);
+    float ra = a, rb = b;
+    if (rot && c) {
+      float cv = c[p], sv = s[p];
+      ra = a * cv - b * sv;
+      rb = a * sv + b * cv;
+    }
+    if (head < H) {
+      hp[i0] = from_float<T>(ra);
+      hp[i1] = from_float<T>(rb);
+    } else if (write_kv) {
+      int g = head - H;
+      T* dst = kv + kbase + ((size_t)g * page_size + off) * d;
+      dst[i0] = from_float<T>(ra);
+      dst[i1] = from_float<T>(rb);
+    }
+  }
+  if (write_kv) {
+    const T* vrow = row + (size_t)(H + G) * d;
+    for (int w = threadIdx.x; w < G * d; w += blockDim.x) {
+      int g = w / d, i = w - g * d;
+      kv[vbase + ((size_t)g * page_size + off) * d + i] = vrow[w];
+    }
+  }
+}
+
+extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d, int rotary_dim,
+                                int pairing, const float* cos_t, const float* sin_t,
+                                const int* positions, void* kv, const int* slot_map, int page_size,
+                                int write_kv, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((d & 1) || (rotary_dim & 1) || rotary_dim > d || rotary_dim < 0) return QD_ERR_UNSUPPORTED;
+  if (dtype == QD_F32)
+    rope_kv_write_kernel<float><<<T, 256, 0, stream>>>((float*)qkv, H, G, d, rotary_dim, pairing, cos_t,
+                                                       sin_t, positions, (float*)kv, slot_map,
+                                                       page_size, write_kv);
+  else if (dtype == QD_BF16)
+    rope_kv_write_kernel<bf16><<<T, 256, 0, stream>>>((bf16*)qkv, H, G, d, rotary_dim, pairing, cos_t,
+                                                      sin_t, positions, (bf16*)kv, slot_map,
+                                                      page_size, write_kv);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// gate_up row = [ gate (F) | up (F) ];  out = gate / (1 + exp(-gate)) * up, in float32
+// (the reference's swiglu_kernel, gpu_kernels.cu:157-158).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int F, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  size_t t = i / F;
+  int f = (int)(i - t * F);
+  float g = to_float(gate_up[t * 2 * F + f]);
+  float u = to_float(gate_up[t * 2 * F + F + f]);
+  out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+extern "C" int qd_swiglu(const void* gate_up, void* out, int dtype, int T, int F, cudaStream_t stream) {
+  size_t n = (size_t)T * F;
+  if (n == 0) return 0;
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == QD_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, F, n);
+  else if (dtype == QD_BF16)
+    swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, F, n);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}

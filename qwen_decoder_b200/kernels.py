@@ -1,0 +1,169 @@
+"""Python side of the CUDA kernels: one function per launcher in ``csrc/``.
+
+Every function takes CUDA tensors, launches on torch's current stream and raises on
+any error.  There is no CPU path and no library fallback here: a tensor that is not
+on a CUDA device, or a kernel library that cannot be built or loaded, is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import library
+
+F32, BF16 = 0, 1
+ERR_UNSUPPORTED = 10001
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernel argument is not on a CUDA device (there is no CPU path)")
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == ERR_UNSUPPORTED:
+        raise KernelError(f"{what}: the kernel refuses these sizes or types")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_I, _LL, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+# ------------------------------------------------------------------ elementwise
+def embedding(x_out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor) -> None:
+    """x_out[t, :] = table[tokens[t], :]; x_out float32 [T, D], tokens int32 [T]."""
+    T, D = x_out.shape
+    assert x_out.dtype == torch.float32 and tokens.dtype == torch.int32 and table.shape[1] == D
+    _contig(x_out, "x_out"); _contig(table, "table")
+    _check(library("elementwise").qd_embedding(_ptr(x_out), _ptr(table), _I(dtype_code(table.dtype)),
+                                               _ptr(tokens), _I(T), _I(D), _stream()), "embedding")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                eps: float, rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+    """out[r] = rmsnorm(x[s] + delta[s]) * weight with s = rows[r] (or r); x float32 [T, D] is
+    updated to x + delta when ``write_back``."""
+    D = x.shape[1]
+    n_rows = out.shape[0]
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == D
+    assert out.shape[1] == D and (rows is None or (rows.dtype == torch.int32 and rows.numel() == n_rows))
+    assert rows is not None or n_rows == x.shape[0]
+    _contig(x, "x"); _contig(out, "out")
+    if delta is not None:
+        assert delta.shape == x.shape
+        _contig(delta, "delta")
+    _check(library("elementwise").qd_add_rmsnorm(
+        _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype) if delta is not None else -1), _ptr(weight),
+        _ptr(out), _I(dtype_code(out.dtype)), _ptr(rows), _I(n_rows), _I(D), _F(eps),
+        _I(1 if write_back else 0), _stream()), "add_rmsnorm")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    assert x.dtype == torch.float32 and x.shape == delta.shape
+    _contig(x, "x"); _contig(delta, "delta")
+    _check(library("elementwise").qd_residual_add(_ptr(x), _ptr(delta), _I(dtype_code(delta.dtype)),
+                                                  _LL(x.numel()), _stream()), "residual_add")
+
+
+def rope_kv_write(qkv: torch.Tensor, H: int, G: int, d: int, rotary_dim: int, pairing: int,
+                  cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                  kv: Optional[torch.Tensor], slot_map: Optional[torch.Tensor], page_size: int,
+                  write_kv: bool) -> None:
+    """Rotate q and k of qkv [T, (H+2G)*d] in place by the table rows of ``positions`` and
+    write k, v to their slots of ``kv`` [pages, 2, G, page_size, d]."""
+    T = qkv.shape[0]
+    assert qkv.shape[1] == (H + 2 * G) * d and positions.dtype == torch.int32
+    _contig(qkv, "qkv")
+    if cos is not None:
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] == rotary_dim // 2
+    if write_kv:
+        assert kv is not None and kv.dtype == qkv.dtype and slot_map.dtype == torch.int32
+        assert tuple(kv.shape[1:]) == (2, G, page_size, d), (kv.shape, G, page_size, d)
+        _contig(kv, "kv")
+    _check(library("elementwise").qd_rope_kv_write(
+        _ptr(qkv), _I(dtype_code(qkv.dtype)), _I(T), _I(H), _I(G), _I(d), _I(rotary_dim), _I(pairing),
+        _ptr(cos), _ptr(sin), _ptr(positions), _ptr(kv), _ptr(slot_map), _I(page_size),
+        _I(1 if write_kv else 0), _stream()), "rope_kv_write")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F) and gate_up.dtype == out.dtype
+    _contig(gate_up, "gate_up"); _contig(out, "out")
+    _check(library("elementwise").qd_swiglu(_ptr(gate_up), _ptr(out), _I(dtype_code(out.dtype)), _I(T),
+                                            _I(F), _stream()), "swiglu")
+
+
+# ------------------------------------------------------------------------ gemm
+def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias), float32 FMA; x and out may be row-strided."""
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (T, N) and x.dtype == w.dtype
+    assert x.stride(1) == 1 and out.stride(1) == 1
+    _contig(w, "w")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    _check(library("gemm_generic").qd_gemm_generic(
+        _ptr(x), _ptr(w), _I(dtype_code(x.dtype)), _ptr(bias), _ptr(out), _I(dtype_code(out.dtype)),
+        _I(T), _I(N), _I(K), _LL(x.stride(0)), _LL(out.stride(0)), _stream()), "gemm_generic")
+
+
+# ------------------------------------------------------------------- attention
+def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                            block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
+                            n_tokens: int, H: int, G: int, d: int, page_size: int, scale: float,
+                            window: int) -> None:
+    """Attention of every token over keys 0..pos (or the last ``window`` of them) of its request,
+    read from ``kv`` [pages, 2, G, page_size, d] through ``block_table`` [R, max_blocks].
+    ``q`` points at the first query element; rows are ``q_stride`` elements apart."""
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    assert token_req.dtype == torch.int32 and positions.dtype == torch.int32
+    assert out.shape == (n_tokens, H * d) and kv.dtype == q.dtype == out.dtype
+    assert tuple(kv.shape[1:]) == (2, G, page_size, d)
+    _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _check(library("attention_generic").qd_paged_attention_generic(
+        _ptr(q), _LL(q_stride), _ptr(out), _LL(out.stride(0)), _ptr(kv), _I(dtype_code(q.dtype)),
+        _ptr(block_table), _I(block_table.shape[1]), _ptr(token_req), _ptr(positions), _I(n_tokens),
+        _I(H), _I(G), _I(d), _I(page_size), _F(scale), _I(window), _stream()), "paged_attention_generic")
+
+
+# -------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, draws: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """out[r] = sampled token of logits[r] (float32 [R, V]); temperature 0 is argmax."""
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and temperature.dtype == torch.float32
+    assert top_k.dtype == torch.int32 and draws.dtype == torch.float32 and out.dtype == torch.int32
+    _contig(logits, "logits")
+    _check(library("sampling").qd_sample(_ptr(logits), _I(R), _I(V), _ptr(temperature), _ptr(top_k),
+                                         _ptr(draws), _ptr(out), _stream()), "sample")

@@ -1,0 +1,71 @@
+"""Grouped-query attention over the paged cache.
+
+As the reference computes it: q, k, v = x Wq^T + bq, x Wk^T + bk, x Wv^T + bv
+(gpu_decoder.cu:334-349); head h of q is columns h*d .. h*d+d-1 and reads kv head
+h / (H / G) (gpu_kernels.cu:222,232); q and k are rotated by position, then k and v are
+written to the token's cache slot (gpu_kernels.cu:82-133); a query at position pos
+attends keys 0..pos with scores (q.k) / sqrt(d), softmax, weighted sum of v
+(gpu_kernels.cu:223-311; cpu_decoder.cpp:166-193); the result goes through Wo with no
+bias (gpu_decoder.cu:423).  Prompt portions and decoded tokens run through the same
+kernels: a portion's keys are in the pages before its queries read them.
+``window`` = w limits a query to the last w keys (the reference has no window).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from .. import kernels
+from ..cache import PagedKV
+from ..config.registry import register_part
+from ..weights.loader import TensorSource, TensorSpec
+from .base import Mixer, PagedCacheView
+from .linear import Linear
+
+
+@register_part("mixer", "gq_attention")
+class GQAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool = True, out_bias: bool = False, position=None,
+                 window: Optional[int] = None, prefix: str = "self_attn.", scale: Optional[float] = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_kv_heads ({num_kv_heads}) must divide num_heads ({num_heads})")
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.num_kv_heads = num_kv_heads
+        self.head_dim = head_dim
+        self.window = window
+        self.position = position        # a PositionEncoding part (Rotary) or None
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.qkv = Linear(hidden_size, [(f"{prefix}q_proj", num_heads * head_dim),
+                                        (f"{prefix}k_proj", num_kv_heads * head_dim),
+                                        (f"{prefix}v_proj", num_kv_heads * head_dim)], bias=qkv_bias)
+        self.out = Linear(num_heads * head_dim, [(f"{prefix}o_proj", hidden_size)], bias=out_bias)
+
+    def cache_need(self):
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return self.qkv.tensor_specs() + self.out.tensor_specs()
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.qkv.bind(source, dtype, device)
+        self.out.bind(source, dtype, device)
+
+    def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
+        H, G, d = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = self.qkv.forward(x)
+        pos = self.position
+        kernels.rope_kv_write(
+            qkv, H, G, d,
+            pos.rotary_dim if pos is not None else 0, pos.pairing_code if pos is not None else 0,
+            pos.cos if pos is not None else None, pos.sin if pos is not None else None,
+            ctx.positions, cache.kv, cache.group.slot_map, cache.group.page_size, cache.write)
+        attn = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+        kernels.paged_attention_generic(
+            qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
+            ctx.positions, ctx.num_tokens, H, G, d, cache.group.page_size, self.scale,
+            self.window or 0)
+        return self.out.forward(attn)

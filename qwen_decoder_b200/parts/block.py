@@ -1,0 +1,44 @@
+"""The pre-norm residual block: x += mixer(norm(x)); x += feed_forward(norm(x))
+(gpu_decoder.cu:321-497: norm, attention, residual, norm, feed-forward, residual).
+A branch's output is left pending on the stream and added by the next norm's kernel.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.registry import register_part
+from ..weights.loader import TensorSource, TensorSpec
+from .base import Block, FeedForward, Mixer, Norm, ResidualStream
+
+
+@register_part("block", "pre_norm")
+class PreNormBlock(Block):
+    norm_roles = ("input", "post_mixer")
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: Dict[str, Norm]):
+        missing = [r for r in self.norm_roles if r not in norms]
+        if missing:
+            raise ValueError(f"pre_norm block needs norms {self.norm_roles}, missing {missing}")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.input_norm = norms["input"]
+        self.post_mixer_norm = norms["post_mixer"]
+
+    def parts(self):
+        return [self.input_norm, self.mixer, self.post_mixer_norm, self.feed_forward]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [s for p in self.parts() for s in p.tensor_specs()]
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.dtype = dtype
+        for p in self.parts():
+            p.bind(source, dtype, device)
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        h = self.input_norm.forward(stream, self.dtype)
+        stream.push(self.mixer.forward(h, ctx, cache))
+        h = self.post_mixer_norm.forward(stream, self.dtype)
+        stream.push(self.feed_forward.forward(h, ctx))

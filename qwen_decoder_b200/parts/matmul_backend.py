@@ -1,0 +1,56 @@
+"""Which kernel a contraction runs on.
+
+float32: always the float32 FMA kernel (``csrc/gemm_generic.cu``); no TF32 anywhere.
+bfloat16: ``mode`` chooses.
+  * ``auto``    the hand-written tensor-core kernel where its sizes allow, else cuBLAS
+                for products large enough to matter, else the generic kernel;
+  * ``generic`` always the generic kernel (any size);
+  * ``cublas``  the library product through torch, as the reference calls cublasHgemm
+                (gpu_kernels.cu:431-436), for every bfloat16 product.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import kernels
+
+mode = os.environ.get("QD_BF16_GEMM", "auto")
+
+# bookkeeping for benchmarks: how many launches of our own kernels / library products ran
+counters = {"own": 0, "library": 0}
+
+
+def _cublas(x, w, bias, out):
+    if out.dtype == torch.float32:
+        y = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if bias is not None:
+            y += bias
+        out.copy_(y)
+    elif bias is not None:
+        torch.addmm(bias.to(out.dtype), x, w.t(), out=out)
+    else:
+        torch.mm(x, w.t(), out=out)
+    counters["library"] += 1
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N] float32)."""
+    if not x.is_cuda:
+        raise kernels.KernelError("contractions run on a CUDA device only (there is no CPU path)")
+    if x.dtype == torch.float32 or mode == "generic":
+        kernels.gemm_generic(x, w, bias, out)
+        counters["own"] += 1
+        return
+    if mode == "cublas":
+        _cublas(x, w, bias, out)
+        return
+    T, K = x.shape
+    N = w.shape[0]
+    if K % 8 == 0 and N % 8 == 0 and N * K >= 256 * 256:
+        _cublas(x, w, bias, out)
+    else:
+        kernels.gemm_generic(x, w, bias, out)
+        counters["own"] += 1

@@ -1,0 +1,38 @@
+"""SwiGLU feed-forward: h = silu(x W1^T) * (x W3^T); delta = h W2^T, no biases
+(gpu_decoder.cu:457-497, swiglu_kernel gpu_kernels.cu:149-160, cpu_decoder.cpp:204-212;
+W1 = gate_proj, W3 = up_proj, W2 = down_proj).  Gate and up are one stacked product.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import kernels
+from ..config.registry import register_part
+from ..weights.loader import TensorSource, TensorSpec
+from .base import FeedForward
+from .linear import Linear
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp."):
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.gate_up = Linear(hidden_size, [(f"{prefix}gate_proj", intermediate_size),
+                                            (f"{prefix}up_proj", intermediate_size)], bias=False)
+        self.down = Linear(intermediate_size, [(f"{prefix}down_proj", hidden_size)], bias=False)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return self.gate_up.tensor_specs() + self.down.tensor_specs()
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.gate_up.bind(source, dtype, device)
+        self.down.bind(source, dtype, device)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        gu = self.gate_up.forward(x)
+        h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.swiglu(gu, h)
+        return self.down.forward(h)

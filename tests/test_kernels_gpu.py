@@ -1,0 +1,191 @@
+"""Each kernel alone against a plain float64 torch reference, at sizes the engine's tiny
+models do not use (odd widths, other head sizes, other page sizes)."""
+import math
+
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return 2e-6 if dt == torch.float32 else 1e-2
+
+
+def close(got, want, dt, scale=None):
+    want = want.to(torch.float64)
+    s = float(want.abs().max()) if scale is None else scale
+    err = float((got.to(torch.float64).cpu() - want.cpu()).abs().max())
+    assert err <= tol(dt) * max(s, 1e-30), f"max |diff| {err:.3e} vs scale {s:.3e}"
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_embedding(dt):
+    from qwen_decoder_b200 import kernels
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(301, 72, generator=g).to(dt)
+    toks = torch.randint(0, 301, (37,), generator=g, dtype=torch.int32)
+    x = torch.empty(37, 72, dtype=torch.float32, device=DEV)
+    kernels.embedding(x, table.to(DEV), toks.to(DEV))
+    assert torch.equal(x.cpu(), table.float()[toks.long()])
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("D", [72, 1000, 4096])
+def test_add_rmsnorm(dt, D):
+    from qwen_decoder_b200 import kernels
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(19, D, generator=g)
+    delta = torch.randn(19, D, generator=g).to(dt)
+    w = 1 + 0.1 * torch.randn(D, generator=g)
+    eps = 3e-5
+    xs = x.to(DEV).clone()
+    out = torch.empty(19, D, dtype=dt, device=DEV)
+    kernels.add_rmsnorm(xs, delta.to(DEV), w.to(DEV), out, eps)
+    v = x.double() + delta.double()
+    close(xs, v, torch.float32)
+    close(out, plain_model.rmsnorm(v, w.double(), eps), dt)
+    # gathered rows, no write-back, no delta
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32)
+    xs2 = x.to(DEV).clone()
+    out2 = torch.empty(3, D, dtype=dt, device=DEV)
+    kernels.add_rmsnorm(xs2, None, w.to(DEV), out2, eps, rows=rows.to(DEV), write_back=False)
+    assert torch.equal(xs2.cpu(), x)
+    close(out2, plain_model.rmsnorm(x.double()[rows.long()], w.double(), eps), dt)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 40, 24), (7, 130, 99), (70, 65, 257), (129, 200, 64)])
+def test_gemm_generic(dt, shape):
+    from qwen_decoder_b200 import kernels
+    T, N, K = shape
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(T, K, generator=g).to(dt)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(dt)
+    b = torch.randn(N, generator=g)
+    for bias in (None, b):
+        for odt in ([dt] if dt == torch.float32 else [dt, torch.float32]):
+            out = torch.empty(T, N, dtype=odt, device=DEV)
+            kernels.gemm_generic(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out)
+            want = plain_model.linear(x.double(), w.double(), bias.double() if bias is not None else None)
+            close(out, want, odt)
+
+
+def _paged_setup(dt, T_per_req, G, d, page_size, seed):
+    """Random pages for requests of the given lengths; returns k, v per request and the device cache."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages_needed = sum((n + page_size - 1) // page_size for n in T_per_req)
+    num_pages = n_pages_needed + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    kv = torch.zeros(num_pages, 2, G, page_size, d, dtype=dt)
+    tables, ks, vs = [], [], []
+    for n in T_per_req:
+        k = torch.randn(n, G, d, generator=g).to(dt)
+        v = torch.randn(n, G, d, generator=g).to(dt)
+        pages = [perm.pop() for _ in range((n + page_size - 1) // page_size)]
+        for t in range(n):
+            kv[pages[t // page_size], 0, :, t % page_size, :] = k[t]
+            kv[pages[t // page_size], 1, :, t % page_size, :] = v[t]
+        tables.append(pages)
+        ks.append(k)
+        vs.append(v)
+    mb = max(len(p) for p in tables)
+    bt = torch.full((len(tables), mb), -1, dtype=torch.int32)
+    for i, p in enumerate(tables):
+        bt[i, :len(p)] = torch.tensor(p, dtype=torch.int32)
+    return kv, bt, ks, vs
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("cfg", [(4, 2, 16, 16, None), (6, 2, 48, 8, None), (8, 1, 128, 32, None),
+                                 (3, 3, 80, 16, 37), (2, 1, 256, 16, None)])
+def test_paged_attention_generic(dt, cfg):
+    from qwen_decoder_b200 import kernels
+    H, G, d, page_size, window = cfg
+    lens = [70, 1, 33]
+    kv, bt, ks, vs = _paged_setup(dt, lens, G, d, page_size, seed=3)
+    g = torch.Generator().manual_seed(4)
+    # queries: the last 5 positions of request 0 (a portion), position 0 of request 1, all of request 2
+    items = [(0, p) for p in range(65, 70)] + [(1, 0)] + [(2, p) for p in range(33)]
+    q = torch.randn(len(items), H * d, generator=g).to(dt)
+    # one query and one far key scaled so that a single score stands out among many
+    q[2] *= 4.0
+    out = torch.empty(len(items), H * d, dtype=dt, device=DEV)
+    tr = torch.tensor([r for r, _ in items], dtype=torch.int32)
+    pos = torch.tensor([p for _, p in items], dtype=torch.int32)
+    kernels.paged_attention_generic(q.to(DEV), H * d, out, kv.to(DEV), bt.to(DEV), tr.to(DEV), pos.to(DEV),
+                                    len(items), H, G, d, page_size, 1.0 / math.sqrt(d), window or 0)
+    for i, (r, p) in enumerate(items):
+        n = p + 1
+        qq = torch.zeros(n, H * d, dtype=torch.float64)
+        qq[p] = q[i].double()
+        want = plain_model.attention(qq, ks[r][:n].double().reshape(n, G * d), vs[r][:n].double().reshape(n, G * d),
+                                     H, G, d, window)[p]
+        close(out[i], want, dt, scale=float(vs[r][:n].abs().max()))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("pairing", ["adjacent", "half"])
+def test_rope_kv_write(dt, pairing):
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.parts.rotary import Rotary
+    H, G, d, page_size, T = 6, 2, 48, 8, 21
+    base = 50000.0
+    rot = Rotary(d, d, base, pairing)
+    rot.prepare(300, torch.device(DEV))
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(T, (H + 2 * G) * d, generator=g).to(dt)
+    positions = torch.randint(0, 300, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(5 * page_size, generator=g)[:T].to(torch.int32)
+    kv = torch.zeros(5, 2, G, page_size, d, dtype=dt, device=DEV)
+    dq = qkv.to(DEV).clone()
+    kernels.rope_kv_write(dq, H, G, d, d, rot.pairing_code, rot.cos, rot.sin, positions.to(DEV), kv,
+                          slots.to(DEV), page_size, True)
+    x = qkv.double()
+    wq = plain_model.rope(x[:, :H * d], positions, H, d, base, pairing)
+    wk = plain_model.rope(x[:, H * d:(H + G) * d], positions, G, d, base, pairing)
+    wv = x[:, (H + G) * d:]
+    close(dq[:, :H * d], wq, dt)
+    kvc = kv.cpu()
+    for t in range(T):
+        page, off = int(slots[t]) // page_size, int(slots[t]) % page_size
+        close(kvc[page, 0, :, off, :].reshape(-1), wk[t], dt)
+        close(kvc[page, 1, :, off, :].reshape(-1), wv[t], dt)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_swiglu(dt):
+    from qwen_decoder_b200 import kernels
+    g = torch.Generator().manual_seed(6)
+    gu = (3 * torch.randn(13, 2 * 177, generator=g)).to(dt)
+    out = torch.empty(13, 177, dtype=dt, device=DEV)
+    kernels.swiglu(gu.to(DEV), out)
+    x = gu.double()
+    close(out, plain_model.silu(x[:, :177]) * x[:, 177:], dt)
+
+
+def test_sampling():
+    from qwen_decoder_b200 import kernels
+    g = torch.Generator().manual_seed(7)
+    V = 1531
+    R = 64
+    logits = 2.0 * torch.randn(R, V, generator=g)
+    logits[3, 100] = logits[3, 900] = logits[3].max() + 1.0      # a tie: the lower index wins
+    temps = torch.tensor([0.0, 0.7, 1.0, 0.0] * 16)
+    ks = torch.tensor([0, 0, 30, 5, 1, 2000, 7, 0] * 8, dtype=torch.int32)
+    draws = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    kernels.sample(logits.to(DEV), temps.to(DEV), ks.to(DEV), draws.to(DEV), out)
+    out = out.cpu()
+    checked = 0
+    for r in range(R):
+        tok, margin = plain_model.sample_topk(logits[r], int(ks[r]), float(temps[r]), float(draws[r]))
+        if margin < 1e-5:
+            continue      # float32 rounding of the running sum could decide this draw either way
+        assert int(out[r]) == tok, (r, int(out[r]), tok)
+        checked += 1
+    assert checked > R // 2 and int(out[3]) == 100
