@@ -1,0 +1,129 @@
+"""The Python entry point: ``Engine(model_dir, ...)`` and ``generate``.
+
+Option names and meanings are the reference's where it has them: ``max_batch``,
+``max_prefill_len``, ``max_prefill_tokens_per_step`` (its command line's
+max_prefill_step) and ``max_total_tokens`` are GPUDecoder's constructor arguments
+(gpu_decoder.h:72-75, gpu_main.cu:19-34); ``max_new_tokens``, ``temperature`` and
+``top_k`` are generate_continuous's (decoder.h:148-154).  Prompts are lists of token
+ids: the engine starts at token ids and ends at token ids (the reference's tokenizer,
+common.cpp:229-562, is outside it).
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager
+from ..sampling import Sampler, uniform_draw
+from .batch import StepEntry
+from .runner import ModelRunner, resolve_dtype
+from .scheduler import Request, SamplingParams, Scheduler, StepPlan
+
+
+class Engine:
+    def __init__(self, model=None, *, config=None, random_seed: Optional[int] = None, dtype="bfloat16",
+                 device="cuda:0", max_batch: int = 64, max_prefill_len: int = 4096,
+                 max_prefill_tokens_per_step: int = 512, max_total_tokens: int = 4096,
+                 page_size: int = 16, num_pages: Optional[int] = None, kv_memory_fraction: float = 0.8,
+                 max_positions: Optional[int] = None, use_graphs: bool = True):
+        """``model``: a folder with config.json and model.safetensors; or give ``config`` (a typed
+        configuration) and ``random_seed`` for random weights made on the device.
+
+        ``max_batch``: most requests running at once.  ``max_prefill_len``: longest prompt taken
+        (longer prompts end with ``too_long``; the reference stores this number and never uses it,
+        gpu_decoder.h:113-119).  ``max_prefill_tokens_per_step``: prompt tokens per step, shared by
+        all prefilling requests.  ``max_total_tokens``: most tokens in one step.  ``num_pages``:
+        cache pages of ``page_size`` tokens; by default ``kv_memory_fraction`` of the free device
+        memory after the weights, as the reference takes 80 % (gpu_decoder.cu:197-204)."""
+        self.max_prefill_len = max_prefill_len
+        make = dict(dtype=dtype, device=device, page_size=page_size, max_requests=max_batch,
+                    max_positions=max_positions)
+        sizing = _PageSizing(num_pages, kv_memory_fraction, page_size, resolve_dtype(dtype))
+        if model is not None:
+            self.runner = ModelRunner.from_folder(model, num_pages=sizing, **make)
+        elif config is not None:
+            self.runner = ModelRunner.from_random(config, seed=random_seed or 0, num_pages=sizing, **make)
+        else:
+            raise ValueError("give a model folder, or config= and random_seed=")
+        self.config = self.runner.config
+        self.device = self.runner.device
+        self.sampler = Sampler(self.device)
+        self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch,
+                                   max_prefill_tokens_per_step=max_prefill_tokens_per_step,
+                                   max_total_tokens=max_total_tokens,
+                                   max_positions=self.runner.max_positions,
+                                   stop_ids=getattr(self.config, "eos_token_ids", ()))
+        self.use_graphs = use_graphs
+        self._next_id = 0
+        self._keys: Dict[int, int] = {}
+
+    # ---- streaming use -----------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id=None) -> Request:
+        rid = self._next_id if request_id is None else request_id
+        self._next_id += 1
+        req = Request(rid, [int(t) for t in prompt], params or SamplingParams())
+        req.sample_key = self._next_id - 1
+        if len(req.prompt) > self.max_prefill_len:
+            req.finished, req.finish_reason = True, "too_long"
+            return req
+        self.scheduler.add_request(req)
+        return req
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[Request]:
+        """Plan one step, run it, sample, and return the requests that finished in it."""
+        plan = self.scheduler.schedule()
+        finished = list(plan.finished)
+        if not plan.entries:
+            return finished
+        entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.samples else [])
+                   for e in plan.entries]
+        logits = self.runner.step(entries, ensure_pages=False)
+        sampling = [e.request for e in plan.entries if e.samples]
+        tokens: List[int] = []
+        if sampling:
+            if all(r.params.temperature == 0.0 for r in sampling):
+                ids = self.sampler.greedy(logits)
+            else:
+                ids = self.sampler.sample(
+                    logits, [r.params.temperature for r in sampling], [r.params.top_k for r in sampling],
+                    [uniform_draw(r.params.seed, r.sample_key, len(r.output)) for r in sampling])
+            tokens = ids.cpu().tolist()
+        finished += self.scheduler.update(plan, tokens)
+        return finished
+
+    # ---- batch use -----------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
+        """Generate for every prompt (token ids in, token ids out), continuous batching inside.
+        ``params``: one SamplingParams for all, or one per prompt."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.has_work():
+            self.step()
+        return [r.output for r in reqs]
+
+    @property
+    def stats(self) -> dict:
+        return dict(self.scheduler.stats, model_steps=self.runner.steps, model_tokens=self.runner.tokens_run)
+
+
+class _PageSizing:
+    """How many pages the pool gets: a number, or a share of the memory left after the weights."""
+
+    def __init__(self, num_pages, fraction, page_size, dtype):
+        self.num_pages, self.fraction, self.page_size, self.dtype = num_pages, fraction, page_size, dtype
+
+    def resolve(self, layout, device, max_requests, max_positions) -> int:
+        if self.num_pages is not None:
+            return int(self.num_pages)
+        free, _ = torch.cuda.mem_get_info(device)
+        per_page = max(1, CacheManager.bytes_per_page(layout, self.page_size, self.dtype))
+        by_memory = int(free * self.fraction) // per_page
+        # no more than every request at full length could use
+        useful = max_requests * ((max_positions + self.page_size - 1) // self.page_size)
+        return max(1, min(by_memory, useful))

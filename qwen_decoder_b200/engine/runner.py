@@ -52,10 +52,12 @@ class ModelRunner:
         self.device = model.device
         self.dtype = model.dtype
         self.layout = model.cache_layout()
-        self.cache = CacheManager(self.layout, num_pages, page_size, max_requests, dtype=self.dtype,
-                                  device=self.device)
         model.prepare(max_positions or model.max_positions)
         self.max_positions = model.prepared_positions
+        if hasattr(num_pages, "resolve"):      # sized from the memory left after the weights
+            num_pages = num_pages.resolve(self.layout, self.device, max_requests, self.max_positions)
+        self.cache = CacheManager(self.layout, num_pages, page_size, max_requests, dtype=self.dtype,
+                                  device=self.device)
         self.steps = 0
         self.tokens_run = 0
 

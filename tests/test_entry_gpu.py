@@ -1,0 +1,122 @@
+"""Generation through the Python entry point and the command line, and the replay program as a
+user runs it."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import trace_tools
+from tiny_configs import TINY, make_folder
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {n: make_folder(n, str(tmp_path_factory.mktemp(f"m{n}"))) for n in ("A", "B")}
+
+
+def prompts_for(cfg, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+
+
+def check_greedy(cfg, w, prompt, got, dtype):
+    """Greedy tokens equal the plain implementation's, up to the first near tie of its logits."""
+    want, margins = plain_model.greedy_generate(cfg, w, prompt, len(got))
+    limit = 1e-4 if dtype == "float32" else 2e-2
+    n = next((i for i, m in enumerate(margins) if m < limit), len(want))
+    assert got[:n] == want[:n], (prompt, got, want, margins)
+    return n
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(folders, dtype):
+    """Tiny A's workload: prompts of 5, 17 and 33 ids, 16 greedy tokens each."""
+    from qwen_decoder_b200.engine import Engine, SamplingParams
+    cfg, w = plain_model.read_folder(folders["A"])
+    prompts = prompts_for(cfg, [5, 17, 33], seed=0)
+    eng = Engine(folders["A"], dtype=dtype, num_pages=32, max_batch=4)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=16))
+    assert all(len(o) == 16 for o in outs)
+    checked = sum(check_greedy(cfg, w, p, o, dtype) for p, o in zip(prompts, outs))
+    assert checked >= 24
+    assert eng.runner.cache.free_pages() == [32]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_chunked_prefill_mixed_with_decode_and_temperature(folders, dtype):
+    """Tiny B's workload: prompts of 1, 9, 64 and 130 ids in 24-token portions mixed with decode tokens,
+    20 tokens at temperature 0.8 with a fixed sampler seed.  The same request gives the same tokens
+    alone and in the batch, and in a pool so small that requests are preempted."""
+    from qwen_decoder_b200.engine import Engine, SamplingParams
+    cfg, w = plain_model.read_folder(folders["B"])
+    prompts = prompts_for(cfg, [1, 9, 64, 130], seed=1)
+    sp = SamplingParams(temperature=0.8, max_new_tokens=20, seed=123)
+    eng = Engine(folders["B"], dtype=dtype, num_pages=16, page_size=32, max_batch=4, max_prefill_tokens_per_step=24)
+    outs = eng.generate(prompts, sp)
+    assert all(len(o) == 20 for o in outs) and eng.stats["prompt_tokens"] == 204
+    assert len({tuple(o) for o in outs}) == 4
+    # each token is what the plain sampler draws from the plain logits with the same uniform draw
+    from qwen_decoder_b200.sampling import uniform_draw
+    checked = 0
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        seq = list(p)
+        for j, tok in enumerate(o):
+            logits = plain_model.forward(cfg, w, seq)[-1]
+            want, margin = plain_model.sample_topk(logits, 0, 0.8, uniform_draw(123, i, j))
+            if margin < (1e-4 if dtype == "float32" else 2e-2):
+                break
+            assert tok == want, (i, j, tok, want)
+            checked += 1
+            seq.append(tok)
+    assert checked >= 40
+    if dtype == "float32":
+        # alone, one request at a time, nothing cut: same tokens (draws are keyed by request, not by batch)
+        for i, p in enumerate(prompts):
+            solo = Engine(folders["B"], dtype=dtype, num_pages=16, page_size=32)
+            solo._next_id = i
+            assert solo.generate([p], sp)[0] == outs[i]
+        # a pool of 7 pages of 32 tokens cannot hold all four: some are preempted and recomputed
+        small = Engine(folders["B"], dtype=dtype, num_pages=7, page_size=32, max_batch=4,
+                       max_prefill_tokens_per_step=24)
+        assert small.generate(prompts, sp) == outs
+        assert small.stats["preemptions"] >= 1 and small.runner.cache.free_pages() == [7]
+
+
+def test_command_line(folders):
+    cfg, w = plain_model.read_folder(folders["A"])
+    prompts = prompts_for(cfg, [4, 11], seed=2)
+    stdin = "".join(" ".join(map(str, p)) + "\n" for p in prompts) + "\n"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "decoder_main"), folders["A"], "8", "4096", "16",
+                        "64", "0", "--dtype", "float32", "--max-new-tokens", "6", "--num-pages", "16"],
+                       input=stdin, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert len(lines) == 2 and "tokens/s" in r.stderr
+    for p, line in zip(prompts, lines):
+        got = [int(t) for t in line.split(")", 1)[1].split()]
+        assert len(got) == 6 and check_greedy(cfg, w, p, got, "float32") >= 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(folders, dtype, tmp_path):
+    """bin/trace_run as a separate process: steps on stdin, one `done` line per step, .f32 files."""
+    cfg, w = plain_model.read_folder(folders["B"])
+    seqs = prompts_for(cfg, [40, 75, 20, 64, 33], seed=3)
+    want = [plain_model.forward(cfg, w, s).numpy() for s in seqs]
+    tr = trace_tools.mixed(seqs, max_tokens=256, seed=9)
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders["B"], "--dtype",
+                        dtype, "--out", str(out), "--max-tokens", "256"], input=tr.lines(), capture_output=True,
+                       text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.splitlines() == [f"done {s['step']}" for s in tr.steps]
+    got = trace_tools.read_outputs(tr, str(out), cfg["vocab_size"])
+    trace_tools.compare(tr, got, want, 1e-5 if dtype == "float32" else 3e-2)

@@ -1,0 +1,217 @@
+"""Parts chosen layer by layer, the order of layers as data, and parts defined outside the
+framework: a toy architecture with windowed and full attention layers, a schedule that names a
+layer twice and lets a run read another run's cache, and a toy mixer with per-request state of
+its own -- all registered here, without a change to the framework's files."""
+import json
+import os
+import random
+from dataclasses import dataclass, field
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import trace_tools
+from qwen_decoder_b200.cache import FixedState
+from qwen_decoder_b200.config import (LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_architecture,
+                                      register_part, unregister_architecture, unregister_part)
+from qwen_decoder_b200.parts import Mixer
+from qwen_decoder_b200.weights import TensorSpec, write_random_model
+
+pytestmark = pytest.mark.gpu
+TOL = {"float32": 1e-5, "bfloat16": 3e-2}
+
+
+# ------------------------------------------------------------ a toy configuration class
+@dataclass(frozen=True)
+class ToyConfig:
+    architecture: str
+    hidden_size: int = 48
+    intermediate_size: int = 112
+    num_heads: int = 3
+    num_kv_heads: int = 1
+    head_dim: int = 16
+    vocab_size: int = 331
+    max_positions: int = 256
+    eps: float = 2e-6
+    rope_base: float = 777.0
+    window: int = 20
+    kinds: tuple = ()
+    schedule: tuple = ()
+    eos_token_ids: tuple = ()
+
+    @classmethod
+    def from_dict(cls, d):
+        d = dict(d)
+        arch = d.pop("architectures")[0]
+        d["kinds"] = tuple(d.get("kinds", ()))
+        d["schedule"] = tuple(tuple(x) for x in d.get("schedule", ()))
+        return cls(architecture=arch, **d)
+
+    def to_dict(self):
+        d = {k: getattr(self, k) for k in self.__dataclass_fields__ if k not in ("architecture", "eos_token_ids")}
+        d["architectures"] = [self.architecture]
+        d["kinds"] = list(self.kinds)
+        d["schedule"] = [list(x) for x in self.schedule]
+        return d
+
+
+def describe_toy(c: ToyConfig) -> ModelSpec:
+    norm = {"size": c.hidden_size, "eps": c.eps}
+    layers = []
+    for i, kind in enumerate(c.kinds):
+        if kind == "ema":
+            mixer = PartSpec("toy_ema", {"hidden_size": c.hidden_size, "prefix": "mix."})
+        else:
+            mixer = PartSpec("gq_attention", {
+                "hidden_size": c.hidden_size, "num_heads": c.num_heads, "num_kv_heads": c.num_kv_heads,
+                "head_dim": c.head_dim, "qkv_bias": True, "out_bias": False, "position": "rope",
+                "window": c.window if kind == "window" else None, "prefix": "self_attn."})
+        layers.append(LayerSpec(
+            prefix=f"model.layers.{i}.", block="pre_norm", mixer=mixer,
+            feed_forward=PartSpec("swiglu", {"hidden_size": c.hidden_size,
+                                             "intermediate_size": c.intermediate_size, "prefix": "mlp."}),
+            norms={"input": PartSpec("rmsnorm", dict(norm, prefix="input_layernorm.")),
+                   "post_mixer": PartSpec("rmsnorm", dict(norm, prefix="post_attention_layernorm."))}))
+    sched = [ScheduleEntry(l, None if src < 0 else src) for l, src in c.schedule] or \
+        [ScheduleEntry(i) for i in range(len(layers))]
+    return ModelSpec(
+        hidden_size=c.hidden_size, vocab_size=c.vocab_size, max_positions=c.max_positions,
+        embedding_tensor="model.embed_tokens.weight",
+        positions={"rope": PartSpec("rotary", {"head_dim": c.head_dim, "rotary_dim": c.head_dim,
+                                               "base": c.rope_base, "pairing": "adjacent"})},
+        layers=layers, schedule=sched, final_norm=PartSpec("rmsnorm", dict(norm, prefix="")),
+        final_norm_prefix="model.norm.", lm_head_tensor="lm_head.weight")
+
+
+# ------------------------------------------------------------ a toy mixer with its own state
+class ToyEma(Mixer):
+    """y_t = (s_t) W^T with s_t = 0.75 s_{t-1} + 0.25 x_t, s kept per request between steps."""
+
+    def __init__(self, hidden_size, prefix="mix."):
+        self.hidden_size, self.prefix = hidden_size, prefix
+
+    def cache_need(self):
+        return FixedState((self.hidden_size,), torch.float32)
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.prefix}proj.weight", (self.hidden_size, self.hidden_size))]
+
+    def bind(self, source, dtype, device):
+        self.w = source.get(f"{self.prefix}proj.weight").to(device=device, dtype=torch.float32)
+        self.dtype = dtype
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        for r in range(ctx.num_requests):
+            a, b = ctx.host_cu_tokens[r], ctx.host_cu_tokens[r + 1]
+            s = cache.state[ctx.host_state_slots[r]]
+            rows = []
+            for t in range(a, b):
+                s = 0.75 * s + 0.25 * x[t].float()
+                rows.append(s)
+            if cache.write:
+                cache.state[ctx.host_state_slots[r]] = s
+            out[a:b] = (torch.stack(rows) @ self.w.t()).to(x.dtype)
+        return out
+
+
+@pytest.fixture(scope="module", autouse=True)
+def toy_registration():
+    register_part("mixer", "toy_ema")(ToyEma)
+    register_architecture("ToyLM", ToyConfig, describe_toy)
+    yield
+    unregister_architecture("ToyLM")
+    unregister_part("mixer", "toy_ema")
+
+
+# ------------------------------------------------------------ plain forward of the toy models
+def toy_plain(cfg: ToyConfig, w, tokens):
+    x = plain_model.embedding(w["model.embed_tokens.weight"], tokens)
+    T = len(tokens)
+    positions = torch.arange(T)
+    sched = cfg.schedule or tuple((i, -1) for i in range(len(cfg.kinds)))
+    kv_of = {}
+    for e, (l, src) in enumerate(sched):
+        p = f"model.layers.{l}."
+        h = plain_model.rmsnorm(x, w[p + "input_layernorm.weight"], cfg.eps)
+        kind = cfg.kinds[l]
+        if kind == "ema":
+            s = torch.zeros(cfg.hidden_size, dtype=torch.float64)
+            rows = []
+            for t in range(T):
+                s = 0.75 * s + 0.25 * h[t]
+                rows.append(s)
+            a = torch.stack(rows) @ w[p + "mix.proj.weight"].t()
+        else:
+            H, G, d = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+            lin = lambda n: plain_model.linear(h, w[f"{p}self_attn.{n}_proj.weight"], w[f"{p}self_attn.{n}_proj.bias"])
+            q = plain_model.rope(lin("q"), positions, H, d, cfg.rope_base)
+            if src >= 0:
+                k, v = kv_of[src]                       # this run reads what run ``src`` cached
+            else:
+                k, v = plain_model.rope(lin("k"), positions, G, d, cfg.rope_base), lin("v")
+                kv_of[e] = (k, v)
+            a = plain_model.attention(q, k, v, H, G, d, cfg.window if kind == "window" else None)
+            a = plain_model.linear(a, w[p + "self_attn.o_proj.weight"])
+        x = x + a
+        h = plain_model.rmsnorm(x, w[p + "post_attention_layernorm.weight"], cfg.eps)
+        x = x + plain_model.swiglu_ffn(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                       w[p + "mlp.down_proj.weight"])
+    return plain_model.linear(plain_model.rmsnorm(x, w["model.norm.weight"], cfg.eps), w["lm_head.weight"])
+
+
+def run_all_cuttings(cfg, tmp_path, dtype, lengths=(7, 45, 101, 160)):
+    from qwen_decoder_b200.engine import ModelRunner
+    folder = write_random_model(cfg, str(tmp_path / "model"), seed=11)
+    _, w = plain_model.read_folder(folder)
+    rng = random.Random(3)
+    seqs = [[rng.randrange(cfg.vocab_size) for _ in range(n)] for n in lengths]
+    want = [toy_plain(cfg, w, s).numpy() for s in seqs]
+    max_tokens = 2 * 192
+    for i, make in enumerate([trace_tools.whole, trace_tools.decode_tail, trace_tools.portions,
+                              lambda s: trace_tools.mixed(s + s[::-1], max_tokens, seed=5)]):
+        runner = ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", num_pages=max_tokens // 16,
+                                         page_size=16, max_requests=8)
+        tr = make(seqs)
+        got = trace_tools.run_inprocess(runner, tr, str(tmp_path / f"out{i}"))
+        trace_tools.compare(tr, got, want + want[::-1] if i == 3 else want, TOL[dtype])
+        runner.cache.check()
+        assert runner.cache.free_pages() == [runner.cache.num_pages] * len(runner.cache.pools)
+    return runner
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_and_full_layers_in_one_model(tmp_path, dtype):
+    cfg = ToyConfig("ToyLM", kinds=("window", "full", "window"))
+    runner = run_all_cuttings(cfg, tmp_path, dtype)
+    assert len(runner.cache.pools) == 2           # the windowed layers have pages of their own
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_pages_are_given_back_while_a_request_runs(tmp_path, dtype):
+    from qwen_decoder_b200.engine import ModelRunner, StepEntry
+    cfg = ToyConfig("ToyLM", kinds=("window", "full"))
+    folder = write_random_model(cfg, str(tmp_path / "model"), seed=11)
+    runner = ModelRunner.from_folder(folder, dtype=dtype, device="cuda:0", num_pages=16, max_requests=2)
+    rc = runner.open("r")
+    runner.step([StepEntry(rc, list(range(100)), [])])
+    full, win = (runner.cache.pools[g] for g in range(2))
+    by_window = {runner.cache.layout.groups[g].need.window: runner.cache.pools[g] for g in range(2)}
+    assert by_window[None].num_used == 7 and by_window[20].num_used == 2      # tokens 81..99 need pages 5, 6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_named_twice_and_a_run_that_reads_another_runs_cache(tmp_path, dtype):
+    # runs: layer 0, layer 1, layer 0 again (a cache of its own), layer 1 again reading run 1's cache
+    cfg = ToyConfig("ToyLM", kinds=("full", "full"), schedule=((0, -1), (1, -1), (0, -1), (1, 1)))
+    runner = run_all_cuttings(cfg, tmp_path, dtype)
+    assert runner.cache.kv[0].shape[0] == 3       # three runs own a cache layer, the fourth owns none
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_mixer_with_state_of_its_own(tmp_path, dtype):
+    cfg = ToyConfig("ToyLM", kinds=("ema", "full", "ema"))
+    runner = run_all_cuttings(cfg, tmp_path, dtype)
+    assert len(runner.cache.states) == 2 and runner.cache.states[0].shape == (8, 48)

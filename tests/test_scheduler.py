@@ -1,0 +1,148 @@
+"""The scheduler's decisions, driven with a fake step function (no device)."""
+import hashlib
+
+import pytest
+
+from qwen_decoder_b200.cache import CacheLayout, CacheManager, PagedKV
+from qwen_decoder_b200.engine.scheduler import Request, SamplingParams, Scheduler
+
+
+def manager(num_pages, page_size=16, max_requests=8):
+    layout = CacheLayout.from_needs([PagedKV(2, 16), PagedKV(2, 16)], [None, None])
+    return CacheManager(layout, num_pages, page_size, max_requests)
+
+
+def next_token(tokens, vocab=1000):
+    """A stand-in model: the next token is a hash of everything before it."""
+    h = hashlib.sha256(",".join(map(str, tokens)).encode()).digest()
+    return int.from_bytes(h[:4], "little") % vocab
+
+
+def fake_step(sched, plan):
+    """What the engine does with a plan: commit the tokens to the cache, sample where asked."""
+    sampled = []
+    for e in plan.entries:
+        req = e.request
+        start = req.num_computed
+        assert e.tokens == req.all_tokens()[start:start + len(e.tokens)]
+        assert req.cache.num_tokens == start
+        sched.cache.commit(req.cache, len(e.tokens))
+        if e.samples:
+            assert start + len(e.tokens) == len(req.prompt) + len(req.output)
+            sampled.append(next_token(req.all_tokens()))
+    return sched.update(plan, sampled)
+
+
+def run(sched, reqs, max_steps=10000):
+    for r in reqs:
+        sched.add_request(r)
+    plans = []
+    while sched.has_work():
+        plan = sched.schedule()
+        plans.append(plan)
+        fake_step(sched, plan)
+        sched.cache.check()
+        assert len(plans) < max_steps
+    return plans
+
+
+def expected_output(prompt, n):
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(next_token(seq))
+    return seq[len(prompt):]
+
+
+def test_prompts_are_cut_under_the_budget_and_decodes_always_run():
+    s = Scheduler(manager(200), max_batch=4, max_prefill_tokens_per_step=24, max_total_tokens=64)
+    reqs = [Request(i, list(range(1, n + 1)), SamplingParams(max_new_tokens=5)) for i, n in enumerate([30, 10, 50])]
+    plans = run(s, reqs)
+    # step 0: 24 of request 0; step 1: its last 6, all 10 of request 1, 8 of request 2
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in plans[0].entries] == [(0, 24, False)]
+    assert [(e.request.request_id, len(e.tokens), e.samples) for e in plans[1].entries] == \
+        [(0, 6, True), (1, 10, True), (2, 8, False)]
+    # step 2: requests 0 and 1 decode (first), request 2 goes on with 24 prompt tokens
+    assert [(e.request.request_id, len(e.tokens)) for e in plans[2].entries] == [(0, 1), (1, 1), (2, 24)]
+    for p in plans:
+        prompt_tokens = sum(len(e.tokens) for e in p.entries if not (len(e.tokens) == 1 and e.request.output))
+        assert prompt_tokens <= 24
+    for r in reqs:
+        assert r.finished and r.finish_reason == "length" and r.output == expected_output(r.prompt, 5)
+    assert s.cache.free_pages() == [200] and s.cache.slots.num_free == 8
+    assert s.stats["prompt_tokens"] == 90 and s.stats["decode_tokens"] == 3 * 4
+
+
+def test_max_batch_limits_running_and_order_is_fifo():
+    s = Scheduler(manager(200), max_batch=2, max_prefill_tokens_per_step=512)
+    reqs = [Request(i, [i + 1] * 5, SamplingParams(max_new_tokens=3 + i)) for i in range(5)]
+    for r in reqs:
+        s.add_request(r)
+    seen = []
+    while s.has_work():
+        plan = s.schedule()
+        assert len(s.running) <= 2
+        for e in plan.entries:
+            if e.request.request_id not in seen:
+                seen.append(e.request.request_id)
+        fake_step(s, plan)
+    assert seen == [0, 1, 2, 3, 4] and all(r.finished for r in reqs)
+
+
+def test_stop_ids_and_ignore_eos():
+    prompt = [3, 1, 4, 1, 5]
+    out = expected_output(prompt, 6)
+    stop = out[2]
+    s = Scheduler(manager(50), stop_ids=[stop])
+    a = Request("a", prompt, SamplingParams(max_new_tokens=6))
+    b = Request("b", prompt, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    c = Request("c", prompt, SamplingParams(max_new_tokens=6, stop_ids=[out[0]]))
+    run(s, [a, b, c])
+    assert a.finish_reason == "stop" and a.output == out[:2]      # the stop id is not part of the output
+    assert b.finish_reason == "length" and b.output == out
+    assert c.finish_reason == "stop" and c.output == []
+
+
+def test_running_out_of_pages_preempts_the_youngest_and_output_is_unchanged():
+    # 3 requests start with one page each and grow to 5 pages (10 prompt + 60 new tokens); pool of 9
+    def make():
+        return [Request(i, [7 * i + j for j in range(10)], SamplingParams(max_new_tokens=60)) for i in range(3)]
+    small = Scheduler(manager(9), max_batch=4, max_prefill_tokens_per_step=512)
+    reqs = make()
+    plans = run(small, reqs)
+    assert small.stats["preemptions"] >= 1
+    first = next(p for p in plans if p.preempted)
+    assert first.preempted[0].request_id == 2                     # the most recently admitted goes first
+    for r in reqs:
+        assert r.output == expected_output(r.prompt, 60) and r.finish_reason == "length"
+    assert reqs[2].preemptions >= 1 and reqs[0].preemptions == 0
+    assert small.cache.free_pages() == [9]
+    # a preempted request comes back with prompt + what it had generated, and is fed in one go
+    back = next(p for p in plans[plans.index(first) + 1:] if any(e.request.request_id == 2 for e in p.entries))
+    e = next(e for e in back.entries if e.request.request_id == 2)
+    assert len(e.tokens) > 10 and e.tokens[:10] == reqs[2].prompt
+    # same plans again: the decisions are deterministic
+    again = Scheduler(manager(9), max_batch=4, max_prefill_tokens_per_step=512)
+    plans2 = run(again, make())
+    assert [[(e.request.request_id, len(e.tokens)) for e in p.entries] for p in plans] == \
+           [[(e.request.request_id, len(e.tokens)) for e in p.entries] for p in plans2]
+
+
+def test_a_request_that_can_never_fit_ends_with_a_reason():
+    s = Scheduler(manager(3), max_batch=2)
+    big = Request("big", list(range(1, 100)), SamplingParams(max_new_tokens=4))          # 7 pages > 3
+    grows = Request("grows", list(range(1, 41)), SamplingParams(max_new_tokens=30))      # 3 pages, then a 4th
+    ok = Request("ok", [1, 2, 3], SamplingParams(max_new_tokens=2))
+    run(s, [big, grows, ok])
+    assert big.finish_reason == "too_long_for_cache" and big.output == []
+    assert grows.finish_reason == "too_long_for_cache" and len(grows.output) == 9       # 48 cached tokens fill 3 pages; the 49th cannot be fed
+    assert ok.finish_reason == "length" and len(ok.output) == 2
+    assert s.cache.free_pages() == [3]
+
+
+def test_max_positions_ends_a_request():
+    s = Scheduler(manager(50), max_positions=12)
+    a = Request("a", list(range(1, 9)), SamplingParams(max_new_tokens=100))
+    b = Request("b", list(range(1, 20)), SamplingParams(max_new_tokens=1))
+    run(s, [a, b])
+    assert a.finish_reason == "max_positions" and len(a.prompt) + len(a.output) == 12
+    assert b.finish_reason == "too_long"
