@@ -63,6 +63,14 @@ def test_chunked_prefill_mixed_with_decode_and_temperature(folders, dtype):
     outs = eng.generate(prompts, sp)
     assert all(len(o) == 20 for o in outs) and eng.stats["prompt_tokens"] == 204
     assert len({tuple(o) for o in outs}) == 4
+    if dtype == "bfloat16":
+        # with a thousand nearly equal probabilities, bfloat16 rounding of the logits moves the running sum
+        # by more than the distance between its steps, so single tokens cannot be pinned against the plain
+        # implementation here; float32 pins the sampling path, bfloat16 must at least repeat itself
+        again = Engine(folders["B"], dtype=dtype, num_pages=16, page_size=32, max_batch=4,
+                       max_prefill_tokens_per_step=24)
+        assert again.generate(prompts, sp) == outs
+        return
     # each token is what the plain sampler draws from the plain logits with the same uniform draw
     from qwen_decoder_b200.sampling import uniform_draw
     checked = 0
@@ -71,23 +79,23 @@ def test_chunked_prefill_mixed_with_decode_and_temperature(folders, dtype):
         for j, tok in enumerate(o):
             logits = plain_model.forward(cfg, w, seq)[-1]
             want, margin = plain_model.sample_topk(logits, 0, 0.8, uniform_draw(123, i, j))
-            if margin < (1e-4 if dtype == "float32" else 2e-2):
-                break
+            seq.append(tok)        # go on along the engine's own tokens
+            if margin < 1e-5:
+                continue           # float32 rounding of the running sum could decide this draw either way
             assert tok == want, (i, j, tok, want)
             checked += 1
-            seq.append(tok)
-    assert checked >= 40
-    if dtype == "float32":
-        # alone, one request at a time, nothing cut: same tokens (draws are keyed by request, not by batch)
-        for i, p in enumerate(prompts):
-            solo = Engine(folders["B"], dtype=dtype, num_pages=16, page_size=32)
-            solo._next_id = i
-            assert solo.generate([p], sp)[0] == outs[i]
-        # a pool of 7 pages of 32 tokens cannot hold all four: some are preempted and recomputed
-        small = Engine(folders["B"], dtype=dtype, num_pages=7, page_size=32, max_batch=4,
-                       max_prefill_tokens_per_step=24)
-        assert small.generate(prompts, sp) == outs
-        assert small.stats["preemptions"] >= 1 and small.runner.cache.free_pages() == [7]
+    assert checked >= 60
+    # alone, one request at a time, nothing cut: same tokens (draws are keyed by request, not by batch)
+    for i, p in enumerate(prompts):
+        solo = Engine(folders["B"], dtype=dtype, num_pages=16, page_size=32)
+        solo._next_id = i
+        assert solo.generate([p], sp)[0] == outs[i]
+    # a pool of 5 pages of 32 tokens: the longest request is admitted beside another, outgrows the pool,
+    # is preempted and recomputed later -- with the same tokens
+    small = Engine(folders["B"], dtype=dtype, num_pages=5, page_size=32, max_batch=4,
+                   max_prefill_tokens_per_step=24)
+    assert small.generate(prompts, sp) == outs
+    assert small.stats["preemptions"] >= 1 and small.runner.cache.free_pages() == [5]
 
 
 def test_command_line(folders):
