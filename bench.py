@@ -1,0 +1,284 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, at the Qwen2.5-3B shape.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
+
+A step is one decode step of a batch of requests that each hold ``--context`` cached
+tokens.  Prints ONE JSON line: ``value`` = decoded tokens per second (device-timed
+with CUDA events over exactly K steps after W warm-up steps), ``e2e`` = the same
+through the Python entry point (``Engine.step``: host token ids in through pinned
+memory, sampled ids back to the host, every step), ``prefill`` = a 2,048-token
+prompt in one step, ``roofline`` = bytes a decode step must read / its time against
+the measured copy bandwidth, ``points`` = decode at batch 1 and 64.
+
+Weights are random (N(0, 0.02), seeded); the caches of the decode requests are filled
+with random values instead of running 2,048-token prompts first (decode time does not
+depend on the values).  Nothing needs flushing between steps: a step streams all
+weights (6.2 GB), far more than the 126 MB L2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPE_3B = dict(
+    architectures=["Qwen2ForCausalLM"], hidden_size=2048, intermediate_size=11008, num_hidden_layers=36,
+    num_attention_heads=16, num_key_value_heads=2, vocab_size=151936, max_position_embeddings=32768,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(d.get(k), (int, float)):
+                    out[k] = float(d[k])
+            return out, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed regions run."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_bytes(cfg, layers, batch, ctx_mean):
+    D, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, G = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = D // H
+    per_layer = (H * d + 2 * G * d) * D + D * H * d + 3 * F * D
+    weights = (layers * per_layer + V * D) * 2          # every matrix once; the tied table once (output product)
+    kv = batch * ctx_mean * layers * 2 * G * d * 2
+    return weights + kv
+
+
+def prefill_flops(cfg, layers, T):
+    D, F, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    H, G = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = D // H
+    per_layer = (H * d + 2 * G * d) * D + D * H * d + 3 * F * D
+    attn = 4 * d * H * (T * (T + 1) // 2)               # QK^T and PV over the causal triangle
+    return layers * (2 * T * per_layer + attn) + 2 * V * D
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=SHAPE_3B["num_hidden_layers"])
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "nature-li/qwen-decoder is a CMake project of executables (no setup.py/pyproject, "
+                          "pip cannot install it) that needs Drogon, gRPC and MPI, which this image lacks, and a "
+                          "GGUF checkpoint with tokenizer to run at all"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+
+    import torch
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.config import Qwen2Config
+    from qwen_decoder_b200.engine import Engine, SamplingParams, StepEntry
+    from qwen_decoder_b200.parts import matmul_backend
+
+    cfgd = dict(SHAPE_3B, num_hidden_layers=args.layers)
+    cfg = Qwen2Config.from_dict(cfgd)
+    pk, pk_src = peaks()
+    page = 16
+    max_b = max(64, args.batch)
+    span = args.context + 2 * (W + K) + 64
+    num_pages = max_b * ((span + page - 1) // page) + 64
+    torch.manual_seed(0)
+    engine = Engine(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_batch=max_b,
+                    max_prefill_len=1 << 20, max_prefill_tokens_per_step=4096, max_total_tokens=8192,
+                    page_size=page, num_pages=num_pages, max_positions=span + 4096)
+    runner = engine.runner
+    dev = runner.device
+    for kv in runner.cache.kv:                       # random cache contents stand in for real prompts
+        kv.normal_(0.0, 1.0)
+    gen = torch.Generator().manual_seed(1)
+
+    def open_requests(n, tag):
+        rcs = []
+        for i in range(n):
+            rc = runner.open(f"{tag}{i}")
+            runner.cache.ensure(rc, args.context)
+            runner.cache.commit(rc, args.context)
+            rcs.append(rc)
+        return rcs
+
+    def time_decode(batch, steps, warm):
+        rcs = open_requests(batch, f"b{batch}_")
+        toks = torch.randint(0, cfg.vocab_size, (warm + steps, batch), generator=gen).tolist()
+        zeros = ([0.0] * batch, [0] * batch, [0.0] * batch)
+        for i in range(warm):
+            runner.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(rcs)], sampling=zeros)
+        torch.cuda.synchronize(dev)
+        l0 = kernels.launches()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warm, warm + steps):
+            runner.step([StepEntry(rc, [toks[i][j]], [0]) for j, rc in enumerate(rcs)], sampling=zeros)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1)
+        launches = kernels.launches() - l0
+        ctx_mean = args.context + warm + steps / 2.0
+        for rc in rcs:
+            runner.close(rc)
+        return ms, launches, ctx_mean
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches, ctx_mean = time_decode(args.batch, K, W)
+    value = args.batch * K / (ms / 1e3)
+    ms_per_step = ms / K
+    bytes_step = decode_bytes(cfgd, args.layers, args.batch, ctx_mean)
+    achieved = bytes_step / (ms_per_step / 1e3) / 1e9
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _ = time_decode(b, min(K, 128), W)
+            points[f"decode_b{b}"] = round(b * min(K, 128) / (pms / 1e3), 1)
+
+    # prefill: one prompt of T tokens in one step, logits at its last place
+    T = args.prefill_tokens
+    pre_ms = []
+    for i in range(W + 3):
+        rc = runner.open(f"p{i}")
+        prompt = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepEntry(rc, prompt, [T - 1])])
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i >= W:
+            pre_ms.append(e0.elapsed_time(e1))
+        runner.close(rc)
+    pre = sorted(pre_ms)[len(pre_ms) // 2]
+    pflops = prefill_flops(cfgd, args.layers, T)
+    prefill = {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
+               "frac": round(pflops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # end to end through the entry point: host ids in, sampled ids out, every step
+    e2e = None
+    if not args.no_e2e:
+        sp = SamplingParams(max_new_tokens=W + K + 8, ignore_eos=True)
+        reqs = []
+        for i in range(args.batch):
+            r = engine.add_request(torch.randint(0, cfg.vocab_size, (64,), generator=gen).tolist(), sp)
+            reqs.append(r)
+        while any(r.num_pending > 1 or not r.output for r in reqs):
+            engine.step()
+        # lengthen every request's cache to the benchmark context without running long prompts
+        for r in reqs:
+            add = args.context - r.cache.num_tokens
+            runner.cache.ensure(r.cache, r.cache.num_tokens + add)
+            runner.cache.commit(r.cache, add)
+            r.num_computed += add
+            r.prompt = r.prompt + [0] * add
+        for _ in range(W):
+            engine.step()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        n0 = sum(len(r.output) for r in reqs)
+        for _ in range(K):
+            engine.step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        wall = time.perf_counter() - t0
+        n1 = sum(len(r.output) for r in reqs)
+        g = next(iter(runner._graphs.values())) if runner._graphs else None
+        h2d = max((gr.lay.total * 4 for gr in runner._graphs.values()), default=0)
+        e2e = {"value": round((n1 - n0) / max(wall, e0.elapsed_time(e1) / 1e3), 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(wall / K * 1e3, 4)}
+    ck = clocks.stop()
+
+    out = {
+        "metric": "decode tok/s at batch 8 (3B, bf16); prefill tok/s at 2,048 tokens and batch 1/64 beside it",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), random token ids, random cache contents",
+        "config": {"model": "Qwen2.5-3B shape", "layers": args.layers, "layers_full": SHAPE_3B["num_hidden_layers"],
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "tied": True, "global_batch": args.batch, "seq_len": args.context, "new_tokens": W + K,
+                   "page": page, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 6.2 GB/step)",
+                   "bf16_gemm": matmul_backend.mode, "peaks": pk_src},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "e2e": e2e, "gpu_launches": launches, "library_gemms": matmul_backend.counters["library"],
+        "clocks": ck, "impl": "ours",
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -60,18 +60,51 @@ class StepContext:
     max_portion: int = 0
     max_context: int = 0
     num_wanted: int = 0
+    all_decode: bool = False      # every entry is one token (the kernels may take a decode path)
 
 
 def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
-def build_context(entries: Sequence[StepEntry], cache: CacheManager, device, vocab_size: int,
-                  max_positions: int) -> StepContext:
-    """Validate ``entries`` and make the step's device metadata (one host-to-device copy)."""
+class MetaLayout:
+    """Where each array lies in the packed int32 buffer, for given (padded) sizes."""
+
+    def __init__(self, T: int, R: int, n_want: int, max_blocks: Sequence[int], extra: int = 0):
+        self.T, self.R, self.n_want, self.max_blocks = T, R, n_want, list(max_blocks)
+        segs = {"tokens": T, "positions": T, "token_req": T, "cu": R + 1, "start": R, "slots": R,
+                "want": n_want, "extra": extra}
+        self.off, cur = {}, 0
+        for k, n in segs.items():
+            self.off[k] = cur
+            cur += _pad4(n)
+        self.goff = []
+        for mb in self.max_blocks:
+            self.goff.append((cur, cur + _pad4(T)))
+            cur += _pad4(T) + _pad4(R * mb)
+        self.total = max(cur, 4)
+
+    def context(self, dev: torch.Tensor, cache: CacheManager, device, n_want: Optional[int] = None) -> StepContext:
+        """Views into the device copy ``dev`` of the packed buffer."""
+        T, R = self.T, self.R
+        nw = self.n_want if n_want is None else n_want
+        seg = lambda k, n: dev[self.off[k]:self.off[k] + n]
+        groups = []
+        for g, mb in enumerate(self.max_blocks):
+            so, bo = self.goff[g]
+            groups.append(GroupView(block_table=dev[bo:bo + R * mb].view(R, mb), slot_map=dev[so:so + T],
+                                    page_size=cache.page_size, max_blocks=mb))
+        return StepContext(
+            num_tokens=T, num_requests=R, device=torch.device(device),
+            tokens=seg("tokens", T), positions=seg("positions", T), token_request=seg("token_req", T),
+            cu_tokens=seg("cu", R + 1), start_pos=seg("start", R), state_slots=seg("slots", R),
+            logit_rows=seg("want", nw), groups=groups, cache=cache, num_wanted=nw)
+
+
+def validate(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: int, max_positions: int):
+    """Check a batch; returns (lens, starts, slots)."""
     if not entries:
         raise StepError("a step needs at least one entry")
-    R = len(entries)
     lens, starts, slots = [], [], []
     seen = set()
     for e in entries:
@@ -98,72 +131,90 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, device, voc
         lens.append(n)
         starts.append(rc.num_tokens)
         slots.append(rc.state_slot)
+    return lens, starts, slots
+
+
+def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: CacheManager, lens, starts,
+         slots, vocab_size: int):
+    """Write the step's arrays into the host buffer ``h`` (int32) at ``lay``'s places.  When ``lay``
+    is larger than the batch (a padded decode batch), the padding repeats entry 0."""
+    R = len(entries)
     T = sum(lens)
     cu = np.zeros(R + 1, dtype=np.int64)
     np.cumsum(lens, out=cu[1:])
-    tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
+    if T == R:
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=R)
+    else:
+        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64).reshape(-1) for e in entries])
     if tokens.min() < 0 or tokens.max() >= vocab_size:
         bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
         raise StepError(f"token id {bad} is outside the vocabulary of {vocab_size}")
-    token_req = np.repeat(np.arange(R, dtype=np.int64), lens)
-    positions = np.arange(T, dtype=np.int64) - cu[:-1][token_req] + np.asarray(starts, dtype=np.int64)[token_req]
-    want = np.concatenate([cu[i] + np.asarray(e.want, dtype=np.int64).reshape(-1)
-                           for i, e in enumerate(entries)]) if any(len(e.want) for e in entries) \
-        else np.zeros(0, dtype=np.int64)
-    ps = cache.page_size
-    n_groups = len(cache.pools)
-    max_blocks = [max(1, max(len(e.cache.tables[g]) for e in entries)) for g in range(n_groups)]
+    starts_a = np.asarray(starts, dtype=np.int64)
+    if T == R:
+        token_req = np.arange(R, dtype=np.int64)
+        positions = starts_a
+    else:
+        token_req = np.repeat(np.arange(R, dtype=np.int64), lens)
+        positions = np.arange(T, dtype=np.int64) - cu[:-1][token_req] + starts_a[token_req]
+    want = [cu[i] + np.asarray(e.want, dtype=np.int64).reshape(-1) for i, e in enumerate(entries) if len(e.want)]
+    want = np.concatenate(want) if want else np.zeros(0, dtype=np.int64)
+    padded = lay.T != T or lay.R != R
+    if padded and not (T == R and lay.T == lay.R and len(want) == R):
+        raise StepError("only a batch of single tokens that all want logits can be padded")
 
-    # layout of the packed buffer
-    segs = {"tokens": T, "positions": T, "token_req": T, "cu": R + 1, "start": R, "slots": R, "want": len(want)}
-    off, cur = {}, 0
-    for k, n in segs.items():
-        off[k] = cur
-        cur += _pad4(n)
-    goff = []
-    for g in range(n_groups):
-        goff.append((cur, cur + _pad4(T)))
-        cur += _pad4(T) + _pad4(R * max_blocks[g])
-    total = max(cur, 4)
-    host = torch.empty(total, dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
-    h = host.numpy()
-    h[off["tokens"]:off["tokens"] + T] = tokens
-    h[off["positions"]:off["positions"] + T] = positions
-    h[off["token_req"]:off["token_req"] + T] = token_req
-    h[off["cu"]:off["cu"] + R + 1] = cu
-    h[off["start"]:off["start"] + R] = starts
-    h[off["slots"]:off["slots"] + R] = slots
-    h[off["want"]:off["want"] + len(want)] = want
-    for g in range(n_groups):
-        so, bo = goff[g]
-        bt = np.full((R, max_blocks[g]), -1, dtype=np.int64)
+    def put(key, arr, n_real, n_pad):
+        o = lay.off[key]
+        h[o:o + n_real] = arr
+        if n_pad > n_real:
+            h[o + n_real:o + n_pad] = arr[0]
+
+    put("tokens", tokens, T, lay.T)
+    put("positions", positions, T, lay.T)
+    o = lay.off["token_req"]
+    h[o:o + lay.T] = np.arange(lay.T) if padded else token_req
+    o = lay.off["cu"]
+    h[o:o + lay.R + 1] = np.arange(lay.R + 1) if padded else cu
+    put("start", starts_a, R, lay.R)
+    put("slots", np.asarray(slots, dtype=np.int64), R, lay.R)
+    o = lay.off["want"]
+    h[o:o + lay.n_want] = np.arange(lay.n_want) if padded else want
+    ps = cache.page_size
+    for g, mb in enumerate(lay.max_blocks):
+        so, bo = lay.goff[g]
+        bt = np.full((lay.R, mb), -1, dtype=np.int64)
         for i, e in enumerate(entries):
             pages = e.cache.tables[g].pages
             bt[i, :len(pages)] = pages
-        page_idx = positions // ps
-        phys = bt[token_req, page_idx]
+        if lay.R > R:
+            bt[R:] = bt[0]
+        phys = bt[token_req, positions // ps]
         if (phys < 0).any():
             raise StepError("a token of this step would be written to a page that was given back")
-        h[so:so + T] = phys * ps + positions % ps
-        h[bo:bo + R * max_blocks[g]] = bt.reshape(-1)
+        put_arr = phys * ps + positions % ps
+        h[so:so + T] = put_arr
+        if lay.T > T:
+            h[so + T:so + lay.T] = put_arr[0]
+        h[bo:bo + lay.R * mb] = bt.reshape(-1)
+    return cu, want
+
+
+def build_context(entries: Sequence[StepEntry], cache: CacheManager, device, vocab_size: int,
+                  max_positions: int) -> StepContext:
+    """Validate ``entries`` and make the step's device metadata (one host-to-device copy)."""
+    lens, starts, slots = validate(entries, cache, vocab_size, max_positions)
+    R, T = len(entries), sum(lens)
+    n_want = sum(len(e.want) for e in entries)
+    max_blocks = [max(1, max(len(e.cache.tables[g]) for e in entries)) for g in range(len(cache.pools))]
+    lay = MetaLayout(T, R, n_want, max_blocks)
+    host = torch.empty(lay.total, dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
+    cu, _ = fill(host.numpy(), lay, entries, cache, lens, starts, slots, vocab_size)
     dev = host.to(device, non_blocking=True)
-
-    def seg(k, n):
-        return dev[off[k]:off[k] + n]
-
-    groups = []
-    for g in range(n_groups):
-        so, bo = goff[g]
-        groups.append(GroupView(
-            block_table=dev[bo:bo + R * max_blocks[g]].view(R, max_blocks[g]),
-            slot_map=dev[so:so + T], page_size=ps, max_blocks=max_blocks[g]))
-    ctx = StepContext(
-        num_tokens=T, num_requests=R, device=torch.device(device),
-        tokens=seg("tokens", T), positions=seg("positions", T), token_request=seg("token_req", T),
-        cu_tokens=seg("cu", R + 1), start_pos=seg("start", R), state_slots=seg("slots", R),
-        logit_rows=seg("want", len(want)), groups=groups, cache=cache,
-        host_cu_tokens=[int(c) for c in cu], host_start_pos=list(starts), host_state_slots=list(slots),
-        max_portion=max(lens), max_context=max(s + n for s, n in zip(starts, lens)),
-        num_wanted=len(want))
+    ctx = lay.context(dev, cache, device)
+    ctx.host_cu_tokens = [int(c) for c in cu]
+    ctx.host_start_pos = list(starts)
+    ctx.host_state_slots = list(slots)
+    ctx.max_portion = max(lens)
+    ctx.max_context = max(s + n for s, n in zip(starts, lens))
+    ctx.all_decode = T == R
     ctx._host_buffer = host  # keep the pinned buffer alive until the copy has run
     return ctx

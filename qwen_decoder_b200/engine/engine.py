@@ -38,7 +38,7 @@ class Engine:
         memory after the weights, as the reference takes 80 % (gpu_decoder.cu:197-204)."""
         self.max_prefill_len = max_prefill_len
         make = dict(dtype=dtype, device=device, page_size=page_size, max_requests=max_batch,
-                    max_positions=max_positions)
+                    max_positions=max_positions, use_graphs=use_graphs)
         sizing = _PageSizing(num_pages, kv_memory_fraction, page_size, resolve_dtype(dtype))
         if model is not None:
             self.runner = ModelRunner.from_folder(model, num_pages=sizing, **make)
@@ -48,13 +48,11 @@ class Engine:
             raise ValueError("give a model folder, or config= and random_seed=")
         self.config = self.runner.config
         self.device = self.runner.device
-        self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(self.runner.cache, max_batch=max_batch,
                                    max_prefill_tokens_per_step=max_prefill_tokens_per_step,
                                    max_total_tokens=max_total_tokens,
                                    max_positions=self.runner.max_positions,
                                    stop_ids=getattr(self.config, "eos_token_ids", ()))
-        self.use_graphs = use_graphs
         self._next_id = 0
         self._keys: Dict[int, int] = {}
 
@@ -82,17 +80,16 @@ class Engine:
             return finished
         entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                    for e in plan.entries]
-        logits = self.runner.step(entries, ensure_pages=False)
         sampling = [e.request for e in plan.entries if e.samples]
         tokens: List[int] = []
         if sampling:
-            if all(r.params.temperature == 0.0 for r in sampling):
-                ids = self.sampler.greedy(logits)
-            else:
-                ids = self.sampler.sample(
-                    logits, [r.params.temperature for r in sampling], [r.params.top_k for r in sampling],
-                    [uniform_draw(r.params.seed, r.sample_key, len(r.output)) for r in sampling])
+            _, ids = self.runner.step(entries, ensure_pages=False, sampling=(
+                [r.params.temperature for r in sampling], [r.params.top_k for r in sampling],
+                [uniform_draw(r.params.seed, r.sample_key, len(r.output)) if r.params.temperature else 0.0
+                 for r in sampling]))
             tokens = ids.cpu().tolist()
+        else:
+            self.runner.step(entries, ensure_pages=False)
         finished += self.scheduler.update(plan, tokens)
         return finished
 

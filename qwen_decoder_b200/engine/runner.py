@@ -17,7 +17,7 @@ from ..cache import CacheManager, RequestCache
 from ..config import describe_model, load_config
 from ..parts.model import DecoderModel, build_model
 from ..weights import TensorSource, load_into, random_tensors
-from .batch import StepEntry, StepError, build_context
+from .batch import MetaLayout, StepEntry, StepError, build_context, fill, validate
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "f32": torch.float32,
           "fp32": torch.float32}
@@ -46,7 +46,7 @@ class ModelRunner:
     """A bound model, its cache, and ``step``."""
 
     def __init__(self, model: DecoderModel, config, num_pages: int, page_size: int = 16,
-                 max_requests: int = 64, max_positions: Optional[int] = None):
+                 max_requests: int = 64, max_positions: Optional[int] = None, use_graphs: bool = True):
         self.model = model
         self.config = config
         self.device = model.device
@@ -58,6 +58,10 @@ class ModelRunner:
             num_pages = num_pages.resolve(self.layout, self.device, max_requests, self.max_positions)
         self.cache = CacheManager(self.layout, num_pages, page_size, max_requests, dtype=self.dtype,
                                   device=self.device)
+        from ..sampling import Sampler
+        self.sampler = Sampler(self.device)
+        self.use_graphs = use_graphs
+        self._graphs = {}
         self.steps = 0
         self.tokens_run = 0
 
@@ -92,29 +96,135 @@ class ModelRunner:
         self.cache.close(rc)
 
     # ---- the step ------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], ensure_pages: bool = True) -> torch.Tensor:
+    def _ensure(self, entries: Sequence[StepEntry]) -> None:
+        taken = []
+        try:
+            for e in entries:
+                before = [len(t) for t in e.cache.tables]
+                taken.append((e.cache, before))
+                self.cache.ensure(e.cache, e.cache.num_tokens + len(e.tokens))
+        except Exception:
+            for rc, before in taken:     # all or nothing over the whole batch
+                for g, table in enumerate(rc.tables):
+                    while len(table.pages) > before[g]:
+                        self.cache.pools[g].release(table.pages.pop())
+            raise
+
+    def step(self, entries: Sequence[StepEntry], ensure_pages: bool = True, sampling=None):
         """Run one batch; returns float32 logits [wanted places in entry order, vocab] on the device.
 
         With ``ensure_pages`` the pages the new tokens need are taken first (``OutOfPages`` if the
         pool cannot give them; nothing is taken then).  Afterwards each request's cached length has
-        grown by its tokens."""
+        grown by its tokens.  With ``sampling`` = (temperatures, top_ks, draws), one per wanted
+        place, returns (logits, sampled int32 tokens on the device).
+
+        A batch of single tokens that all want logits runs as a replayed CUDA graph (one per padded
+        batch size and block-table width) when ``use_graphs`` is set; the logits then live in a
+        buffer that the next such step overwrites."""
         if ensure_pages:
-            taken = []
-            try:
-                for e in entries:
-                    before = [len(t) for t in e.cache.tables]
-                    taken.append((e.cache, before))
-                    self.cache.ensure(e.cache, e.cache.num_tokens + len(e.tokens))
-            except Exception:
-                for rc, before in taken:     # all or nothing over the whole batch
-                    for g, table in enumerate(rc.tables):
-                        while len(table.pages) > before[g]:
-                            self.cache.pools[g].release(table.pages.pop())
-                raise
-        ctx = build_context(entries, self.cache, self.device, self.model.vocab_size, self.max_positions)
-        logits = self.model.forward(ctx)
+            self._ensure(entries)
+        if self.use_graphs and not self.layout.fixed and all(
+                len(e.tokens) == 1 and len(e.want) == 1 for e in entries):
+            logits, tokens = self._graph_step(entries, sampling)
+            n_tokens = len(entries)
+        else:
+            ctx = build_context(entries, self.cache, self.device, self.model.vocab_size, self.max_positions)
+            logits = self.model.forward(ctx)
+            tokens = None
+            if sampling is not None and ctx.num_wanted:
+                tokens = self.sampler.sample(logits, *sampling)
+            n_tokens = ctx.num_tokens
         for e in entries:
             self.cache.commit(e.cache, len(e.tokens))
         self.steps += 1
-        self.tokens_run += ctx.num_tokens
-        return logits
+        self.tokens_run += n_tokens
+        return logits if sampling is None else (logits, tokens)
+
+    # ---- decode steps as CUDA graphs ---------------------------------------------
+    def _graph_step(self, entries: Sequence[StepEntry], sampling):
+        import numpy as np
+        lens, starts, slots = validate(entries, self.cache, self.model.vocab_size, self.max_positions)
+        R = len(entries)
+        Bp = 1
+        while Bp < R:
+            Bp *= 2
+        mbs = tuple((max(len(e.cache.tables[g]) for e in entries) + 31) // 32 * 32
+                    for g in range(len(self.cache.pools)))
+        key = (Bp, mbs)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph(self, Bp, mbs)
+        host = g.next_host()
+        h = host.numpy()
+        fill(h, g.lay, entries, self.cache, lens, starts, slots, self.model.vocab_size)
+        o = g.lay.off["extra"]
+        if sampling is not None:
+            temps, top_ks, draws = sampling
+            hf = h.view(np.float32)
+            hf[o:o + R] = temps
+            h[o + Bp:o + Bp + R] = top_ks
+            hf[o + 2 * Bp:o + 2 * Bp + R] = draws
+        else:
+            h[o:o + 3 * Bp] = 0
+        g.upload(host)
+        g.run()
+        return g.logits[:R], g.tokens[:R]
+
+
+class _DecodeGraph:
+    """One captured decode step for a padded batch size and block-table widths."""
+
+    def __init__(self, runner: "ModelRunner", Bp: int, mbs):
+        self.runner = runner
+        self.lay = MetaLayout(Bp, Bp, Bp, mbs, extra=3 * Bp)
+        # two pinned staging buffers: one may still be in flight while the next step is written
+        self.hosts = [torch.empty(self.lay.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.events = [None, None]
+        self.turn = 0
+        self.dev = torch.zeros(self.lay.total, dtype=torch.int32, device=runner.device)
+        self.ctx = self.lay.context(self.dev, runner.cache, runner.device)
+        self.ctx.all_decode = True
+        self.ctx.max_portion = 1
+        self.ctx.max_context = min(runner.max_positions, max(mbs) * runner.cache.page_size) if mbs else 1
+        o = self.lay.off["extra"]
+        self.temps = self.dev[o:o + Bp].view(torch.float32)
+        self.top_ks = self.dev[o + Bp:o + 2 * Bp]
+        self.draws = self.dev[o + 2 * Bp:o + 3 * Bp].view(torch.float32)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits = None
+        self.tokens = None
+
+    def next_host(self) -> torch.Tensor:
+        self.turn ^= 1
+        if self.events[self.turn] is not None:
+            self.events[self.turn].synchronize()
+        return self.hosts[self.turn]
+
+    def upload(self, host: torch.Tensor) -> None:
+        self.dev.copy_(host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[self.turn] = ev
+
+    def _forward(self):
+        from .. import kernels
+        self.logits = self.runner.model.forward(self.ctx)
+        self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.runner.device)
+        kernels.sample(self.logits, self.temps, self.top_ks, self.draws, self.tokens)
+
+    def run(self) -> None:
+        if self.graph is None:
+            # the first step of this shape runs eagerly (loads every kernel), then is captured; the
+            # eager run and the first replay write the same values to the same cache slots
+            self._forward()
+            torch.cuda.synchronize(self.runner.device)
+            from .. import kernels
+            graph = torch.cuda.CUDAGraph()
+            n0 = kernels.launches()
+            with torch.cuda.graph(graph):
+                self._forward()
+            self.own_launches = kernels.launches() - n0
+            self.graph = graph
+        self.graph.replay()
+        from .. import kernels
+        kernels.add_launches(self.own_launches)

@@ -37,7 +37,20 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(t.data_ptr())
 
 
+_launch_count = [0]
+
+
+def launches() -> int:
+    """How many kernels of this package have been launched (replays of captured steps included)."""
+    return _launch_count[0]
+
+
+def add_launches(n: int) -> None:
+    _launch_count[0] += n
+
+
 def _stream():
+    _launch_count[0] += 1          # every launcher fetches the stream exactly once
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
