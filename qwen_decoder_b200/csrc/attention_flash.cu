@@ -1,0 +1,505 @@
+// Paged attention on tensor cores for the bfloat16 path: a prefill kernel (portions of any
+// length, causal over the cached history plus the portion itself) and a decode kernel
+// (one query token per request, keys split over CTAs and warps, partial results merged).
+// Scores, softmax and the output accumulators are float32; Q K^T and P V are
+// mma.sync m16n8k16 bf16 products.  K and V tiles are fetched page by page through the
+// block table with cp.async; all query heads of a KV head's group share each tile, where
+// the reference's kernels re-read K and V for every (head, token) pair
+// (gpu_kernels.cu:197-312, 320-429) and run the dot products on CUDA cores.
+//
+// Rows of a tile are (token, head within the group) pairs, so a group of 8 heads fills a
+// 64-row tile with 8 tokens: short portions still fill tiles and a decode token's group is
+// one 16-row tile.  Head sizes 16..128 in steps of 16 (instantiated: 16, 32, 48, 64, 96,
+// 128); page sizes that are multiples of 16; groups of up to 16 heads (decode) / 64 heads
+// (prefill).  Anything else is refused and the caller takes the generic kernel.
+#include "common.cuh"
+#include <math.h>
+
+#define FA_PAD 8  // bf16 elements of padding per smem row: 16 bytes, keeps ldmatrix conflict-free
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, int src_bytes) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  return v + __shfl_xor_sync(0xffffffffu, v, 2);
+}
+
+// ===================================================================== decode
+#define DEC_WARPS 4
+#define DEC_STAGES 3
+#define DEC_CHUNK 16  // keys per warp iteration; a chunk never straddles a page
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                        const bf16* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ token_req, const int* __restrict__ positions, int H, int G,
+                        int page_size, float scale_log2e, int window, int splits,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+  constexpr int LD = HD + FA_PAD;
+  constexpr int TILE = DEC_CHUNK * LD;            // elements of one K or V chunk in smem
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);
+  const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gs = H / G;
+  const int pos = positions[t];
+  const int n_keys = pos + 1;
+  const int key_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int chunk_lo = key_lo / DEC_CHUNK, chunk_hi = (n_keys + DEC_CHUNK - 1) / DEC_CHUNK;
+  const int per = (chunk_hi - chunk_lo + splits - 1) / splits;
+  const int c0 = chunk_lo + s * per;
+  const int c1 = min(chunk_hi, c0 + per);
+  const int* bt = block_table + (size_t)token_req[t] * max_blocks;
+  const size_t page_elems = (size_t)2 * G * page_size * HD;
+  const size_t k_off = (size_t)g * page_size * HD, v_off = ((size_t)G + g) * page_size * HD;
+
+  // Q fragments: rows are the heads of this KV head's group (rows >= gs are zero)
+  unsigned qa[HD / 16][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
+    const bf16* q0 = q + (size_t)t * q_stride + (size_t)(g * gs + r0) * HD + cq;
+    const bf16* q1 = q + (size_t)t * q_stride + (size_t)(g * gs + r1) * HD + cq;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+      qa[kk][0] = r0 < gs ? *reinterpret_cast<const unsigned*>(q0 + kk * 16) : 0u;
+      qa[kk][1] = r1 < gs ? *reinterpret_cast<const unsigned*>(q1 + kk * 16) : 0u;
+      qa[kk][2] = r0 < gs ? *reinterpret_cast<const unsigned*>(q0 + kk * 16 + 8) : 0u;
+      qa[kk][3] = r1 < gs ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + 8) : 0u;
+    }
+  }
+  bf16* wbuf = smem + (size_t)warp * DEC_STAGES * 2 * TILE;
+  auto load_chunk = [&](int c, int stage) {
+    bf16* ks = wbuf + (size_t)stage * 2 * TILE;
+    bf16* vs = ks + TILE;
+    int key0 = c * DEC_CHUNK;
+    int page = bt[key0 / page_size];
+    int in_page = key0 % page_size;
+    const bf16* kg = kv + (page < 0 ? 0 : (size_t)page * page_elems) + k_off + (size_t)in_page * HD;
+    const bf16* vg = kv + (page < 0 ? 0 : (size_t)page * page_elems) + v_off + (size_t)in_page * HD;
+    constexpr int CPR = HD / 8;  // 16-byte pieces per row
+    for (int i = lane; i < DEC_CHUNK * CPR; i += 32) {
+      int row = i / CPR, col = (i % CPR) * 8;
+      int bytes = (page >= 0 && key0 + row < n_keys) ? 16 : 0;   // rows past the end are zero-filled
+      cp_async16(ks + row * LD + col, kg + (bytes ? row * HD + col : 0), bytes);
+      cp_async16(vs + row * LD + col, vg + (bytes ? row * HD + col : 0), bytes);
+    }
+  };
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  const int first = c0 + warp;
+  const int n_my = first < c1 ? (c1 - first + DEC_WARPS - 1) / DEC_WARPS : 0;
+#pragma unroll
+  for (int p = 0; p < DEC_STAGES - 1; p++) {
+    if (p < n_my) load_chunk(first + p * DEC_WARPS, p);
+    cp_async_commit();
+  }
+  for (int i = 0; i < n_my; i++) {
+    int nx = i + DEC_STAGES - 1;
+    if (nx < n_my) load_chunk(first + nx * DEC_WARPS, nx % DEC_STAGES);
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
+    __syncwarp();
+    const bf16* ks = wbuf + (size_t)(i % DEC_STAGES) * 2 * TILE;
+    const bf16* vs = ks + TILE;
+    const int c = first + i * DEC_WARPS;
+    float sc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+      unsigned b[4];
+      ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+      mma_bf16(sc[0], qa[kk], b[0], b[1]);
+      mma_bf16(sc[1], qa[kk], b[2], b[3]);
+    }
+#pragma unroll
+    for (int n = 0; n < 2; n++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        int key = c * DEC_CHUNK + n * 8 + (lane & 3) * 2 + (j & 1);
+        bool ok = key >= key_lo && key < n_keys;
+        sc[n][j] = ok ? sc[n][j] * scale_log2e : -INFINITY;
+      }
+    float mx0 = quad_max(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])));
+    float mx1 = quad_max(fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])));
+    float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+    float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
+    m0 = mn0; m1 = mn1;
+    float p[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+      p[n][0] = exp2f(sc[n][0] - ref0); p[n][1] = exp2f(sc[n][1] - ref0);
+      p[n][2] = exp2f(sc[n][2] - ref1); p[n][3] = exp2f(sc[n][3] - ref1);
+    }
+    l0 = l0 * a0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+    l1 = l1 * a1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+    unsigned pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
+                      pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+#pragma unroll
+    for (int dn = 0; dn < HD / 16; dn++) {
+      o[2 * dn][0] *= a0; o[2 * dn][1] *= a0; o[2 * dn][2] *= a1; o[2 * dn][3] *= a1;
+      o[2 * dn + 1][0] *= a0; o[2 * dn + 1][1] *= a0; o[2 * dn + 1][2] *= a1; o[2 * dn + 1][3] *= a1;
+      unsigned b[4];
+      ldmatrix_x4_trans(b, vs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dn * 16 + 8 * (lane >> 4));
+      mma_bf16(o[2 * dn], pa, b[0], b[1]);
+      mma_bf16(o[2 * dn + 1], pa, b[2], b[3]);
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  l0 = quad_sum(l0);
+  l1 = quad_sum(l1);
+  __syncthreads();  // every warp is done with its stage buffers: reuse them for the merge
+
+  float* mo = reinterpret_cast<float*>(smem_raw);             // [warps][16][HD]
+  float* mm = mo + DEC_WARPS * 16 * HD;                       // [warps][16]
+  float* ml = mm + DEC_WARPS * 16;                            // [warps][16]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) {
+      float* d0 = mo + ((size_t)warp * 16 + r0) * HD + n * 8 + cq;
+      float* d1 = mo + ((size_t)warp * 16 + r1) * HD + n * 8 + cq;
+      d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+      mm[warp * 16 + r0] = m0; mm[warp * 16 + r1] = m1;
+      ml[warp * 16 + r0] = l0; ml[warp * 16 + r1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < gs * HD; idx += DEC_WARPS * 32) {
+    int row = idx / HD, dim = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mm[w * 16 + row]);
+    float L = 0.f, O = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; w++) {
+        float f = exp2f(mm[w * 16 + row] - M);
+        L += ml[w * 16 + row] * f;
+        O += mo[((size_t)w * 16 + row) * HD + dim] * f;
+      }
+    }
+    int h = g * gs + row;
+    if (splits == 1) {
+      out[(size_t)t * H * HD + (size_t)h * HD + dim] = __float2bfloat16_rn(O / L);
+    } else {
+      size_t pi = ((size_t)t * H + h) * splits + s;
+      part_o[pi * HD + dim] = O;
+      if (dim == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+    }
+  }
+}
+
+// out[t, h, :] = sum_s O_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      bf16* __restrict__ out, int HD, int splits) {
+  size_t th = blockIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; s++) M = fmaxf(M, part_ml[(th * splits + s) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < splits; s++) L += part_ml[(th * splits + s) * 2 + 1] * exp2f(part_ml[(th * splits + s) * 2] - M);
+  for (int dim = threadIdx.x; dim < HD; dim += blockDim.x) {
+    float O = 0.f;
+    for (int s = 0; s < splits; s++)
+      O += part_o[(th * splits + s) * HD + dim] * exp2f(part_ml[(th * splits + s) * 2] - M);
+    out[th * HD + dim] = __float2bfloat16_rn(O / L);
+  }
+}
+
+template <int HD>
+static int launch_decode(const bf16* q, long long q_stride, bf16* out, const bf16* kv, const int* block_table,
+                         int max_blocks, const int* token_req, const int* positions, int T, int H, int G,
+                         int page_size, float scale, int window, int splits, float* part_o, float* part_ml,
+                         cudaStream_t stream) {
+  constexpr int LD = HD + FA_PAD;
+  size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_CHUNK * LD * sizeof(bf16);
+  size_t merge = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
+  if (merge > smem) smem = merge;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid(splits, G, T);
+  decode_attention_kernel<HD><<<grid, DEC_WARPS * 32, smem, stream>>>(
+      q, q_stride, out, kv, block_table, max_blocks, token_req, positions, H, G, page_size,
+      scale * 1.4426950408889634f, window, splits, part_o, part_ml);
+  int e = qd_last_error();
+  if (e) return e;
+  if (splits > 1) {
+    decode_combine_kernel<<<(unsigned)((size_t)T * H), HD < 32 ? 32 : (HD > 128 ? 128 : HD), 0, stream>>>(
+        part_o, part_ml, out, HD, splits);
+    e = qd_last_error();
+  }
+  return e;
+}
+
+// One query token per entry of positions/token_req.  part_o must hold T*H*splits*HD floats and
+// part_ml T*H*splits*2 floats when splits > 1 (scratch; contents need not be initialised).
+extern "C" int qd_decode_attention(const void* q, long long q_stride, void* out, const void* kv,
+                                   const int* block_table, int max_blocks, const int* token_req,
+                                   const int* positions, int T, int H, int G, int d, int page_size,
+                                   float scale, int window, int splits, float* part_o, float* part_ml,
+                                   cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (G <= 0 || H % G != 0 || H / G > 16 || page_size % DEC_CHUNK != 0 || splits < 1 || T > 65535 || G > 65535)
+    return QD_ERR_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml)) return QD_ERR_UNSUPPORTED;
+#define CASE(HD)                                                                                          \
+  case HD:                                                                                                \
+    return launch_decode<HD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv, block_table, max_blocks, \
+                             token_req, positions, T, H, G, page_size, scale, window, splits, part_o,     \
+                             part_ml, stream);
+  switch (d) {
+    CASE(16) CASE(32) CASE(48) CASE(64) CASE(96) CASE(128)
+    default: return QD_ERR_UNSUPPORTED;
+  }
+#undef CASE
+}
+
+// ==================================================================== prefill
+#define PF_WARPS 4
+#define PF_ROWS (PF_WARPS * 16)
+#define PF_KEYS 64  // keys per tile
+
+template <int HD>
+__global__ void __launch_bounds__(PF_WARPS * 32)
+prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
+                         const bf16* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
+                         const int* __restrict__ cu_tokens, const int* __restrict__ start_pos, int R, int H,
+                         int G, int page_size, float scale_log2e, int window, int tok_tile) {
+  constexpr int LD = HD + FA_PAD;
+  constexpr int TILE = PF_KEYS * LD;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);    // [2 stages][K tile, V tile]
+  const int g = blockIdx.y;
+  const int gs = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // which request and which tokens: tiles are numbered request by request; the last tiles
+  // (longest histories within a request) are taken first
+  int b = gridDim.x - 1 - blockIdx.x;
+  int r = 0, before = 0;
+  for (; r < R; r++) {
+    int n = cu_tokens[r + 1] - cu_tokens[r];
+    int nt = (n + tok_tile - 1) / tok_tile;
+    if (b < before + nt) break;
+    before += nt;
+  }
+  if (r == R) return;
+  const int tok0 = cu_tokens[r] + (b - before) * tok_tile;
+  const int n_tok = min(tok_tile, cu_tokens[r + 1] - tok0);
+  const int pos0 = start_pos[r] + (tok0 - cu_tokens[r]);
+  const int key_hi = pos0 + n_tok;                                  // keys [.., key_hi) may be read
+  const int key_lo_tile = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int* bt = block_table + (size_t)r * max_blocks;
+  const size_t page_elems = (size_t)2 * G * page_size * HD;
+  const size_t k_off = (size_t)g * page_size * HD, v_off = ((size_t)G + g) * page_size * HD;
+
+  // this thread's two rows
+  const int row0 = warp * 16 + (lane >> 2), row1 = row0 + 8;
+  const int t0 = row0 / gs, h0 = row0 - t0 * gs, t1 = row1 / gs, h1 = row1 - t1 * gs;
+  const bool ok0 = t0 < n_tok, ok1 = t1 < n_tok;
+  const int p0 = pos0 + t0, p1 = pos0 + t1;                          // positions of the rows
+  const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+  const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+
+  unsigned qa[HD / 16][4];
+  {
+    const int cq = (lane & 3) * 2;
+    const bf16* q0 = q + (size_t)(tok0 + t0) * q_stride + (size_t)(g * gs + h0) * HD + cq;
+    const bf16* q1 = q + (size_t)(tok0 + t1) * q_stride + (size_t)(g * gs + h1) * HD + cq;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+      qa[kk][0] = ok0 ? *reinterpret_cast<const unsigned*>(q0 + kk * 16) : 0u;
+      qa[kk][1] = ok1 ? *reinterpret_cast<const unsigned*>(q1 + kk * 16) : 0u;
+      qa[kk][2] = ok0 ? *reinterpret_cast<const unsigned*>(q0 + kk * 16 + 8) : 0u;
+      qa[kk][3] = ok1 ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + 8) : 0u;
+    }
+  }
+
+  auto load_tile = [&](int kt, int stage) {
+    bf16* ks = smem + (size_t)stage * 2 * TILE;
+    bf16* vs = ks + TILE;
+    constexpr int CPR = HD / 8;
+    const int key_base = kt * PF_KEYS;
+    for (int i = threadIdx.x; i < PF_KEYS * CPR; i += PF_WARPS * 32) {
+      int row = i / CPR, col = (i % CPR) * 8;
+      int key = key_base + row;
+      int page = key < key_hi ? bt[key / page_size] : -1;
+      int bytes = page >= 0 ? 16 : 0;
+      size_t base = page >= 0 ? (size_t)page * page_elems + (size_t)(key % page_size) * HD + col : 0;
+      cp_async16(ks + row * LD + col, kv + base + (page >= 0 ? k_off : 0), bytes);
+      cp_async16(vs + row * LD + col, kv + base + (page >= 0 ? v_off : 0), bytes);
+    }
+  };
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  const int kt_lo = key_lo_tile / PF_KEYS, kt_hi = (key_hi + PF_KEYS - 1) / PF_KEYS;
+  load_tile(kt_lo, 0);
+  cp_async_commit();
+  for (int kt = kt_lo; kt < kt_hi; kt++) {
+    const int stage = (kt - kt_lo) & 1;
+    if (kt + 1 < kt_hi) load_tile(kt + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const bf16* ks = smem + (size_t)stage * 2 * TILE;
+    const bf16* vs = ks + TILE;
+    float sc[PF_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < PF_KEYS / 8; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+#pragma unroll
+      for (int kb = 0; kb < PF_KEYS / 16; kb++) {
+        unsigned bq[4];
+        ldmatrix_x4(bq, ks + (kb * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+        mma_bf16(sc[2 * kb], qa[kk], bq[0], bq[1]);
+        mma_bf16(sc[2 * kb + 1], qa[kk], bq[2], bq[3]);
+      }
+    }
+    const int key_base = kt * PF_KEYS + (lane & 3) * 2;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < PF_KEYS / 8; n++) {
+#pragma unroll
+      for (int j = 0; j < 2; j++) {
+        int key = key_base + n * 8 + j;
+        bool a = ok0 && key <= p0 && key >= lo0;
+        bool c = ok1 && key <= p1 && key >= lo1;
+        sc[n][j] = a ? sc[n][j] * scale_log2e : -INFINITY;
+        sc[n][2 + j] = c ? sc[n][2 + j] * scale_log2e : -INFINITY;
+        mx0 = fmaxf(mx0, sc[n][j]);
+        mx1 = fmaxf(mx1, sc[n][2 + j]);
+      }
+    }
+    mx0 = quad_max(mx0);
+    mx1 = quad_max(mx1);
+    float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+    float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
+    m0 = mn0; m1 = mn1;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int n = 0; n < PF_KEYS / 8; n++) {
+      sc[n][0] = exp2f(sc[n][0] - ref0); sc[n][1] = exp2f(sc[n][1] - ref0);
+      sc[n][2] = exp2f(sc[n][2] - ref1); sc[n][3] = exp2f(sc[n][3] - ref1);
+      s0 += sc[n][0] + sc[n][1];
+      s1 += sc[n][2] + sc[n][3];
+    }
+    l0 = l0 * a0 + s0;
+    l1 = l1 * a1 + s1;
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+#pragma unroll
+    for (int kb = 0; kb < PF_KEYS / 16; kb++) {
+      unsigned pa[4] = {pack_bf16(sc[2 * kb][0], sc[2 * kb][1]), pack_bf16(sc[2 * kb][2], sc[2 * kb][3]),
+                        pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]),
+                        pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3])};
+#pragma unroll
+      for (int dn = 0; dn < HD / 16; dn++) {
+        unsigned bv[4];
+        ldmatrix_x4_trans(bv, vs + (kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dn * 16 + 8 * (lane >> 4));
+        mma_bf16(o[2 * dn], pa, bv[0], bv[1]);
+        mma_bf16(o[2 * dn + 1], pa, bv[2], bv[3]);
+      }
+    }
+    __syncthreads();  // all warps are done with this stage before the next load overwrites it
+  }
+  cp_async_wait<0>();
+  l0 = quad_sum(l0);
+  l1 = quad_sum(l1);
+  const int cq = (lane & 3) * 2;
+  if (ok0) {
+    float inv = 1.f / l0;
+    bf16* d = out + (size_t)(tok0 + t0) * H * HD + (size_t)(g * gs + h0) * HD + cq;
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++)
+      *reinterpret_cast<unsigned*>(d + n * 8) = pack_bf16(o[n][0] * inv, o[n][1] * inv);
+  }
+  if (ok1) {
+    float inv = 1.f / l1;
+    bf16* d = out + (size_t)(tok0 + t1) * H * HD + (size_t)(g * gs + h1) * HD + cq;
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++)
+      *reinterpret_cast<unsigned*>(d + n * 8) = pack_bf16(o[n][2] * inv, o[n][3] * inv);
+  }
+}
+
+template <int HD>
+static int launch_prefill(const bf16* q, long long q_stride, bf16* out, const bf16* kv, const int* block_table,
+                          int max_blocks, const int* cu_tokens, const int* start_pos, int R, int T, int H, int G,
+                          int page_size, float scale, int window, cudaStream_t stream) {
+  constexpr int LD = HD + FA_PAD;
+  size_t smem = (size_t)2 * 2 * PF_KEYS * LD * sizeof(bf16);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(prefill_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int gs = H / G;
+  int tok_tile = PF_ROWS / gs;
+  int tiles = (T + tok_tile - 1) / tok_tile + R;   // upper bound on the tiles of R requests
+  dim3 grid(tiles, G);
+  prefill_attention_kernel<HD><<<grid, PF_WARPS * 32, smem, stream>>>(
+      q, q_stride, out, kv, block_table, max_blocks, cu_tokens, start_pos, R, H, G, page_size,
+      scale * 1.4426950408889634f, window, tok_tile);
+  return qd_last_error();
+}
+
+// Portions of R requests: tokens cu_tokens[r]..cu_tokens[r+1]-1 of the flat batch sit at positions
+// start_pos[r].. of request r (block-table row r).  Their K/V are already in the pages.
+extern "C" int qd_prefill_attention(const void* q, long long q_stride, void* out, const void* kv,
+                                    const int* block_table, int max_blocks, const int* cu_tokens,
+                                    const int* start_pos, int R, int T, int H, int G, int d, int page_size,
+                                    float scale, int window, cudaStream_t stream) {
+  if (T <= 0 || R <= 0) return 0;
+  if (G <= 0 || H % G != 0 || H / G > PF_ROWS || page_size <= 0 || G > 65535) return QD_ERR_UNSUPPORTED;
+#define CASE(HD)                                                                                           \
+  case HD:                                                                                                 \
+    return launch_prefill<HD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv, block_table, max_blocks, \
+                              cu_tokens, start_pos, R, T, H, G, page_size, scale, window, stream);
+  switch (d) {
+    CASE(16) CASE(32) CASE(48) CASE(64) CASE(96) CASE(128)
+    default: return QD_ERR_UNSUPPORTED;
+  }
+#undef CASE
+}

@@ -170,6 +170,54 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
         _I(H), _I(G), _I(d), _I(page_size), _F(scale), _I(window), _stream()), "paged_attention_generic")
 
 
+FLASH_HEAD_DIMS = (16, 32, 48, 64, 96, 128)
+
+
+def flash_decode_supported(dtype, H: int, G: int, d: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and d in FLASH_HEAD_DIMS and H // G <= 16 and page_size % 16 == 0
+
+
+def flash_prefill_supported(dtype, H: int, G: int, d: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and d in FLASH_HEAD_DIMS and H // G <= 64
+
+
+def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                     block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
+                     n_tokens: int, H: int, G: int, d: int, page_size: int, scale: float, window: int,
+                     splits: int) -> None:
+    """One query token per request over its cached keys (tensor cores, keys split over ``splits``
+    CTAs per (request, kv head); partial results go through scratch memory when splits > 1)."""
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2
+    _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((n_tokens * H * splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_tokens * H * splits, 2), dtype=torch.float32, device=q.device)
+    _check(library("attention_flash").qd_decode_attention(
+        _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
+        _ptr(token_req), _ptr(positions), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
+        _I(window), _I(splits), _ptr(part_o), _ptr(part_ml), _stream()), "decode_attention")
+
+
+def prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                      block_table: torch.Tensor, cu_tokens: torch.Tensor, start_pos: torch.Tensor,
+                      n_requests: int, n_tokens: int, H: int, G: int, d: int, page_size: int, scale: float,
+                      window: int) -> None:
+    """Portions of ``n_requests`` requests (tokens cu_tokens[r]..cu_tokens[r+1]-1 at positions
+    start_pos[r]..) over their cached keys, causal, on tensor cores."""
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
+    assert block_table.dtype == torch.int32 and block_table.shape[0] >= n_requests
+    assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
+    _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _check(library("attention_flash").qd_prefill_attention(
+        _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
+        _ptr(cu_tokens), _ptr(start_pos), _I(n_requests), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size),
+        _F(scale), _I(window), _stream()), "prefill_attention")
+
+
 # -------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, draws: torch.Tensor,
            out: torch.Tensor) -> None:

@@ -64,8 +64,26 @@ class GQAttention(Mixer):
             pos.cos if pos is not None else None, pos.sin if pos is not None else None,
             ctx.positions, cache.kv, cache.group.slot_map, cache.group.page_size, cache.write)
         attn = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
-        kernels.paged_attention_generic(
-            qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
-            ctx.positions, ctx.num_tokens, H, G, d, cache.group.page_size, self.scale,
-            self.window or 0)
+        ps, window = cache.group.page_size, self.window or 0
+        if ctx.all_decode and kernels.flash_decode_supported(x.dtype, H, G, d, ps):
+            kernels.decode_attention(
+                qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
+                ctx.positions, ctx.num_tokens, H, G, d, ps, self.scale, window,
+                decode_splits(ctx.num_tokens * G, min(ctx.max_context, window or ctx.max_context)))
+        elif kernels.flash_prefill_supported(x.dtype, H, G, d, ps):
+            kernels.prefill_attention(
+                qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
+                ctx.num_requests, ctx.num_tokens, H, G, d, ps, self.scale, window)
+        else:
+            kernels.paged_attention_generic(
+                qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
+                ctx.positions, ctx.num_tokens, H, G, d, ps, self.scale, window)
         return self.out.forward(attn)
+
+
+def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = 296) -> int:
+    """How many CTAs share one (request, kv head) in decode attention: enough to fill the GPU
+    (two CTAs on each of 148 SMs), but no CTA with fewer than four 16-key chunks."""
+    by_fill = max(1, target_ctas // max(1, ctas_without_split))
+    by_work = max(1, (max_keys + 63) // 64)
+    return max(1, min(by_fill, by_work, 64))

@@ -189,3 +189,70 @@ def test_sampling():
         assert int(out[r]) == tok, (r, int(out[r]), tok)
         checked += 1
     assert checked > R // 2 and int(out[3]) == 100
+
+
+def _plain_attention_row(q_row, k, v, H, G, d, p, window):
+    n = p + 1
+    qq = torch.zeros(n, H * d, dtype=torch.float64)
+    qq[p] = q_row.double()
+    return plain_model.attention(qq, k[:n].double().reshape(n, G * d), v[:n].double().reshape(n, G * d),
+                                 H, G, d, window)[p]
+
+
+@pytest.mark.parametrize("cfg", [(16, 2, 128, 16, None, 1), (16, 2, 128, 16, None, 7), (4, 2, 16, 16, None, 3),
+                                 (6, 2, 48, 32, None, 2), (14, 2, 64, 64, 300, 5), (5, 5, 96, 16, None, 4),
+                                 (32, 2, 32, 16, 50, 2)])
+def test_decode_attention_tensor_cores(cfg):
+    """One query token per request; contexts that end inside a page, at a page's edge, of one key;
+    a window; keys split over several CTAs; one far key made to stand out."""
+    from qwen_decoder_b200 import kernels
+    H, G, d, page_size, window, splits = cfg
+    dt = torch.bfloat16
+    lens = [1, 16, 17, 255, 256, 700, 1031]
+    kv, bt, ks, vs = _paged_setup(dt, lens, G, d, page_size, seed=11)
+    g = torch.Generator().manual_seed(12)
+    q = torch.randn(len(lens), H * d, generator=g).to(dt)
+    # request 5: key 3 (far back) gets a large score for head 0 only
+    ks[5][3, 0] = (q[5, :d].float() * 0.5).to(dt)
+    page = int(bt[5, 3 // page_size])
+    kv[page, 0, 0, 3 % page_size] = ks[5][3, 0]
+    out = torch.empty(len(lens), H * d, dtype=dt, device=DEV)
+    tr = torch.arange(len(lens), dtype=torch.int32)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    kernels.decode_attention(q.to(DEV), H * d, out, kv.to(DEV), bt.to(DEV), tr.to(DEV), pos.to(DEV), len(lens),
+                             H, G, d, page_size, 1.0 / math.sqrt(d), window or 0, splits)
+    for i, n in enumerate(lens):
+        want = _plain_attention_row(q[i], ks[i], vs[i], H, G, d, n - 1, window)
+        close(out[i], want, dt, scale=float(vs[i].abs().max()))
+    if window is None:
+        # the far key dominates head 0 of request 5
+        assert float((out[5, :d].float().cpu() - vs[5][3, 0].float()).abs().max()) < 0.3
+
+
+@pytest.mark.parametrize("cfg", [(16, 2, 128, 16, None), (4, 2, 16, 16, None), (6, 2, 48, 8, None),
+                                 (4, 1, 32, 32, None), (3, 3, 64, 16, 40), (8, 1, 96, 16, None), (7, 7, 128, 16, 100)])
+def test_prefill_attention_tensor_cores(cfg):
+    """Portions with and without history, of one token up to hundreds, several requests in a batch."""
+    from qwen_decoder_b200 import kernels
+    H, G, d, page_size, window = cfg
+    dt = torch.bfloat16
+    # (cached before, portion): whole prompt, portion after history, single token, two tokens at a page edge
+    plan = [(0, 150), (70, 45), (129, 1), (15, 2), (0, 1), (200, 130)]
+    lens = [a + b for a, b in plan]
+    kv, bt, ks, vs = _paged_setup(dt, lens, G, d, page_size, seed=13)
+    g = torch.Generator().manual_seed(14)
+    T = sum(b for _, b in plan)
+    q = torch.randn(T, H * d, generator=g).to(dt)
+    cu = torch.tensor([0] + list(torch.tensor([b for _, b in plan]).cumsum(0)), dtype=torch.int32)
+    start = torch.tensor([a for a, _ in plan], dtype=torch.int32)
+    out = torch.empty(T, H * d, dtype=dt, device=DEV)
+    kernels.prefill_attention(q.to(DEV), H * d, out, kv.to(DEV), bt.to(DEV), cu.to(DEV), start.to(DEV), len(plan), T,
+                              H, G, d, page_size, 1.0 / math.sqrt(d), window or 0)
+    outc = out.cpu()
+    for r, (a, b) in enumerate(plan):
+        n = a + b
+        qq = torch.zeros(n, H * d, dtype=torch.float64)
+        qq[a:] = q[int(cu[r]):int(cu[r + 1])].double()
+        want = plain_model.attention(qq, ks[r].double().reshape(n, G * d), vs[r].double().reshape(n, G * d),
+                                     H, G, d, window)[a:]
+        close(outc[int(cu[r]):int(cu[r + 1])], want, dt, scale=float(vs[r].abs().max()))
