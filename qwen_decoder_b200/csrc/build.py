@@ -32,6 +32,7 @@ NVCC_FLAGS = [
 LIBRARIES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "gemm_generic": "gemm_generic.cu",
+    "gemm_skinny": "gemm_skinny.cu",
     "attention_generic": "attention_generic.cu",
     "attention_flash": "attention_flash.cu",
     "sampling": "sampling.cu",

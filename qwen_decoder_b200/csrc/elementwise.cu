@@ -33,14 +33,16 @@ extern "C" int qd_embedding(float* x, const void* table, int table_dtype, const 
 
 // ------------------------------------------------- residual add + RMSNorm
 // For output row r (source row s = rows ? rows[r] : r):
-//   v = x[s] + delta[s]            (float32; delta may be absent)
+//   v = x[s] + delta[s]            (float32; delta may be absent, or be n_parts float32 partial
+//                                   sums [n_parts, T, D] that are added up here)
 //   x[s] = v                       (if write_back)
 //   out[r] = v / sqrt(mean(v^2) + eps) * w
 // The sum of squares is taken in a fixed order that depends only on D.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                    const float* __restrict__ w, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int D, float eps, int write_back) {
+                                   const int* __restrict__ rows, int D, float eps, int write_back,
+                                   int n_parts, size_t part_stride) {
   extern __shared__ float sm[];  // D values + 33 scratch
   float* v = sm;
   float* scratch = sm + D;
@@ -50,7 +52,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   float ss = 0.0f;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float a = xr[i];
-    if (delta) a += to_float(delta[s * D + i]);
+    if (delta) {
+      float dsum = to_float(delta[s * D + i]);
+      for (int p = 1; p < n_parts; p++) dsum += to_float(delta[p * part_stride + s * D + i]);
+      a += dsum;
+    }
     v[i] = a;
     if (write_back && delta) xr[i] = a;
     ss += a * a;
@@ -63,7 +69,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
 
 extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* w, void* out,
                               int out_dtype, const int* rows, int n_rows, int D, float eps,
-                              int write_back, cudaStream_t stream) {
+                              int write_back, int n_parts, long long part_stride, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   size_t smem = (size_t)(D + 40) * sizeof(float);
   if (smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
@@ -73,10 +79,12 @@ extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
       cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                          \
     add_rmsnorm_kernel<TD, TO><<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, w, (TO*)out, rows, \
-                                                              D, eps, write_back);              \
+                                                              D, eps, write_back, n_parts,      \
+                                                              (size_t)part_stride);             \
   } while (0)
   bool dbf = delta && delta_dtype == QD_BF16;
   if (delta && delta_dtype != QD_BF16 && delta_dtype != QD_F32) return QD_ERR_UNSUPPORTED;
+  if (n_parts < 1 || (n_parts > 1 && delta_dtype != QD_F32)) return QD_ERR_UNSUPPORTED;
   if (out_dtype == QD_F32) {
     if (dbf) LAUNCH(bf16, float); else LAUNCH(float, float);
   } else if (out_dtype == QD_BF16) {
@@ -91,19 +99,23 @@ extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
 // x[t] += delta[t] with no norm after it (used when a residual is left pending at
 // the end of a schedule that does not finish with a norm).
 template <typename TD>
-__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n, int n_parts) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) x[i] += to_float(delta[i]);
+  if (i >= n) return;
+  float d = to_float(delta[i]);
+  for (int p = 1; p < n_parts; p++) d += to_float(delta[p * n + i]);
+  x[i] += d;
 }
 
-extern "C" int qd_residual_add(float* x, const void* delta, int delta_dtype, long long n,
+extern "C" int qd_residual_add(float* x, const void* delta, int delta_dtype, long long n, int n_parts,
                                cudaStream_t stream) {
   if (n <= 0) return 0;
+  if (n_parts < 1) return QD_ERR_UNSUPPORTED;
   unsigned blocks = (unsigned)((n + 255) / 256);
   if (delta_dtype == QD_F32)
-    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n);
-  else if (delta_dtype == QD_BF16)
-    residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, (size_t)n);
+    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n, n_parts);
+  else if (delta_dtype == QD_BF16 && n_parts == 1)
+    residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, (size_t)n, 1);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
@@ -192,6 +204,81 @@ extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d
                                                       page_size, write_kv);
   else
     return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// The same from float32 partial sums: qkv[t] = sum_p part[p, t] + bias, as the few-token
+// contraction leaves them.  q goes to a bfloat16 buffer of its own [T, H*d].
+__global__ void rope_kv_write_partial_kernel(const float* __restrict__ part, int n_parts,
+                                             const float* __restrict__ bias, bf16* __restrict__ q_out, int T,
+                                             int H, int G, int d, int rotary_dim, int pairing,
+                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                             const int* __restrict__ positions, bf16* __restrict__ kv,
+                                             const int* __restrict__ slot_map, int page_size, int write_kv) {
+  int t = blockIdx.x;
+  int row_w = (H + 2 * G) * d;
+  size_t pstride = (size_t)T * row_w;
+  const float* row = part + (size_t)t * row_w;
+  auto val = [&](int idx) {
+    float v = bias ? bias[idx] : 0.f;
+    for (int p = 0; p < n_parts; p++) v += row[p * pstride + idx];
+    return v;
+  };
+  int half = rotary_dim >> 1;
+  const float* c = cos_t ? cos_t + (size_t)positions[t] * half : nullptr;
+  const float* s = cos_t ? sin_t + (size_t)positions[t] * half : nullptr;
+  size_t kbase = 0, vbase = 0;
+  int off = 0;
+  if (write_kv) {
+    int slot = slot_map[t];
+    int page = slot / page_size;
+    off = slot - page * page_size;
+    kbase = (size_t)page * 2 * G * page_size * d;
+    vbase = kbase + (size_t)G * page_size * d;
+  }
+  int pairs_per_head = d >> 1;
+  int n_qk = (H + G) * pairs_per_head;
+  for (int w = threadIdx.x; w < n_qk; w += blockDim.x) {
+    int head = w / pairs_per_head, p = w - head * pairs_per_head;
+    int i0, i1;
+    bool rot = p < half;
+    if (pairing == 0) { i0 = 2 * p; i1 = 2 * p + 1; }
+    else if (rot)     { i0 = p; i1 = p + half; }
+    else              { int jj = 2 * (p - half) + rotary_dim; i0 = jj; i1 = jj + 1; }
+    float a = val(head * d + i0), b = val(head * d + i1);
+    float ra = a, rb = b;
+    if (rot && c) {
+      float cv = c[p], sv = s[p];
+      ra = a * cv - b * sv;
+      rb = a * sv + b * cv;
+    }
+    if (head < H) {
+      bf16* dst = q_out + (size_t)t * H * d + (size_t)head * d;
+      dst[i0] = __float2bfloat16_rn(ra);
+      dst[i1] = __float2bfloat16_rn(rb);
+    } else if (write_kv) {
+      bf16* dst = kv + kbase + ((size_t)(head - H) * page_size + off) * d;
+      dst[i0] = __float2bfloat16_rn(ra);
+      dst[i1] = __float2bfloat16_rn(rb);
+    }
+  }
+  if (write_kv) {
+    for (int w = threadIdx.x; w < G * d; w += blockDim.x) {
+      int g = w / d, i = w - g * d;
+      kv[vbase + ((size_t)g * page_size + off) * d + i] = __float2bfloat16_rn(val((H + G) * d + w));
+    }
+  }
+}
+
+extern "C" int qd_rope_kv_write_partial(const float* part, int n_parts, const float* bias, void* q_out, int T,
+                                        int H, int G, int d, int rotary_dim, int pairing, const float* cos_t,
+                                        const float* sin_t, const int* positions, void* kv,
+                                        const int* slot_map, int page_size, int write_kv, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((d & 1) || (rotary_dim & 1) || rotary_dim > d || rotary_dim < 0 || n_parts < 1) return QD_ERR_UNSUPPORTED;
+  rope_kv_write_partial_kernel<<<T, 256, 0, stream>>>(part, n_parts, bias, (bf16*)q_out, T, H, G, d, rotary_dim,
+                                                      pairing, cos_t, sin_t, positions, (bf16*)kv, slot_map,
+                                                      page_size, write_kv);
   return qd_last_error();
 }
 

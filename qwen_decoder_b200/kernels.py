@@ -90,20 +90,49 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Te
     assert out.shape[1] == D and (rows is None or (rows.dtype == torch.int32 and rows.numel() == n_rows))
     assert rows is not None or n_rows == x.shape[0]
     _contig(x, "x"); _contig(out, "out")
+    n_parts = 1
     if delta is not None:
-        assert delta.shape == x.shape
+        # delta [T, D], or float32 partial sums [n_parts, T, D] that the kernel adds up
+        if delta.dim() == 3:
+            n_parts = delta.shape[0]
+            assert delta.dtype == torch.float32 and tuple(delta.shape[1:]) == tuple(x.shape)
+        else:
+            assert delta.shape == x.shape
         _contig(delta, "delta")
     _check(library("elementwise").qd_add_rmsnorm(
         _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype) if delta is not None else -1), _ptr(weight),
         _ptr(out), _I(dtype_code(out.dtype)), _ptr(rows), _I(n_rows), _I(D), _F(eps),
-        _I(1 if write_back else 0), _stream()), "add_rmsnorm")
+        _I(1 if write_back else 0), _I(n_parts), _LL(x.numel()), _stream()), "add_rmsnorm")
 
 
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
-    assert x.dtype == torch.float32 and x.shape == delta.shape
+    """x += delta (delta [T, D], or float32 partial sums [n_parts, T, D])."""
+    n_parts = delta.shape[0] if delta.dim() == 3 else 1
+    assert x.dtype == torch.float32 and tuple(x.shape) == tuple(delta.shape[-2:])
     _contig(x, "x"); _contig(delta, "delta")
     _check(library("elementwise").qd_residual_add(_ptr(x), _ptr(delta), _I(dtype_code(delta.dtype)),
-                                                  _LL(x.numel()), _stream()), "residual_add")
+                                                  _LL(x.numel()), _I(n_parts), _stream()), "residual_add")
+
+
+def rope_kv_write_partial(part: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor, H: int, G: int,
+                          d: int, rotary_dim: int, pairing: int, cos: Optional[torch.Tensor],
+                          sin: Optional[torch.Tensor], positions: torch.Tensor, kv: Optional[torch.Tensor],
+                          slot_map: Optional[torch.Tensor], page_size: int, write_kv: bool) -> None:
+    """As ``rope_kv_write`` from float32 partial sums part [n_parts, T, (H+2G)*d] (+ bias): rotated q goes
+    to q_out bfloat16 [T, H*d], k and v to the cache."""
+    n_parts, T, W = part.shape
+    assert part.dtype == torch.float32 and W == (H + 2 * G) * d and q_out.shape == (T, H * d)
+    assert q_out.dtype == torch.bfloat16 and positions.dtype == torch.int32
+    _contig(part, "part"); _contig(q_out, "q_out")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == W
+    if write_kv:
+        assert kv.dtype == torch.bfloat16 and tuple(kv.shape[1:]) == (2, G, page_size, d)
+        _contig(kv, "kv")
+    _check(library("elementwise").qd_rope_kv_write_partial(
+        _ptr(part), _I(n_parts), _ptr(bias), _ptr(q_out), _I(T), _I(H), _I(G), _I(d), _I(rotary_dim),
+        _I(pairing), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(kv), _ptr(slot_map), _I(page_size),
+        _I(1 if write_kv else 0), _stream()), "rope_kv_write_partial")
 
 
 def rope_kv_write(qkv: torch.Tensor, H: int, G: int, d: int, rotary_dim: int, pairing: int,
@@ -149,6 +178,59 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     _check(library("gemm_generic").qd_gemm_generic(
         _ptr(x), _ptr(w), _I(dtype_code(x.dtype)), _ptr(bias), _ptr(out), _I(dtype_code(out.dtype)),
         _I(T), _I(N), _I(K), _LL(x.stride(0)), _LL(out.stride(0)), _stream()), "gemm_generic")
+
+
+SKINNY_MAX_TOKENS = 64
+EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
+
+
+def skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def skinny_splits(N: int, K: int, target_ctas: int = 592) -> int:
+    """Shares of K over the grid: enough CTAs (16 rows of W each) for four per SM, every warp at
+    least one group of 128 k."""
+    tiles = (N + 15) // 16
+    groups = (K + 127) // 128
+    return max(1, min((target_ctas + tiles - 1) // tiles, groups // 4, 16))
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[T, N] = x @ w^T (+ bias) for T <= 64, bfloat16 in, out bfloat16 or float32."""
+    T, K = x.shape
+    N = w.shape[0]
+    assert skinny_supported(x, w) and out.shape == (T, N) and out.stride(1) == 1
+    _contig(w, "w")
+    _check(library("gemm_skinny").qd_gemm_skinny(
+        _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(dtype_code(out.dtype)),
+        _LL(out.stride(0)), _ptr(None), _I(T), _I(N), _I(K), _I(1), _I(EPI_STORE), _stream()), "gemm_skinny")
+
+
+def gemm_skinny_partial(x: torch.Tensor, w: torch.Tensor, splits: int) -> torch.Tensor:
+    """float32 partial sums [splits, T, N] of x @ w^T over ``splits`` shares of K."""
+    T, K = x.shape
+    N = w.shape[0]
+    assert skinny_supported(x, w)
+    _contig(w, "w")
+    part = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
+    _check(library("gemm_skinny").qd_gemm_skinny(
+        _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(None), _ptr(None), _I(F32), _LL(0), _ptr(part), _I(T), _I(N),
+        _I(K), _I(splits), _I(EPI_PARTIAL), _stream()), "gemm_skinny_partial")
+    return part
+
+
+def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[T, F] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg; Wu] of shape [2F, K]."""
+    T, K = x.shape
+    N = w_gate_up.shape[0]
+    assert skinny_supported(x, w_gate_up) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
+    _contig(w_gate_up, "w"); _contig(out, "out")
+    _check(library("gemm_skinny").qd_gemm_skinny(
+        _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(None), _ptr(out), _I(BF16), _LL(out.stride(0)),
+        _ptr(None), _I(T), _I(N), _I(K), _I(1), _I(EPI_SWIGLU), _stream()), "gemm_skinny_swiglu")
 
 
 # ------------------------------------------------------------------- attention

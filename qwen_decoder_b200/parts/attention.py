@@ -22,6 +22,7 @@ from ..cache import PagedKV
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
 from .base import Mixer, PagedCacheView
+from . import matmul_backend
 from .linear import Linear
 
 
@@ -56,13 +57,21 @@ class GQAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
         H, G, d = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.qkv.forward(x)
         pos = self.position
-        kernels.rope_kv_write(
-            qkv, H, G, d,
-            pos.rotary_dim if pos is not None else 0, pos.pairing_code if pos is not None else 0,
-            pos.cos if pos is not None else None, pos.sin if pos is not None else None,
-            ctx.positions, cache.kv, cache.group.slot_map, cache.group.page_size, cache.write)
+        rope = (pos.rotary_dim if pos is not None else 0, pos.pairing_code if pos is not None else 0,
+                pos.cos if pos is not None else None, pos.sin if pos is not None else None)
+        if matmul_backend.use_skinny(x, self.qkv.weight):
+            # few tokens: the product leaves float32 partial sums; bias, rotation and cache write take them
+            part = kernels.gemm_skinny_partial(x, self.qkv.weight,
+                                               kernels.skinny_splits(self.qkv.out_features, self.hidden_size))
+            matmul_backend.counters["own"] += 1
+            qkv = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)       # q only
+            kernels.rope_kv_write_partial(part, self.qkv.bias, qkv, H, G, d, *rope, ctx.positions, cache.kv,
+                                          cache.group.slot_map, cache.group.page_size, cache.write)
+        else:
+            qkv = self.qkv.forward(x)
+            kernels.rope_kv_write(qkv, H, G, d, *rope, ctx.positions, cache.kv, cache.group.slot_map,
+                                  cache.group.page_size, cache.write)
         attn = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
         ps, window = cache.group.page_size, self.window or 0
         if ctx.all_decode and kernels.flash_decode_supported(x.dtype, H, G, d, ps):
@@ -78,7 +87,7 @@ class GQAttention(Mixer):
             kernels.paged_attention_generic(
                 qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
                 ctx.positions, ctx.num_tokens, H, G, d, ps, self.scale, window)
-        return self.out.forward(attn)
+        return self.out.forward_partial(attn)
 
 
 def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = 296) -> int:

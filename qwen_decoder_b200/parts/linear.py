@@ -53,3 +53,12 @@ class Linear:
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
         matmul_backend.linear(x, self.weight, self.bias, out)
         return out
+
+    def forward_partial(self, x: torch.Tensor) -> torch.Tensor:
+        """The product as something a residual stream can take: [T, N] in x's dtype, or -- from the
+        few-token kernel -- float32 partial sums [n_parts, T, N] (bias not added) that the next
+        norm's kernel adds up."""
+        if self.bias is None and matmul_backend.use_skinny(x, self.weight):
+            matmul_backend.counters["own"] += 1
+            return kernels.gemm_skinny_partial(x, self.weight, kernels.skinny_splits(self.out_features, self.in_features))
+        return self.forward(x)

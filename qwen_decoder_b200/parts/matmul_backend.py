@@ -2,8 +2,9 @@
 
 float32: always the float32 FMA kernel (``csrc/gemm_generic.cu``); no TF32 anywhere.
 bfloat16: ``mode`` chooses.
-  * ``auto``    the hand-written tensor-core kernel where its sizes allow, else cuBLAS
-                for products large enough to matter, else the generic kernel;
+  * ``auto``    few tokens (<= 64): the hand-written weight-streaming tensor-core kernel
+                (``csrc/gemm_skinny.cu``); more tokens: cuBLAS for products large enough to
+                matter, else the generic kernel;
   * ``generic`` always the generic kernel (any size);
   * ``cublas``  the library product through torch, as the reference calls cublasHgemm
                 (gpu_kernels.cu:431-436), for every bfloat16 product.
@@ -49,8 +50,17 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         return
     T, K = x.shape
     N = w.shape[0]
+    if kernels.skinny_supported(x, w) and out.stride(1) == 1:
+        kernels.gemm_skinny(x, w, bias, out)
+        counters["own"] += 1
+        return
     if K % 8 == 0 and N % 8 == 0 and N * K >= 256 * 256:
         _cublas(x, w, bias, out)
     else:
         kernels.gemm_generic(x, w, bias, out)
         counters["own"] += 1
+
+
+def use_skinny(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the few-token kernel (and its fused epilogues) takes this product."""
+    return mode == "auto" and x.is_cuda and kernels.skinny_supported(x, w)

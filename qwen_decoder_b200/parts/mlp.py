@@ -12,6 +12,7 @@ from .. import kernels
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
 from .base import FeedForward
+from . import matmul_backend
 from .linear import Linear
 
 
@@ -32,7 +33,10 @@ class SwiGLU(FeedForward):
         self.down.bind(source, dtype, device)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        gu = self.gate_up.forward(x)
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.swiglu(gu, h)
-        return self.down.forward(h)
+        if matmul_backend.use_skinny(x, self.gate_up.weight):
+            kernels.gemm_skinny_swiglu(x, self.gate_up.weight, h)       # gate, up and SwiGLU in one kernel
+            matmul_backend.counters["own"] += 1
+        else:
+            kernels.swiglu(self.gate_up.forward(x), h)
+        return self.down.forward_partial(h)
