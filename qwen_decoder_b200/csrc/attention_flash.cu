@@ -66,6 +66,8 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         const int* __restrict__ token_req, const int* __restrict__ positions, int H, int G,
                         int page_size, float scale_log2e, int window, int splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int LD = HD + FA_PAD;
   constexpr int TILE = DEC_CHUNK * LD;            // elements of one K or V chunk in smem
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -232,6 +234,8 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 // out[t, h, :] = sum_s O_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       bf16* __restrict__ out, int HD, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t th = blockIdx.x;
   float M = -INFINITY;
   for (int s = 0; s < splits; s++) M = fmaxf(M, part_ml[(th * splits + s) * 2]);
@@ -257,13 +261,13 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, const bf1
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(splits, G, T);
-  decode_attention_kernel<HD><<<grid, DEC_WARPS * 32, smem, stream>>>(
+  qd_launch(decode_attention_kernel<HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
       q, q_stride, out, kv, block_table, max_blocks, token_req, positions, H, G, page_size,
       scale * 1.4426950408889634f, window, splits, part_o, part_ml);
   int e = qd_last_error();
   if (e) return e;
   if (splits > 1) {
-    decode_combine_kernel<<<(unsigned)((size_t)T * H), HD < 32 ? 32 : (HD > 128 ? 128 : HD), 0, stream>>>(
+    qd_launch(decode_combine_kernel, dim3((unsigned)((size_t)T * H)), dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)), 0, stream, 
         part_o, part_ml, out, HD, splits);
     e = qd_last_error();
   }
@@ -304,6 +308,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          const bf16* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ cu_tokens, const int* __restrict__ start_pos, int R, int H,
                          int G, int page_size, float scale_log2e, int window, int tok_tile) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int LD = HD + FA_PAD;
   constexpr int TILE = PF_KEYS * LD;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -479,7 +485,7 @@ static int launch_prefill(const bf16* q, long long q_stride, bf16* out, const bf
   int tok_tile = PF_ROWS / gs;
   int tiles = (T + tok_tile - 1) / tok_tile + R;   // upper bound on the tiles of R requests
   dim3 grid(tiles, G);
-  prefill_attention_kernel<HD><<<grid, PF_WARPS * 32, smem, stream>>>(
+  qd_launch(prefill_attention_kernel<HD>, dim3(grid), dim3(PF_WARPS * 32), smem, stream, 
       q, q_stride, out, kv, block_table, max_blocks, cu_tokens, start_pos, R, H, G, page_size,
       scale * 1.4426950408889634f, window, tok_tile);
   return qd_last_error();

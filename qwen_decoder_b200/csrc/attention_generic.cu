@@ -23,6 +23,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
                                const int* __restrict__ token_req, const int* __restrict__ positions,
                                int n_tokens, int H, int G, int d, int page_size, float scale,
                                int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float smem[];
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   long long item = (long long)blockIdx.x * AG_WARPS + warp;
@@ -99,11 +101,11 @@ extern "C" int qd_paged_attention_generic(const void* q, long long q_stride, voi
   unsigned blocks = (unsigned)((items + AG_WARPS - 1) / AG_WARPS);
   size_t smem = (size_t)AG_WARPS * d * sizeof(float);
   if (dtype == QD_F32)
-    paged_attention_generic_kernel<float><<<blocks, AG_WARPS * 32, smem, stream>>>(
+    qd_launch(paged_attention_generic_kernel<float>, dim3(blocks), dim3(AG_WARPS * 32), smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)kv, block_table, max_blocks,
         token_req, positions, n_tokens, H, G, d, page_size, scale, window);
   else if (dtype == QD_BF16)
-    paged_attention_generic_kernel<bf16><<<blocks, AG_WARPS * 32, smem, stream>>>(
+    qd_launch(paged_attention_generic_kernel<bf16>, dim3(blocks), dim3(AG_WARPS * 32), smem, stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_table, max_blocks,
         token_req, positions, n_tokens, H, G, d, page_size, scale, window);
   else

@@ -52,3 +52,40 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 }
 
 static inline int qd_last_error() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch -------------------------------------------------
+// Every kernel here is launched so that it may begin while the kernel before it in the
+// stream is still running (cudaLaunchAttributeProgrammaticStreamSerialization).  A kernel
+// first lets its own successor be scheduled (pdl_launch_dependents), may prefetch data that
+// no kernel of the step writes (weights), and calls pdl_wait() before it reads or writes
+// anything else: pdl_wait() returns when the preceding kernel has completed and its writes
+// are visible.  This hides launch latency and first-load latency between the many small
+// kernels of a decode step.  QD_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+
+#include <stdlib.h>
+static inline bool qd_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("QD_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = qd_pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -13,6 +13,8 @@
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ x, const TW* __restrict__ table,
                                  const int* __restrict__ tokens, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x;
   const TW* row = table + (size_t)tokens[t] * D;
   float* out = x + (size_t)t * D;
@@ -23,9 +25,9 @@ extern "C" int qd_embedding(float* x, const void* table, int table_dtype, const 
                             int T, int D, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (table_dtype == QD_F32)
-    embedding_kernel<float><<<T, 256, 0, stream>>>(x, (const float*)table, tokens, D);
+    qd_launch(embedding_kernel<float>, dim3(T), dim3(256), 0, stream, x, (const float*)table, tokens, D);
   else if (table_dtype == QD_BF16)
-    embedding_kernel<bf16><<<T, 256, 0, stream>>>(x, (const bf16*)table, tokens, D);
+    qd_launch(embedding_kernel<bf16>, dim3(T), dim3(256), 0, stream, x, (const bf16*)table, tokens, D);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
@@ -43,6 +45,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const float* __restrict__ w, TO* __restrict__ out,
                                    const int* __restrict__ rows, int D, float eps, int write_back,
                                    int n_parts, size_t part_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sm[];  // D values + 33 scratch
   float* v = sm;
   float* scratch = sm + D;
@@ -67,6 +71,72 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
   for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_float<TO>(v[i] * inv * w[i]);
 }
 
+// The same with one or two float4 per thread held in registers (D a multiple of 4, D <= 8192):
+// every load of a row is issued at once, so a few-row launch costs one memory round trip
+// instead of one per element, which is what decode steps need.
+template <typename TD, typename TO, int VPT>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, const float* __restrict__ w,
+                       TO* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back,
+                       int n_parts, size_t part_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[40];
+  int r = blockIdx.x;
+  size_t s = rows ? (size_t)rows[r] : (size_t)r;
+  int n4 = D >> 2;
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int q = 0; q < VPT; q++) {
+    int i4 = threadIdx.x + q * blockDim.x;
+    v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i4 < n4) {
+      float4 a = reinterpret_cast<const float4*>(x + s * D)[i4];
+      if (delta) {
+        if (sizeof(TD) == 4) {
+          const float* dp = reinterpret_cast<const float*>(delta) + s * D;
+          float4 acc = reinterpret_cast<const float4*>(dp)[i4];
+#pragma unroll 4
+          for (int p = 1; p < n_parts; p++) {
+            float4 d = reinterpret_cast<const float4*>(dp + p * part_stride)[i4];
+            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+          }
+          a.x += acc.x; a.y += acc.y; a.z += acc.z; a.w += acc.w;
+        } else {
+          const bf16* dp = reinterpret_cast<const bf16*>(delta) + s * D + 4 * (size_t)i4;
+          uint2 raw = *reinterpret_cast<const uint2*>(dp);
+          __nv_bfloat162 d0 = *reinterpret_cast<__nv_bfloat162*>(&raw.x);
+          __nv_bfloat162 d1 = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+          a.x += __low2float(d0); a.y += __high2float(d0); a.z += __low2float(d1); a.w += __high2float(d1);
+        }
+        if (write_back) reinterpret_cast<float4*>(x + s * D)[i4] = a;
+      }
+      v[q] = a;
+      ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  float inv = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+  for (int q = 0; q < VPT; q++) {
+    int i4 = threadIdx.x + q * blockDim.x;
+    if (i4 < n4) {
+      float4 ww = reinterpret_cast<const float4*>(w)[i4];
+      float o0 = v[q].x * inv * ww.x, o1 = v[q].y * inv * ww.y, o2 = v[q].z * inv * ww.z, o3 = v[q].w * inv * ww.w;
+      if (sizeof(TO) == 4) {
+        reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)r * D)[i4] = make_float4(o0, o1, o2, o3);
+      } else {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned*>(&p0);
+        raw.y = *reinterpret_cast<unsigned*>(&p1);
+        *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(out) + (size_t)r * D + 4 * (size_t)i4) = raw;
+      }
+    }
+  }
+}
+
 extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* w, void* out,
                               int out_dtype, const int* rows, int n_rows, int D, float eps,
                               int write_back, int n_parts, long long part_stride, cudaStream_t stream) {
@@ -78,13 +148,29 @@ extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
     if (smem > 48 * 1024)                                                                       \
       cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                          \
-    add_rmsnorm_kernel<TD, TO><<<n_rows, 256, smem, stream>>>(x, (const TD*)delta, w, (TO*)out, rows, \
+    qd_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(256), smem, stream, x, (const TD*)delta, w, (TO*)out, rows, \
                                                               D, eps, write_back, n_parts,      \
                                                               (size_t)part_stride);             \
   } while (0)
   bool dbf = delta && delta_dtype == QD_BF16;
   if (delta && delta_dtype != QD_BF16 && delta_dtype != QD_F32) return QD_ERR_UNSUPPORTED;
   if (n_parts < 1 || (n_parts > 1 && delta_dtype != QD_F32)) return QD_ERR_UNSUPPORTED;
+  if (out_dtype != QD_F32 && out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;
+  bool aligned = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)out) & 15) && part_stride % 4 == 0;
+  if (D % 4 == 0 && D <= 8192 && aligned) {
+    int n4 = D / 4;
+    int vpt = n4 <= 1024 ? 1 : 2;
+    int threads = ((n4 + vpt - 1) / vpt + 31) / 32 * 32;
+#define VLAUNCH(TD, TO, V)                                                                              \
+    qd_launch(add_rmsnorm_vec_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), 0, stream, x, (const TD*)delta, w, (TO*)out, rows, D, \
+                                                                      eps, write_back, n_parts, (size_t)part_stride)
+#define VPICK(TD, TO) do { if (vpt == 1) VLAUNCH(TD, TO, 1); else VLAUNCH(TD, TO, 2); } while (0)
+    if (out_dtype == QD_F32) { if (dbf) VPICK(bf16, float); else VPICK(float, float); }
+    else { if (dbf) VPICK(bf16, bf16); else VPICK(float, bf16); }
+#undef VPICK
+#undef VLAUNCH
+    return qd_last_error();
+  }
   if (out_dtype == QD_F32) {
     if (dbf) LAUNCH(bf16, float); else LAUNCH(float, float);
   } else if (out_dtype == QD_BF16) {
@@ -100,6 +186,8 @@ extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, cons
 // the end of a schedule that does not finish with a norm).
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n, int n_parts) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float d = to_float(delta[i]);
@@ -113,9 +201,9 @@ extern "C" int qd_residual_add(float* x, const void* delta, int delta_dtype, lon
   if (n_parts < 1) return QD_ERR_UNSUPPORTED;
   unsigned blocks = (unsigned)((n + 255) / 256);
   if (delta_dtype == QD_F32)
-    residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)delta, (size_t)n, n_parts);
+    qd_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, stream, x, (const float*)delta, (size_t)n, n_parts);
   else if (delta_dtype == QD_BF16 && n_parts == 1)
-    residual_add_kernel<bf16><<<blocks, 256, 0, stream>>>(x, (const bf16*)delta, (size_t)n, 1);
+    qd_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, x, (const bf16*)delta, (size_t)n, 1);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
@@ -134,6 +222,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int H, int G, int d, i
                                      const float* __restrict__ sin_t,
                                      const int* __restrict__ positions, T* __restrict__ kv,
                                      const int* __restrict__ slot_map, int page_size, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x;
   int row_w = (H + 2 * G) * d;
   T* row = qkv + (size_t)t * row_w;
@@ -195,11 +285,11 @@ extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d
   if (T <= 0) return 0;
   if ((d & 1) || (rotary_dim & 1) || rotary_dim > d || rotary_dim < 0) return QD_ERR_UNSUPPORTED;
   if (dtype == QD_F32)
-    rope_kv_write_kernel<float><<<T, 256, 0, stream>>>((float*)qkv, H, G, d, rotary_dim, pairing, cos_t,
+    qd_launch(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                        sin_t, positions, (float*)kv, slot_map,
                                                        page_size, write_kv);
   else if (dtype == QD_BF16)
-    rope_kv_write_kernel<bf16><<<T, 256, 0, stream>>>((bf16*)qkv, H, G, d, rotary_dim, pairing, cos_t,
+    qd_launch(rope_kv_write_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                       sin_t, positions, (bf16*)kv, slot_map,
                                                       page_size, write_kv);
   else
@@ -215,58 +305,45 @@ __global__ void rope_kv_write_partial_kernel(const float* __restrict__ part, int
                                              const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                              const int* __restrict__ positions, bf16* __restrict__ kv,
                                              const int* __restrict__ slot_map, int page_size, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  // grid (token, block of pairs); one thread owns one pair of elements of q, k or v
   int t = blockIdx.x;
+  int pairs_per_head = d >> 1;
+  int w = blockIdx.y * blockDim.x + threadIdx.x;
+  if (w >= (H + 2 * G) * pairs_per_head) return;
+  int head = w / pairs_per_head, p = w - head * pairs_per_head;
   int row_w = (H + 2 * G) * d;
   size_t pstride = (size_t)T * row_w;
   const float* row = part + (size_t)t * row_w;
-  auto val = [&](int idx) {
-    float v = bias ? bias[idx] : 0.f;
-    for (int p = 0; p < n_parts; p++) v += row[p * pstride + idx];
-    return v;
-  };
   int half = rotary_dim >> 1;
-  const float* c = cos_t ? cos_t + (size_t)positions[t] * half : nullptr;
-  const float* s = cos_t ? sin_t + (size_t)positions[t] * half : nullptr;
-  size_t kbase = 0, vbase = 0;
-  int off = 0;
-  if (write_kv) {
+  int i0, i1;
+  bool rot = p < half && head < H + G;
+  if (head >= H + G || pairing == 0) { i0 = 2 * p; i1 = 2 * p + 1; }
+  else if (p < half) { i0 = p; i1 = p + half; }
+  else { int jj = 2 * (p - half) + rotary_dim; i0 = jj; i1 = jj + 1; }
+  int e0 = head * d + i0, e1 = head * d + i1;
+  float a = bias ? bias[e0] : 0.f, b = bias ? bias[e1] : 0.f;
+#pragma unroll 4
+  for (int q = 0; q < n_parts; q++) { a += row[q * pstride + e0]; b += row[q * pstride + e1]; }
+  if (rot && cos_t) {
+    float cv = cos_t[(size_t)positions[t] * half + p], sv = sin_t[(size_t)positions[t] * half + p];
+    float ra = a * cv - b * sv, rb = a * sv + b * cv;
+    a = ra; b = rb;
+  }
+  if (head < H) {
+    bf16* dst = q_out + (size_t)t * H * d + (size_t)head * d;
+    dst[i0] = __float2bfloat16_rn(a);
+    dst[i1] = __float2bfloat16_rn(b);
+  } else if (write_kv) {
     int slot = slot_map[t];
-    int page = slot / page_size;
-    off = slot - page * page_size;
-    kbase = (size_t)page * 2 * G * page_size * d;
-    vbase = kbase + (size_t)G * page_size * d;
-  }
-  int pairs_per_head = d >> 1;
-  int n_qk = (H + G) * pairs_per_head;
-  for (int w = threadIdx.x; w < n_qk; w += blockDim.x) {
-    int head = w / pairs_per_head, p = w - head * pairs_per_head;
-    int i0, i1;
-    bool rot = p < half;
-    if (pairing == 0) { i0 = 2 * p; i1 = 2 * p + 1; }
-    else if (rot)     { i0 = p; i1 = p + half; }
-    else              { int jj = 2 * (p - half) + rotary_dim; i0 = jj; i1 = jj + 1; }
-    float a = val(head * d + i0), b = val(head * d + i1);
-    float ra = a, rb = b;
-    if (rot && c) {
-      float cv = c[p], sv = s[p];
-      ra = a * cv - b * sv;
-      rb = a * sv + b * cv;
-    }
-    if (head < H) {
-      bf16* dst = q_out + (size_t)t * H * d + (size_t)head * d;
-      dst[i0] = __float2bfloat16_rn(ra);
-      dst[i1] = __float2bfloat16_rn(rb);
-    } else if (write_kv) {
-      bf16* dst = kv + kbase + ((size_t)(head - H) * page_size + off) * d;
-      dst[i0] = __float2bfloat16_rn(ra);
-      dst[i1] = __float2bfloat16_rn(rb);
-    }
-  }
-  if (write_kv) {
-    for (int w = threadIdx.x; w < G * d; w += blockDim.x) {
-      int g = w / d, i = w - g * d;
-      kv[vbase + ((size_t)g * page_size + off) * d + i] = __float2bfloat16_rn(val((H + G) * d + w));
-    }
+    int page = slot / page_size, off = slot - page * page_size;
+    bool is_v = head >= H + G;
+    int g = head - H - (is_v ? G : 0);
+    bf16* dst = kv + (size_t)page * 2 * G * page_size * d + (is_v ? (size_t)G * page_size * d : 0) +
+                ((size_t)g * page_size + off) * d;
+    dst[i0] = __float2bfloat16_rn(a);
+    dst[i1] = __float2bfloat16_rn(b);
   }
 }
 
@@ -276,7 +353,10 @@ extern "C" int qd_rope_kv_write_partial(const float* part, int n_parts, const fl
                                         const int* slot_map, int page_size, int write_kv, cudaStream_t stream) {
   if (T <= 0) return 0;
   if ((d & 1) || (rotary_dim & 1) || rotary_dim > d || rotary_dim < 0 || n_parts < 1) return QD_ERR_UNSUPPORTED;
-  rope_kv_write_partial_kernel<<<T, 256, 0, stream>>>(part, n_parts, bias, (bf16*)q_out, T, H, G, d, rotary_dim,
+  int work = (H + 2 * G) * (d / 2);
+  dim3 grid(T, (work + 255) / 256);
+  if (grid.y > 65535) return QD_ERR_UNSUPPORTED;
+  qd_launch(rope_kv_write_partial_kernel, dim3(grid), dim3(256), 0, stream, part, n_parts, bias, (bf16*)q_out, T, H, G, d, rotary_dim,
                                                       pairing, cos_t, sin_t, positions, (bf16*)kv, slot_map,
                                                       page_size, write_kv);
   return qd_last_error();
@@ -287,6 +367,8 @@ extern "C" int qd_rope_kv_write_partial(const float* part, int n_parts, const fl
 // (the reference's swiglu_kernel, gpu_kernels.cu:157-158).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int F, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   size_t t = i / F;
@@ -301,9 +383,9 @@ extern "C" int qd_swiglu(const void* gate_up, void* out, int dtype, int T, int F
   if (n == 0) return 0;
   unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == QD_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, F, n);
+    qd_launch(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out, F, n);
   else if (dtype == QD_BF16)
-    swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, F, n);
+    qd_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out, F, n);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();

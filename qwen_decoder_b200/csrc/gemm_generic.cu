@@ -16,6 +16,8 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_generic_kernel(const TI* __restrict__ X, const TI* __restrict__ W, const float* __restrict__ bias,
                     TO* __restrict__ Y, int T, int N, int K, long long ldx, long long ldy) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[GBK][GBM + 4];
   __shared__ float Bs[GBK][GBN + 4];
   int tid = threadIdx.x;
@@ -76,13 +78,13 @@ extern "C" int qd_gemm_generic(const void* X, const void* W, int x_dtype, const 
   dim3 grid((N + GBN - 1) / GBN, (T + GBM - 1) / GBM);
   if (grid.y > 65535) return QD_ERR_UNSUPPORTED;
   if (x_dtype == QD_F32 && y_dtype == QD_F32)
-    gemm_generic_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)X, (const float*)W, bias,
+    qd_launch(gemm_generic_kernel<float, float>, dim3(grid), dim3(256), 0, stream, (const float*)X, (const float*)W, bias,
                                                                 (float*)Y, T, N, K, ldx, ldy);
   else if (x_dtype == QD_BF16 && y_dtype == QD_BF16)
-    gemm_generic_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)X, (const bf16*)W, bias,
+    qd_launch(gemm_generic_kernel<bf16, bf16>, dim3(grid), dim3(256), 0, stream, (const bf16*)X, (const bf16*)W, bias,
                                                               (bf16*)Y, T, N, K, ldx, ldy);
   else if (x_dtype == QD_BF16 && y_dtype == QD_F32)
-    gemm_generic_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)X, (const bf16*)W, bias,
+    qd_launch(gemm_generic_kernel<bf16, float>, dim3(grid), dim3(256), 0, stream, (const bf16*)X, (const bf16*)W, bias,
                                                                (float*)Y, T, N, K, ldx, ldy);
   else
     return QD_ERR_UNSUPPORTED;

@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long long ldx,
                    const float* __restrict__ bias, TO* __restrict__ out, long long ldo,
                    float* __restrict__ part, int T, int N, int K, int splits) {
+  pdl_launch_dependents();
   __shared__ float red[SK_WARPS][16][TN * 8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = lane & 3, r = lane >> 2;
@@ -78,37 +79,42 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long 
 #pragma unroll
   for (int n = 0; n < TN; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
 
-  uint4 a_lo[2][SK_U], a_hi[2][SK_U];
-  auto load_group = [&](int g, int buf) {
+  // two register buffers of SK_U k-steps each, named apart so that nothing is indexed at run time
+  uint4 lo0[SK_U], hi0[SK_U], lo1[SK_U], hi1[SK_U];
+  auto load_group = [&](int g, uint4 (&lo)[SK_U], uint4 (&hi)[SK_U]) {
 #pragma unroll
     for (int u = 0; u < SK_U; u++) {
       int k = (g * SK_U + u) * 32;
       if (k + 8 * j < K) {
-        a_lo[buf][u] = ldg_stream(w_lo + k);
-        a_hi[buf][u] = ldg_stream(w_hi + k);
+        lo[u] = ldg_stream(w_lo + k);
+        hi[u] = ldg_stream(w_hi + k);
       } else {
-        a_lo[buf][u] = make_uint4(0, 0, 0, 0);
-        a_hi[buf][u] = make_uint4(0, 0, 0, 0);
+        lo[u] = make_uint4(0, 0, 0, 0);
+        hi[u] = make_uint4(0, 0, 0, 0);
       }
     }
   };
-  int g = g_begin + warp;
-  if (g < g_end) load_group(g, 0);
-  int buf = 0;
-  for (; g < g_end; g += SK_WARPS) {
-    if (g + SK_WARPS < g_end) load_group(g + SK_WARPS, buf ^ 1);
+  auto compute_group = [&](int g, const uint4 (&lo)[SK_U], const uint4 (&hi)[SK_U]) {
 #pragma unroll
     for (int u = 0; u < SK_U; u++) {
       int k = (g * SK_U + u) * 32;
       bool in = k + 8 * j < K;
 #pragma unroll
       for (int n = 0; n < TN; n++) {
-        uint4 b = in ? *reinterpret_cast<const uint4*>(xp[n] + k) : make_uint4(0, 0, 0, 0);
-        mma16816(acc[n], a_lo[buf][u].x, a_hi[buf][u].x, a_lo[buf][u].y, a_hi[buf][u].y, b.x, b.y);
-        mma16816(acc[n], a_lo[buf][u].z, a_hi[buf][u].z, a_lo[buf][u].w, a_hi[buf][u].w, b.z, b.w);
+        uint4 b = in ? __ldg(reinterpret_cast<const uint4*>(xp[n] + k)) : make_uint4(0, 0, 0, 0);
+        mma16816(acc[n], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b.x, b.y);
+        mma16816(acc[n], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b.z, b.w);
       }
     }
-    buf ^= 1;
+  };
+  int g = g_begin + warp;
+  if (g < g_end) load_group(g, lo0, hi0);   // weights: no kernel of the step writes them
+  pdl_wait();                               // the tokens come from the kernel before this one
+  for (; g < g_end; g += 2 * SK_WARPS) {
+    if (g + SK_WARPS < g_end) load_group(g + SK_WARPS, lo1, hi1);
+    compute_group(g, lo0, hi0);
+    if (g + 2 * SK_WARPS < g_end) load_group(g + 2 * SK_WARPS, lo0, hi0);
+    if (g + SK_WARPS < g_end) compute_group(g + SK_WARPS, lo1, hi1);
   }
   // sum the four warps' shares of K
 #pragma unroll
@@ -156,19 +162,19 @@ static int launch_skinny(const bf16* W, const bf16* X, long long ldx, const floa
   if (epi == EPI_SWIGLU) {
     dim3 grid((N / 2 + 7) / 8, 1);
     if (out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;
-    gemm_skinny_kernel<TN, EPI_SWIGLU, bf16><<<grid, block, 0, stream>>>(W, X, ldx, nullptr, (bf16*)out, ldo,
+    qd_launch(gemm_skinny_kernel<TN, EPI_SWIGLU, bf16>, dim3(grid), dim3(block), 0, stream, W, X, ldx, nullptr, (bf16*)out, ldo,
                                                                          nullptr, T, N, K, 1);
   } else if (epi == EPI_PARTIAL) {
     dim3 grid((N + 15) / 16, splits);
-    gemm_skinny_kernel<TN, EPI_PARTIAL, float><<<grid, block, 0, stream>>>(W, X, ldx, nullptr, nullptr, 0, part,
+    qd_launch(gemm_skinny_kernel<TN, EPI_PARTIAL, float>, dim3(grid), dim3(block), 0, stream, W, X, ldx, nullptr, nullptr, 0, part,
                                                                            T, N, K, splits);
   } else {
     dim3 grid((N + 15) / 16, 1);
     if (out_dtype == QD_BF16)
-      gemm_skinny_kernel<TN, EPI_STORE, bf16><<<grid, block, 0, stream>>>(W, X, ldx, bias, (bf16*)out, ldo,
+      qd_launch(gemm_skinny_kernel<TN, EPI_STORE, bf16>, dim3(grid), dim3(block), 0, stream, W, X, ldx, bias, (bf16*)out, ldo,
                                                                           nullptr, T, N, K, 1);
     else if (out_dtype == QD_F32)
-      gemm_skinny_kernel<TN, EPI_STORE, float><<<grid, block, 0, stream>>>(W, X, ldx, bias, (float*)out, ldo,
+      qd_launch(gemm_skinny_kernel<TN, EPI_STORE, float>, dim3(grid), dim3(block), 0, stream, W, X, ldx, bias, (float*)out, ldo,
                                                                            nullptr, T, N, K, 1);
     else
       return QD_ERR_UNSUPPORTED;

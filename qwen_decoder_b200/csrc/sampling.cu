@@ -24,6 +24,8 @@ __device__ __forceinline__ float key_to_float(unsigned k) {
 __global__ void __launch_bounds__(SB)
 sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ draws, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_val[SB];
   __shared__ int s_idx[SB];
   __shared__ unsigned s_hist[256];
@@ -134,6 +136,6 @@ extern "C" int qd_sample(const float* logits, int R, int V, const float* tempera
                          const float* draws, int* out, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0) return QD_ERR_UNSUPPORTED;
-  sample_kernel<<<R, SB, 0, stream>>>(logits, V, temperature, top_k, draws, out);
+  qd_launch(sample_kernel, dim3(R), dim3(SB), 0, stream, logits, V, temperature, top_k, draws, out);
   return qd_last_error();
 }

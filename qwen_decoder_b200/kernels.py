@@ -180,12 +180,13 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         _I(T), _I(N), _I(K), _LL(x.stride(0)), _LL(out.stride(0)), _stream()), "gemm_generic")
 
 
-SKINNY_MAX_TOKENS = 64
+SKINNY_MAX_TOKENS = 64      # what the kernel takes
+SKINNY_POLICY_TOKENS = 16   # up to here it is the faster choice; beyond, cuBLAS until the tcgen05 kernel
 EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
 
 
-def skinny_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_TOKENS
+def skinny_supported(x: torch.Tensor, w: torch.Tensor, limit: int = SKINNY_POLICY_TOKENS) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= limit
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
@@ -202,7 +203,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     """out[T, N] = x @ w^T (+ bias) for T <= 64, bfloat16 in, out bfloat16 or float32."""
     T, K = x.shape
     N = w.shape[0]
-    assert skinny_supported(x, w) and out.shape == (T, N) and out.stride(1) == 1
+    assert skinny_supported(x, w, SKINNY_MAX_TOKENS) and out.shape == (T, N) and out.stride(1) == 1
     _contig(w, "w")
     _check(library("gemm_skinny").qd_gemm_skinny(
         _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(dtype_code(out.dtype)),
@@ -213,7 +214,7 @@ def gemm_skinny_partial(x: torch.Tensor, w: torch.Tensor, splits: int) -> torch.
     """float32 partial sums [splits, T, N] of x @ w^T over ``splits`` shares of K."""
     T, K = x.shape
     N = w.shape[0]
-    assert skinny_supported(x, w)
+    assert skinny_supported(x, w, SKINNY_MAX_TOKENS)
     _contig(w, "w")
     part = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
     _check(library("gemm_skinny").qd_gemm_skinny(
@@ -226,7 +227,7 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
     """out[T, F] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg; Wu] of shape [2F, K]."""
     T, K = x.shape
     N = w_gate_up.shape[0]
-    assert skinny_supported(x, w_gate_up) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
+    assert skinny_supported(x, w_gate_up, SKINNY_MAX_TOKENS) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
     _contig(w_gate_up, "w"); _contig(out, "out")
     _check(library("gemm_skinny").qd_gemm_skinny(
         _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(None), _ptr(out), _I(BF16), _LL(out.stride(0)),
