@@ -66,7 +66,6 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         const int* __restrict__ token_req, const int* __restrict__ positions, int H, int G,
                         int page_size, float scale_log2e, int window, int splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml) {
-  pdl_launch_dependents();
   pdl_wait();
   constexpr int LD = HD + FA_PAD;
   constexpr int TILE = DEC_CHUNK * LD;            // elements of one K or V chunk in smem
@@ -185,6 +184,7 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
     __syncwarp();
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();
   l0 = quad_sum(l0);
   l1 = quad_sum(l1);
   __syncthreads();  // every warp is done with its stage buffers: reuse them for the merge
@@ -308,7 +308,6 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          const bf16* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ cu_tokens, const int* __restrict__ start_pos, int R, int H,
                          int G, int page_size, float scale_log2e, int window, int tok_tile) {
-  pdl_launch_dependents();
   pdl_wait();
   constexpr int LD = HD + FA_PAD;
   constexpr int TILE = PF_KEYS * LD;
@@ -454,6 +453,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     __syncthreads();  // all warps are done with this stage before the next load overwrites it
   }
   cp_async_wait<0>();
+  pdl_launch_dependents();
   l0 = quad_sum(l0);
   l1 = quad_sum(l1);
   const int cq = (lane & 3) * 2;

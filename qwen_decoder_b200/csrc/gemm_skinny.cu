@@ -44,7 +44,6 @@ __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long long ldx,
                    const float* __restrict__ bias, TO* __restrict__ out, long long ldo,
                    float* __restrict__ part, int T, int N, int K, int splits) {
-  pdl_launch_dependents();
   __shared__ float red[SK_WARPS][16][TN * 8 + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = lane & 3, r = lane >> 2;
@@ -116,6 +115,7 @@ gemm_skinny_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long 
     if (g + 2 * SK_WARPS < g_end) load_group(g + 2 * SK_WARPS, lo0, hi0);
     if (g + SK_WARPS < g_end) compute_group(g + SK_WARPS, lo1, hi1);
   }
+  pdl_launch_dependents();   // the next kernel may start its prologue while this one reduces
   // sum the four warps' shares of K
 #pragma unroll
   for (int n = 0; n < TN; n++) {
