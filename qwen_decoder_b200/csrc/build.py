@@ -36,8 +36,13 @@ LIBRARIES: Dict[str, str] = {
     "attention_generic": "attention_generic.cu",
     "attention_flash": "attention_flash.cu",
     "sampling": "sampling.cu",
+    "decode_attention_noalloc": "decode_attention_noalloc.cu",
 }
 HEADERS = ["common.cuh"]
+# further files a library's source includes (hashed into its key)
+EXTRA_DEPS: Dict[str, List[str]] = {
+    "decode_attention_noalloc": ["attention_flash.cu", "decode_attention_noalloc.h"],
+}
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -95,7 +100,7 @@ def _build_dir() -> str:
 
 def _key(name: str, nvcc: str) -> str:
     h = hashlib.sha256()
-    for f in [LIBRARIES[name]] + HEADERS:
+    for f in [LIBRARIES[name]] + HEADERS + EXTRA_DEPS.get(name, []):
         with open(os.path.join(CSRC, f), "rb") as fh:
             h.update(f.encode() + b"\0" + fh.read() + b"\0")
     h.update(" ".join(NVCC_FLAGS).encode())
