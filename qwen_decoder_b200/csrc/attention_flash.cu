@@ -298,12 +298,17 @@ extern "C" int qd_decode_attention(const void* q, long long q_stride, void* out,
 }
 
 // ==================================================================== prefill
-#define PF_WARPS 4
-#define PF_ROWS (PF_WARPS * 16)
 #define PF_KEYS 64  // keys per tile
 
-template <int HD>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// NW warps of 16 rows each; NST cp.async stages of one K tile + one V tile.
+template <int HD, int NW, int NST>
+__global__ void __launch_bounds__(NW * 32)
 prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ cu_tokens, const int* __restrict__ start_pos, int R, int H,
@@ -312,7 +317,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   constexpr int LD = HD + FA_PAD;
   constexpr int TILE = PF_KEYS * LD;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* smem = reinterpret_cast<bf16*>(smem_raw);    // [2 stages][K tile, V tile]
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw);    // [NST stages][K tile, V tile]
   const int g = blockIdx.y;
   const int gs = H / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -344,6 +349,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int p0 = pos0 + t0, p1 = pos0 + t1;                          // positions of the rows
   const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
   const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+  // keys in [full_lo, full_hi) are visible to every valid row of the tile: no masking there
+  const int full_hi = pos0 + 1;
+  const int full_lo = (window > 0 && key_hi - 1 - window + 1 > 0) ? key_hi - window : 0;
 
   unsigned qa[HD / 16][4];
   {
@@ -364,7 +372,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     bf16* vs = ks + TILE;
     constexpr int CPR = HD / 8;
     const int key_base = kt * PF_KEYS;
-    for (int i = threadIdx.x; i < PF_KEYS * CPR; i += PF_WARPS * 32) {
+    for (int i = threadIdx.x; i < PF_KEYS * CPR; i += NW * 32) {
       int row = i / CPR, col = (i % CPR) * 8;
       int key = key_base + row;
       int page = key < key_hi ? bt[key / page_size] : -1;
@@ -381,55 +389,83 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
 
   const int kt_lo = key_lo_tile / PF_KEYS, kt_hi = (key_hi + PF_KEYS - 1) / PF_KEYS;
-  load_tile(kt_lo, 0);
-  cp_async_commit();
-  for (int kt = kt_lo; kt < kt_hi; kt++) {
-    const int stage = (kt - kt_lo) & 1;
-    if (kt + 1 < kt_hi) load_tile(kt + 1, stage ^ 1);
+#pragma unroll
+  for (int p = 0; p < NST - 1; p++) {
+    if (kt_lo + p < kt_hi) load_tile(kt_lo + p, p);
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+  for (int kt = kt_lo; kt < kt_hi; kt++) {
+    const int it = kt - kt_lo;
+    const int stage = it % NST;
+    if (kt + NST - 1 < kt_hi) load_tile(kt + NST - 1, (it + NST - 1) % NST);
+    cp_async_commit();
+    cp_async_wait<NST - 1>();
     __syncthreads();
     const bf16* ks = smem + (size_t)stage * 2 * TILE;
     const bf16* vs = ks + TILE;
     float sc[PF_KEYS / 8][4];
 #pragma unroll
     for (int n = 0; n < PF_KEYS / 8; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    // K fragments of the next 16 dims are fetched while the MMAs of the current 16 run
+    {
+      const bf16* kfrag = ks + ((lane & 7) + 8 * (lane >> 4)) * LD + 8 * ((lane >> 3) & 1);
+      unsigned bq[2][PF_KEYS / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < HD / 16; kk++) {
+      for (int kb = 0; kb < PF_KEYS / 16; kb++) ldmatrix_x4(bq[0][kb], kfrag + kb * 16 * LD);
 #pragma unroll
-      for (int kb = 0; kb < PF_KEYS / 16; kb++) {
-        unsigned bq[4];
-        ldmatrix_x4(bq, ks + (kb * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
-        mma_bf16(sc[2 * kb], qa[kk], bq[0], bq[1]);
-        mma_bf16(sc[2 * kb + 1], qa[kk], bq[2], bq[3]);
+      for (int kk = 0; kk < HD / 16; kk++) {
+        if (kk + 1 < HD / 16) {
+#pragma unroll
+          for (int kb = 0; kb < PF_KEYS / 16; kb++)
+            ldmatrix_x4(bq[(kk + 1) & 1][kb], kfrag + kb * 16 * LD + (kk + 1) * 16);
+        }
+#pragma unroll
+        for (int kb = 0; kb < PF_KEYS / 16; kb++) {
+          mma_bf16(sc[2 * kb], qa[kk], bq[kk & 1][kb][0], bq[kk & 1][kb][1]);
+          mma_bf16(sc[2 * kb + 1], qa[kk], bq[kk & 1][kb][2], bq[kk & 1][kb][3]);
+        }
       }
     }
     const int key_base = kt * PF_KEYS + (lane & 3) * 2;
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    const bool interior = kt * PF_KEYS >= full_lo && kt * PF_KEYS + PF_KEYS <= full_hi;
+    if (interior) {
 #pragma unroll
-    for (int n = 0; n < PF_KEYS / 8; n++) {
+      for (int n = 0; n < PF_KEYS / 8; n++) {
 #pragma unroll
-      for (int j = 0; j < 2; j++) {
-        int key = key_base + n * 8 + j;
-        bool a = ok0 && key <= p0 && key >= lo0;
-        bool c = ok1 && key <= p1 && key >= lo1;
-        sc[n][j] = a ? sc[n][j] * scale_log2e : -INFINITY;
-        sc[n][2 + j] = c ? sc[n][2 + j] * scale_log2e : -INFINITY;
-        mx0 = fmaxf(mx0, sc[n][j]);
-        mx1 = fmaxf(mx1, sc[n][2 + j]);
+        for (int j = 0; j < 2; j++) {
+          sc[n][j] = ok0 ? sc[n][j] * scale_log2e : -INFINITY;
+          sc[n][2 + j] = ok1 ? sc[n][2 + j] * scale_log2e : -INFINITY;
+          mx0 = fmaxf(mx0, sc[n][j]);
+          mx1 = fmaxf(mx1, sc[n][2 + j]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < PF_KEYS / 8; n++) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          int key = key_base + n * 8 + j;
+          bool a = ok0 && key <= p0 && key >= lo0;
+          bool c = ok1 && key <= p1 && key >= lo1;
+          sc[n][j] = a ? sc[n][j] * scale_log2e : -INFINITY;
+          sc[n][2 + j] = c ? sc[n][2 + j] * scale_log2e : -INFINITY;
+          mx0 = fmaxf(mx0, sc[n][j]);
+          mx1 = fmaxf(mx1, sc[n][2 + j]);
+        }
       }
     }
     mx0 = quad_max(mx0);
     mx1 = quad_max(mx1);
     float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
     float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
-    float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
+    float a0 = fast_exp2(m0 - ref0), a1 = fast_exp2(m1 - ref1);
     m0 = mn0; m1 = mn1;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
     for (int n = 0; n < PF_KEYS / 8; n++) {
-      sc[n][0] = exp2f(sc[n][0] - ref0); sc[n][1] = exp2f(sc[n][1] - ref0);
-      sc[n][2] = exp2f(sc[n][2] - ref1); sc[n][3] = exp2f(sc[n][3] - ref1);
+      sc[n][0] = fast_exp2(sc[n][0] - ref0); sc[n][1] = fast_exp2(sc[n][1] - ref0);
+      sc[n][2] = fast_exp2(sc[n][2] - ref1); sc[n][3] = fast_exp2(sc[n][3] - ref1);
       s0 += sc[n][0] + sc[n][1];
       s1 += sc[n][2] + sc[n][3];
     }
@@ -437,20 +473,32 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     l1 = l1 * a1 + s1;
 #pragma unroll
     for (int n = 0; n < HD / 8; n++) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+    {
+      // V fragments: four 16-dim groups are fetched ahead of the MMAs that use them
+      const bf16* vfrag = vs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + 8 * (lane >> 4);
+      constexpr int DG = HD / 16;               // 16-dim groups
+      constexpr int STEPS = (PF_KEYS / 16) * DG;
+      constexpr int AHEAD = DG < 4 ? DG : 4;
+      unsigned bv[AHEAD][4];
 #pragma unroll
-    for (int kb = 0; kb < PF_KEYS / 16; kb++) {
-      unsigned pa[4] = {pack_bf16(sc[2 * kb][0], sc[2 * kb][1]), pack_bf16(sc[2 * kb][2], sc[2 * kb][3]),
-                        pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]),
-                        pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3])};
+      for (int st = 0; st < AHEAD; st++)
+        ldmatrix_x4_trans(bv[st], vfrag + (st / DG) * 16 * LD + (st % DG) * 16);
 #pragma unroll
-      for (int dn = 0; dn < HD / 16; dn++) {
-        unsigned bv[4];
-        ldmatrix_x4_trans(bv, vs + (kb * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dn * 16 + 8 * (lane >> 4));
-        mma_bf16(o[2 * dn], pa, bv[0], bv[1]);
-        mma_bf16(o[2 * dn + 1], pa, bv[2], bv[3]);
+      for (int st = 0; st < STEPS; st++) {
+        const int kb = st / DG, dn = st % DG;
+        unsigned pa[4] = {pack_bf16(sc[2 * kb][0], sc[2 * kb][1]), pack_bf16(sc[2 * kb][2], sc[2 * kb][3]),
+                          pack_bf16(sc[2 * kb + 1][0], sc[2 * kb + 1][1]),
+                          pack_bf16(sc[2 * kb + 1][2], sc[2 * kb + 1][3])};
+        unsigned b0 = bv[st % AHEAD][0], b1 = bv[st % AHEAD][1], b2 = bv[st % AHEAD][2], b3 = bv[st % AHEAD][3];
+        if (st + AHEAD < STEPS) {
+          const int nx = st + AHEAD;
+          ldmatrix_x4_trans(bv[st % AHEAD], vfrag + (nx / DG) * 16 * LD + (nx % DG) * 16);
+        }
+        mma_bf16(o[2 * dn], pa, b0, b1);
+        mma_bf16(o[2 * dn + 1], pa, b2, b3);
       }
     }
-    __syncthreads();  // all warps are done with this stage before the next load overwrites it
+    __syncthreads();  // all warps are done with this stage before a later load overwrites it
   }
   cp_async_wait<0>();
   pdl_launch_dependents();
@@ -473,22 +521,47 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   }
 }
 
+template <int HD, int NW, int NST>
+static int launch_prefill_v(const bf16* q, long long q_stride, bf16* out, const bf16* kv, const int* block_table,
+                            int max_blocks, const int* cu_tokens, const int* start_pos, int R, int T, int H, int G,
+                            int page_size, float scale, int window, cudaStream_t stream) {
+  constexpr int LD = HD + FA_PAD;
+  size_t smem = (size_t)NST * 2 * PF_KEYS * LD * sizeof(bf16);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(prefill_attention_kernel<HD, NW, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int gs = H / G;
+  int tok_tile = (NW * 16) / gs;
+  int tiles = (T + tok_tile - 1) / tok_tile + R;   // upper bound on the tiles of R requests
+  dim3 grid(tiles, G);
+  qd_launch(prefill_attention_kernel<HD, NW, NST>, dim3(grid), dim3(NW * 32), smem, stream,
+      q, q_stride, out, kv, block_table, max_blocks, cu_tokens, start_pos, R, H, G, page_size,
+      scale * 1.4426950408889634f, window, tok_tile);
+  return qd_last_error();
+}
+
+static int pf_variant() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("QD_PF_VARIANT"); v = e ? atoi(e) : 0; }
+  return v;
+}
+
 template <int HD>
 static int launch_prefill(const bf16* q, long long q_stride, bf16* out, const bf16* kv, const int* block_table,
                           int max_blocks, const int* cu_tokens, const int* start_pos, int R, int T, int H, int G,
                           int page_size, float scale, int window, cudaStream_t stream) {
-  constexpr int LD = HD + FA_PAD;
-  size_t smem = (size_t)2 * 2 * PF_KEYS * LD * sizeof(bf16);
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(prefill_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+#define PFV(NW, NST) launch_prefill_v<HD, NW, NST>(q, q_stride, out, kv, block_table, max_blocks, cu_tokens, \
+                                                   start_pos, R, T, H, G, page_size, scale, window, stream)
   int gs = H / G;
-  int tok_tile = PF_ROWS / gs;
-  int tiles = (T + tok_tile - 1) / tok_tile + R;   // upper bound on the tiles of R requests
-  dim3 grid(tiles, G);
-  qd_launch(prefill_attention_kernel<HD>, dim3(grid), dim3(PF_WARPS * 32), smem, stream, 
-      q, q_stride, out, kv, block_table, max_blocks, cu_tokens, start_pos, R, H, G, page_size,
-      scale * 1.4426950408889634f, window, tok_tile);
-  return qd_last_error();
+  // eight warps (128 rows) halve the K/V traffic per row, but only pay with enough tokens per request
+  bool big = T / R >= 128 && gs <= 128;
+  switch (pf_variant()) {
+    case 1: return PFV(4, 2);
+    case 2: return PFV(4, 3);
+    case 3: return PFV(8, 2);
+    case 4: return PFV(8, 3);
+    default: return big && gs <= 64 ? PFV(8, 2) : PFV(4, 2);
+  }
+#undef PFV
 }
 
 // Portions of R requests: tokens cu_tokens[r]..cu_tokens[r+1]-1 of the flat batch sit at positions
@@ -498,7 +571,7 @@ extern "C" int qd_prefill_attention(const void* q, long long q_stride, void* out
                                     const int* start_pos, int R, int T, int H, int G, int d, int page_size,
                                     float scale, int window, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return 0;
-  if (G <= 0 || H % G != 0 || H / G > PF_ROWS || page_size <= 0 || G > 65535) return QD_ERR_UNSUPPORTED;
+  if (G <= 0 || H % G != 0 || H / G > 64 || page_size <= 0 || G > 65535) return QD_ERR_UNSUPPORTED;
 #define CASE(HD)                                                                                           \
   case HD:                                                                                                 \
     return launch_prefill<HD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv, block_table, max_blocks, \

@@ -150,10 +150,10 @@ class ModelRunner:
             Bp *= 2
         mbs = tuple((max(len(e.cache.tables[g]) for e in entries) + 31) // 32 * 32
                     for g in range(len(self.cache.pools)))
-        key = (Bp, mbs)
+        key = (Bp, mbs, sampling is not None)
         g = self._graphs.get(key)
         if g is None:
-            g = self._graphs[key] = _DecodeGraph(self, Bp, mbs)
+            g = self._graphs[key] = _DecodeGraph(self, Bp, mbs, sampling is not None)
         host = g.next_host()
         h = host.numpy()
         fill(h, g.lay, entries, self.cache, lens, starts, slots, self.model.vocab_size)
@@ -168,14 +168,15 @@ class ModelRunner:
             h[o:o + 3 * Bp] = 0
         g.upload(host)
         g.run()
-        return g.logits[:R], g.tokens[:R]
+        return g.logits[:R], (g.tokens[:R] if g.tokens is not None else None)
 
 
 class _DecodeGraph:
     """One captured decode step for a padded batch size and block-table widths."""
 
-    def __init__(self, runner: "ModelRunner", Bp: int, mbs):
+    def __init__(self, runner: "ModelRunner", Bp: int, mbs, with_sampling: bool):
         self.runner = runner
+        self.with_sampling = with_sampling
         self.lay = MetaLayout(Bp, Bp, Bp, mbs, extra=3 * Bp)
         # two pinned staging buffers: one may still be in flight while the next step is written
         self.hosts = [torch.empty(self.lay.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
@@ -209,8 +210,9 @@ class _DecodeGraph:
     def _forward(self):
         from .. import kernels
         self.logits = self.runner.model.forward(self.ctx)
-        self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.runner.device)
-        kernels.sample(self.logits, self.temps, self.top_ks, self.draws, self.tokens)
+        if self.with_sampling:
+            self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.runner.device)
+            kernels.sample(self.logits, self.temps, self.top_ks, self.draws, self.tokens)
 
     def run(self) -> None:
         if self.graph is None:
