@@ -54,6 +54,12 @@ __device__ __forceinline__ float quad_sum(float v) {
   return v + __shfl_xor_sync(0xffffffffu, v, 2);
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ===================================================================== decode
 #define DEC_WARPS 4
 #define DEC_STAGES 3
@@ -65,8 +71,11 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         const bf16* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
                         const int* __restrict__ token_req, const int* __restrict__ positions, int H, int G,
                         int page_size, float scale_log2e, int window, int splits,
-                        float* __restrict__ part_o, float* __restrict__ part_ml) {
-  pdl_wait();
+                        float* __restrict__ part_o, float* __restrict__ part_ml,
+                        unsigned* __restrict__ tickets) {
+  // Before pdl_wait() only data that no kernel of this step writes is touched: positions and block
+  // table (copied in before the step's first kernel) and cache chunks of *earlier* tokens.  The
+  // query and the chunk that holds this step's own key are read after the wait.
   constexpr int LD = HD + FA_PAD;
   constexpr int TILE = DEC_CHUNK * LD;            // elements of one K or V chunk in smem
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -85,6 +94,55 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   const size_t page_elems = (size_t)2 * G * page_size * HD;
   const size_t k_off = (size_t)g * page_size * HD, v_off = ((size_t)G + g) * page_size * HD;
 
+  bf16* wbuf = smem + (size_t)warp * DEC_STAGES * 2 * TILE;
+  constexpr int CPR = HD / 8;                        // 16-byte pieces per row
+  constexpr int ROWS_PER_IT = 32 / CPR > 0 ? 32 / CPR : 1;
+  const int l_row = lane / CPR, l_col = (lane % CPR) * 8;
+  // Page ids of this warp's chunks go through a ring of 64 entries in shared memory that is
+  // filled 32 chunks ahead, so that no cache load waits for a block-table load.
+  __shared__ int page_ring[DEC_WARPS][64];
+  const int first = c0 + warp;
+  const int n_my = first < c1 ? (c1 - first + DEC_WARPS - 1) / DEC_WARPS : 0;
+  auto fill_ring = [&](int from) {      // entries [from, from + 32) of this warp's chunk sequence
+    int i = from + lane;
+    if (i < n_my) page_ring[warp][i & 63] = bt[((first + i * DEC_WARPS) * DEC_CHUNK) / page_size];
+  };
+  fill_ring(0);
+  fill_ring(32);
+  __syncwarp();
+  auto load_chunk = [&](int i, int stage) {          // i-th chunk of this warp
+    bf16* ks = wbuf + (size_t)stage * 2 * TILE;
+    bf16* vs = ks + TILE;
+    int key0 = (first + i * DEC_WARPS) * DEC_CHUNK;
+    int page = page_ring[warp][i & 63];
+    int in_page = key0 % page_size;
+    const bf16* kg = kv + (page < 0 ? 0 : (size_t)page * page_elems) + k_off + (size_t)in_page * HD;
+    const bf16* vg = kv + (page < 0 ? 0 : (size_t)page * page_elems) + v_off + (size_t)in_page * HD;
+    const int rows_ok = page < 0 ? 0 : n_keys - key0;           // rows past the end are zero-filled
+#pragma unroll
+    for (int row = l_row; row < DEC_CHUNK; row += ROWS_PER_IT) {
+      int bytes = row < rows_ok ? 16 : 0;
+      cp_async16(ks + row * LD + l_col, kg + (bytes ? row * HD + l_col : 0), bytes);
+      cp_async16(vs + row * LD + l_col, vg + (bytes ? row * HD + l_col : 0), bytes);
+    }
+  };
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  const int hot = chunk_hi - 1;        // the chunk this step's own key was just written to
+  int deferred = -1;
+#pragma unroll
+  for (int p = 0; p < DEC_STAGES - 1; p++) {
+    if (p < n_my) {
+      if (first + p * DEC_WARPS == hot) deferred = p; else load_chunk(p, p);
+    }
+    cp_async_commit();
+  }
+  pdl_wait();
+  if (deferred >= 0) { load_chunk(deferred, deferred); cp_async_commit(); }
   // Q fragments: rows are the heads of this KV head's group (rows >= gs are zero)
   unsigned qa[HD / 16][4];
   {
@@ -99,41 +157,12 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       qa[kk][3] = r1 < gs ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + 8) : 0u;
     }
   }
-  bf16* wbuf = smem + (size_t)warp * DEC_STAGES * 2 * TILE;
-  auto load_chunk = [&](int c, int stage) {
-    bf16* ks = wbuf + (size_t)stage * 2 * TILE;
-    bf16* vs = ks + TILE;
-    int key0 = c * DEC_CHUNK;
-    int page = bt[key0 / page_size];
-    int in_page = key0 % page_size;
-    const bf16* kg = kv + (page < 0 ? 0 : (size_t)page * page_elems) + k_off + (size_t)in_page * HD;
-    const bf16* vg = kv + (page < 0 ? 0 : (size_t)page * page_elems) + v_off + (size_t)in_page * HD;
-    constexpr int CPR = HD / 8;  // 16-byte pieces per row
-    for (int i = lane; i < DEC_CHUNK * CPR; i += 32) {
-      int row = i / CPR, col = (i % CPR) * 8;
-      int bytes = (page >= 0 && key0 + row < n_keys) ? 16 : 0;   // rows past the end are zero-filled
-      cp_async16(ks + row * LD + col, kg + (bytes ? row * HD + col : 0), bytes);
-      cp_async16(vs + row * LD + col, vg + (bytes ? row * HD + col : 0), bytes);
-    }
-  };
-
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  float o[HD / 8][4];
-#pragma unroll
-  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-
-  const int first = c0 + warp;
-  const int n_my = first < c1 ? (c1 - first + DEC_WARPS - 1) / DEC_WARPS : 0;
-#pragma unroll
-  for (int p = 0; p < DEC_STAGES - 1; p++) {
-    if (p < n_my) load_chunk(first + p * DEC_WARPS, p);
-    cp_async_commit();
-  }
   for (int i = 0; i < n_my; i++) {
     int nx = i + DEC_STAGES - 1;
-    if (nx < n_my) load_chunk(first + nx * DEC_WARPS, nx % DEC_STAGES);
+    if ((i & 31) == 0 && i > 0) fill_ring(i + 32);     // entries [i, i+32) are in place; refill the other half
+    if (nx < n_my) load_chunk(nx, nx % DEC_STAGES);
     cp_async_commit();
-    cp_async_wait<DEC_STAGES - 1>();
+    if (i == n_my - 1) cp_async_wait<0>(); else cp_async_wait<DEC_STAGES - 1>();
     __syncwarp();
     const bf16* ks = wbuf + (size_t)(i % DEC_STAGES) * 2 * TILE;
     const bf16* vs = ks + TILE;
@@ -160,22 +189,25 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
     float mx1 = quad_max(fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])));
     float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
     float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
-    float a0 = exp2f(m0 - ref0), a1 = exp2f(m1 - ref1);
+    float a0 = fast_exp2(m0 - ref0), a1 = fast_exp2(m1 - ref1);
     m0 = mn0; m1 = mn1;
     float p[2][4];
 #pragma unroll
     for (int n = 0; n < 2; n++) {
-      p[n][0] = exp2f(sc[n][0] - ref0); p[n][1] = exp2f(sc[n][1] - ref0);
-      p[n][2] = exp2f(sc[n][2] - ref1); p[n][3] = exp2f(sc[n][3] - ref1);
+      p[n][0] = fast_exp2(sc[n][0] - ref0); p[n][1] = fast_exp2(sc[n][1] - ref0);
+      p[n][2] = fast_exp2(sc[n][2] - ref1); p[n][3] = fast_exp2(sc[n][3] - ref1);
     }
     l0 = l0 * a0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
     l1 = l1 * a1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
     unsigned pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
                       pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+    // the running maxima rarely move after the first chunks: rescale only when one did
+    if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+      for (int n = 0; n < HD / 8; n++) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+    }
 #pragma unroll
     for (int dn = 0; dn < HD / 16; dn++) {
-      o[2 * dn][0] *= a0; o[2 * dn][1] *= a0; o[2 * dn][2] *= a1; o[2 * dn][3] *= a1;
-      o[2 * dn + 1][0] *= a0; o[2 * dn + 1][1] *= a0; o[2 * dn + 1][2] *= a1; o[2 * dn + 1][3] *= a1;
       unsigned b[4];
       ldmatrix_x4_trans(b, vs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dn * 16 + 8 * (lane >> 4));
       mma_bf16(o[2 * dn], pa, b[0], b[1]);
@@ -229,6 +261,55 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       if (dim == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
     }
   }
+  if (splits == 1 || tickets == nullptr) return;   // without tickets a combine kernel follows
+  // the CTA that finishes last for this (token, kv head) adds up all partial results
+  __shared__ unsigned s_ticket;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[(size_t)t * G + g], 1u);
+  __syncthreads();
+  if (s_ticket != (unsigned)splits - 1) return;
+  __threadfence();
+  // weights of the partial results: f[row][sp] = 2^(m_sp - M) / sum_sp l_sp 2^(m_sp - M), in smem
+  // (reusing the merge area: [16 rows][splits] after the (m, l) pairs have been read)
+  float* fac = reinterpret_cast<float*>(smem_raw);                 // [gs][splits]
+  float* pm = fac + 16 * 64;                                       // [gs][splits] maxima
+  float* pl = pm + 16 * 64;                                        // [gs][splits] denominators
+  for (int idx = threadIdx.x; idx < gs * splits; idx += DEC_WARPS * 32) {
+    int row = idx / splits, sp = idx - row * splits;
+    size_t pi = ((size_t)t * H + (size_t)g * gs + row) * splits + sp;
+    float2 ml2 = __ldcg(reinterpret_cast<const float2*>(part_ml) + pi);
+    pm[row * 64 + sp] = ml2.x;
+    pl[row * 64 + sp] = ml2.y;
+  }
+  __syncthreads();
+  if (threadIdx.x < gs) {
+    int row = threadIdx.x;
+    float M = -INFINITY;
+    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, pm[row * 64 + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < splits; sp++) L += pl[row * 64 + sp] * exp2f(pm[row * 64 + sp] - M);
+    float invL = 1.f / L;
+    for (int sp = 0; sp < splits; sp++) fac[row * 64 + sp] = exp2f(pm[row * 64 + sp] - M) * invL;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < gs * (HD / 4); idx += DEC_WARPS * 32) {
+    int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
+    size_t base = ((size_t)t * H + (size_t)g * gs + row) * splits;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < splits; sp++) {
+      float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + sp) * HD) + d4);
+      float f = fac[row * 64 + sp];
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+    bf16* dst = out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
+    uint2 raw;
+    raw.x = pack_bf16(acc.x, acc.y);
+    raw.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst) = raw;
+  }
+  if (threadIdx.x == 0) tickets[(size_t)t * G + g] = 0;   // ready for the next launch
 }
 
 // out[t, h, :] = sum_s O_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
@@ -253,20 +334,21 @@ template <int HD>
 static int launch_decode(const bf16* q, long long q_stride, bf16* out, const bf16* kv, const int* block_table,
                          int max_blocks, const int* token_req, const int* positions, int T, int H, int G,
                          int page_size, float scale, int window, int splits, float* part_o, float* part_ml,
-                         cudaStream_t stream) {
+                         unsigned* tickets, cudaStream_t stream) {
   constexpr int LD = HD + FA_PAD;
   size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_CHUNK * LD * sizeof(bf16);
   size_t merge = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
   if (merge > smem) smem = merge;
+  if (smem < 3 * 16 * 64 * sizeof(float)) smem = 3 * 16 * 64 * sizeof(float);   // the last CTA's combine
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(splits, G, T);
   qd_launch(decode_attention_kernel<HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
       q, q_stride, out, kv, block_table, max_blocks, token_req, positions, H, G, page_size,
-      scale * 1.4426950408889634f, window, splits, part_o, part_ml);
+      scale * 1.4426950408889634f, window, splits, part_o, part_ml, tickets);
   int e = qd_last_error();
   if (e) return e;
-  if (splits > 1) {
+  if (splits > 1 && !tickets) {
     qd_launch(decode_combine_kernel, dim3((unsigned)((size_t)T * H)), dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)), 0, stream, 
         part_o, part_ml, out, HD, splits);
     e = qd_last_error();
@@ -276,20 +358,24 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, const bf1
 
 // One query token per entry of positions/token_req.  part_o must hold T*H*splits*HD floats and
 // part_ml T*H*splits*2 floats when splits > 1 (scratch; contents need not be initialised).
+// tickets: T*G unsigned counters that are ZERO on entry (the kernel leaves them zero again); with
+// them the last CTA of each (token, kv head) adds up the partial results itself; with a null
+// pointer a second small kernel does it.
 extern "C" int qd_decode_attention(const void* q, long long q_stride, void* out, const void* kv,
                                    const int* block_table, int max_blocks, const int* token_req,
                                    const int* positions, int T, int H, int G, int d, int page_size,
                                    float scale, int window, int splits, float* part_o, float* part_ml,
-                                   cudaStream_t stream) {
+                                   unsigned* tickets, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (G <= 0 || H % G != 0 || H / G > 16 || page_size % DEC_CHUNK != 0 || splits < 1 || T > 65535 || G > 65535)
     return QD_ERR_UNSUPPORTED;
   if (splits > 1 && (!part_o || !part_ml)) return QD_ERR_UNSUPPORTED;
+  if (splits > 64 && tickets) return QD_ERR_UNSUPPORTED;
 #define CASE(HD)                                                                                          \
   case HD:                                                                                                \
     return launch_decode<HD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv, block_table, max_blocks, \
                              token_req, positions, T, H, G, page_size, scale, window, splits, part_o,     \
-                             part_ml, stream);
+                             part_ml, tickets, stream);
   switch (d) {
     CASE(16) CASE(32) CASE(48) CASE(64) CASE(96) CASE(128)
     default: return QD_ERR_UNSUPPORTED;
@@ -299,12 +385,6 @@ extern "C" int qd_decode_attention(const void* q, long long q_stride, void* out,
 
 // ==================================================================== prefill
 #define PF_KEYS 64  // keys per tile
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 // NW warps of 16 rows each; NST cp.async stages of one K tile + one V tile.
 template <int HD, int NW, int NST>
@@ -367,19 +447,35 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
     }
   }
 
-  auto load_tile = [&](int kt, int stage) {
+  // Each thread copies PIECES 16-byte pieces of K and of V per tile; the page ids of a tile's
+  // rows are fetched one tile ahead, so that no cache load waits for a block-table load.
+  constexpr int CPR = HD / 8;
+  constexpr int PIECES = (PF_KEYS * CPR + NW * 32 - 1) / (NW * 32);
+  int pg_next[PIECES];
+  auto fetch_pages = [&](int kt) {
+#pragma unroll
+    for (int j = 0; j < PIECES; j++) {
+      int i = threadIdx.x + j * NW * 32;
+      int key = kt * PF_KEYS + i / CPR;
+      pg_next[j] = (i < PF_KEYS * CPR && key < key_hi) ? bt[key / page_size] : -1;
+    }
+  };
+  auto load_tile = [&](int kt, int stage) {          // uses pg_next fetched for this kt
     bf16* ks = smem + (size_t)stage * 2 * TILE;
     bf16* vs = ks + TILE;
-    constexpr int CPR = HD / 8;
     const int key_base = kt * PF_KEYS;
-    for (int i = threadIdx.x; i < PF_KEYS * CPR; i += NW * 32) {
-      int row = i / CPR, col = (i % CPR) * 8;
-      int key = key_base + row;
-      int page = key < key_hi ? bt[key / page_size] : -1;
-      int bytes = page >= 0 ? 16 : 0;
-      size_t base = page >= 0 ? (size_t)page * page_elems + (size_t)(key % page_size) * HD + col : 0;
-      cp_async16(ks + row * LD + col, kv + base + (page >= 0 ? k_off : 0), bytes);
-      cp_async16(vs + row * LD + col, kv + base + (page >= 0 ? v_off : 0), bytes);
+#pragma unroll
+    for (int j = 0; j < PIECES; j++) {
+      int i = threadIdx.x + j * NW * 32;
+      if (i < PF_KEYS * CPR) {
+        int row = i / CPR, col = (i % CPR) * 8;
+        int key = key_base + row;
+        int page = pg_next[j];
+        int bytes = page >= 0 ? 16 : 0;
+        size_t base = page >= 0 ? (size_t)page * page_elems + (size_t)(key % page_size) * HD + col : 0;
+        cp_async16(ks + row * LD + col, kv + base + (page >= 0 ? k_off : 0), bytes);
+        cp_async16(vs + row * LD + col, kv + base + (page >= 0 ? v_off : 0), bytes);
+      }
     }
   };
 
@@ -391,14 +487,16 @@ prefill_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
   const int kt_lo = key_lo_tile / PF_KEYS, kt_hi = (key_hi + PF_KEYS - 1) / PF_KEYS;
 #pragma unroll
   for (int p = 0; p < NST - 1; p++) {
-    if (kt_lo + p < kt_hi) load_tile(kt_lo + p, p);
+    if (kt_lo + p < kt_hi) { fetch_pages(kt_lo + p); load_tile(kt_lo + p, p); }
     cp_async_commit();
   }
+  if (kt_lo + NST - 1 < kt_hi) fetch_pages(kt_lo + NST - 1);
   for (int kt = kt_lo; kt < kt_hi; kt++) {
     const int it = kt - kt_lo;
     const int stage = it % NST;
     if (kt + NST - 1 < kt_hi) load_tile(kt + NST - 1, (it + NST - 1) % NST);
     cp_async_commit();
+    if (kt + NST < kt_hi) fetch_pages(kt + NST);      // for the load of the next iteration
     cp_async_wait<NST - 1>();
     __syncthreads();
     const bf16* ks = smem + (size_t)stage * 2 * TILE;

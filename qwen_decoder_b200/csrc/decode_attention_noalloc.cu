@@ -47,8 +47,10 @@ extern "C" int qd_decode_attention_noalloc(const void* q, long long q_stride, vo
   if (rc != QD_NOALLOC_OK) return rc;
   float* part_o = scratch;
   float* part_ml = scratch + (size_t)T * H * splits * d;
+  // no ticket counters: the partial results are added up by the small second kernel, so this
+  // entry point needs no state that must start at zero
   rc = qd_decode_attention(q, q_stride, out, kv, block_table, max_blocks, token_req, positions, T, H, G, d,
-                           page_size, scale, window, splits, part_o, part_ml, stream);
+                           page_size, scale, window, splits, part_o, part_ml, nullptr, stream);
   return rc == QD_ERR_UNSUPPORTED ? QD_NOALLOC_BAD_ARGUMENT : rc;
 }
 

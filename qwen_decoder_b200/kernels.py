@@ -264,24 +264,32 @@ def flash_prefill_supported(dtype, H: int, G: int, d: int, page_size: int) -> bo
     return dtype == torch.bfloat16 and d in FLASH_HEAD_DIMS and H // G <= 64
 
 
+_TICKETS = 1 << 16
+_tickets = {}
+
+
 def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                      block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
                      n_tokens: int, H: int, G: int, d: int, page_size: int, scale: float, window: int,
-                     splits: int) -> None:
+                     splits: int, fused_combine: bool = True) -> None:
     """One query token per request over its cached keys (tensor cores, keys split over ``splits``
     CTAs per (request, kv head); partial results go through scratch memory when splits > 1)."""
     assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
-    part_o = part_ml = None
+    part_o = part_ml = tickets = None
     if splits > 1:
         part_o = torch.empty((n_tokens * H * splits, d), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n_tokens * H * splits, 2), dtype=torch.float32, device=q.device)
+        if fused_combine and n_tokens * G <= _TICKETS:
+            tickets = _tickets.get(q.device)
+            if tickets is None:     # zero once; every launch leaves them zero again
+                tickets = _tickets[q.device] = torch.zeros(_TICKETS, dtype=torch.int32, device=q.device)
     _check(library("attention_flash").qd_decode_attention(
         _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
         _ptr(token_req), _ptr(positions), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
-        _I(window), _I(splits), _ptr(part_o), _ptr(part_ml), _stream()), "decode_attention")
+        _I(window), _I(splits), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _stream()), "decode_attention")
 
 
 def prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
