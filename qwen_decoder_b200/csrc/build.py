@@ -33,6 +33,7 @@ LIBRARIES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "gemm_generic": "gemm_generic.cu",
     "gemm_skinny": "gemm_skinny.cu",
+    "gemm_stream": "gemm_stream.cu",
     "attention_generic": "attention_generic.cu",
     "attention_flash": "attention_flash.cu",
     "sampling": "sampling.cu",

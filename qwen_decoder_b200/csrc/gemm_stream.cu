@@ -1,0 +1,326 @@
+// Few-token contraction as a persistent weight streamer: Y[T, N] = X[T, K] * W[N, K]^T for
+// T <= 64 (decode steps), bfloat16 in, float32 accumulation.
+//
+// A decode step is bound by reading every weight once.  Here a CTA stays on its SM and walks
+// a list of work items (16 rows of W x a share of K).  One producer warp keeps a ring of
+// shared-memory stages full with bulk asynchronous copies (cp.async.bulk, completion counted
+// on an mbarrier per stage): 16 rows of W and the tokens' rows of X for 1024 k per stage (copies of 2 KB: the copy engine is
+// bound by the number of copies, 1 KB rows ran a quarter slower), several
+// stages in flight per CTA, no registers tied up, and the stream runs on across item boundaries.  Four consumer warps read
+// a stage (each a quarter of its k range) with 16-byte shared loads and feed mma.sync
+// m16n8k16 with the tokens as the N dimension; the 16-byte operand trick is the one of
+// gemm_skinny.cu.  After an item's last stage the four partial sums are added in shared
+// memory and the epilogue runs: store (+ bias), split-K partial sums, or SwiGLU.
+// The producer starts before the programmatic-dependency wait (weights are written by no
+// kernel of the step); the consumers wait before they read the tokens.
+//
+// Every wait on an mbarrier is bounded: after ST_SPIN_LIMIT polls a warp records an error in
+// `status`, marks the CTA dead (no wait of it spins again) and runs on to the end without
+// leaving early, so that all warps still meet at every barrier; the host turns a non-zero
+// status into an error.
+#include "common.cuh"
+
+#define ST_CONSUMERS 4
+#define ST_THREADS ((ST_CONSUMERS + 1) * 32)
+#define ST_KC 1024                        // k per stage
+#define ST_ROW_BYTES (ST_KC * 2 + 64)     // padded row: 16-byte reads of 8 rows x 4 lanes hit 32 banks once
+// a stage holds 16 rows of W and TN*8 token rows of X for the same ST_KC k; stages per CTA are
+// chosen so that two CTAs fit on an SM (about 104 KB each) and the L1 keeps nothing it needs
+template <int TN> struct StageCfg {
+  static constexpr int ROWS = 16 + TN * 8;
+  static constexpr int BYTES = ROWS * ST_ROW_BYTES;
+  static constexpr int STAGES = TN == 1 ? 2 : (TN == 2 ? 2 : 1);
+};
+#define ST_SPIN_LIMIT (1u << 24)
+
+#define EPI_STORE 0
+#define EPI_PARTIAL 1
+#define EPI_SWIGLU 2
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// true when the phase with the given parity has completed; false after ST_SPIN_LIMIT polls (or at
+// once when a wait of this CTA has already run out: *dead is then set and nobody waits any more)
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
+  unsigned addr = smem_u32(bar);
+  if (*dead) return false;
+  for (unsigned spin = 0; spin < ST_SPIN_LIMIT; spin++) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  *dead = 1;
+  return false;
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int TN, int EPI, typename TO>
+__global__ void __launch_bounds__(ST_THREADS)
+gemm_stream_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long long ldx,
+                   const float* __restrict__ bias, TO* __restrict__ out, long long ldo,
+                   float* __restrict__ part, int T, int N, int K, int splits, int n_tiles,
+                   int* __restrict__ status) {
+  constexpr int NST = StageCfg<TN>::STAGES;
+  constexpr int STAGE_BYTES = StageCfg<TN>::BYTES;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* stages = smem_raw;                                         // NST x stage
+  float* red = reinterpret_cast<float*>(smem_raw + NST * STAGE_BYTES);      // [4][16][TN*8+1]
+  __shared__ unsigned long long full_bar[NST], empty_bar[NST];
+  __shared__ int dead;   // set when a bounded wait ran out: every warp then runs on without waiting, so that
+                         // all of them still meet at every barrier and the kernel ends; the result is void
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    dead = 0;
+    for (int s = 0; s < NST; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ST_CONSUMERS); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int n_chunks = (K + ST_KC - 1) / ST_KC;
+  const int n_items = n_tiles * splits;
+  constexpr int RED_LD = TN * 8 + 1;
+
+  if (warp == ST_CONSUMERS) {
+    // ------------------------------------------------------------ producer
+    // Weights are written by no kernel of the step: the first NST stages' W rows are requested
+    // before the dependency wait, their X rows after it.
+    unsigned it = 0;                      // stages issued so far
+    bool waited = false;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+      const int tile = item / splits, sp = item - tile * splits;
+      const int c_begin = (int)((long long)n_chunks * sp / splits), c_end = (int)((long long)n_chunks * (sp + 1) / splits);
+      long long row;                      // the row of W this lane copies (lanes 0..15)
+      if (EPI == EPI_SWIGLU) {
+        int F = N >> 1, f = tile * 8 + (lane & 7);
+        if (f >= F) f = F - 1;
+        row = (lane & 8) ? (long long)F + f : f;
+      } else {
+        row = (long long)tile * 16 + (lane & 15);
+        if (row >= N) row = N - 1;
+      }
+      for (int c = c_begin; c < c_end; c++, it++) {
+        const int s = it % NST;
+        const unsigned ph = (it / NST) & 1;
+        if (it >= (unsigned)NST && !waited) {
+          // the ring is full of W requests: now the tokens of the first stages
+          pdl_wait();
+          waited = true;
+          unsigned jt = 0;
+          for (int item2 = blockIdx.x; item2 < n_items && jt < (unsigned)NST; item2 += gridDim.x) {
+            const int sp2 = item2 % splits;
+            const int cb = (int)((long long)n_chunks * sp2 / splits), ce = (int)((long long)n_chunks * (sp2 + 1) / splits);
+            for (int c2 = cb; c2 < ce && jt < (unsigned)NST; c2++, jt++) {
+              const int k2 = c2 * ST_KC;
+              const unsigned rb = (unsigned)(min(ST_KC, K - k2) * 2);
+              for (int t = lane; t < T; t += 32)
+                bulk_copy(stages + (size_t)jt * STAGE_BYTES + (size_t)(16 + t) * ST_ROW_BYTES, X + (size_t)t * ldx + k2,
+                          rb, &full_bar[jt]);
+            }
+          }
+        }
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, &dead) && lane == 0) atomicExch(status, 1);
+        const int k0 = c * ST_KC;
+        const unsigned row_bytes = (unsigned)(min(ST_KC, K - k0) * 2);
+        if (lane == 0) mbar_expect_tx(&full_bar[s], row_bytes * (16 + T));
+        __syncwarp();
+        unsigned char* st = stages + (size_t)s * STAGE_BYTES;
+        if (lane < 16) bulk_copy(st + (size_t)lane * ST_ROW_BYTES, W + row * K + k0, row_bytes, &full_bar[s]);
+        if (waited)
+          for (int t = lane; t < T; t += 32)
+            bulk_copy(st + (size_t)(16 + t) * ST_ROW_BYTES, X + (size_t)t * ldx + k0, row_bytes, &full_bar[s]);
+      }
+    }
+    if (!waited) {
+      // fewer stages than the ring holds: all W requests are out, now the tokens
+      pdl_wait();
+      unsigned jt = 0;
+      for (int item2 = blockIdx.x; item2 < n_items; item2 += gridDim.x) {
+        const int sp2 = item2 % splits;
+        const int cb = (int)((long long)n_chunks * sp2 / splits), ce = (int)((long long)n_chunks * (sp2 + 1) / splits);
+        for (int c2 = cb; c2 < ce; c2++, jt++) {
+          const int k2 = c2 * ST_KC;
+          const unsigned rb = (unsigned)(min(ST_KC, K - k2) * 2);
+          for (int t = lane; t < T; t += 32)
+            bulk_copy(stages + (size_t)jt * STAGE_BYTES + (size_t)(16 + t) * ST_ROW_BYTES, X + (size_t)t * ldx + k2, rb,
+                      &full_bar[jt]);
+        }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int j = lane & 3, r = lane >> 2;
+  unsigned it = 0;
+  for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int tile = item / splits, sp = item - tile * splits;
+    const int c_begin = (int)((long long)n_chunks * sp / splits), c_end = (int)((long long)n_chunks * (sp + 1) / splits);
+    float acc[TN][4];
+#pragma unroll
+    for (int n = 0; n < TN; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+    for (int c = c_begin; c < c_end; c++, it++) {
+      const int s = it % NST;
+      const unsigned ph = (it / NST) & 1;
+      if (!mbar_wait(&full_bar[s], ph, &dead) && lane == 0) atomicExch(status, 2);
+      const unsigned char* st = stages + (size_t)s * STAGE_BYTES;
+      // this warp's quarter of the stage: k-steps of 32 at kq = warp * (ST_KC / 4) + u * 32
+#pragma unroll
+      for (int u = 0; u < ST_KC / 32 / ST_CONSUMERS; u++) {
+        const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
+        if (c * ST_KC + kq >= K) break;                 // the whole k-step lies past K (same for all lanes)
+        const bool in = c * ST_KC + kq + 8 * j < K;     // lanes past K feed zeros; every lane runs the MMAs
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        const size_t col = (size_t)(kq + 8 * j) * 2;
+        uint4 lo = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
+        uint4 hi = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
+#pragma unroll
+        for (int n = 0; n < TN; n++) {
+          // token rows past T were never copied: whatever is there only reaches columns that are not stored
+          uint4 b = in ? *reinterpret_cast<const uint4*>(st + (size_t)(16 + n * 8 + r) * ST_ROW_BYTES + col) : zero;
+          mma16816(acc[n], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+          mma16816(acc[n], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    // add the four warps' shares of K and write the item's result
+#pragma unroll
+    for (int n = 0; n < TN; n++) {
+      float* base = red + (size_t)warp * 16 * RED_LD;
+      base[r * RED_LD + n * 8 + 2 * j] = acc[n][0];
+      base[r * RED_LD + n * 8 + 2 * j + 1] = acc[n][1];
+      base[(r + 8) * RED_LD + n * 8 + 2 * j] = acc[n][2];
+      base[(r + 8) * RED_LD + n * 8 + 2 * j + 1] = acc[n][3];
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
+    if (EPI == EPI_SWIGLU) {
+      const int F = N >> 1;
+      for (int idx = threadIdx.x; idx < 8 * TN * 8; idx += ST_CONSUMERS * 32) {
+        int row = idx & 7, tok = idx >> 3;
+        int f = tile * 8 + row;
+        if (tok >= T || f >= F) continue;
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_CONSUMERS; w++) {
+          gate += red[((size_t)w * 16 + row) * RED_LD + tok];
+          up += red[((size_t)w * 16 + row + 8) * RED_LD + tok];
+        }
+        out[(size_t)tok * ldo + f] = from_float<TO>(gate / (1.0f + expf(-gate)) * up);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < 16 * TN * 8; idx += ST_CONSUMERS * 32) {
+        int row = idx & 15, tok = idx >> 4;
+        int n = tile * 16 + row;
+        if (tok >= T || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_CONSUMERS; w++) v += red[((size_t)w * 16 + row) * RED_LD + tok];
+        if (EPI == EPI_PARTIAL) {
+          part[((size_t)sp * T + tok) * N + n] = v;
+        } else {
+          if (bias) v += bias[n];
+          out[(size_t)tok * ldo + n] = from_float<TO>(v);
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");   // red is reused by the next item
+  }
+  pdl_launch_dependents();
+}
+
+static int* g_status[64];   // per device: one int of device memory for the kernels' error status
+
+static int* status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!g_status[dev]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, sizeof(int));
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+template <int TN>
+static int launch_stream(const bf16* W, const bf16* X, long long ldx, const float* bias, void* out, int out_dtype,
+                         long long ldo, float* part, int T, int N, int K, int splits, int epi, int max_ctas,
+                         cudaStream_t stream) {
+  int* status = status_word();
+  if (!status) return QD_ERR_UNSUPPORTED;
+  int n_tiles = epi == EPI_SWIGLU ? (N / 2 + 7) / 8 : (N + 15) / 16;
+  int n_items = n_tiles * splits;
+  int grid = n_items < max_ctas ? n_items : max_ctas;
+  size_t smem = (size_t)StageCfg<TN>::STAGES * StageCfg<TN>::BYTES + (size_t)ST_CONSUMERS * 16 * (TN * 8 + 1) * sizeof(float);
+#define LAUNCH(E, TO)                                                                                       \
+  do {                                                                                                      \
+    cudaFuncSetAttribute(gemm_stream_kernel<TN, E, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    qd_launch(gemm_stream_kernel<TN, E, TO>, dim3(grid), dim3(ST_THREADS), smem, stream, W, X, ldx, bias,   \
+              (TO*)out, ldo, part, T, N, K, splits, n_tiles, status);                                       \
+  } while (0)
+  if (epi == EPI_SWIGLU) {
+    if (out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;
+    LAUNCH(EPI_SWIGLU, bf16);
+  } else if (epi == EPI_PARTIAL) {
+    LAUNCH(EPI_PARTIAL, float);
+  } else if (out_dtype == QD_BF16) {
+    LAUNCH(EPI_STORE, bf16);
+  } else if (out_dtype == QD_F32) {
+    LAUNCH(EPI_STORE, float);
+  } else {
+    return QD_ERR_UNSUPPORTED;
+  }
+#undef LAUNCH
+  return qd_last_error();
+}
+
+// Arguments as qd_gemm_skinny (gemm_skinny.cu); max_ctas bounds the persistent grid (two per SM is
+// a good value).  K a multiple of 8, W and X 16-byte aligned, ldx a multiple of 8, splits <= ceil(K / 1024).
+extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const float* bias, void* out,
+                              int out_dtype, long long ldo, float* part, int T, int N, int K, int splits,
+                              int epi, int max_ctas, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (T > 64 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || splits < 1 || max_ctas < 1) return QD_ERR_UNSUPPORTED;
+  if (splits > (K + ST_KC - 1) / ST_KC) return QD_ERR_UNSUPPORTED;
+  if (((uintptr_t)W & 15) || ((uintptr_t)X & 15)) return QD_ERR_UNSUPPORTED;
+  if (epi == EPI_SWIGLU && (N & 1)) return QD_ERR_UNSUPPORTED;
+  if (epi == EPI_PARTIAL && !part) return QD_ERR_UNSUPPORTED;
+  if (epi != EPI_PARTIAL && splits != 1) return QD_ERR_UNSUPPORTED;
+  const bf16* w = (const bf16*)W;
+  const bf16* x = (const bf16*)X;
+  if (T <= 8) return launch_stream<1>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
+  if (T <= 16) return launch_stream<2>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
+  if (T <= 32) return launch_stream<4>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
+  return launch_stream<8>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
+}
+
+// 0 if no kernel of this library has recorded a bounded-wait expiry on the current device
+// (1: producer gave up waiting for a free stage, 2: a consumer gave up waiting for data).  Synchronises.
+extern "C" int qd_gemm_stream_status() {
+  int* status = status_word();
+  if (!status) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return v;
+}

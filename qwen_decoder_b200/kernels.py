@@ -195,8 +195,36 @@ def skinny_splits(N: int, K: int, target_ctas: int = 592) -> int:
     """Shares of K over the grid: enough CTAs (16 rows of W each) for four per SM, every warp at
     least one group of 128 k."""
     tiles = (N + 15) // 16
+    if skinny_impl == "stream":
+        chunks = (K + 1023) // 1024          # the streaming kernel splits K in whole stages of 1024
+        return max(1, min((target_ctas + tiles - 1) // tiles, chunks, 16))
     groups = (K + 127) // 128
     return max(1, min((target_ctas + tiles - 1) // tiles, groups // 4, 16))
+
+
+# Which few-token kernel runs: "stream" (persistent CTAs fed by bulk asynchronous copies,
+# csrc/gemm_stream.cu) or "regs" (one wave of CTAs loading straight into registers, csrc/gemm_skinny.cu).
+import os as _os
+skinny_impl = _os.environ.get("QD_SKINNY_IMPL", "stream")
+STREAM_MAX_CTAS = 296          # two persistent CTAs on each of 148 SMs
+
+
+def _skinny_call(x, w, bias, out, part, T, N, K, splits, epi, what):
+    out_code = dtype_code(out.dtype) if out is not None else F32
+    ldo = out.stride(0) if out is not None else 0
+    if skinny_impl == "stream":
+        _check(library("gemm_stream").qd_gemm_stream(
+            _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
+            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(STREAM_MAX_CTAS), _stream()), what)
+    else:
+        _check(library("gemm_skinny").qd_gemm_skinny(
+            _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
+            _I(T), _I(N), _I(K), _I(splits), _I(epi), _stream()), what)
+
+
+def gemm_stream_status() -> int:
+    """0 unless a bounded wait inside the streaming kernel ran out on the current device."""
+    return int(library("gemm_stream").qd_gemm_stream_status())
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
@@ -205,9 +233,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     N = w.shape[0]
     assert skinny_supported(x, w, SKINNY_MAX_TOKENS) and out.shape == (T, N) and out.stride(1) == 1
     _contig(w, "w")
-    _check(library("gemm_skinny").qd_gemm_skinny(
-        _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(dtype_code(out.dtype)),
-        _LL(out.stride(0)), _ptr(None), _I(T), _I(N), _I(K), _I(1), _I(EPI_STORE), _stream()), "gemm_skinny")
+    _skinny_call(x, w, bias, out, None, T, N, K, 1, EPI_STORE, "gemm_skinny")
 
 
 def gemm_skinny_partial(x: torch.Tensor, w: torch.Tensor, splits: int) -> torch.Tensor:
@@ -217,9 +243,7 @@ def gemm_skinny_partial(x: torch.Tensor, w: torch.Tensor, splits: int) -> torch.
     assert skinny_supported(x, w, SKINNY_MAX_TOKENS)
     _contig(w, "w")
     part = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
-    _check(library("gemm_skinny").qd_gemm_skinny(
-        _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(None), _ptr(None), _I(F32), _LL(0), _ptr(part), _I(T), _I(N),
-        _I(K), _I(splits), _I(EPI_PARTIAL), _stream()), "gemm_skinny_partial")
+    _skinny_call(x, w, None, None, part, T, N, K, splits, EPI_PARTIAL, "gemm_skinny_partial")
     return part
 
 
@@ -229,9 +253,7 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
     N = w_gate_up.shape[0]
     assert skinny_supported(x, w_gate_up, SKINNY_MAX_TOKENS) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
     _contig(w_gate_up, "w"); _contig(out, "out")
-    _check(library("gemm_skinny").qd_gemm_skinny(
-        _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(None), _ptr(out), _I(BF16), _LL(out.stride(0)),
-        _ptr(None), _I(T), _I(N), _I(K), _I(1), _I(EPI_SWIGLU), _stream()), "gemm_skinny_swiglu")
+    _skinny_call(x, w_gate_up, None, out, None, T, N, K, 1, EPI_SWIGLU, "gemm_skinny_swiglu")
 
 
 # ------------------------------------------------------------------- attention

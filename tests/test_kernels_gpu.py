@@ -277,6 +277,8 @@ def test_gemm_skinny(shape):
             close(out, want + (bias.double() if bias is not None else 0), odt if odt == dt else torch.float32,
                   scale=float(want.abs().max()) + 1)
     for splits in (1, 3):
+        if kernels.skinny_impl == "stream":
+            splits = min(splits, (K + 1023) // 1024)      # the streaming kernel splits K in whole stages of 1024
         part = kernels.gemm_skinny_partial(x.to(DEV), w.to(DEV), splits)
         assert part.shape == (splits, T, N)
         close(part.sum(0), want, torch.float32, scale=float(want.abs().max()))
@@ -332,3 +334,24 @@ def test_partial_sums_are_added_by_the_consumers():
         page, off = int(slots[t]) // page_size, int(slots[t]) % page_size
         close(kvc[page, 0, :, off, :].reshape(-1), wk[t], torch.bfloat16)
         close(kvc[page, 1, :, off, :].reshape(-1), full[t, (H + G) * d:], torch.bfloat16)
+
+
+@pytest.mark.parametrize("impl", ["stream", "regs"])
+def test_gemm_skinny_both_implementations(impl, monkeypatch):
+    """The persistent bulk-copy streamer and the register-load kernel give the same products."""
+    from qwen_decoder_b200 import kernels
+    monkeypatch.setattr(kernels, "skinny_impl", impl)
+    for shape in [(1, 48, 64), (8, 2048, 2048), (5, 130, 1096), (16, 22, 2560), (16, 704, 520), (40, 96, 1032)]:
+        test_gemm_skinny(shape)
+    # many items per persistent CTA, K split in shares: every stage of the ring is reused many times
+    g = torch.Generator().manual_seed(23)
+    T, N, K = 8, 16 * 700, 3072
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16)
+    want = plain_model.linear(x.double(), w.double())
+    part = kernels.gemm_skinny_partial(x.to(DEV), w.to(DEV), 3)
+    close(part.sum(0), want, torch.float32, scale=float(want.abs().max()))
+    h = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny_swiglu(x.to(DEV), w.to(DEV), h)
+    close(h, plain_model.silu(want[:, :N // 2]) * want[:, N // 2:], torch.bfloat16)
+    assert kernels.gemm_stream_status() == 0
