@@ -52,12 +52,19 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
   unsigned addr = smem_u32(bar);
   if (*dead) return false;
+  unsigned long long start = 0;
   for (unsigned spin = 0; spin < ST_SPIN_LIMIT; spin++) {
     unsigned ok;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return true;
+    if ((spin & 255) == 255) {              // also bounded in time: two seconds
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (start == 0) start = now;
+      else if (now - start > 2000000000ull) break;
+    }
   }
   *dead = 1;
   return false;

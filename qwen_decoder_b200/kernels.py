@@ -7,6 +7,7 @@ on a CUDA device, or a kernel library that cannot be built or loaded, is an erro
 from __future__ import annotations
 
 import ctypes
+import os as _os
 from typing import Optional
 
 import torch
@@ -180,22 +181,42 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         _I(T), _I(N), _I(K), _LL(x.stride(0)), _LL(out.stride(0)), _stream()), "gemm_generic")
 
 
-SKINNY_MAX_TOKENS = 64      # what the kernel takes
-SKINNY_POLICY_TOKENS = 16   # up to here it is the faster choice; beyond, cuBLAS until the tcgen05 kernel
+SKINNY_MAX_TOKENS = 64      # what the mma.sync few-token kernels take
+SKINNY_POLICY_TOKENS = 16   # up to here they are the faster choice
+TC5_POLICY_TOKENS = int(_os.environ.get("QD_TC5_TOKENS", "16"))   # from there up to here the tcgen05 kernel; 16 = never:
+# on row-major weights it reads 128-byte pieces of 128 rows per copy and stays below the library product
 EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
 
 
-def skinny_supported(x: torch.Tensor, w: torch.Tensor, limit: int = SKINNY_POLICY_TOKENS) -> bool:
+def few_token_impl(T: int) -> str:
+    """Which kernel takes a product of T tokens: "stream" / "regs" (mma.sync weight streamers), "tc5"
+    (tcgen05 + TMA), or "" (none of the few-token kernels: the caller takes the library product)."""
+    if skinny_impl == "tc5":
+        return "tc5" if T <= max(TC5_POLICY_TOKENS, SKINNY_POLICY_TOKENS) else ""
+    if T <= SKINNY_POLICY_TOKENS:
+        return skinny_impl
+    return "tc5" if T <= TC5_POLICY_TOKENS else ""
+
+
+def skinny_supported(x: torch.Tensor, w: torch.Tensor, limit: Optional[int] = None) -> bool:
+    if limit is None:
+        limit = max(TC5_POLICY_TOKENS, SKINNY_POLICY_TOKENS)
+        if not few_token_impl(x.shape[0]):
+            return False
     return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[0] <= limit
             and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.stride(1) == 1
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_splits(N: int, K: int, target_ctas: int = 592) -> int:
+def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
     """Shares of K over the grid: enough CTAs (16 rows of W each) for four per SM, every warp at
-    least one group of 128 k."""
+    least one group of 128 k.  The tcgen05 kernel has tiles of 128 rows and one CTA per SM."""
+    impl = few_token_impl(T) or "tc5"
+    if impl == "tc5":
+        tiles = (N + 127) // 128
+        return max(1, min((TC5_MAX_CTAS + tiles - 1) // tiles, ((K + 63) // 64) // 8, 16))
     tiles = (N + 15) // 16
-    if skinny_impl == "stream":
+    if impl == "stream":
         chunks = (K + 1023) // 1024          # the streaming kernel splits K in whole stages of 1024
         return max(1, min((target_ctas + tiles - 1) // tiles, chunks, 16))
     groups = (K + 127) // 128
@@ -204,15 +225,25 @@ def skinny_splits(N: int, K: int, target_ctas: int = 592) -> int:
 
 # Which few-token kernel runs: "stream" (persistent CTAs fed by bulk asynchronous copies,
 # csrc/gemm_stream.cu) or "regs" (one wave of CTAs loading straight into registers, csrc/gemm_skinny.cu).
-import os as _os
 skinny_impl = _os.environ.get("QD_SKINNY_IMPL", "stream")
 STREAM_MAX_CTAS = 296          # two persistent CTAs on each of 148 SMs
+TC5_MAX_CTAS = 148             # the tcgen05 kernel runs one persistent CTA per SM
+
+
+def gemm_tc5_status() -> int:
+    """0 unless a bounded wait inside the tcgen05 kernel ran out on the current device."""
+    return int(library("gemm_tc5").qd_gemm_tc5_status())
 
 
 def _skinny_call(x, w, bias, out, part, T, N, K, splits, epi, what):
     out_code = dtype_code(out.dtype) if out is not None else F32
     ldo = out.stride(0) if out is not None else 0
-    if skinny_impl == "stream":
+    impl = few_token_impl(T) or "tc5"
+    if impl == "tc5":
+        _check(library("gemm_tc5").qd_gemm_tc5(
+            _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
+            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(TC5_MAX_CTAS), _stream()), what)
+    elif impl == "stream":
         _check(library("gemm_stream").qd_gemm_stream(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
             _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(STREAM_MAX_CTAS), _stream()), what)
@@ -231,7 +262,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
     """out[T, N] = x @ w^T (+ bias) for T <= 64, bfloat16 in, out bfloat16 or float32."""
     T, K = x.shape
     N = w.shape[0]
-    assert skinny_supported(x, w, SKINNY_MAX_TOKENS) and out.shape == (T, N) and out.stride(1) == 1
+    assert skinny_supported(x, w, 1 << 30) and out.shape == (T, N) and out.stride(1) == 1
     _contig(w, "w")
     _skinny_call(x, w, bias, out, None, T, N, K, 1, EPI_STORE, "gemm_skinny")
 
@@ -240,7 +271,7 @@ def gemm_skinny_partial(x: torch.Tensor, w: torch.Tensor, splits: int) -> torch.
     """float32 partial sums [splits, T, N] of x @ w^T over ``splits`` shares of K."""
     T, K = x.shape
     N = w.shape[0]
-    assert skinny_supported(x, w, SKINNY_MAX_TOKENS)
+    assert skinny_supported(x, w, 1 << 30)
     _contig(w, "w")
     part = torch.empty((splits, T, N), dtype=torch.float32, device=x.device)
     _skinny_call(x, w, None, None, part, T, N, K, splits, EPI_PARTIAL, "gemm_skinny_partial")
@@ -251,7 +282,7 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
     """out[T, F] = silu(x @ Wg^T) * (x @ Wu^T) with w_gate_up = [Wg; Wu] of shape [2F, K]."""
     T, K = x.shape
     N = w_gate_up.shape[0]
-    assert skinny_supported(x, w_gate_up, SKINNY_MAX_TOKENS) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
+    assert skinny_supported(x, w_gate_up, 1 << 30) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
     _contig(w_gate_up, "w"); _contig(out, "out")
     _skinny_call(x, w_gate_up, None, out, None, T, N, K, 1, EPI_SWIGLU, "gemm_skinny_swiglu")
 

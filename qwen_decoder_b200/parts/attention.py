@@ -63,7 +63,7 @@ class GQAttention(Mixer):
         if matmul_backend.use_skinny(x, self.qkv.weight):
             # few tokens: the product leaves float32 partial sums; bias, rotation and cache write take them
             part = kernels.gemm_skinny_partial(x, self.qkv.weight,
-                                               kernels.skinny_splits(self.qkv.out_features, self.hidden_size))
+                                               kernels.skinny_splits(self.qkv.out_features, self.hidden_size, x.shape[0]))
             matmul_backend.counters["own"] += 1
             qkv = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)       # q only
             kernels.rope_kv_write_partial(part, self.qkv.bias, qkv, H, G, d, *rope, ctx.positions, cache.kv,
