@@ -111,6 +111,70 @@ def prefill_flops(cfg, layers, T):
     return layers * (2 * T * per_layer + attn) + 2 * V * D
 
 
+def micro(args):
+    """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
+    import math
+    import torch
+    from qwen_decoder_b200 import kernels
+    dev = "cuda:0"
+    H, G, d, ps = 16, 2, 128, 16
+    T = args.tokens
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    if args.micro == "gemm":
+        N, K = {"qkv": (2560, 2048), "o": (2048, 2048), "gate_up": (22016, 2048), "down": (2048, 11008),
+                "lm_head": (151936, 2048)}[args.micro_shape]
+        x = torch.randn(T, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
+        out = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
+        if args.micro_impl == "cublas":
+            run = lambda: torch.mm(x, w.t(), out=out)
+        else:
+            kernels.skinny_impl = args.micro_impl
+            run = lambda: kernels._skinny_call(x, w, None, out, None, T, N, K, 1, kernels.EPI_STORE, "micro")
+        work = {"bytes": N * K * 2, "flops": 2 * T * N * K}
+    elif args.micro == "decode_attention":
+        ctx = args.context + 128
+        npg = (ctx + ps - 1) // ps
+        kv = torch.randn(T * npg + 4, 2, G, ps, d, device=dev).bfloat16()
+        bt = torch.arange(T * npg, dtype=torch.int32, device=dev).view(T, npg).contiguous()
+        q = torch.randn(T, H * d, device=dev).bfloat16()
+        out = torch.empty(T, H * d, device=dev, dtype=torch.bfloat16)
+        tr = torch.arange(T, dtype=torch.int32, device=dev)
+        pos = torch.full((T,), ctx - 1, dtype=torch.int32, device=dev)
+        from qwen_decoder_b200.parts.attention import decode_splits
+        splits = decode_splits(T * G, ctx)
+        run = lambda: kernels.decode_attention(q, H * d, out, kv, bt, tr, pos, T, H, G, d, ps, 1 / math.sqrt(d), 0, splits)
+        work = {"bytes": T * ctx * 2 * G * d * 2, "flops": 4 * T * ctx * H * d, "splits": splits}
+    else:
+        T = args.prefill_tokens
+        kv = torch.randn(T // ps + 4, 2, G, ps, d, device=dev).bfloat16()
+        bt = torch.arange(T // ps, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+        q = torch.randn(T, (H + 2 * G) * d, device=dev).bfloat16()
+        out = torch.empty(T, H * d, device=dev, dtype=torch.bfloat16)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        st = torch.tensor([0], dtype=torch.int32, device=dev)
+        run = lambda: kernels.prefill_attention(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0)
+        work = {"bytes": T * (H + 2 * G) * d * 2 * 2, "flops": 4 * d * H * (T * (T + 1) // 2)}
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(20):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); run(); e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    us = ts[len(ts) // 2]
+    print(json.dumps({"micro": args.micro, "impl": args.micro_impl if args.micro == "gemm" else "ours",
+                      "shape": args.micro_shape if args.micro == "gemm" else None, "tokens": T, "us": round(us, 2),
+                      "GB/s": round(work["bytes"] / us / 1e3, 1), "TFLOP/s": round(work["flops"] / us / 1e6, 2),
+                      "note": "eager launch between CUDA events after an L2 flush; includes ~8 us of launch latency",
+                      **{k: v for k, v in work.items() if k == "splits"}}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -123,7 +187,14 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "prefill_attention"],
+                    help="time one kernel alone at the 3B shape (for profiles/), print one JSON line and exit")
+    ap.add_argument("--micro-impl", default="stream", choices=["stream", "regs", "tc5", "cublas"])
+    ap.add_argument("--micro-shape", default="lm_head", choices=["qkv", "o", "gate_up", "down", "lm_head"])
+    ap.add_argument("--tokens", type=int, default=8)
     args = ap.parse_args()
+    if args.micro:
+        return micro(args)
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "nature-li/qwen-decoder is a CMake project of executables (no setup.py/pyproject, "

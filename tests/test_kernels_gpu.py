@@ -16,11 +16,17 @@ def tol(dt):
     return 2e-6 if dt == torch.float32 else 1e-2
 
 
+# bfloat16 products summed in float32 by the tensor cores: the sum of K terms is not an IEEE sequential
+# sum; its error grows like sqrt(K) * 2^-24 (2.7e-6 at K = 2048), bounded here at 1e-5 of the largest result
+TENSOR_F32 = "tensor-core float32 accumulation"
+
+
 def close(got, want, dt, scale=None):
     want = want.to(torch.float64)
     s = float(want.abs().max()) if scale is None else scale
     err = float((got.to(torch.float64).cpu() - want.cpu()).abs().max())
-    assert err <= tol(dt) * max(s, 1e-30), f"max |diff| {err:.3e} vs scale {s:.3e}"
+    t = 1e-5 if dt == TENSOR_F32 else tol(dt)
+    assert err <= t * max(s, 1e-30), f"max |diff| {err:.3e} vs scale {s:.3e}"
 
 
 @pytest.mark.parametrize("dt", DTYPES)
@@ -274,21 +280,23 @@ def test_gemm_skinny(shape):
         for bias in (None, b):
             out = torch.empty(T, N, dtype=odt, device=DEV)
             kernels.gemm_skinny(x.to(DEV), w.to(DEV), bias.to(DEV) if bias is not None else None, out)
-            close(out, want + (bias.double() if bias is not None else 0), odt if odt == dt else torch.float32,
+            close(out, want + (bias.double() if bias is not None else 0), odt if odt == dt else TENSOR_F32,
                   scale=float(want.abs().max()) + 1)
     for splits in (1, 3):
-        if kernels.skinny_impl == "stream":
+        if kernels.few_token_impl(T) == "stream":
             splits = min(splits, (K + 1023) // 1024)      # the streaming kernel splits K in whole stages of 1024
+        elif kernels.few_token_impl(T) in ("tc5", ""):
+            splits = min(splits, (K + 63) // 64)          # the tcgen05 kernel in whole blocks of 64
         part = kernels.gemm_skinny_partial(x.to(DEV), w.to(DEV), splits)
         assert part.shape == (splits, T, N)
-        close(part.sum(0), want, torch.float32, scale=float(want.abs().max()))
+        close(part.sum(0), want, TENSOR_F32, scale=float(want.abs().max()))
     # x as a column slice of a wider buffer (row stride > K)
     wide = torch.zeros(T, K + 64, dtype=dt)
     wide[:, 32:32 + K] = x
     xs = wide.to(DEV)[:, 32:32 + K]
     out = torch.empty(T, N, dtype=torch.float32, device=DEV)
     kernels.gemm_skinny(xs, w.to(DEV), None, out)
-    close(out, want, torch.float32, scale=float(want.abs().max()))
+    close(out, want, TENSOR_F32, scale=float(want.abs().max()))
     if N % 2 == 0:
         F = N // 2
         h = torch.empty(T, F, dtype=dt, device=DEV)
@@ -336,9 +344,10 @@ def test_partial_sums_are_added_by_the_consumers():
         close(kvc[page, 1, :, off, :].reshape(-1), full[t, (H + G) * d:], torch.bfloat16)
 
 
-@pytest.mark.parametrize("impl", ["stream", "regs"])
+@pytest.mark.parametrize("impl", ["stream", "regs", "tc5"])
 def test_gemm_skinny_both_implementations(impl, monkeypatch):
-    """The persistent bulk-copy streamer and the register-load kernel give the same products."""
+    """The persistent bulk-copy streamer, the register-load kernel and the tcgen05 kernel give the same
+    products."""
     from qwen_decoder_b200 import kernels
     monkeypatch.setattr(kernels, "skinny_impl", impl)
     for shape in [(1, 48, 64), (8, 2048, 2048), (5, 130, 1096), (16, 22, 2560), (16, 704, 520), (40, 96, 1032)]:
@@ -350,8 +359,33 @@ def test_gemm_skinny_both_implementations(impl, monkeypatch):
     w = (0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16)
     want = plain_model.linear(x.double(), w.double())
     part = kernels.gemm_skinny_partial(x.to(DEV), w.to(DEV), 3)
-    close(part.sum(0), want, torch.float32, scale=float(want.abs().max()))
+    close(part.sum(0), want, TENSOR_F32, scale=float(want.abs().max()))
     h = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_skinny_swiglu(x.to(DEV), w.to(DEV), h)
     close(h, plain_model.silu(want[:, :N // 2]) * want[:, N // 2:], torch.bfloat16)
-    assert kernels.gemm_stream_status() == 0
+    assert kernels.gemm_stream_status() == 0 and kernels.gemm_tc5_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(200, 384, 256), (700, 1000, 1096), (129, 130, 72), (2048, 512, 512)])
+def test_gemm_tcgen05_many_tokens(shape, monkeypatch):
+    """The tcgen05 + TMA kernel with token tiles of 128 and 256: stores with bias, SwiGLU, sizes that are
+    no multiple of its tiles (TMA fills what lies outside with zeros)."""
+    from qwen_decoder_b200 import kernels
+    monkeypatch.setattr(kernels, "skinny_impl", "tc5")
+    T, N, K = shape
+    g = torch.Generator().manual_seed(24)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    want = plain_model.linear(x.double(), w.double())
+    out = torch.empty(T, N, dtype=torch.float32, device=DEV)
+    kernels.gemm_skinny(x.to(DEV), w.to(DEV), b.to(DEV), out)
+    close(out, want + b.double(), TENSOR_F32, scale=float(want.abs().max()) + 1)
+    out16 = torch.empty(T, N, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny(x.to(DEV), w.to(DEV), None, out16)
+    close(out16, want, torch.bfloat16)
+    if N % 2 == 0:
+        h = torch.empty(T, N // 2, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_skinny_swiglu(x.to(DEV), w.to(DEV), h)
+        close(h, plain_model.silu(want[:, :N // 2]) * want[:, N // 2:], torch.bfloat16)
+    assert kernels.gemm_tc5_status() == 0
