@@ -20,6 +20,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .pages import BlockTable, CacheAccountingError, OutOfPages, PagePool, StateSlots
+from .prefix import PrefixIndex
 
 
 @dataclass(frozen=True)
@@ -106,13 +107,16 @@ class RequestCache:
         self.tables = [BlockTable() for _ in range(num_groups)]
         self.state_slot = state_slot
         self.closed = False
+        # prefix cache: the tokens cached so far and the index entry of each full page (-1: none)
+        self.token_log: List[int] = []
+        self.prefix_ids: List[int] = []
 
 
 class CacheManager:
     """Pools, tables and state slots of all live requests; device tensors if ``device`` is given."""
 
     def __init__(self, layout: CacheLayout, num_pages: int, page_size: int, max_requests: int,
-                 dtype: torch.dtype = torch.bfloat16, device=None):
+                 dtype: torch.dtype = torch.bfloat16, device=None, prefix_cache: bool = False):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.layout = layout
@@ -122,6 +126,12 @@ class CacheManager:
         self.pools = [PagePool(num_pages) for _ in layout.groups]
         self.slots = StateSlots(max_requests)
         self.live: Dict[object, RequestCache] = {}
+        # Sharing pages of a common prefix needs every group to keep all keys and no per-request state:
+        # a windowed group gives pages back early and a fixed-size state cannot be shared.
+        self.prefix: Optional[PrefixIndex] = None
+        if prefix_cache and layout.groups and not layout.fixed_needs and \
+                all(g.need.window is None for g in layout.groups):
+            self.prefix = PrefixIndex(self.pools, page_size)
         self.dtype = dtype
         self.device = torch.device(device) if device is not None else None
         self.kv: List[Optional[torch.Tensor]] = [None] * len(layout.groups)
@@ -171,7 +181,10 @@ class CacheManager:
         return [p.num_free for p in self.pools]
 
     # ---- life of a request ----------------------------------------------
-    def open(self, request_id) -> RequestCache:
+    def open(self, request_id, tokens: Optional[Sequence[int]] = None) -> RequestCache:
+        """Start a request.  With the prefix cache on and the request's ``tokens`` given, full pages
+        that an earlier request cached for the same beginning are shared: ``num_tokens`` then starts
+        above zero and the caller feeds only the rest."""
         if request_id in self.live:
             raise CacheAccountingError(f"request {request_id!r} is already live")
         slot = self.slots.allocate()
@@ -180,6 +193,15 @@ class CacheManager:
         for st in self.states:
             if st is not None:
                 st[slot].zero_()
+        if self.prefix is not None and tokens is not None:
+            for eid in self.prefix.match(tokens):
+                pages = self.prefix.acquire(eid)
+                for g, p in enumerate(pages):
+                    rc.tables[g].pages.append(p)
+                rc.prefix_ids.append(eid)
+            n = len(rc.prefix_ids) * self.page_size
+            rc.num_tokens = n
+            rc.token_log = [int(t) for t in tokens[:n]]
         return rc
 
     def ensure(self, rc: RequestCache, total_tokens: int) -> None:
@@ -194,9 +216,21 @@ class CacheManager:
             for _ in range(m):
                 rc.tables[g].pages.append(self.pools[g].allocate())
 
-    def commit(self, rc: RequestCache, n_tokens: int) -> None:
-        """The step wrote ``n_tokens`` more tokens; give back pages a window has passed."""
+    def commit(self, rc: RequestCache, n_tokens: int, tokens: Optional[Sequence[int]] = None) -> None:
+        """The step wrote ``n_tokens`` more tokens (``tokens``: which ones, for the prefix cache); give
+        back pages a window has passed."""
         rc.num_tokens += n_tokens
+        if self.prefix is not None and tokens is not None and len(rc.token_log) == rc.num_tokens - n_tokens:
+            rc.token_log.extend(int(t) for t in tokens)
+            ps = self.page_size
+            while (len(rc.prefix_ids) + 1) * ps <= rc.num_tokens:
+                i = len(rc.prefix_ids)
+                parent = rc.prefix_ids[-1] if rc.prefix_ids else PrefixIndex.ROOT
+                if parent < 0:
+                    rc.prefix_ids.append(-1)          # the chain broke earlier: nothing below is recorded
+                    continue
+                rc.prefix_ids.append(self.prefix.record(parent, rc.token_log[i * ps:(i + 1) * ps],
+                                                        [t.pages[i] for t in rc.tables]))
         for g, table in enumerate(rc.tables):
             if rc.num_tokens > len(table) * self.page_size:
                 raise CacheAccountingError(

@@ -11,8 +11,8 @@ notion is the running-slot index (decoder.cpp:123).
 """
 from __future__ import annotations
 
-from collections import deque
-from typing import Deque, List
+from collections import OrderedDict
+from typing import Callable, List, Optional
 
 
 class OutOfPages(RuntimeError):
@@ -29,7 +29,10 @@ class PagePool:
             raise ValueError("num_pages must be >= 0")
         self.num_pages = num_pages
         self._ref: List[int] = [0] * num_pages
-        self._free: Deque[int] = deque(range(num_pages - 1, -1, -1))  # back of the deque = page 0 first
+        # ordered front -> back; release puts a page at the front, allocate takes from the back
+        self._free: "OrderedDict[int, None]" = OrderedDict((p, None) for p in range(num_pages - 1, -1, -1))
+        # called with the page id when a free page is handed out again (its old content is about to be lost)
+        self.on_allocate: Optional[Callable[[int], None]] = None
 
     @property
     def num_free(self) -> int:
@@ -45,11 +48,21 @@ class PagePool:
     def allocate(self) -> int:
         if not self._free:
             raise OutOfPages("no free cache page")
-        page = self._free.pop()
+        page, _ = self._free.popitem(last=True)
         if self._ref[page] != 0:
             raise CacheAccountingError(f"page {page} on the free list has reference count {self._ref[page]}")
         self._ref[page] = 1
+        if self.on_allocate is not None:
+            self.on_allocate(page)
         return page
+
+    def take(self, page: int) -> None:
+        """Take this particular free page (its content is wanted again: a prefix hit on a page
+        nobody holds; kv_cache.h:147-158 take_from_free_list)."""
+        if page not in self._free:
+            raise CacheAccountingError(f"take of page {page} that is not free")
+        del self._free[page]
+        self._ref[page] = 1
 
     def retain(self, page: int) -> None:
         if self._ref[page] <= 0:
@@ -61,15 +74,14 @@ class PagePool:
             raise CacheAccountingError(f"release of page {page} that is not held")
         self._ref[page] -= 1
         if self._ref[page] == 0:
-            self._free.appendleft(page)
+            self._free[page] = None
+            self._free.move_to_end(page, last=False)
 
     def check(self) -> None:
         """Every page is either free exactly once or held; raises otherwise."""
-        free = list(self._free)
-        if len(set(free)) != len(free):
-            raise CacheAccountingError("a page is on the free list twice")
+        free = set(self._free)
         for p in range(self.num_pages):
-            if (self._ref[p] == 0) != (p in set(free)):
+            if (self._ref[p] == 0) != (p in free):
                 raise CacheAccountingError(f"page {p}: reference count {self._ref[p]} disagrees with the free list")
 
 

@@ -8,8 +8,7 @@ input (gpu_main.cu:50-57); a prompt is a list of token ids separated by spaces o
 commas, since the tokenizer is outside this engine.  Each request's generated ids are
 printed, then the total tokens per second (decoder.cpp:244-251).  What the reference
 fixes in its main (temperature 0, top_k 30, 256 new tokens, seed 42; gpu_main.cu:45-48)
-are named options here with those defaults.  ``enable_prefix_cache`` is accepted for
-compatibility; this engine has no prefix cache and says so when it is set.
+are named options here with those defaults.
 """
 from __future__ import annotations
 
@@ -46,8 +45,6 @@ def main(argv=None) -> int:
     print(f"max_batch={args.max_batch} max_total_tokens={args.max_total_tokens} "
           f"max_prefill_len={args.max_prefill_len} max_prefill_step={args.max_prefill_step} "
           f"enable_prefix_cache={args.enable_prefix_cache}", file=sys.stderr)
-    if args.enable_prefix_cache:
-        print("note: this engine has no prefix cache; enable_prefix_cache is ignored", file=sys.stderr)
 
     prompts = []
     interactive = sys.stdin.isatty()
@@ -67,7 +64,8 @@ def main(argv=None) -> int:
     from .scheduler import SamplingParams
     engine = Engine(args.model, dtype=args.dtype, device=args.device, max_batch=args.max_batch,
                     max_prefill_len=args.max_prefill_len, max_prefill_tokens_per_step=args.max_prefill_step,
-                    max_total_tokens=args.max_total_tokens, page_size=args.page_size, num_pages=args.num_pages)
+                    max_total_tokens=args.max_total_tokens, page_size=args.page_size, num_pages=args.num_pages,
+                    enable_prefix_cache=bool(args.enable_prefix_cache))
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k,
                             max_new_tokens=args.max_new_tokens, seed=args.seed, ignore_eos=args.ignore_eos)
     t0 = time.time()

@@ -26,7 +26,8 @@ class Engine:
                  device="cuda:0", max_batch: int = 64, max_prefill_len: int = 4096,
                  max_prefill_tokens_per_step: int = 512, max_total_tokens: int = 4096,
                  page_size: int = 16, num_pages: Optional[int] = None, kv_memory_fraction: float = 0.8,
-                 max_positions: Optional[int] = None, use_graphs: bool = True):
+                 max_positions: Optional[int] = None, use_graphs: bool = True,
+                 enable_prefix_cache: bool = False):
         """``model``: a folder with config.json and model.safetensors; or give ``config`` (a typed
         configuration) and ``random_seed`` for random weights made on the device.
 
@@ -35,10 +36,12 @@ class Engine:
         gpu_decoder.h:113-119).  ``max_prefill_tokens_per_step``: prompt tokens per step, shared by
         all prefilling requests.  ``max_total_tokens``: most tokens in one step.  ``num_pages``:
         cache pages of ``page_size`` tokens; by default ``kv_memory_fraction`` of the free device
-        memory after the weights, as the reference takes 80 % (gpu_decoder.cu:197-204)."""
+        memory after the weights, as the reference takes 80 % (gpu_decoder.cu:197-204).
+        ``enable_prefix_cache``: requests whose prompts begin alike share the full pages of the common
+        part (the reference's generate_continuous argument, decoder.h:148-154)."""
         self.max_prefill_len = max_prefill_len
         make = dict(dtype=dtype, device=device, page_size=page_size, max_requests=max_batch,
-                    max_positions=max_positions, use_graphs=use_graphs)
+                    max_positions=max_positions, use_graphs=use_graphs, prefix_cache=enable_prefix_cache)
         sizing = _PageSizing(num_pages, kv_memory_fraction, page_size, resolve_dtype(dtype))
         if model is not None:
             self.runner = ModelRunner.from_folder(model, num_pages=sizing, **make)

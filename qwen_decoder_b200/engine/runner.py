@@ -46,7 +46,8 @@ class ModelRunner:
     """A bound model, its cache, and ``step``."""
 
     def __init__(self, model: DecoderModel, config, num_pages: int, page_size: int = 16,
-                 max_requests: int = 64, max_positions: Optional[int] = None, use_graphs: bool = True):
+                 max_requests: int = 64, max_positions: Optional[int] = None, use_graphs: bool = True,
+                 prefix_cache: bool = False):
         self.model = model
         self.config = config
         self.device = model.device
@@ -57,7 +58,7 @@ class ModelRunner:
         if hasattr(num_pages, "resolve"):      # sized from the memory left after the weights
             num_pages = num_pages.resolve(self.layout, self.device, max_requests, self.max_positions)
         self.cache = CacheManager(self.layout, num_pages, page_size, max_requests, dtype=self.dtype,
-                                  device=self.device)
+                                  device=self.device, prefix_cache=prefix_cache)
         from ..sampling import Sampler
         self.sampler = Sampler(self.device)
         self.use_graphs = use_graphs
@@ -89,8 +90,8 @@ class ModelRunner:
         return cls(model, config, **kw)
 
     # ---- requests ----------------------------------------------------------
-    def open(self, request_id) -> RequestCache:
-        return self.cache.open(request_id)
+    def open(self, request_id, tokens=None) -> RequestCache:
+        return self.cache.open(request_id, tokens)
 
     def close(self, rc: RequestCache) -> None:
         self.cache.close(rc)
@@ -135,7 +136,7 @@ class ModelRunner:
                 tokens = self.sampler.sample(logits, *sampling)
             n_tokens = ctx.num_tokens
         for e in entries:
-            self.cache.commit(e.cache, len(e.tokens))
+            self.cache.commit(e.cache, len(e.tokens), e.tokens)
         self.steps += 1
         self.tokens_run += n_tokens
         return logits if sampling is None else (logits, tokens)

@@ -191,12 +191,17 @@ class Scheduler:
             if any(need > free for free in self.cache.free_pages()) or self.cache.slots.num_free == 0:
                 break
             self.waiting.popleft()
-            req.cache = self.cache.open(req.request_id)
+            tokens = req.all_tokens()
+            req.cache = self.cache.open(req.request_id, tokens)    # with the prefix cache: pages of a known beginning
+            req.num_computed = req.cache.num_tokens
             req.admitted_at = self._admissions
             self._admissions += 1
             self.running.append(req)
-            self.cache.ensure(req.cache, n)
-            plan.entries.append(PlannedEntry(req, req.all_tokens()[:n], n == total))
+            n = min(total - req.num_computed, n)
+            self.cache.ensure(req.cache, req.num_computed + n)
+            self.stats["prefix_hit_tokens"] = self.stats.get("prefix_hit_tokens", 0) + req.num_computed
+            plan.entries.append(PlannedEntry(req, tokens[req.num_computed:req.num_computed + n],
+                                             req.num_computed + n == total))
             prompt_budget -= n
             budget -= n
         return plan

@@ -126,3 +126,99 @@ def test_random_orders_lose_no_page(seed):
     for rc in list(live.values()):
         m.close(rc)
     assert m.free_pages() == [12, 12]
+
+
+# ------------------------------------------------------------------ prefix cache
+def prefix_manager(num_pages=12, page_size=4, groups=1):
+    needs = [PagedKV(2, 16)] + ([PagedKV(1, 8)] if groups == 2 else [])
+    lo = CacheLayout.from_needs(needs, [None] * len(needs))
+    return CacheManager(lo, num_pages, page_size, max_requests=4, prefix_cache=True)
+
+
+def feed(m, rc, tokens):
+    m.ensure(rc, rc.num_tokens + len(tokens))
+    m.commit(rc, len(tokens), tokens)
+
+
+def test_prefix_pages_are_shared_exactly_and_leave_one_token():
+    m = prefix_manager(groups=2)
+    a = m.open("a", list(range(100, 111)))           # 11 tokens: nothing cached yet
+    assert a.num_tokens == 0
+    feed(m, a, list(range(100, 111)))                # pages 0 and 1 are full and recorded
+    b = m.open("b", list(range(100, 108)) + [7, 7, 7])
+    assert b.num_tokens == 8 and [t.pages[:2] for t in b.tables] == [t.pages[:2] for t in a.tables]
+    assert all(m.pools[g].ref_count(a.tables[g].pages[0]) == 2 for g in range(2))
+    c = m.open("c", list(range(100, 108)))           # all 8 tokens known: one page stays to be computed
+    assert c.num_tokens == 4
+    d = m.open("d", [100, 101, 102, 999] + list(range(104, 111)))   # differs inside the first page: no hit
+    assert d.num_tokens == 0
+    m.check()
+    for rc in (a, b, c, d):
+        m.close(rc)
+    m.check()
+    assert m.free_pages() == [12, 12]
+
+
+def test_freed_pages_stay_cached_until_they_are_handed_out_again():
+    m = prefix_manager(num_pages=4, page_size=4)
+    a = m.open("a", None)
+    feed(m, a, list(range(8)))                       # two full pages
+    pages = list(a.tables[0].pages)
+    m.close(a)
+    assert m.free_pages() == [4]
+    b = m.open("b", list(range(8)) + [50])           # hit on pages nobody holds: taken back off the free list
+    assert b.num_tokens == 8 and b.tables[0].pages == pages and m.free_pages() == [2]
+    m.close(b)
+    c = m.open("c", None)
+    feed(m, c, [9] * 16)                             # needs all four pages: the cached ones are overwritten
+    m.close(c)
+    d = m.open("d", list(range(8)) + [50])
+    assert d.num_tokens == 0 and not any(k[1] == (0, 1, 2, 3) for k in m.prefix.children)
+    m.close(d)
+    m.check()
+
+
+def test_prefix_cache_is_off_for_windows_and_state():
+    lo = CacheLayout.from_needs([PagedKV(2, 16, 8)], [None])
+    assert CacheManager(lo, 4, 4, 2, prefix_cache=True).prefix is None
+    lo = CacheLayout.from_needs([PagedKV(2, 16), FixedState((3,))], [None, None])
+    assert CacheManager(lo, 4, 4, 2, prefix_cache=True).prefix is None
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_prefix_cache_random_orders_keep_the_books(seed):
+    rng = random.Random(seed)
+    m = prefix_manager(num_pages=10, page_size=4, groups=2)
+    stems = [[rng.randrange(5) for _ in range(12)] for _ in range(3)]
+    live = {}
+    for step in range(500):
+        op = rng.random()
+        if op < 0.3 and len(live) < 4:
+            toks = rng.choice(stems)[:rng.choice([4, 8, 12])] + [rng.randrange(5) for _ in range(rng.randrange(1, 6))]
+            try:
+                rc = m.open(step, toks)
+            except OutOfPages:
+                continue
+            assert rc.num_tokens % 4 == 0 and rc.num_tokens < len(toks) and rc.token_log == toks[:rc.num_tokens]
+            live[step] = (rc, toks)
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            rc, toks = live[rid]
+            n = rng.choice([1, 2, 5])
+            new = toks[rc.num_tokens:rc.num_tokens + n] or [rng.randrange(5)]
+            try:
+                feed(m, rc, new)
+                if rc.num_tokens > len(toks):
+                    toks.extend(new[len(new) - (rc.num_tokens - len(toks)):])
+            except OutOfPages:
+                m.close(live.pop(rid)[0])
+        elif live:
+            m.close(live.pop(rng.choice(list(live)))[0])
+        m.check()
+        # every recorded entry points at pages whose books agree: held by someone or on the free list
+        for e in m.prefix.entries.values():
+            for g, p in enumerate(e.pages):
+                assert m.prefix._by_page[g][p] in m.prefix.entries
+    for rc, _ in list(live.values()):
+        m.close(rc)
+    assert m.free_pages() == [10, 10]

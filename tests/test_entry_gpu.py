@@ -128,3 +128,45 @@ def test_trace_run_program(folders, dtype, tmp_path):
     assert r.stdout.splitlines() == [f"done {s['step']}" for s in tr.steps]
     got = trace_tools.read_outputs(tr, str(out), cfg["vocab_size"])
     trace_tools.compare(tr, got, want, 1e-5 if dtype == "float32" else 3e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefix_cache_shares_pages_and_keeps_logits(folders, dtype, tmp_path):
+    """Requests with a common beginning: with the prefix cache the later ones skip the shared full pages,
+    their logits still equal the plain implementation's, and generation gives the same tokens."""
+    from qwen_decoder_b200.engine import Engine, ModelRunner, SamplingParams, StepEntry
+    cfg, w = plain_model.read_folder(folders["A"])
+    stem = prompts_for(cfg, [70], seed=5)[0]
+    tails = prompts_for(cfg, [9, 3, 20], seed=6)
+    seqs = [stem + t for t in tails]
+    want = [plain_model.forward(cfg, w, s).numpy() for s in seqs]
+    runner = ModelRunner.from_folder(folders["A"], dtype=dtype, device="cuda:0", num_pages=24, page_size=16,
+                                     max_requests=4, prefix_cache=True)
+    tol = 1e-5 if dtype == "float32" else 3e-2
+    scale = max(float(np.abs(x).max()) for x in want)
+    skipped = []
+    live = []
+    for i, s in enumerate(seqs):
+        rc = runner.open(f"r{i}", s)
+        skipped.append(rc.num_tokens)
+        rest = s[rc.num_tokens:]
+        logits = runner.step([StepEntry(rc, rest, list(range(len(rest))))]).cpu().numpy()
+        err = float(np.abs(logits - want[i][rc.num_tokens:]).max())
+        assert err <= tol * scale, (i, err)
+        live.append(rc)
+        if i == 1:
+            runner.close(live.pop(0))            # the first request ends; its pages stay cached
+    assert skipped == [0, 64, 64]                # four full pages of the 70-token stem are shared
+    runner.cache.check()
+    for rc in live:
+        runner.close(rc)
+    assert runner.cache.free_pages() == [24]
+    # through the entry point: same tokens with and without the cache, fewer prompt tokens computed
+    sp = SamplingParams(max_new_tokens=6)
+    outs = {}
+    for on in (False, True):
+        eng = Engine(folders["A"], dtype=dtype, num_pages=40, max_batch=2, enable_prefix_cache=on)
+        outs[on] = (eng.generate(seqs, sp), eng.stats)
+    assert outs[False][0] == outs[True][0]
+    assert outs[True][1]["prompt_tokens"] < outs[False][1]["prompt_tokens"]
+    assert outs[True][1].get("prefix_hit_tokens", 0) >= 64

@@ -146,3 +146,35 @@ def test_max_positions_ends_a_request():
     run(s, [a, b])
     assert a.finish_reason == "max_positions" and len(a.prompt) + len(a.output) == 12
     assert b.finish_reason == "too_long"
+
+
+def test_prefix_cache_skips_known_beginnings_and_keeps_the_output():
+    layout = CacheLayout.from_needs([PagedKV(2, 16)], [None])
+
+    def run_with(prefix):
+        cache = CacheManager(layout, 64, 16, 8, prefix_cache=prefix)
+        s = Scheduler(cache, max_batch=2, max_prefill_tokens_per_step=512)
+        stem = list(range(1, 41))
+        reqs = [Request(i, stem + [100 + i, 200 + i], SamplingParams(max_new_tokens=4)) for i in range(4)]
+        for r in reqs:
+            s.add_request(r)
+        while s.has_work():
+            plan = s.schedule()
+            sampled = []
+            for e in plan.entries:
+                req = e.request
+                assert e.tokens == req.all_tokens()[req.num_computed:req.num_computed + len(e.tokens)]
+                cache.commit(req.cache, len(e.tokens), e.tokens)
+                if e.samples:
+                    sampled.append(next_token(req.all_tokens()))
+            s.update(plan, sampled)
+            cache.check()
+        return reqs, s
+
+    plain, s0 = run_with(False)
+    cached, s1 = run_with(True)
+    assert [r.output for r in plain] == [r.output for r in cached]
+    assert s0.stats["prompt_tokens"] == 4 * 42
+    # requests 2 and 3 start after 0 and 1 have cached the 32 tokens of the stem's two full pages
+    assert s1.stats["prefix_hit_tokens"] >= 2 * 32 and s1.stats["prompt_tokens"] == 4 * 42 - s1.stats["prefix_hit_tokens"]
+    assert s1.cache.free_pages() == [64]
