@@ -148,10 +148,11 @@ def test_prefix_cache_shares_pages_and_keeps_logits(folders, dtype, tmp_path):
     live = []
     for i, s in enumerate(seqs):
         rc = runner.open(f"r{i}", s)
-        skipped.append(rc.num_tokens)
-        rest = s[rc.num_tokens:]
+        start = rc.num_tokens
+        skipped.append(start)
+        rest = s[start:]
         logits = runner.step([StepEntry(rc, rest, list(range(len(rest))))]).cpu().numpy()
-        err = float(np.abs(logits - want[i][rc.num_tokens:]).max())
+        err = float(np.abs(logits - want[i][start:]).max())
         assert err <= tol * scale, (i, err)
         live.append(rc)
         if i == 1:
