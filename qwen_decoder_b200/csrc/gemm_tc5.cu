@@ -51,11 +51,13 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
 // true when the phase with this parity has completed; false after TC_SPIN_LIMIT polls, or at once
 // when a wait of this CTA has already run out (*dead set): then nobody spins again, every role runs
 // on to its end without leaving early, the kernel ends and the host sees a non-zero status.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead,
+                                          unsigned backoff_ns = 0) {
   unsigned addr = smem_u32(bar);
   if (*dead) return false;
   unsigned long long start = 0;
   for (unsigned spin = 0; spin < TC_SPIN_LIMIT; spin++) {
+    if (backoff_ns && spin) __nanosleep(backoff_ns);     // long waits of many threads: leave the issue slots alone
     unsigned ok;
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -75,6 +77,11 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// plain bulk copy of ``bytes`` contiguous bytes (16-byte aligned) onto the same kind of mbarrier
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes with the 128-byte
 // swizzle, as the TMA copies above leave it: rows of 8 form groups 1024 bytes apart.
@@ -115,15 +122,22 @@ struct TcParams {
   int stages;             // shared-memory stages in the ring
   int kbs;                // 64-wide k blocks per stage (several: long contiguous reads of each weight row)
   int acc_cols;           // TMEM columns of one accumulator buffer
+  int nacc;               // independent accumulators per buffer, used round-robin over the k-steps and added in
+                          // the epilogue: back-to-back MMAs into one accumulator wait for each other (about 220
+                          // cycles each at N = 16), MMAs into different accumulators overlap
+  int set_cols;           // TMEM columns of one accumulator set (BN, or 2 BN for SwiGLU)
   int tmem_cols;          // TMEM columns allocated (power of two >= 32)
   long long ldo;          // row stride of out, elements
+  int debug;              // 1: skip the MMAs (timing experiments only: results are void)
+  int w_tiled;            // W is stored tile by tile: [feature tile][k block][128][64], each tile one 16 KB run
+  int w_up_tile0;         // SwiGLU with tiled W: index of the first feature tile of the up half
 };
 
 template <int EPI, typename TO>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                const float* __restrict__ bias, TO* __restrict__ out, float* __restrict__ part,
-                const TcParams p, int* __restrict__ status) {
+                const bf16* __restrict__ w_tiles, const float* __restrict__ bias, TO* __restrict__ out,
+                float* __restrict__ part, const TcParams p, int* __restrict__ status) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   __shared__ unsigned long long full_bar[TC_MAX_STAGES], empty_bar[TC_MAX_STAGES], acc_ready[2], acc_free[2];
   __shared__ unsigned tmem_base_slot;
@@ -177,8 +191,16 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       // sub-block j of stage s holds k block kb: [A (gate) | A (up, SwiGLU only) | B]
       auto load_a = [&](unsigned s, int j, int ft, int kb) {
         unsigned char* st = tiles + (size_t)s * stage_bytes + (size_t)j * blk_bytes;
-        tma_load_2d(st, &map_w, kb * TC_BK, ft * TC_BM, &full_bar[s]);
-        if (EPI == EPI_SWIGLU) tma_load_2d(st + a_bytes, &map_w, kb * TC_BK, F + ft * TC_BM, &full_bar[s]);
+        if (p.w_tiled) {
+          // the tile is stored as its shared-memory image (swizzle applied): one contiguous 16 KB copy
+          const unsigned char* wt = reinterpret_cast<const unsigned char*>(w_tiles);
+          bulk_load(st, wt + (size_t)(ft * kb_total + kb) * a_bytes, a_bytes, &full_bar[s]);
+          if (EPI == EPI_SWIGLU)
+            bulk_load(st + a_bytes, wt + (size_t)((p.w_up_tile0 + ft) * kb_total + kb) * a_bytes, a_bytes, &full_bar[s]);
+        } else {
+          tma_load_2d(st, &map_w, kb * TC_BK, ft * TC_BM, &full_bar[s]);
+          if (EPI == EPI_SWIGLU) tma_load_2d(st + a_bytes, &map_w, kb * TC_BK, F + ft * TC_BM, &full_bar[s]);
+        }
       };
       auto load_b = [&](unsigned s, int j, int tt, int kb) {
         tma_load_2d(tiles + (size_t)s * stage_bytes + (size_t)j * blk_bytes + A_TILES * a_bytes, &map_x, kb * TC_BK,
@@ -212,8 +234,13 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // One thread issues every MMA of the CTA, so its instruction count per MMA bounds the tensor rate:
+    // descriptors are one 64-bit add apart (32 bytes of k = 2 units of 16 bytes), nothing is divided.
     if (lane == 0) {
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(p.BN >> 3) << 17) | ((unsigned)(TC_BM >> 4) << 24);
+      const unsigned long long desc_hi = smem_desc_sw128(0);       // everything but the start address
+      const unsigned tiles_addr = smem_u32(tiles);
+      const unsigned set_cols = p.set_cols, nacc = p.nacc;
       unsigned it = 0, n_done = 0;
       for (int item = blockIdx.x; item < n_items; item += gridDim.x, n_done++) {
         int ft, tt, kb0, kb1;
@@ -222,20 +249,26 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (!mbar_wait(&acc_free[buf], (use & 1) ^ 1, &dead)) atomicExch(status, 3);   // epilogue has drained it
         tc_fence_after();
         const unsigned d0 = tmem_base + buf * p.acc_cols;
+        unsigned d = d0, acc_i = 0, fresh = nacc;     // accumulators still unwritten in this item
         for (int kb = kb0; kb < kb1; kb += p.kbs, it++) {
           const unsigned s = it % p.stages, ph = (it / p.stages) & 1;
           if (!mbar_wait(&full_bar[s], ph, &dead)) atomicExch(status, 2);
           tc_fence_after();
           const int nb = min(p.kbs, kb1 - kb);
-          for (int j = 0; j < nb; j++) {
-            const unsigned a_addr = smem_u32(tiles + (size_t)s * stage_bytes + (size_t)j * blk_bytes);
-            const unsigned b_addr = a_addr + A_TILES * a_bytes;
+          unsigned a_addr = tiles_addr + s * (unsigned)stage_bytes;
+          if (p.debug == 1) { mbar_arrive(&empty_bar[s]); continue; }
+          for (int j = 0; j < nb; j++, a_addr += (unsigned)blk_bytes) {
+            const unsigned long long da = desc_hi | (unsigned long long)((a_addr & 0x3FFFF) >> 4);
+            const unsigned long long du = desc_hi | (unsigned long long)(((a_addr + a_bytes) & 0x3FFFF) >> 4);
+            const unsigned long long db = desc_hi | (unsigned long long)(((a_addr + A_TILES * a_bytes) & 0x3FFFF) >> 4);
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; k++) {
-              const unsigned acc = (kb + j > kb0 || k > 0) ? 1u : 0u;
-              const unsigned long long db = smem_desc_sw128(b_addr + k * 32);
-              umma_bf16(d0, smem_desc_sw128(a_addr + k * 32), db, idesc, acc);
-              if (EPI == EPI_SWIGLU) umma_bf16(d0 + p.BN, smem_desc_sw128(a_addr + a_bytes + k * 32), db, idesc, acc);
+              const unsigned accf = fresh ? 0u : 1u;            // the first use of an accumulator overwrites it
+              umma_bf16(d, da + 2 * k, db + 2 * k, idesc, accf);
+              if (EPI == EPI_SWIGLU) umma_bf16(d + p.BN, du + 2 * k, db + 2 * k, idesc, accf);
+              if (fresh) fresh--;
+              d += set_cols;
+              if (++acc_i == nacc) { acc_i = 0; d = d0; }
             }
           }
           umma_commit(&empty_bar[s]);        // the stage is free once these MMAs have read it
@@ -251,26 +284,36 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
       int ft, tt, kb0, kb1;
       const int sp = decode(item, ft, tt, kb0, kb1);
       const unsigned buf = n_done & 1, use = n_done >> 1;
-      if (!mbar_wait(&acc_ready[buf], use & 1, &dead) && lane == 0) atomicExch(status, 4);
+      if (!mbar_wait(&acc_ready[buf], use & 1, &dead, 256) && lane == 0) atomicExch(status, 4);
       tc_fence_after();
       const int feature = ft * TC_BM + lane_base + lane;           // within a half for SwiGLU
       const int n_feat = EPI == EPI_SWIGLU ? F : p.N;
       const float bv = (EPI == EPI_STORE && bias && feature < n_feat) ? bias[feature] : 0.f;
       const unsigned t0 = tmem_base + ((unsigned)lane_base << 16) + buf * p.acc_cols;
+      const int n_used = min(p.nacc, (kb1 - kb0) * (TC_BK / 16));    // accumulators this item wrote
       for (int c = 0; c < p.BN; c += 16) {
-        unsigned v[16], u[16];
-        tmem_ld16(t0 + c, v);
-        if (EPI == EPI_SWIGLU) tmem_ld16(t0 + p.BN + c, u);
-        tmem_ld_wait();
+        float v[16], u[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) { v[i] = 0.f; u[i] = 0.f; }
+        for (int a = 0; a < n_used; a++) {
+          unsigned r[16], q[16];
+          tmem_ld16(t0 + a * p.set_cols + c, r);
+          if (EPI == EPI_SWIGLU) tmem_ld16(t0 + a * p.set_cols + p.BN + c, q);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; i++) {
+            v[i] += __uint_as_float(r[i]);
+            if (EPI == EPI_SWIGLU) u[i] += __uint_as_float(q[i]);
+          }
+        }
         if (feature < n_feat) {
 #pragma unroll
           for (int i = 0; i < 16; i++) {
             const int tok = tt * p.BN + c + i;
             if (tok < p.T) {
-              float a = __uint_as_float(v[i]);
+              float a = v[i];
               if (EPI == EPI_SWIGLU) {
-                float up = __uint_as_float(u[i]);
-                out[(size_t)tok * p.ldo + feature] = from_float<TO>(a / (1.0f + expf(-a)) * up);
+                out[(size_t)tok * p.ldo + feature] = from_float<TO>(a / (1.0f + expf(-a)) * u[i]);
               } else if (EPI == EPI_PARTIAL) {
                 part[((size_t)sp * p.T + tok) * p.N + feature] = a;
               } else {
@@ -341,9 +384,12 @@ static int* status_word() {
 // over ``splits`` shares of K; epi 2: W = [gate rows; up rows] of shape [2F, K] (F a multiple of 128 is not
 // required), out[T, F] = silu(X Wg^T) * (X Wu^T) in bfloat16.  X rows are ldx elements apart, out rows ldo.
 // K a multiple of 8, ldx a multiple of 8, W and X 16-byte aligned.  max_ctas bounds the persistent grid.
+// w_tiled: W is given tile by tile, [ceil(N/128)][ceil(K/64)][128][64] zero-padded, each tile stored as its
+// shared-memory image with the 128-byte swizzle applied (see ``tile_weight`` in kernels.py): a tile then arrives
+// with one contiguous 16 KB bulk copy instead of a TMA box of 128 rows x 128 bytes.
 extern "C" int qd_gemm_tc5(const void* W, const void* X, long long ldx, const float* bias, void* out, int out_dtype,
                            long long ldo, float* part, int T, int N, int K, int splits, int epi, int max_ctas,
-                           cudaStream_t stream) {
+                           int w_tiled, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || splits < 1 || max_ctas < 1) return QD_ERR_UNSUPPORTED;
   if (((uintptr_t)W & 15) || ((uintptr_t)X & 15)) return QD_ERR_UNSUPPORTED;
@@ -367,28 +413,44 @@ extern "C" int qd_gemm_tc5(const void* W, const void* X, long long ldx, const fl
   // few tokens: the product is bound by reading W, and DRAM likes long runs: four k blocks (512 bytes
   // of every weight row) per stage; many tokens: one k block per stage, more stages
   p.kbs = T <= 64 ? 4 : 1;
+  int min_stages = 3;
+  int smem_budget = 200 * 1024;
+  if (const char* e = getenv("QD_TC5_KBS")) { p.kbs = atoi(e); min_stages = 1; }
+  if (const char* e = getenv("QD_TC5_SMEM_KB")) smem_budget = atoi(e) * 1024;
   if (p.kbs > (kb_total + splits - 1) / splits) p.kbs = (kb_total + splits - 1) / splits;
-  while (p.kbs > 1 && (200 * 1024) / (p.kbs * blk_bytes) < 3) p.kbs /= 2;     // keep at least three stages
+  while (p.kbs > 1 && smem_budget / (p.kbs * blk_bytes) < min_stages) p.kbs /= 2;     // keep at least three stages
   const int stage_bytes = p.kbs * blk_bytes;
-  p.stages = (200 * 1024) / stage_bytes;
+  p.stages = smem_budget / stage_bytes;
   if (p.stages > TC_MAX_STAGES) p.stages = TC_MAX_STAGES;
-  if (p.stages < 2) return QD_ERR_UNSUPPORTED;
-  p.acc_cols = a_tiles * p.BN < 32 ? 32 : a_tiles * p.BN;
+  if (p.stages < 1) return QD_ERR_UNSUPPORTED;
+  p.set_cols = a_tiles * p.BN;
+  p.nacc = 4;
+  if (const char* e = getenv("QD_TC5_NACC")) p.nacc = atoi(e);
+  while (p.nacc > 1 && 2 * p.nacc * p.set_cols > 512) p.nacc /= 2;
+  if (p.nacc < 1) p.nacc = 1;
+  p.acc_cols = p.nacc * p.set_cols < 32 ? 32 : p.nacc * p.set_cols;
   int cols = 2 * p.acc_cols;
   p.tmem_cols = 32;
   while (p.tmem_cols < cols) p.tmem_cols *= 2;
   if (p.tmem_cols > 512) return QD_ERR_UNSUPPORTED;
 
   CUtensorMap map_w, map_x;
-  if (!make_map(&map_w, W, N, K, K, TC_BM) || !make_map(&map_x, X, T, K, ldx, p.BN)) return QD_ERR_UNSUPPORTED;
+  p.w_tiled = w_tiled;
+  p.debug = 0;
+  if (const char* e = getenv("QD_TC5_DEBUG")) p.debug = atoi(e);
+  p.w_up_tile0 = p.n_ftiles;
+  // tiled W: tile (ft, kb) is the 16 KB at ((ft * kb_total + kb) * 16 KB); SwiGLU: the gate half's tiles, then the
+  // up half's (each half padded to whole tiles); no tensor map is needed for it (map_w then describes X as well)
+  bool ok_w = w_tiled ? make_map(&map_w, X, T, K, ldx, p.BN) : make_map(&map_w, W, N, K, K, TC_BM);
+  if (!ok_w || !make_map(&map_x, X, T, K, ldx, p.BN)) return QD_ERR_UNSUPPORTED;
   const long long n_items = (long long)p.n_ftiles * p.n_ttiles * splits;
   const int grid = (int)(n_items < max_ctas ? n_items : max_ctas);
   const size_t smem = (size_t)p.stages * stage_bytes + 1024;
 #define LAUNCH(E, TO)                                                                                        \
   do {                                                                                                       \
     cudaFuncSetAttribute(gemm_tc5_kernel<E, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    qd_launch(gemm_tc5_kernel<E, TO>, dim3(grid), dim3(TC_THREADS), smem, stream, map_w, map_x, bias, (TO*)out, \
-              part, p, status);                                                                              \
+    qd_launch(gemm_tc5_kernel<E, TO>, dim3(grid), dim3(TC_THREADS), smem, stream, map_w, map_x,               \
+              (const bf16*)W, bias, (TO*)out, part, p, status);                                              \
   } while (0)
   if (epi == EPI_SWIGLU) {
     if (out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;

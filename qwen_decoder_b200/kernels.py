@@ -227,7 +227,29 @@ def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
 # csrc/gemm_stream.cu) or "regs" (one wave of CTAs loading straight into registers, csrc/gemm_skinny.cu).
 skinny_impl = _os.environ.get("QD_SKINNY_IMPL", "stream")
 STREAM_MAX_CTAS = 296          # two persistent CTAs on each of 148 SMs
-TC5_MAX_CTAS = 148             # the tcgen05 kernel runs one persistent CTA per SM
+TC5_MAX_CTAS = int(_os.environ.get("QD_TC5_CTAS", "148"))   # the tcgen05 kernel runs one persistent CTA per SM
+
+
+def tile_weight(w: torch.Tensor, halves: int = 1) -> torch.Tensor:
+    """W [N, K] bfloat16 -> [ceil(N/128) * ceil(K/64), 128, 64], zero-padded, each tile stored as the
+    shared-memory image the tensor cores read (rows of 128 bytes; the 16-byte piece c of row r sits at
+    piece c ^ (r % 8): the 128-byte swizzle): ``gemm_tc5`` fetches a tile with one contiguous 16 KB copy.
+    ``halves`` = 2 tiles the gate and the up half of a stacked [2F, K] matrix separately (gate tiles
+    first), as the SwiGLU epilogue wants them."""
+    N, K = w.shape
+    parts = w.chunk(halves, dim=0)
+    out = []
+    for part in parts:
+        n = part.shape[0]
+        nt, kt = (n + 127) // 128, (K + 63) // 64
+        padded = torch.zeros((nt * 128, kt * 64), dtype=w.dtype, device=w.device)
+        padded[:n, :K] = part
+        tiles = padded.view(nt, 128, kt, 64).permute(0, 2, 1, 3).contiguous().view(nt * kt, 128, 8, 8)
+        r = torch.arange(128, device=w.device).view(128, 1)
+        c = torch.arange(8, device=w.device).view(1, 8)
+        src = (c ^ (r & 7)).view(1, 128, 8, 1).expand(tiles.shape[0], 128, 8, 8)    # piece at position p holds piece p ^ (r % 8)
+        out.append(torch.gather(tiles, 2, src).view(nt * kt, 128, 64))
+    return torch.cat(out, dim=0).contiguous()
 
 
 def gemm_tc5_status() -> int:
@@ -235,14 +257,14 @@ def gemm_tc5_status() -> int:
     return int(library("gemm_tc5").qd_gemm_tc5_status())
 
 
-def _skinny_call(x, w, bias, out, part, T, N, K, splits, epi, what):
+def _skinny_call(x, w, bias, out, part, T, N, K, splits, epi, what, w_tiled=False):
     out_code = dtype_code(out.dtype) if out is not None else F32
     ldo = out.stride(0) if out is not None else 0
     impl = few_token_impl(T) or "tc5"
     if impl == "tc5":
         _check(library("gemm_tc5").qd_gemm_tc5(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
-            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(TC5_MAX_CTAS), _stream()), what)
+            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(TC5_MAX_CTAS), _I(1 if w_tiled else 0), _stream()), what)
     elif impl == "stream":
         _check(library("gemm_stream").qd_gemm_stream(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),

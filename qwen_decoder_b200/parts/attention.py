@@ -90,9 +90,14 @@ class GQAttention(Mixer):
         return self.out.forward_partial(attn)
 
 
-def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = 296) -> int:
-    """How many CTAs share one (request, kv head) in decode attention: enough to fill the GPU
-    (two CTAs on each of 148 SMs), but no CTA with fewer than four 16-key chunks."""
-    by_fill = max(1, target_ctas // max(1, ctas_without_split))
+import os as _os
+_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ATTN_CTAS", "148"))
+
+
+def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = _TARGET_CTAS) -> int:
+    """How many CTAs share one (request, kv head) in decode attention: enough for one CTA on each of
+    the 148 SMs (more splits cost more in the combine than they gain: measured in whole decode steps at
+    batch 1, 8 and 64), but no CTA with fewer than four 16-key chunks."""
+    by_fill = max(1, -(-target_ctas // max(1, ctas_without_split)))
     by_work = max(1, (max_keys + 63) // 64)
     return max(1, min(by_fill, by_work, 64))
