@@ -128,7 +128,6 @@ struct TcParams {
   int set_cols;           // TMEM columns of one accumulator set (BN, or 2 BN for SwiGLU)
   int tmem_cols;          // TMEM columns allocated (power of two >= 32)
   long long ldo;          // row stride of out, elements
-  int debug;              // 1: skip the MMAs (timing experiments only: results are void)
   int w_tiled;            // W is stored tile by tile: [feature tile][k block][128][64], each tile one 16 KB run
   int w_up_tile0;         // SwiGLU with tiled W: index of the first feature tile of the up half
 };
@@ -256,7 +255,6 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
           tc_fence_after();
           const int nb = min(p.kbs, kb1 - kb);
           unsigned a_addr = tiles_addr + s * (unsigned)stage_bytes;
-          if (p.debug == 1) { mbar_arrive(&empty_bar[s]); continue; }
           for (int j = 0; j < nb; j++, a_addr += (unsigned)blk_bytes) {
             const unsigned long long da = desc_hi | (unsigned long long)((a_addr & 0x3FFFF) >> 4);
             const unsigned long long du = desc_hi | (unsigned long long)(((a_addr + a_bytes) & 0x3FFFF) >> 4);
@@ -436,8 +434,6 @@ extern "C" int qd_gemm_tc5(const void* W, const void* X, long long ldx, const fl
 
   CUtensorMap map_w, map_x;
   p.w_tiled = w_tiled;
-  p.debug = 0;
-  if (const char* e = getenv("QD_TC5_DEBUG")) p.debug = atoi(e);
   p.w_up_tile0 = p.n_ftiles;
   // tiled W: tile (ft, kb) is the 16 KB at ((ft * kb_total + kb) * 16 KB); SwiGLU: the gate half's tiles, then the
   // up half's (each half padded to whole tiles); no tensor map is needed for it (map_w then describes X as well)
