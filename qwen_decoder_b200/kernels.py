@@ -394,3 +394,43 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _contig(logits, "logits")
     _check(library("sampling").qd_sample(_ptr(logits), _I(R), _I(V), _ptr(temperature), _ptr(top_k),
                                          _ptr(draws), _ptr(out), _stream()), "sample")
+
+
+# ------------------------------------------------------------------ a whole decode step in one kernel
+class FusedLayer(ctypes.Structure):
+    """One schedule entry of the fused decode step (FdLayer in csrc/decode_fused.cu)."""
+    _fields_ = [("norm1_w", ctypes.c_void_p), ("eps1", ctypes.c_float),
+                ("wqkv", ctypes.c_void_p), ("bqkv", ctypes.c_void_p), ("wo", ctypes.c_void_p),
+                ("norm2_w", ctypes.c_void_p), ("eps2", ctypes.c_float),
+                ("wgu", ctypes.c_void_p), ("wd", ctypes.c_void_p), ("kv", ctypes.c_void_p)]
+
+
+class FusedParams(ctypes.Structure):
+    """Arguments of the fused decode step (FdParams in csrc/decode_fused.cu)."""
+    _fields_ = [(n, ctypes.c_int) for n in ("T", "D", "H", "G", "d", "F", "V", "L")] + \
+        [(n, ctypes.c_void_p) for n in ("x", "qkv", "attn_out", "h", "part_o", "part_ml", "tickets",
+                                        "scratch", "gemm_tickets")] + \
+        [("scratch_floats", ctypes.c_int), ("n_gemm_tickets", ctypes.c_int)] + \
+        [(n, ctypes.c_void_p) for n in ("positions", "token_req", "block_table", "slot_map")] + \
+        [(n, ctypes.c_int) for n in ("max_blocks", "page_size", "splits", "window")] + \
+        [("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p), ("rotary_dim", ctypes.c_int),
+         ("pairing", ctypes.c_int), ("scale_log2e", ctypes.c_float), ("layers", ctypes.c_void_p),
+         ("final_w", ctypes.c_void_p), ("final_eps", ctypes.c_float), ("lm_head", ctypes.c_void_p),
+         ("logits", ctypes.c_void_p), ("barrier", ctypes.c_void_p), ("status", ctypes.c_void_p),
+         ("host_status", ctypes.c_void_p), ("timeline", ctypes.c_void_p)]
+
+
+def fused_decode_struct_sizes_match() -> bool:
+    lib = library("decode_fused")
+    return (lib.qd_decode_fused_param_bytes() == ctypes.sizeof(FusedParams)
+            and lib.qd_decode_fused_layer_bytes() == ctypes.sizeof(FusedLayer))
+
+
+_FUSED_MAX_CTAS = int(_os.environ.get("QD_FUSED_CTAS", "100000"))
+
+
+def decode_step_fused(params: FusedParams) -> None:
+    """All layers, the final norm and the output projection of a decode step of at most 16 tokens in
+    one cooperative launch; raises KernelError(unsupported) for sizes the kernel does not take."""
+    _check(library("decode_fused").qd_decode_step_fused(ctypes.byref(params), _I(_FUSED_MAX_CTAS), _stream()),
+           "decode_step_fused")

@@ -55,6 +55,17 @@ class GQAttention(Mixer):
         self.qkv.bind(source, dtype, device)
         self.out.bind(source, dtype, device)
 
+    def fused_decode_params(self):
+        from .rotary import Rotary
+        pos = self.position
+        if self.out.bias is not None or not (pos is None or type(pos) is Rotary):
+            return None
+        return {"D": self.hidden_size, "H": self.num_heads, "G": self.num_kv_heads, "d": self.head_dim,
+                "window": self.window, "scale": self.scale, "position": pos,
+                "rotary_dim": pos.rotary_dim if pos is not None else 0,
+                "pairing": pos.pairing_code if pos is not None else 0,
+                "wqkv": self.qkv.weight, "bqkv": self.qkv.bias, "wo": self.out.weight}
+
     def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
         H, G, d = self.num_heads, self.num_kv_heads, self.head_dim
         pos = self.position

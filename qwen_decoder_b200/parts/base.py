@@ -33,6 +33,11 @@ class Part:
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
         pass
 
+    def fused_decode_params(self) -> Optional[dict]:
+        """The part's tensors and constants, if a fused decode kernel may stand in for its
+        ``forward`` (see ``parts/fused_decode.py``); None, the default, keeps the part's own path."""
+        return None
+
 
 class ResidualStream:
     """The residual sum of a step: ``x`` float32 [T, D], and a branch output ``delta`` that has

@@ -37,6 +37,19 @@ class PreNormBlock(Block):
         for p in self.parts():
             p.bind(source, dtype, device)
 
+    def fused_decode_params(self):
+        n1, mx = self.input_norm.fused_decode_params(), self.mixer.fused_decode_params()
+        n2, ff = self.post_mixer_norm.fused_decode_params(), self.feed_forward.fused_decode_params()
+        if None in (n1, mx, n2, ff) or not all(k in mx for k in ("wqkv", "wo", "H", "G", "d")) \
+                or not all(k in ff for k in ("wgu", "wd", "F")) or "weight" not in n1 or "weight" not in n2:
+            return None
+        if not (n1["size"] == n2["size"] == mx["D"] == ff["D"]):
+            return None
+        out = dict(mx)
+        out.update(F=ff["F"], wgu=ff["wgu"], wd=ff["wd"], norm1_w=n1["weight"], eps1=n1["eps"],
+                   norm2_w=n2["weight"], eps2=n2["eps"])
+        return out
+
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         h = self.input_norm.forward(stream, self.dtype)
         stream.push(self.mixer.forward(h, ctx, cache))

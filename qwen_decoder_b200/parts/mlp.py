@@ -32,6 +32,10 @@ class SwiGLU(FeedForward):
         self.gate_up.bind(source, dtype, device)
         self.down.bind(source, dtype, device)
 
+    def fused_decode_params(self):
+        return {"D": self.hidden_size, "F": self.intermediate_size, "wgu": self.gate_up.weight,
+                "wd": self.down.weight}
+
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if matmul_backend.use_skinny(x, self.gate_up.weight):

@@ -389,3 +389,36 @@ def test_gemm_tcgen05_many_tokens(shape, monkeypatch):
         kernels.gemm_skinny_swiglu(x.to(DEV), w.to(DEV), h)
         close(h, plain_model.silu(want[:, :N // 2]) * want[:, N // 2:], torch.bfloat16)
     assert kernels.gemm_tc5_status() == 0
+
+
+# ---- the whole decode step as one cooperative kernel (opt-in path) against the unfused kernels
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("batch", [1, 5, 13])
+def test_fused_decode_step_matches_unfused(name, batch):
+    from tiny_configs import TINY
+    from qwen_decoder_b200.config import Qwen2Config
+    from qwen_decoder_b200.engine.batch import StepEntry
+    from qwen_decoder_b200.engine.runner import ModelRunner
+    from qwen_decoder_b200.parts.fused_decode import FusedDecode
+    cfg = Qwen2Config.from_dict(TINY[name])
+    outs = []
+    for fused in (False, True):
+        r = ModelRunner.from_random(cfg, seed=3, dtype="bfloat16", num_pages=128, page_size=16,
+                                    max_requests=16, use_graphs=False)
+        r.model.fused_decode = FusedDecode.try_build(r.model, force=True) if fused else None
+        assert (r.model.fused_decode is not None) == fused
+        g = torch.Generator().manual_seed(batch)
+        rcs = [r.open(i) for i in range(batch)]
+        prompts = [torch.randint(0, cfg.vocab_size, (7 + 5 * i,), generator=g).tolist() for i in range(batch)]
+        r.step([StepEntry(rc, p, []) for rc, p in zip(rcs, prompts)])
+        seq = []
+        for _ in range(20):          # crosses page edges (16) for several requests
+            toks = torch.randint(0, cfg.vocab_size, (batch,), generator=g).tolist()
+            seq.append(r.step([StepEntry(rc, [t], [0]) for rc, t in zip(rcs, toks)]).float().cpu())
+        if fused:
+            r.model.fused_decode.check_status()
+        outs.append(torch.stack(seq))
+    a, b = outs
+    assert torch.isfinite(b).all()
+    assert (a - b).abs().max().item() <= 3e-2 * a.abs().max().item()
