@@ -1,0 +1,424 @@
+// Decode attention for a few tokens that starts from what the few-token contraction leaves: float32
+// partial sums of q, k and v.  One kernel adds them up with the bias, rotates q and k by position,
+// writes the token's k and v to its cache slot and attends over the paged cache -- the work of
+// rope_kv_write_partial (elementwise.cu) and decode_attention (attention_flash.cu) in one launch, with
+// one CTA of 8 warps per (token, kv head, split) and every warp's first 16-key chunk requested before
+// the kernel waits for its predecessor.  Formulas: gpu_kernels.cu:82-133 (rotation, cache write) and
+// :223-311 (attention) of the reference; softmax, rotation and sums in float32.
+#include "common.cuh"
+#include <math.h>
+
+#define AR_WARPS 8
+#define AR_THREADS (AR_WARPS * 32)
+#define AR_PAD 8
+
+struct ArParams {
+  const float* part; int n_parts;      // [n_parts, T, (H + 2G) d] float32
+  const float* bias;                   // [(H + 2G) d] or null
+  bf16* out;                           // [T, H d]
+  bf16* kv;                            // [pages, 2, G, page_size, d]
+  const int* block_table; int max_blocks;
+  const int* token_req; const int* positions; const int* slot_map;
+  int T, H, G, page_size, window, splits, write_kv;
+  const float* cos_t; const float* sin_t; int rotary_dim, pairing; float scale_log2e;
+  float* part_o; float* part_ml; unsigned* tickets;
+  long long* timeline;                 // null, or 16 nanosecond stamps per CTA (for measurements)
+};
+
+__device__ __forceinline__ void ar_stamp(const ArParams& p, int i) {
+  if (p.timeline && threadIdx.x == 0) {
+    long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    p.timeline[(size_t)blockIdx.x * 16 + i] = now;
+  }
+}
+__device__ __forceinline__ void ar_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                       unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ar_cp_async16(void* smem, const void* gmem, int src_bytes) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(src_bytes));
+}
+__device__ __forceinline__ void ar_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ar_ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ unsigned ar_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ float ar_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(const ArParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int LD = HD + AR_PAD;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = p.H, G = p.G, gs = H / G, Nqkv = (H + 2 * G) * HD;
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);                       // [16][LD] rotated q of the group
+  bf16* kvs = qs + 16 * LD;                                           // per warp: K chunk, V chunk [16][LD] each
+  float* mm = reinterpret_cast<float*>(kvs + (size_t)AR_WARPS * 2 * 16 * LD);   // merge: [warps][16]
+  float* ml = mm + AR_WARPS * 16;                                     // [warps][16]
+  float* fac = ml + AR_WARPS * 16;                                    // combine: [16][64] x 3
+  bf16* newkv = reinterpret_cast<bf16*>(fac + 3 * 16 * 64);          // the token's own k and v: [2][HD]
+  __shared__ unsigned s_ticket;
+  const size_t page_elems = (size_t)2 * G * p.page_size * HD;
+  const int half = p.rotary_dim >> 1;
+
+  {
+    ar_stamp(p, 0);
+    const int item = blockIdx.x;
+    const int s = item % p.splits, g = (item / p.splits) % G, t = item / (p.splits * G);
+    const int pos = p.positions[t];
+    const int n_keys = pos + 1;
+    const int key_lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    const int chunk_lo = key_lo / 16, chunk_hi = (n_keys + 15) / 16;
+    const int per = (chunk_hi - chunk_lo + p.splits - 1) / p.splits;
+    const int c0 = chunk_lo + s * per, c1 = min(chunk_hi, c0 + per);
+    const int* bt = p.block_table + (size_t)p.token_req[t] * p.max_blocks;
+    const float* acc = p.part + (size_t)t * Nqkv;
+    const size_t part_stride = (size_t)p.T * Nqkv;
+    const size_t k_off = (size_t)g * p.page_size * HD, v_off = ((size_t)G + g) * p.page_size * HD;
+
+    // ---- before waiting for the kernel that makes q, k, v: ask for this warp's first chunk of old keys
+    bf16* ks = kvs + (size_t)warp * 2 * 16 * LD;
+    bf16* vs = ks + 16 * LD;
+    constexpr int CPR = HD / 8;
+    constexpr int ROWS_PER_IT = 32 / CPR > 0 ? 32 / CPR : 1;
+    const int l_row = lane / CPR, l_col = (lane % CPR) * 8;
+    auto request_chunk = [&](int c) {
+      const int key0 = c * 16;
+      const int page = bt[key0 / p.page_size];
+      const int in_page = key0 % p.page_size;
+      const bf16* kg = p.kv + (page < 0 ? 0 : (size_t)page * page_elems) + k_off + (size_t)in_page * HD;
+      const bf16* vg = p.kv + (page < 0 ? 0 : (size_t)page * page_elems) + v_off + (size_t)in_page * HD;
+      // keys already in the cache: all of them, but not the token's own when this kernel writes it
+      const int rows_ok = page < 0 ? 0 : (n_keys - (p.write_kv ? 1 : 0)) - key0;
+      for (int row = l_row; row < 16; row += ROWS_PER_IT) {
+        int bytes = row < rows_ok ? 16 : 0;
+        ar_cp_async16(ks + row * LD + l_col, kg + (bytes ? row * HD + l_col : 0), bytes);
+        ar_cp_async16(vs + row * LD + l_col, vg + (bytes ? row * HD + l_col : 0), bytes);
+      }
+      asm volatile("cp.async.commit_group;\n" ::);
+    };
+    const int c_first = c0 + warp;
+    const bool early = c_first < c1;
+    if (early) request_chunk(c_first);
+    ar_stamp(p, 1);
+    pdl_wait();
+    ar_stamp(p, 2);
+
+    // ---- q of the group (gs heads) and, in the CTA that holds the chunk of the token's own position, its
+    // k and v: sums of the parts + bias, rotated; q as bfloat16 rows in shared memory (rows >= gs zero),
+    // k and v to the cache slot and to a staging row.  A task is one rotation pair; a thread takes up to
+    // four tasks at a time and issues all their loads before it uses any.
+    const bool owns_new = p.write_kv && (chunk_hi - 1 >= c0 && chunk_hi - 1 < c1);
+    bf16* kdst = nullptr;
+    bf16* vdst = nullptr;
+    if (owns_new) {
+      const int slot = p.slot_map[t];
+      const int page = slot / p.page_size, off = slot - page * p.page_size;
+      kdst = p.kv + (size_t)page * page_elems + k_off + (size_t)off * HD;
+      vdst = p.kv + (size_t)page * page_elems + v_off + (size_t)off * HD;
+    }
+    for (int w = threadIdx.x; w < (16 - gs) * (HD / 2); w += AR_THREADS)
+      reinterpret_cast<unsigned*>(qs + (size_t)gs * LD)[(w / (HD / 2)) * (LD / 2) + (w % (HD / 2))] = 0u;
+    const int n_tasks = (gs + (owns_new ? 2 : 0)) * (HD / 2);
+    constexpr int NB = 4;
+    for (int base = threadIdx.x; base < n_tasks; base += AR_THREADS * NB) {
+      float a[NB], b[NB], cv[NB], sv[NB];
+      int i0[NB], i1[NB], row[NB];
+#pragma unroll
+      for (int u = 0; u < NB; u++) {
+        const int w = base + u * AR_THREADS;
+        a[u] = b[u] = 0.f; cv[u] = 1.f; sv[u] = 0.f; i0[u] = i1[u] = 0;
+        row[u] = -1;
+        if (w < n_tasks) {
+          row[u] = w / (HD / 2);                       // 0..gs-1: q heads; gs: k; gs + 1: v
+          const int pp = w - row[u] * (HD / 2);
+          const bool is_v = row[u] == gs + 1;
+          const bool rot = pp < half && !is_v;
+          if (is_v || p.pairing == 0) { i0[u] = 2 * pp; i1[u] = 2 * pp + 1; }
+          else if (pp < half) { i0[u] = pp; i1[u] = pp + half; }
+          else { int jj = 2 * (pp - half) + p.rotary_dim; i0[u] = jj; i1[u] = jj + 1; }
+          const int e = (row[u] < gs ? g * gs + row[u] : (row[u] == gs ? H + g : H + G + g)) * HD;
+          if (p.bias) { a[u] = p.bias[e + i0[u]]; b[u] = p.bias[e + i1[u]]; }
+          if (rot && p.cos_t) { cv[u] = p.cos_t[(size_t)pos * half + pp]; sv[u] = p.sin_t[(size_t)pos * half + pp]; }
+          const float* src = acc + e;
+          for (int q = 0; q < p.n_parts; q++) {
+            a[u] += __ldcg(src + q * part_stride + i0[u]);
+            b[u] += __ldcg(src + q * part_stride + i1[u]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < NB; u++) {
+        if (row[u] < 0) continue;
+        const bf16 ha = __float2bfloat16_rn(a[u] * cv[u] - b[u] * sv[u]);
+        const bf16 hb = __float2bfloat16_rn(a[u] * sv[u] + b[u] * cv[u]);
+        if (row[u] < gs) {
+          qs[row[u] * LD + i0[u]] = ha; qs[row[u] * LD + i1[u]] = hb;
+        } else {
+          bf16* stage = newkv + (row[u] - gs) * HD;
+          bf16* dst = row[u] == gs ? kdst : vdst;
+          stage[i0[u]] = ha; stage[i1[u]] = hb;
+          dst[i0[u]] = ha; dst[i1[u]] = hb;
+        }
+      }
+    }
+    __syncthreads();
+    ar_stamp(p, 3);
+
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int c = c_first; c < c1; c += AR_WARPS) {
+      const int key0 = c * 16;
+      if (!(early && c == c_first)) request_chunk(c);
+      asm volatile("cp.async.wait_group 0;\n" ::);
+      __syncwarp();
+      if (p.write_kv && c == chunk_hi - 1) {
+        // the token's own k and v, made above: into this warp's copy of the chunk (no trip through memory)
+        const int new_row = pos - key0;
+        for (int i = lane; i < HD / 4; i += 32) {
+          reinterpret_cast<uint2*>(ks + new_row * LD)[i] = reinterpret_cast<const uint2*>(newkv)[i];
+          reinterpret_cast<uint2*>(vs + new_row * LD)[i] = reinterpret_cast<const uint2*>(newkv + HD)[i];
+        }
+        __syncwarp();
+      }
+      float sc[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk++) {
+        unsigned qa[4], b[4];
+        // q fragment: matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15) in the order a0..a3 of the mma
+        ar_ldmatrix_x4(qa, qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+        ar_ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
+        ar_mma(sc[0], qa[0], qa[1], qa[2], qa[3], b[0], b[1]);
+        ar_mma(sc[1], qa[0], qa[1], qa[2], qa[3], b[2], b[3]);
+      }
+#pragma unroll
+      for (int n = 0; n < 2; n++)
+#pragma unroll
+        for (int jx = 0; jx < 4; jx++) {
+          int key = key0 + n * 8 + (lane & 3) * 2 + (jx & 1);
+          bool ok = key >= key_lo && key < n_keys;
+          sc[n][jx] = ok ? sc[n][jx] * p.scale_log2e : -INFINITY;
+        }
+      float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+      float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+      float a0 = ar_exp2(m0 - ref0), a1 = ar_exp2(m1 - ref1);
+      m0 = mn0; m1 = mn1;
+      float pr[2][4];
+#pragma unroll
+      for (int n = 0; n < 2; n++) {
+        pr[n][0] = ar_exp2(sc[n][0] - ref0); pr[n][1] = ar_exp2(sc[n][1] - ref0);
+        pr[n][2] = ar_exp2(sc[n][2] - ref1); pr[n][3] = ar_exp2(sc[n][3] - ref1);
+      }
+      l0 = l0 * a0 + pr[0][0] + pr[0][1] + pr[1][0] + pr[1][1];
+      l1 = l1 * a1 + pr[0][2] + pr[0][3] + pr[1][2] + pr[1][3];
+      unsigned pa0 = ar_pack(pr[0][0], pr[0][1]), pa1 = ar_pack(pr[0][2], pr[0][3]);
+      unsigned pa2 = ar_pack(pr[1][0], pr[1][1]), pa3 = ar_pack(pr[1][2], pr[1][3]);
+#pragma unroll
+      for (int n = 0; n < HD / 8; n++) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+#pragma unroll
+      for (int dn = 0; dn < HD / 16; dn++) {
+        unsigned b[4];
+        ar_ldmatrix_x4_trans(b, vs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + dn * 16 + 8 * (lane >> 4));
+        ar_mma(o[2 * dn], pa0, pa1, pa2, pa3, b[0], b[1]);
+        ar_mma(o[2 * dn + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
+      }
+      __syncwarp();
+    }
+    ar_stamp(p, 4);
+    pdl_launch_dependents();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    // ---- merge the 8 warps; a warp's partial output [16][HD] float32 lies over its own K/V chunk buffers
+    // (2 * 16 * LD bfloat16 = 16 * (HD + 8) floats), which it no longer reads
+    {
+      const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
+      __syncwarp();
+#pragma unroll
+      for (int n = 0; n < HD / 8; n++) {
+        float* d0 = reinterpret_cast<float*>(ks) + (size_t)r0 * HD + n * 8 + cq;
+        float* d1 = reinterpret_cast<float*>(ks) + (size_t)r1 * HD + n * 8 + cq;
+        d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
+      }
+      if ((lane & 3) == 0) {
+        mm[warp * 16 + r0] = m0; mm[warp * 16 + r1] = m1;
+        ml[warp * 16 + r0] = l0; ml[warp * 16 + r1] = l1;
+      }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gs * HD; idx += AR_THREADS) {
+      int row = idx / HD, dim = idx - row * HD;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < AR_WARPS; w++) M = fmaxf(M, mm[w * 16 + row]);
+      float Lsum = 0.f, O = 0.f;
+      if (M != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < AR_WARPS; w++) {
+          float f = ar_exp2(mm[w * 16 + row] - M);
+          Lsum += ml[w * 16 + row] * f;
+          O += reinterpret_cast<const float*>(kvs + (size_t)w * 2 * 16 * LD)[(size_t)row * HD + dim] * f;
+        }
+      }
+      int hd = g * gs + row;
+      if (p.splits == 1) {
+        p.out[(size_t)t * H * HD + (size_t)hd * HD + dim] = __float2bfloat16_rn(O / Lsum);
+      } else {
+        size_t pi = ((size_t)t * H + hd) * p.splits + s;
+        p.part_o[pi * HD + dim] = O;
+        if (dim == 0) { p.part_ml[pi * 2] = M; p.part_ml[pi * 2 + 1] = Lsum; }
+      }
+    }
+    ar_stamp(p, 5);
+    if (p.splits > 1) {
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) s_ticket = atomicAdd(&p.tickets[(size_t)t * G + g], 1u);
+      __syncthreads();
+      ar_stamp(p, 6);
+      if (s_ticket == (unsigned)p.splits - 1) {          // the last item of this (t, g) combines
+        __threadfence();
+        float* pm = fac + 16 * 64;
+        float* pl = pm + 16 * 64;
+        // the partial outputs of the first 16 splits are requested first, so that they travel while the
+        // maxima and sums are read and the factors made
+        constexpr int PB = 16;
+        const int n_out = gs * (HD / 4);
+        float4 pv[PB];
+        {
+          const int idx = threadIdx.x;
+          const int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
+          const size_t base = ((size_t)t * H + (size_t)g * gs + row) * p.splits;
+#pragma unroll
+          for (int u = 0; u < PB; u++)
+            pv[u] = (idx < n_out && u < p.splits)
+                        ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + u) * HD) + d4)
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int idx = threadIdx.x; idx < gs * p.splits; idx += AR_THREADS) {
+          int row = idx / p.splits, sp = idx - row * p.splits;
+          size_t pi = ((size_t)t * H + (size_t)g * gs + row) * p.splits + sp;
+          float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + pi);
+          pm[row * 64 + sp] = v.x;
+          pl[row * 64 + sp] = v.y;
+        }
+        __syncthreads();
+        for (int row = warp; row < gs; row += AR_WARPS) {        // a warp per row; a lane takes splits lane, lane + 32
+          const float ma = lane < p.splits ? pm[row * 64 + lane] : -INFINITY;
+          const float mb = lane + 32 < p.splits ? pm[row * 64 + lane + 32] : -INFINITY;
+          float M = fmaxf(ma, mb);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+          const float ea = lane < p.splits ? ar_exp2(ma - M) : 0.f;
+          const float eb = lane + 32 < p.splits ? ar_exp2(mb - M) : 0.f;
+          float Lsum = (lane < p.splits ? pl[row * 64 + lane] * ea : 0.f) +
+                       (lane + 32 < p.splits ? pl[row * 64 + lane + 32] * eb : 0.f);
+          Lsum = warp_sum(Lsum);
+          const float inv = 1.f / Lsum;
+          if (lane < p.splits) fac[row * 64 + lane] = ea * inv;
+          if (lane + 32 < p.splits) fac[row * 64 + lane + 32] = eb * inv;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n_out; idx += AR_THREADS) {
+          const int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
+          const size_t base = ((size_t)t * H + (size_t)g * gs + row) * p.splits;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s0 = 0; s0 < p.splits; s0 += PB) {
+            if (idx != (int)threadIdx.x || s0 > 0) {
+#pragma unroll
+              for (int u = 0; u < PB; u++)
+                pv[u] = s0 + u < p.splits
+                            ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + s0 + u) * HD) + d4)
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < PB; u++) {
+              const float f = s0 + u < p.splits ? fac[row * 64 + s0 + u] : 0.f;
+              a.x += pv[u].x * f; a.y += pv[u].y * f; a.z += pv[u].z * f; a.w += pv[u].w * f;
+            }
+          }
+          bf16* dst = p.out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
+          uint2 raw;
+          raw.x = ar_pack(a.x, a.y);
+          raw.y = ar_pack(a.z, a.w);
+          *reinterpret_cast<uint2*>(dst) = raw;
+        }
+        if (threadIdx.x == 0) p.tickets[(size_t)t * G + g] = 0;
+        ar_stamp(p, 7);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+
+template <int HD>
+static int ar_launch(const ArParams& p, cudaStream_t stream) {
+  size_t smem = (size_t)16 * (HD + AR_PAD) * sizeof(bf16) + (size_t)AR_WARPS * 2 * 16 * (HD + AR_PAD) * sizeof(bf16) +
+                (size_t)AR_WARPS * 16 * 2 * sizeof(float) + (size_t)3 * 16 * 64 * sizeof(float) +
+                (size_t)2 * HD * sizeof(bf16);
+  auto kernel = decode_attention_rope_kernel<HD>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    cudaGetLastError();
+    return QD_ERR_UNSUPPORTED;
+  }
+  qd_launch(kernel, dim3((unsigned)(p.T * p.G * p.splits)), dim3(AR_THREADS), smem, stream, p);
+  return (int)cudaGetLastError();
+}
+
+// One decoded token per request: q, k, v from partial sums, rotation, cache write and attention.
+// Refuses head sizes other than 16..128 in steps as listed, more than 16 query heads per kv head, a
+// page size that is no multiple of 16, more than 64 splits.
+extern "C" int qd_decode_attention_rope(const float* part, int n_parts, const float* bias, bf16* out, bf16* kv,
+                                        const int* block_table, int max_blocks, const int* token_req,
+                                        const int* positions, const int* slot_map, int T, int H, int G, int d,
+                                        int page_size, float scale, int window, int splits, int write_kv,
+                                        const float* cos_t, const float* sin_t, int rotary_dim, int pairing,
+                                        float* part_o, float* part_ml, unsigned* tickets, long long* timeline,
+                                        cudaStream_t stream) {
+  if (T < 1 || G < 1 || H % G != 0 || H / G > 16 || page_size % 16 != 0 || splits < 1 || splits > 64 || n_parts < 1)
+    return QD_ERR_UNSUPPORTED;
+  if ((rotary_dim & 1) || rotary_dim > d || (rotary_dim > 0 && (!cos_t || !sin_t))) return QD_ERR_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml || !tickets)) return QD_ERR_UNSUPPORTED;
+  ArParams p;
+  p.part = part; p.n_parts = n_parts; p.bias = bias; p.out = out; p.kv = kv;
+  p.block_table = block_table; p.max_blocks = max_blocks; p.token_req = token_req; p.positions = positions;
+  p.slot_map = slot_map; p.T = T; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.splits = splits;
+  p.write_kv = write_kv; p.cos_t = rotary_dim > 0 ? cos_t : nullptr; p.sin_t = sin_t; p.rotary_dim = rotary_dim;
+  p.pairing = pairing; p.scale_log2e = scale * 1.4426950408889634f;
+  p.part_o = part_o; p.part_ml = part_ml; p.tickets = tickets; p.timeline = timeline;
+  switch (d) {
+    case 16: return ar_launch<16>(p, stream);
+    case 32: return ar_launch<32>(p, stream);
+    case 48: return ar_launch<48>(p, stream);
+    case 64: return ar_launch<64>(p, stream);
+    case 96: return ar_launch<96>(p, stream);
+    case 128: return ar_launch<128>(p, stream);
+    default: return QD_ERR_UNSUPPORTED;
+  }
+}

@@ -37,6 +37,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_tc5": "gemm_tc5.cu",
     "attention_generic": "attention_generic.cu",
     "attention_flash": "attention_flash.cu",
+    "attention_decode_rope": "attention_decode_rope.cu",
     "sampling": "sampling.cu",
     "decode_fused": "decode_fused.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",

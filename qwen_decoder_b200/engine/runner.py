@@ -176,7 +176,10 @@ class _DecodeGraph:
     """One captured decode step for a padded batch size and block-table widths."""
 
     def __init__(self, runner: "ModelRunner", Bp: int, mbs, with_sampling: bool):
-        self.runner = runner
+        # no reference back to the runner: a cycle would leave the captured graph to the garbage
+        # collector, which might then destroy it in the middle of another capture
+        self.model = runner.model
+        self.device = runner.device
         self.with_sampling = with_sampling
         self.lay = MetaLayout(Bp, Bp, Bp, mbs, extra=3 * Bp)
         # two pinned staging buffers: one may still be in flight while the next step is written
@@ -210,9 +213,9 @@ class _DecodeGraph:
 
     def _forward(self):
         from .. import kernels
-        self.logits = self.runner.model.forward(self.ctx)
+        self.logits = self.model.forward(self.ctx)
         if self.with_sampling:
-            self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.runner.device)
+            self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.device)
             kernels.sample(self.logits, self.temps, self.top_ks, self.draws, self.tokens)
 
     def run(self) -> None:
@@ -220,12 +223,21 @@ class _DecodeGraph:
             # the first step of this shape runs eagerly (loads every kernel), then is captured; the
             # eager run and the first replay write the same values to the same cache slots
             self._forward()
-            torch.cuda.synchronize(self.runner.device)
+            torch.cuda.synchronize(self.device)
+            import gc
             from .. import kernels
             graph = torch.cuda.CUDAGraph()
             n0 = kernels.launches()
-            with torch.cuda.graph(graph):
-                self._forward()
+            # no garbage collection while capturing: freeing another graph or its memory in the
+            # middle of a capture invalidates it
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self._forward()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.own_launches = kernels.launches() - n0
             self.graph = graph
         self.graph.replay()

@@ -182,7 +182,8 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 
 
 SKINNY_MAX_TOKENS = 64      # what the mma.sync few-token kernels take
-SKINNY_POLICY_TOKENS = 16   # up to here they are the faster choice
+SKINNY_POLICY_TOKENS = int(_os.environ.get("QD_SKINNY_TOKENS", "16"))   # up to here they are the faster choice
+STREAM_POLICY_TOKENS = int(_os.environ.get("QD_STREAM_TOKENS", "8"))     # the streaming kernel up to here
 TC5_POLICY_TOKENS = int(_os.environ.get("QD_TC5_TOKENS", "16"))   # from there up to here the tcgen05 kernel; 16 = never:
 # on row-major weights it reads 128-byte pieces of 128 rows per copy and stays below the library product
 EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
@@ -194,7 +195,9 @@ def few_token_impl(T: int) -> str:
     if skinny_impl == "tc5":
         return "tc5" if T <= max(TC5_POLICY_TOKENS, SKINNY_POLICY_TOKENS) else ""
     if T <= SKINNY_POLICY_TOKENS:
-        return skinny_impl
+        # the streaming kernel is the faster one up to 8 tokens (one 8-token tile per row block); with two
+        # tiles its stages shrink and the register-load kernel wins clearly (measured in whole decode steps)
+        return "regs" if skinny_impl == "stream" and T > STREAM_POLICY_TOKENS else skinny_impl
     return "tc5" if T <= TC5_POLICY_TOKENS else ""
 
 
@@ -365,6 +368,42 @@ def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torc
         _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
         _ptr(token_req), _ptr(positions), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
         _I(window), _I(splits), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _stream()), "decode_attention")
+
+
+def decode_rope_supported(dtype: torch.dtype, H: int, G: int, d: int, page_size: int) -> bool:
+    return (dtype == torch.bfloat16 and d in (16, 32, 48, 64, 96, 128) and H % G == 0 and H // G <= 16
+            and page_size % 16 == 0)
+
+
+def decode_attention_rope(part: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, kv: torch.Tensor,
+                          block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
+                          slot_map: torch.Tensor, H: int, G: int, d: int, page_size: int, scale: float,
+                          window: int, splits: int, write_kv: bool, rotary_dim: int, pairing: int,
+                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                          timeline: Optional[torch.Tensor] = None) -> None:
+    """One decoded token per request, from the float32 partial sums part [n_parts, T, (H+2G)*d] of q, k, v:
+    bias, rotation by position, cache write and attention over the paged cache in one launch."""
+    n_parts, T, W = part.shape
+    assert part.dtype == torch.float32 and W == (H + 2 * G) * d and out.shape == (T, H * d)
+    assert out.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and tuple(kv.shape[1:]) == (2, G, page_size, d)
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and positions.dtype == torch.int32
+    _contig(part, "part"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == W
+    part_o = part_ml = tickets = None
+    if splits > 1:
+        if T * G > _TICKETS:
+            raise KernelError("decode_attention_rope: more (token, kv head) pairs than tickets")
+        part_o = torch.empty((T * H * splits, d), dtype=torch.float32, device=part.device)
+        part_ml = torch.empty((T * H * splits, 2), dtype=torch.float32, device=part.device)
+        tickets = _tickets.get(part.device)
+        if tickets is None:     # zero once; every launch leaves them zero again
+            tickets = _tickets[part.device] = torch.zeros(_TICKETS, dtype=torch.int32, device=part.device)
+    _check(library("attention_decode_rope").qd_decode_attention_rope(
+        _ptr(part), _I(n_parts), _ptr(bias), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
+        _ptr(token_req), _ptr(positions), _ptr(slot_map), _I(T), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
+        _I(window), _I(splits), _I(1 if write_kv else 0), _ptr(cos), _ptr(sin), _I(rotary_dim), _I(pairing),
+        _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(timeline), _stream()), "decode_attention_rope")
 
 
 def prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,

@@ -76,6 +76,16 @@ class GQAttention(Mixer):
             part = kernels.gemm_skinny_partial(x, self.qkv.weight,
                                                kernels.skinny_splits(self.qkv.out_features, self.hidden_size, x.shape[0]))
             matmul_backend.counters["own"] += 1
+            ps, window = cache.group.page_size, self.window or 0
+            if ctx.all_decode and _DECODE_ROPE and kernels.decode_rope_supported(x.dtype, H, G, d, ps):
+                # ... and so does attention itself: one kernel from the partial sums to the attention output
+                attn = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+                kernels.decode_attention_rope(
+                    part, self.qkv.bias, attn, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions,
+                    cache.group.slot_map, H, G, d, ps, self.scale, window,
+                    decode_rope_splits(ctx.num_tokens * G, min(ctx.max_context, window or ctx.max_context)),
+                    cache.write, *rope)
+                return self.out.forward_partial(attn)
             qkv = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)       # q only
             kernels.rope_kv_write_partial(part, self.qkv.bias, qkv, H, G, d, *rope, ctx.positions, cache.kv,
                                           cache.group.slot_map, cache.group.page_size, cache.write)
@@ -103,6 +113,17 @@ class GQAttention(Mixer):
 
 import os as _os
 _TARGET_CTAS = int(_os.environ.get("QD_DECODE_ATTN_CTAS", "148"))
+_DECODE_ROPE = _os.environ.get("QD_DECODE_ROPE", "1") != "0"
+_ROPE_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ROPE_CTAS", "148"))
+
+
+def decode_rope_splits(ctas_without_split: int, max_keys: int) -> int:
+    """CTAs (of 8 warps) per (request, kv head) in the kernel that also rotates and writes the cache: one
+    CTA for each of the 148 SMs (two were slower in whole decode steps at batch 4 and 8, equal at 1 and 2),
+    never more than that, and none with fewer than eight 16-key chunks, one per warp."""
+    by_fill = max(1, _ROPE_TARGET_CTAS // max(1, ctas_without_split))      # never a second wave
+    by_work = max(1, (max_keys + 127) // 128)
+    return max(1, min(by_fill, by_work, 64))
 
 
 def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = _TARGET_CTAS) -> int:

@@ -32,7 +32,7 @@ _TARGET_CTAS = 296
 def attention_splits(n_token_heads: int, max_keys: int) -> int:
     """CTAs per (token, kv head): enough items for every resident CTA, but none with fewer than
     eight 16-key chunks (one per warp)."""
-    by_fill = max(1, -(-_TARGET_CTAS // max(1, n_token_heads)))
+    by_fill = max(1, _TARGET_CTAS // max(1, n_token_heads))      # no CTA with two items
     by_work = max(1, (max_keys + 127) // 128)
     return max(1, min(by_fill, by_work, 64))
 
@@ -41,7 +41,10 @@ class FusedDecode:
     """Collected tensors of a model whose decode step the fused kernel can run."""
 
     def __init__(self, model, entries, common):
-        self.model = model
+        # the model's tensors, not the model: the model refers to this object
+        self.embedding = model.embedding
+        self.vocab_size = model.vocab_size
+        self.lm_head_weight = model.lm_head.weight
         self.entries = entries            # per schedule entry: dict of the block's answer
         self.common = common
         self.device = model.device
@@ -124,9 +127,9 @@ class FusedDecode:
     def forward(self, ctx) -> torch.Tensor:
         c, dev = self.common, self.device
         T, D, H, G, d, F = ctx.num_tokens, c["D"], c["H"], c["G"], c["d"], c["F"]
-        V = self.model.vocab_size
+        V = self.vocab_size
         x = torch.empty((T, D), dtype=torch.float32, device=dev)
-        kernels.embedding(x, self.model.embedding, ctx.tokens)
+        kernels.embedding(x, self.embedding, ctx.tokens)
         window = c["window"] or 0
         splits = attention_splits(T * G, min(ctx.max_context, window or ctx.max_context))
         qkv = torch.empty((T, (H + 2 * G) * d), dtype=torch.float32, device=dev)
@@ -153,7 +156,7 @@ class FusedDecode:
         p.layers = self._layers(ctx.cache).data_ptr()
         fin = c["final"]
         p.final_w, p.final_eps = fin["weight"].data_ptr(), fin["eps"]
-        p.lm_head, p.logits = self.model.lm_head.weight.data_ptr(), logits.data_ptr()
+        p.lm_head, p.logits = self.lm_head_weight.data_ptr(), logits.data_ptr()
         p.barrier, p.status = self.barrier.data_ptr(), self.status.data_ptr()
         p.host_status = self.host_status.data_ptr()
         if self.timeline is not None:

@@ -391,6 +391,64 @@ def test_gemm_tcgen05_many_tokens(shape, monkeypatch):
     assert kernels.gemm_tc5_status() == 0
 
 
+@pytest.mark.parametrize("cfg", [(16, 2, 128, 16, None, 1, "adjacent"), (16, 2, 128, 16, None, 9, "adjacent"),
+                                 (4, 2, 16, 16, None, 3, "half"), (6, 2, 48, 32, None, 2, "half"),
+                                 (14, 2, 64, 64, 300, 5, "adjacent"), (5, 5, 96, 16, None, 4, "adjacent"),
+                                 (32, 2, 32, 16, 50, 2, "half")])
+def test_decode_attention_from_partial_sums(cfg):
+    """The kernel that takes q, k, v as float32 partial sums: bias, rotation, cache write and attention in
+    one launch, against the plain rotation and attention; the new token's k and v must be in its slot."""
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.parts.rotary import Rotary
+    H, G, d, page_size, window, splits, pairing = cfg
+    dt = torch.bfloat16
+    base = 50000.0
+    lens = [1, 16, 17, 255, 256, 700, 1031]          # cached length after this step, the new token included
+    T, W = len(lens), (H + 2 * G) * d
+    rot = Rotary(d, d, base, pairing)
+    rot.prepare(1100, torch.device(DEV))
+    kv, bt, ks, vs = _paged_setup(dt, lens, G, d, page_size, seed=21)
+    g = torch.Generator().manual_seed(22)
+    part = torch.randn(3, T, W, generator=g) * 0.6
+    bias = torch.randn(W, generator=g) * 0.3
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    slots = torch.tensor([int(bt[i, (n - 1) // page_size]) * page_size + (n - 1) % page_size
+                          for i, n in enumerate(lens)], dtype=torch.int32)
+    # the slot of the new token holds junk before the step
+    for i, n in enumerate(lens):
+        kv[int(slots[i]) // page_size, :, :, int(slots[i]) % page_size, :] = 7.0
+    qkv = part.double().sum(0) + bias.double()
+    wq = plain_model.rope(qkv[:, :H * d], pos, H, d, base, pairing)
+    wk = plain_model.rope(qkv[:, H * d:(H + G) * d], pos, G, d, base, pairing).to(dt)
+    wv = qkv[:, (H + G) * d:].to(dt)
+    dkv = kv.to(DEV)
+    out = torch.empty(T, H * d, dtype=dt, device=DEV)
+    tr = torch.arange(T, dtype=torch.int32)
+    kernels.decode_attention_rope(part.to(DEV), bias.to(DEV), out, dkv, bt.to(DEV), tr.to(DEV), pos.to(DEV),
+                                  slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d), window or 0, splits, True,
+                                  d, rot.pairing_code, rot.cos, rot.sin)
+    kvc = dkv.cpu()
+    for i, n in enumerate(lens):
+        page, off = int(slots[i]) // page_size, int(slots[i]) % page_size
+        close(kvc[page, 0, :, off, :].reshape(-1), wk[i].double(), dt)
+        close(kvc[page, 1, :, off, :].reshape(-1), wv[i].double(), dt)
+        k_all = torch.cat([ks[i][:n - 1].reshape(n - 1, G, d), wk[i].reshape(1, G, d)])
+        v_all = torch.cat([vs[i][:n - 1].reshape(n - 1, G, d), wv[i].reshape(1, G, d)])
+        want = _plain_attention_row(wq[i], k_all, v_all, H, G, d, n - 1, window)
+        close(out[i], want, dt, scale=float(v_all.abs().max()))
+    # reading another layer's cache: nothing is written, the slot's old content is attended
+    dkv2 = kv.to(DEV)
+    kernels.decode_attention_rope(part.to(DEV), bias.to(DEV), out, dkv2, bt.to(DEV), tr.to(DEV), pos.to(DEV),
+                                  slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d), window or 0, splits, False,
+                                  d, rot.pairing_code, rot.cos, rot.sin)
+    assert torch.equal(dkv2.cpu(), kv)
+    i, n = 3, lens[3]
+    k_all = torch.cat([ks[i][:n - 1].reshape(n - 1, G, d), torch.full((1, G, d), 7.0, dtype=dt)])
+    v_all = torch.cat([vs[i][:n - 1].reshape(n - 1, G, d), torch.full((1, G, d), 7.0, dtype=dt)])
+    want = _plain_attention_row(wq[i], k_all, v_all, H, G, d, n - 1, window)
+    close(out[i], want, dt, scale=7.0)
+
+
 # ---- the whole decode step as one cooperative kernel (opt-in path) against the unfused kernels
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", ["A", "B", "C"])
