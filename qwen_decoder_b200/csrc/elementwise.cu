@@ -96,11 +96,17 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, cons
       if (delta) {
         if (sizeof(TD) == 4) {
           const float* dp = reinterpret_cast<const float*>(delta) + s * D;
-          float4 acc = reinterpret_cast<const float4*>(dp)[i4];
-#pragma unroll 4
-          for (int p = 1; p < n_parts; p++) {
-            float4 d = reinterpret_cast<const float4*>(dp + p * part_stride)[i4];
-            acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+          // partial sums in batches of 16: all loads of a batch are in flight together, the sum keeps
+          // the order of the parts
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int p0 = 0; p0 < n_parts; p0 += 16) {
+            float4 d[16];
+#pragma unroll
+            for (int u = 0; u < 16; u++)
+              d[u] = p0 + u < n_parts ? reinterpret_cast<const float4*>(dp + (size_t)(p0 + u) * part_stride)[i4]
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 16; u++) { acc.x += d[u].x; acc.y += d[u].y; acc.z += d[u].z; acc.w += d[u].w; }
           }
           a.x += acc.x; a.y += acc.y; a.z += acc.z; a.w += acc.w;
         } else {

@@ -19,6 +19,7 @@
 // leaving early, so that all warps still meet at every barrier; the host turns a non-zero
 // status into an error.
 #include "common.cuh"
+#include <cstdlib>
 
 #define ST_CONSUMERS 4
 #define ST_THREADS ((ST_CONSUMERS + 1) * 32)
@@ -256,6 +257,167 @@ gemm_stream_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long 
   pdl_launch_dependents();
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same streamer with the tokens RESIDENT in shared memory: for up to 8 tokens and a k range per
+// CTA of at most XR_KMAX.  Above, every stage carries the tokens' rows for its k beside the 16 rows
+// of W -- half as many bytes again through the copy engine, which is what bounds the stream.  Here a
+// CTA keeps ONE share of K for the whole launch (CTA b: share b % splits, tiles b / splits,
+// b / splits + grid / splits, ...), copies the tokens' rows for that share once, and its stages
+// carry weights only.
+#define XR_KMAX 2048
+#define XR_ROW_BYTES (XR_KMAX * 2 + 64)
+#define XR_STAGES 2
+#define XR_STAGE_BYTES (16 * ST_ROW_BYTES)
+
+template <int EPI, typename TO>
+__global__ void __launch_bounds__(ST_THREADS)
+gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long long ldx,
+                        const float* __restrict__ bias, TO* __restrict__ out, long long ldo,
+                        float* __restrict__ part, int T, int N, int K, int splits, int n_tiles,
+                        int* __restrict__ status) {
+  constexpr int NST = XR_STAGES;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* stages = smem_raw;                                               // NST x 16 rows of W
+  unsigned char* xres = smem_raw + NST * XR_STAGE_BYTES;                          // 8 token rows
+  float* red = reinterpret_cast<float*>(xres + 8 * XR_ROW_BYTES);                 // [4][16][9]
+  __shared__ unsigned long long full_bar[NST], empty_bar[NST], x_bar;
+  __shared__ int dead;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    dead = 0;
+    for (int s = 0; s < NST; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ST_CONSUMERS); }
+    mbar_init(&x_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int n_chunks = (K + ST_KC - 1) / ST_KC;
+  const int stride = (int)gridDim.x / splits;                 // CTAs per share of K (the host made it >= 1)
+  const int sp = (int)blockIdx.x % splits;
+  const int first = (int)blockIdx.x / splits;
+  const bool idle = first >= stride;
+  const int c_begin = (int)((long long)n_chunks * sp / splits), c_end = (int)((long long)n_chunks * (sp + 1) / splits);
+  const int k_begin = c_begin * ST_KC, k_end = min(K, c_end * ST_KC);
+  constexpr int RED_LD = 9;
+
+  if (warp == ST_CONSUMERS) {
+    // ------------------------------------------------------------ producer
+    if (idle) { pdl_wait(); return; }
+    unsigned it = 0;
+    bool waited = false;
+    auto tokens = [&]() {
+      // after the dependency wait: the tokens' rows for this CTA's share of K, once
+      pdl_wait();
+      waited = true;
+      const unsigned xb = (unsigned)((k_end - k_begin) * 2);
+      if (lane == 0) mbar_expect_tx(&x_bar, xb * T);
+      __syncwarp();
+      for (int t = lane; t < T; t += 32)
+        bulk_copy(xres + (size_t)t * XR_ROW_BYTES, X + (size_t)t * ldx + k_begin, xb, &x_bar);
+    };
+    for (int tile = first; tile < n_tiles; tile += stride) {
+      long long row;                      // the row of W this lane copies (lanes 0..15)
+      if (EPI == EPI_SWIGLU) {
+        int F = N >> 1, f = tile * 8 + (lane & 7);
+        if (f >= F) f = F - 1;
+        row = (lane & 8) ? (long long)F + f : f;
+      } else {
+        row = (long long)tile * 16 + (lane & 15);
+        if (row >= N) row = N - 1;
+      }
+      for (int c = c_begin; c < c_end; c++, it++) {
+        const int s = it % NST;
+        const unsigned ph = (it / NST) & 1;
+        if (it >= (unsigned)NST && !waited) tokens();        // the ring is full of W requests
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, &dead) && lane == 0) atomicExch(status, 1);
+        const int k0 = c * ST_KC;
+        const unsigned row_bytes = (unsigned)(min(ST_KC, K - k0) * 2);
+        if (lane == 0) mbar_expect_tx(&full_bar[s], row_bytes * 16);
+        __syncwarp();
+        if (lane < 16)
+          bulk_copy(stages + (size_t)s * XR_STAGE_BYTES + (size_t)lane * ST_ROW_BYTES, W + row * K + k0, row_bytes,
+                    &full_bar[s]);
+      }
+    }
+    if (!waited) tokens();
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  if (idle) { pdl_launch_dependents(); return; }
+  const int j = lane & 3, r = lane >> 2;
+  unsigned it = 0;
+  bool have_x = false;
+  for (int tile = first; tile < n_tiles; tile += stride) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = c_begin; c < c_end; c++, it++) {
+      const int s = it % NST;
+      const unsigned ph = (it / NST) & 1;
+      if (!mbar_wait(&full_bar[s], ph, &dead) && lane == 0) atomicExch(status, 2);
+      if (!have_x) {
+        if (!mbar_wait(&x_bar, 0, &dead) && lane == 0) atomicExch(status, 2);
+        have_x = true;
+      }
+      const unsigned char* st = stages + (size_t)s * XR_STAGE_BYTES;
+      const unsigned char* xs = xres + (size_t)(c - c_begin) * ST_KC * 2;
+#pragma unroll
+      for (int u = 0; u < ST_KC / 32 / ST_CONSUMERS; u++) {
+        const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
+        if (c * ST_KC + kq >= K) break;                 // the whole k-step lies past K (same for all lanes)
+        const bool in = c * ST_KC + kq + 8 * j < K;     // lanes past K feed zeros; every lane runs the MMAs
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        const size_t col = (size_t)(kq + 8 * j) * 2;
+        uint4 lo = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
+        uint4 hi = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
+        // token rows past T were never copied: whatever is there only reaches columns that are not stored
+        uint4 b = in ? *reinterpret_cast<const uint4*>(xs + (size_t)r * XR_ROW_BYTES + col) : zero;
+        mma16816(acc, lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+        mma16816(acc, lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    float* base = red + (size_t)warp * 16 * RED_LD;
+    base[r * RED_LD + 2 * j] = acc[0];
+    base[r * RED_LD + 2 * j + 1] = acc[1];
+    base[(r + 8) * RED_LD + 2 * j] = acc[2];
+    base[(r + 8) * RED_LD + 2 * j + 1] = acc[3];
+    asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
+    if (EPI == EPI_SWIGLU) {
+      const int F = N >> 1;
+      for (int idx = threadIdx.x; idx < 8 * 8; idx += ST_CONSUMERS * 32) {
+        int row = idx & 7, tok = idx >> 3;
+        int f = tile * 8 + row;
+        if (tok >= T || f >= F) continue;
+        float gate = 0.f, up = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_CONSUMERS; w++) {
+          gate += red[((size_t)w * 16 + row) * RED_LD + tok];
+          up += red[((size_t)w * 16 + row + 8) * RED_LD + tok];
+        }
+        out[(size_t)tok * ldo + f] = from_float<TO>(gate / (1.0f + expf(-gate)) * up);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < 16 * 8; idx += ST_CONSUMERS * 32) {
+        int row = idx & 15, tok = idx >> 4;
+        int n = tile * 16 + row;
+        if (tok >= T || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_CONSUMERS; w++) v += red[((size_t)w * 16 + row) * RED_LD + tok];
+        if (EPI == EPI_PARTIAL) {
+          part[((size_t)sp * T + tok) * N + n] = v;
+        } else {
+          if (bias) v += bias[n];
+          out[(size_t)tok * ldo + n] = from_float<TO>(v);
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");   // red is reused by the next tile
+  }
+  pdl_launch_dependents();
+}
+
 static int* g_status[64];   // per device: one int of device memory for the kernels' error status
 
 static int* status_word() {
@@ -268,6 +430,50 @@ static int* status_word() {
     g_status[dev] = p;
   }
   return g_status[dev];
+}
+
+// The resident-token form: up to 8 tokens, every share of K at most XR_KMAX wide, at least one CTA per share.
+static bool xres_fits(int T, int K, int splits, int max_ctas) {
+  if (T > 8 || splits > max_ctas) return false;
+  const int n_chunks = (K + ST_KC - 1) / ST_KC;
+  for (int sp = 0; sp < splits; sp++) {
+    int cb = (int)((long long)n_chunks * sp / splits), ce = (int)((long long)n_chunks * (sp + 1) / splits);
+    if ((ce - cb) * ST_KC > XR_KMAX) return false;
+  }
+  return true;
+}
+
+static int launch_stream_xres(const bf16* W, const bf16* X, long long ldx, const float* bias, void* out, int out_dtype,
+                              long long ldo, float* part, int T, int N, int K, int splits, int epi, int max_ctas,
+                              cudaStream_t stream) {
+  int* status = status_word();
+  if (!status) return QD_ERR_UNSUPPORTED;
+  int n_tiles = epi == EPI_SWIGLU ? (N / 2 + 7) / 8 : (N + 15) / 16;
+  // CTAs per share of K: no more than there are tiles, a multiple of `splits` in all
+  int per_share = max_ctas / splits;
+  if (per_share > n_tiles) per_share = n_tiles;
+  int grid = per_share * splits;
+  size_t smem = (size_t)XR_STAGES * XR_STAGE_BYTES + (size_t)8 * XR_ROW_BYTES + (size_t)ST_CONSUMERS * 16 * 9 * sizeof(float);
+#define LAUNCH(E, TO)                                                                                            \
+  do {                                                                                                           \
+    cudaFuncSetAttribute(gemm_stream_xres_kernel<E, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    qd_launch(gemm_stream_xres_kernel<E, TO>, dim3(grid), dim3(ST_THREADS), smem, stream, W, X, ldx, bias,       \
+              (TO*)out, ldo, part, T, N, K, splits, n_tiles, status);                                            \
+  } while (0)
+  if (epi == EPI_SWIGLU) {
+    if (out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;
+    LAUNCH(EPI_SWIGLU, bf16);
+  } else if (epi == EPI_PARTIAL) {
+    LAUNCH(EPI_PARTIAL, float);
+  } else if (out_dtype == QD_BF16) {
+    LAUNCH(EPI_STORE, bf16);
+  } else if (out_dtype == QD_F32) {
+    LAUNCH(EPI_STORE, float);
+  } else {
+    return QD_ERR_UNSUPPORTED;
+  }
+#undef LAUNCH
+  return qd_last_error();
 }
 
 template <int TN>
@@ -316,6 +522,8 @@ extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const
   if (epi != EPI_PARTIAL && splits != 1) return QD_ERR_UNSUPPORTED;
   const bf16* w = (const bf16*)W;
   const bf16* x = (const bf16*)X;
+  if (xres_fits(T, K, splits, max_ctas) && !getenv("QD_STREAM_NO_XRES"))
+    return launch_stream_xres(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 8) return launch_stream<1>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 16) return launch_stream<2>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 32) return launch_stream<4>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);

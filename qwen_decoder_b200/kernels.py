@@ -221,6 +221,21 @@ def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
     tiles = (N + 15) // 16
     if impl == "stream":
         chunks = (K + 1023) // 1024          # the streaming kernel splits K in whole stages of 1024
+        if T <= 8 and chunks > 2:
+            # The kernel keeps the tokens in shared memory when no share of K is wider than two stages, and
+            # a CTA then keeps one share for the whole launch: among the splits that allow it, take the one
+            # whose busiest CTA reads least (rounds over the tiles x stages per share).
+            best = None
+            for sp in range((chunks + 1) // 2, min(chunks, 16) + 1):
+                per_share = max(1, min(STREAM_MAX_CTAS // sp, tiles))
+                widest = max(chunks * (i + 1) // sp - chunks * i // sp for i in range(sp))
+                if widest > 2:
+                    continue
+                cost = -(-tiles // per_share) * widest
+                if best is None or cost < best[0]:
+                    best = (cost, sp)
+            if best is not None:
+                return best[1]
         return max(1, min((target_ctas + tiles - 1) // tiles, chunks, 16))
     groups = (K + 127) // 128
     return max(1, min((target_ctas + tiles - 1) // tiles, groups // 4, 16))
