@@ -217,20 +217,12 @@ class CacheManager:
                 rc.tables[g].pages.append(self.pools[g].allocate())
 
     def commit(self, rc: RequestCache, n_tokens: int, tokens: Optional[Sequence[int]] = None) -> None:
-        """The step wrote ``n_tokens`` more tokens (``tokens``: which ones, for the prefix cache); give
-        back pages a window has passed."""
+        """The step wrote ``n_tokens`` more tokens (``tokens``: which ones, for the prefix cache; a caller
+        that does not know them yet gives None and calls ``log_tokens`` later); give back pages a
+        window has passed."""
         rc.num_tokens += n_tokens
-        if self.prefix is not None and tokens is not None and len(rc.token_log) == rc.num_tokens - n_tokens:
-            rc.token_log.extend(int(t) for t in tokens)
-            ps = self.page_size
-            while (len(rc.prefix_ids) + 1) * ps <= rc.num_tokens:
-                i = len(rc.prefix_ids)
-                parent = rc.prefix_ids[-1] if rc.prefix_ids else PrefixIndex.ROOT
-                if parent < 0:
-                    rc.prefix_ids.append(-1)          # the chain broke earlier: nothing below is recorded
-                    continue
-                rc.prefix_ids.append(self.prefix.record(parent, rc.token_log[i * ps:(i + 1) * ps],
-                                                        [t.pages[i] for t in rc.tables]))
+        if tokens is not None:
+            self.log_tokens(rc, tokens)
         for g, table in enumerate(rc.tables):
             if rc.num_tokens > len(table) * self.page_size:
                 raise CacheAccountingError(
@@ -241,6 +233,22 @@ class CacheManager:
                     self.pools[g].release(table.pages[p])
                     table.pages[p] = BlockTable.RELEASED
             table.first_live = max(table.first_live, first)
+
+    def log_tokens(self, rc: RequestCache, tokens: Sequence[int]) -> None:
+        """Tell the prefix cache which tokens the request's next cached positions hold; every page that is
+        full of known tokens is recorded."""
+        if self.prefix is None or rc.closed or len(rc.token_log) + len(tokens) > rc.num_tokens:
+            return
+        rc.token_log.extend(int(t) for t in tokens)
+        ps = self.page_size
+        while (len(rc.prefix_ids) + 1) * ps <= len(rc.token_log):
+            i = len(rc.prefix_ids)
+            parent = rc.prefix_ids[-1] if rc.prefix_ids else PrefixIndex.ROOT
+            if parent < 0:
+                rc.prefix_ids.append(-1)          # the chain broke earlier: nothing below is recorded
+                continue
+            rc.prefix_ids.append(self.prefix.record(parent, rc.token_log[i * ps:(i + 1) * ps],
+                                                    [t.pages[i] for t in rc.tables]))
 
     def close(self, rc: RequestCache) -> None:
         """Give back everything the request holds (last page first, as kv_cache.h:231-236)."""

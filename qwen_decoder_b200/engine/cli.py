@@ -40,6 +40,8 @@ def main(argv=None) -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--num-pages", type=int, default=None)
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--no-run-ahead", action="store_true",
+                    help="read every step's tokens before the next step is launched")
     args = ap.parse_args(argv)
 
     print(f"max_batch={args.max_batch} max_total_tokens={args.max_total_tokens} "
@@ -65,7 +67,7 @@ def main(argv=None) -> int:
     engine = Engine(args.model, dtype=args.dtype, device=args.device, max_batch=args.max_batch,
                     max_prefill_len=args.max_prefill_len, max_prefill_tokens_per_step=args.max_prefill_step,
                     max_total_tokens=args.max_total_tokens, page_size=args.page_size, num_pages=args.num_pages,
-                    enable_prefix_cache=bool(args.enable_prefix_cache))
+                    enable_prefix_cache=bool(args.enable_prefix_cache), run_ahead=not args.no_run_ahead)
     params = SamplingParams(temperature=args.temperature, top_k=args.top_k,
                             max_new_tokens=args.max_new_tokens, seed=args.seed, ignore_eos=args.ignore_eos)
     t0 = time.time()

@@ -27,7 +27,7 @@ class Engine:
                  max_prefill_tokens_per_step: int = 512, max_total_tokens: int = 4096,
                  page_size: int = 16, num_pages: Optional[int] = None, kv_memory_fraction: float = 0.8,
                  max_positions: Optional[int] = None, use_graphs: bool = True,
-                 enable_prefix_cache: bool = False):
+                 enable_prefix_cache: bool = False, run_ahead: bool = True):
         """``model``: a folder with config.json and model.safetensors; or give ``config`` (a typed
         configuration) and ``random_seed`` for random weights made on the device.
 
@@ -38,7 +38,10 @@ class Engine:
         cache pages of ``page_size`` tokens; by default ``kv_memory_fraction`` of the free device
         memory after the weights, as the reference takes 80 % (gpu_decoder.cu:197-204).
         ``enable_prefix_cache``: requests whose prompts begin alike share the full pages of the common
-        part (the reference's generate_continuous argument, decoder.h:148-154)."""
+        part (the reference's generate_continuous argument, decoder.h:148-154).
+        ``run_ahead``: while a decode step runs on the device, the next one is already planned and
+        launched with the tokens it needs taken from the device; the host reads a step's tokens one
+        step late.  The tokens are the same; a request that ends on a stop token costs one wasted row."""
         self.max_prefill_len = max_prefill_len
         make = dict(dtype=dtype, device=device, page_size=page_size, max_requests=max_batch,
                     max_positions=max_positions, use_graphs=use_graphs, prefix_cache=enable_prefix_cache)
@@ -58,6 +61,11 @@ class Engine:
                                    stop_ids=getattr(self.config, "eos_token_ids", ()))
         self._next_id = 0
         self._keys: Dict[int, int] = {}
+        self.run_ahead = run_ahead
+        self._in_flight: Optional[_InFlight] = None      # a launched step whose tokens are not read yet
+        self._host_tokens = [torch.empty(self.scheduler.max_batch, dtype=torch.int32, pin_memory=True)
+                             for _ in range(2)]
+        self._turn = 0
 
     # ---- streaming use -----------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -73,27 +81,59 @@ class Engine:
         return req
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self._in_flight is not None or self.scheduler.has_work()
 
-    def step(self) -> List[Request]:
-        """Plan one step, run it, sample, and return the requests that finished in it."""
-        plan = self.scheduler.schedule()
-        finished = list(plan.finished)
-        if not plan.entries:
-            return finished
+    def _launch(self, plan: StepPlan, device_tokens=None) -> "_InFlight":
+        """Run ``plan``'s step; its sampled tokens start their way to a pinned host buffer."""
         entries = [StepEntry(e.request.cache, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                    for e in plan.entries]
         sampling = [e.request for e in plan.entries if e.samples]
-        tokens: List[int] = []
-        if sampling:
-            _, ids = self.runner.step(entries, ensure_pages=False, sampling=(
-                [r.params.temperature for r in sampling], [r.params.top_k for r in sampling],
-                [uniform_draw(r.params.seed, r.sample_key, len(r.output)) if r.params.temperature else 0.0
-                 for r in sampling]))
-            tokens = ids.cpu().tolist()
-        else:
+        flight = _InFlight(plan, len(sampling), device_tokens is not None)
+        if not sampling:
             self.runner.step(entries, ensure_pages=False)
-        finished += self.scheduler.update(plan, tokens)
+            return flight
+        ahead = 1 if device_tokens is not None else 0       # a step planned ahead samples one token later
+        _, ids = self.runner.step(entries, ensure_pages=False, device_tokens=device_tokens, sampling=(
+            [r.params.temperature for r in sampling], [r.params.top_k for r in sampling],
+            [uniform_draw(r.params.seed, r.sample_key, len(r.output) + ahead) if r.params.temperature else 0.0
+             for r in sampling]))
+        self._turn ^= 1
+        flight.host = self._host_tokens[self._turn][:len(sampling)]
+        flight.host.copy_(ids, non_blocking=True)
+        flight.event = torch.cuda.Event()
+        flight.event.record()
+        flight.device = ids
+        return flight
+
+    def step(self) -> List[Request]:
+        """Plan one step, run it, sample, and return the requests that finished in it.  With
+        ``run_ahead`` the step whose results are returned was launched by the call before, and this
+        call launches the next one before it waits."""
+        finished: List[Request] = []
+        cur = self._in_flight
+        self._in_flight = None
+        if cur is None:
+            plan = self.scheduler.schedule()
+            finished = list(plan.finished)
+            if not plan.entries:
+                return finished
+            cur = self._launch(plan)
+        if self.run_ahead and cur.n_samples == len(cur.plan.entries) and cur.device is not None:
+            entries = [StepEntry(e.request.cache, [0], [0]) for e in cur.plan.entries]
+            if self.runner.can_take_device_tokens(entries):
+                ahead = self.scheduler.plan_ahead(cur.plan)
+                if ahead is not None:
+                    self._in_flight = self._launch(ahead, device_tokens=cur.device)
+        tokens: List[int] = []
+        if cur.n_samples:
+            cur.event.synchronize()
+            tokens = cur.host.tolist()
+        if self._in_flight is not None:
+            # the step launched ahead feeds exactly these tokens: now the prefix cache may know them
+            for e, t in zip(cur.plan.entries, tokens):
+                if e.request.cache is not None:
+                    self.runner.cache.log_tokens(e.request.cache, [t])
+        finished += self.scheduler.update(cur.plan, tokens)
         return finished
 
     # ---- batch use -----------------------------------------------------------
@@ -110,6 +150,18 @@ class Engine:
     @property
     def stats(self) -> dict:
         return dict(self.scheduler.stats, model_steps=self.runner.steps, model_tokens=self.runner.tokens_run)
+
+
+class _InFlight:
+    """A launched step: its plan, and where its sampled tokens arrive."""
+
+    def __init__(self, plan: StepPlan, n_samples: int, ahead: bool):
+        self.plan = plan
+        self.n_samples = n_samples
+        self.ahead = ahead
+        self.host: Optional[torch.Tensor] = None       # pinned; valid once ``event`` has passed
+        self.event: Optional[torch.cuda.Event] = None
+        self.device: Optional[torch.Tensor] = None     # the same tokens on the device
 
 
 class _PageSizing:

@@ -111,7 +111,8 @@ class ModelRunner:
                         self.cache.pools[g].release(table.pages.pop())
             raise
 
-    def step(self, entries: Sequence[StepEntry], ensure_pages: bool = True, sampling=None):
+    def step(self, entries: Sequence[StepEntry], ensure_pages: bool = True, sampling=None,
+             device_tokens: Optional[torch.Tensor] = None):
         """Run one batch; returns float32 logits [wanted places in entry order, vocab] on the device.
 
         With ``ensure_pages`` the pages the new tokens need are taken first (``OutOfPages`` if the
@@ -119,15 +120,21 @@ class ModelRunner:
         grown by its tokens.  With ``sampling`` = (temperatures, top_ks, draws), one per wanted
         place, returns (logits, sampled int32 tokens on the device).
 
+        ``device_tokens`` (int32 on the device, one per entry): the entries' single tokens are not known
+        on the host yet -- they are what an earlier step sampled and has not been read back -- and are
+        taken from there; the entries' own token values are ignored and the prefix cache is told later
+        (``cache.log_tokens``).  Only for batches that run as a graph (``can_take_device_tokens``).
+
         A batch of single tokens that all want logits runs as a replayed CUDA graph (one per padded
         batch size and block-table width) when ``use_graphs`` is set; the logits then live in a
         buffer that the next such step overwrites."""
         if ensure_pages:
             self._ensure(entries)
-        if self.use_graphs and not self.layout.fixed and all(
-                len(e.tokens) == 1 and len(e.want) == 1 for e in entries):
-            logits, tokens = self._graph_step(entries, sampling)
+        if self.can_take_device_tokens(entries):
+            logits, tokens = self._graph_step(entries, sampling, device_tokens)
             n_tokens = len(entries)
+        elif device_tokens is not None:
+            raise StepError("device_tokens: only a batch of single tokens that all want logits takes them")
         else:
             ctx = build_context(entries, self.cache, self.device, self.model.vocab_size, self.max_positions)
             logits = self.model.forward(ctx)
@@ -136,13 +143,18 @@ class ModelRunner:
                 tokens = self.sampler.sample(logits, *sampling)
             n_tokens = ctx.num_tokens
         for e in entries:
-            self.cache.commit(e.cache, len(e.tokens), e.tokens)
+            self.cache.commit(e.cache, len(e.tokens), e.tokens if device_tokens is None else None)
         self.steps += 1
         self.tokens_run += n_tokens
         return logits if sampling is None else (logits, tokens)
 
+    def can_take_device_tokens(self, entries: Sequence[StepEntry]) -> bool:
+        """True if this batch runs as a replayed graph: single tokens that all want logits."""
+        return self.use_graphs and not self.layout.fixed and all(
+            len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+
     # ---- decode steps as CUDA graphs ---------------------------------------------
-    def _graph_step(self, entries: Sequence[StepEntry], sampling):
+    def _graph_step(self, entries: Sequence[StepEntry], sampling, device_tokens=None):
         import numpy as np
         lens, starts, slots = validate(entries, self.cache, self.model.vocab_size, self.max_positions)
         R = len(entries)
@@ -168,6 +180,11 @@ class ModelRunner:
         else:
             h[o:o + 3 * Bp] = 0
         g.upload(host)
+        if device_tokens is not None:
+            o = g.lay.off["tokens"]
+            g.dev[o:o + R].copy_(device_tokens[:R])
+            if Bp > R:      # the padding repeats entry 0 and writes to its cache slot: it must carry its token too
+                g.dev[o + R:o + Bp].copy_(device_tokens[0:1].expand(Bp - R))
         g.run()
         return g.logits[:R], (g.tokens[:R] if g.tokens is not None else None)
 

@@ -206,6 +206,30 @@ class Scheduler:
             budget -= n
         return plan
 
+    def plan_ahead(self, plan: StepPlan) -> Optional[StepPlan]:
+        """The step after ``plan``, planned before ``plan``'s sampled tokens are known: possible when
+        ``plan`` is one decoded token for every running request, nobody waits, and no request can be
+        seen to end with it.  The entries' tokens are placeholders (the step function takes them from
+        the device); a request that ends with ``plan`` after all (a stop token) keeps its entry and
+        ``update`` skips it.  None if the next step has to be planned the usual way."""
+        if self.waiting or not plan.entries or plan.preempted or len(plan.entries) != len(self.running):
+            return None
+        for e in plan.entries:
+            r = e.request
+            if len(e.tokens) != 1 or not e.samples or r.cache is None:
+                return None
+            if len(r.output) + 1 >= r.params.max_new_tokens or \
+                    len(r.prompt) + len(r.output) + 1 >= self.max_positions:
+                return None                  # its last token: the usual path ends it
+        ahead = StepPlan()
+        try:
+            for e in plan.entries:
+                self.cache.ensure(e.request.cache, e.request.cache.num_tokens + 1)
+                ahead.entries.append(PlannedEntry(e.request, [0], True))
+        except OutOfPages:
+            return None                      # the usual path decides whom to preempt
+        return ahead
+
     # ---- results -----------------------------------------------------------
     def _stops(self, req: Request, token: int) -> bool:
         if req.params.ignore_eos:
@@ -220,6 +244,10 @@ class Scheduler:
         self.stats["steps"] += 1
         for e in plan.entries:
             req = e.request
+            if req.finished:               # planned ahead, and the step before ended it
+                if e.samples:
+                    next(it, None)
+                continue
             n = len(e.tokens)
             req.num_computed += n          # the step function has committed them to the cache
             if n == 1 and req.output and e.samples:

@@ -171,3 +171,41 @@ def test_prefix_cache_shares_pages_and_keeps_logits(folders, dtype, tmp_path):
     assert outs[False][0] == outs[True][0]
     assert outs[True][1]["prompt_tokens"] < outs[False][1]["prompt_tokens"]
     assert outs[True][1].get("prefix_hit_tokens", 0) >= 64
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_changes_no_token(folders, dtype):
+    """With ``run_ahead`` a decode step is launched before the tokens of the step before it are read:
+    the outputs must equal those of the step-by-step engine -- greedy and with temperature, with stop
+    tokens that end requests one step late for the device, with the prefix cache recording generated
+    tokens -- and most decode steps must indeed have run ahead."""
+    from qwen_decoder_b200.engine import Engine, SamplingParams
+    cfg, _ = plain_model.read_folder(folders["A"])
+    prompts = prompts_for(cfg, [5, 17, 33, 8], seed=3)
+
+    def run(run_ahead):
+        eng = Engine(folders["A"], dtype=dtype, num_pages=64, max_batch=4, run_ahead=run_ahead,
+                     enable_prefix_cache=True)
+        probe = eng.generate(prompts[:1], SamplingParams(max_new_tokens=12))[0]
+        params = [SamplingParams(max_new_tokens=40, stop_ids=[probe[7]]),          # ends on a stop token
+                  SamplingParams(max_new_tokens=25, temperature=0.7, seed=5, ignore_eos=True),
+                  SamplingParams(max_new_tokens=31, ignore_eos=True),
+                  SamplingParams(max_new_tokens=18, temperature=1.1, top_k=20, seed=9, ignore_eos=True)]
+        # all requests are there from the start, so that both engines run the same batches (a request
+        # that arrives in between is planned one step later when running ahead, and other batches round
+        # the logits differently)
+        reqs = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while eng.has_work():
+            eng.step()
+        assert eng.runner.cache.free_pages() == [64]
+        eng.runner.cache.check()
+        # the same prompt again: its pages, generated tokens included, are known to the prefix cache
+        again = eng.generate([prompts[2] + reqs[2].output[:20]], SamplingParams(max_new_tokens=4, ignore_eos=True))
+        return [r.output for r in reqs] + again, [r.finish_reason for r in reqs], eng.stats
+
+    out_a, why_a, stats_a = run(True)
+    out_b, why_b, stats_b = run(False)
+    assert out_a == out_b and why_a == why_b
+    assert why_a[0] == "stop" and len(out_a[0]) < 40
+    assert stats_a["prefix_hit_tokens"] == stats_b["prefix_hit_tokens"] > 0
+    assert stats_a["model_steps"] >= stats_b["model_steps"]      # a wasted row now and then, never fewer steps

@@ -178,3 +178,100 @@ def test_prefix_cache_skips_known_beginnings_and_keeps_the_output():
     # requests 2 and 3 start after 0 and 1 have cached the 32 tokens of the stem's two full pages
     assert s1.stats["prefix_hit_tokens"] >= 2 * 32 and s1.stats["prompt_tokens"] == 4 * 42 - s1.stats["prefix_hit_tokens"]
     assert s1.cache.free_pages() == [64]
+
+
+def run_ahead(sched, reqs, max_steps=10000):
+    """The engine's pipelined loop with a fake step: a step's sampled tokens are handed to ``update`` only
+    after the next step has been planned (``plan_ahead``) and committed."""
+    for r in reqs:
+        sched.add_request(r)
+    ahead_steps = usual_steps = 0
+    in_flight = None                      # (plan, sampled tokens not yet given to update)
+
+    def launch(plan, ahead):
+        sampled = []
+        for e in plan.entries:
+            req = e.request
+            # what the cache holds after the tokens of this step: known from the cache alone
+            sched.cache.commit(req.cache, len(e.tokens))
+            if e.samples:
+                known = req.all_tokens() + ([pending[req.request_id]] if ahead else [])
+                sampled.append(next_token(known))
+        return plan, sampled
+
+    pending = {}
+    while sched.has_work() or in_flight is not None:
+        if in_flight is None:
+            plan = sched.schedule()
+            if not plan.entries:
+                continue
+            in_flight = launch(plan, False)
+            usual_steps += 1
+        plan, sampled = in_flight
+        in_flight = None
+        pending = {e.request.request_id: t for e, t in zip([e for e in plan.entries if e.samples], sampled)}
+        nxt = sched.plan_ahead(plan)
+        if nxt is not None:
+            in_flight = launch(nxt, True)
+            ahead_steps += 1
+        sched.update(plan, sampled)
+        sched.cache.check()
+        assert ahead_steps + usual_steps < max_steps
+    return usual_steps, ahead_steps
+
+
+def test_planning_ahead_gives_the_same_output_and_stops_where_it_must():
+    def requests():
+        return [Request(i, list(range(1, n + 1)), SamplingParams(max_new_tokens=m, ignore_eos=True))
+                for i, (n, m) in enumerate([(30, 12), (10, 40), (50, 25)])]
+    a = requests()
+    usual, ahead = run_ahead(Scheduler(manager(200), max_batch=4, max_prefill_tokens_per_step=24), a)
+    for r in a:
+        assert r.output == expected_output(r.prompt, r.params.max_new_tokens) and r.finish_reason == "length"
+    assert ahead > usual          # most decode steps were planned before their tokens were known
+    # a stop token ends a request one step late for the device, never for the output
+    probe = Request(0, [5, 6, 7], SamplingParams(max_new_tokens=30, ignore_eos=True))
+    run(Scheduler(manager(50)), [probe])
+    stop = probe.output[9]
+    b = [Request(0, [5, 6, 7], SamplingParams(max_new_tokens=30, stop_ids=[stop])),
+         Request(1, [9, 9, 9, 9], SamplingParams(max_new_tokens=30, ignore_eos=True))]
+    s = Scheduler(manager(50))
+    run_ahead(s, b)
+    assert b[0].finish_reason == "stop" and b[0].output == probe.output[:probe.output.index(stop)]
+    assert b[1].output == expected_output(b[1].prompt, 30)
+    assert s.cache.free_pages() == [50] and not s.cache.live
+
+
+def test_planning_ahead_declines_when_the_usual_path_has_to_decide():
+    s = Scheduler(manager(4, page_size=16), max_batch=4)
+    r0 = Request(0, list(range(1, 31)), SamplingParams(max_new_tokens=40, ignore_eos=True))
+    s.add_request(r0)
+    plan = s.schedule()
+    for e in plan.entries:
+        s.cache.commit(e.request.cache, len(e.tokens))
+    # the plan fed a prompt of several tokens: entries are not single decoded tokens
+    assert s.plan_ahead(plan) is None
+    s.update(plan, [7])
+    plan = s.schedule()
+    s.cache.commit(r0.cache, 1)
+    # somebody waits: admission is the usual path's business
+    s.add_request(Request(1, [1, 2, 3], SamplingParams(max_new_tokens=4)))
+    assert s.plan_ahead(plan) is None
+    s.waiting.clear()
+    ahead = s.plan_ahead(plan)
+    assert ahead is not None and [e.request for e in ahead.entries] == [r0]
+    s.update(plan, [8])
+    # out of pages: 4 pages of 16 hold 64 tokens; at 64 cached tokens the next one needs a fifth page
+    while r0.cache.num_tokens < 63:
+        s.cache.commit(r0.cache, 1)
+        s.update(ahead, [9])
+        ahead = s.plan_ahead(ahead) or ahead
+    s.cache.commit(r0.cache, 1)
+    assert r0.cache.num_tokens == 64 and s.plan_ahead(ahead) is None
+    # the last token of a request: the usual path ends it
+    s2 = Scheduler(manager(20))
+    r = Request(0, [1, 2, 3], SamplingParams(max_new_tokens=2, ignore_eos=True))
+    s2.add_request(r)
+    p = s2.schedule(); s2.cache.commit(r.cache, 3); s2.update(p, [4])
+    p = s2.schedule(); s2.cache.commit(r.cache, 1)
+    assert s2.plan_ahead(p) is None
