@@ -145,6 +145,25 @@ def micro(args):
         splits = decode_splits(T * G, ctx)
         run = lambda: kernels.decode_attention(q, H * d, out, kv, bt, tr, pos, T, H, G, d, ps, 1 / math.sqrt(d), 0, splits)
         work = {"bytes": T * ctx * 2 * G * d * 2, "flops": 4 * T * ctx * H * d, "splits": splits}
+    elif args.micro == "decode_attention_rope":
+        # from the float32 partial sums of q, k, v: bias, rotation, cache write and attention in one kernel
+        ctx = args.context + 128
+        npg = (ctx + ps) // ps
+        kv = torch.randn(T * npg + 4, 2, G, ps, d, device=dev).bfloat16()
+        bt = torch.arange(T * npg, dtype=torch.int32, device=dev).view(T, npg).contiguous()
+        part = torch.randn(2, T, (H + 2 * G) * d, device=dev) * 0.5
+        bias = torch.randn((H + 2 * G) * d, device=dev)
+        out = torch.empty(T, H * d, device=dev, dtype=torch.bfloat16)
+        tr = torch.arange(T, dtype=torch.int32, device=dev)
+        pos = torch.full((T,), ctx - 1, dtype=torch.int32, device=dev)
+        slots = (bt[:, (ctx - 1) // ps] * ps + (ctx - 1) % ps).to(torch.int32)
+        ang = torch.arange(ctx, device=dev, dtype=torch.float32)[:, None] * torch.rand(d // 2, device=dev)[None, :]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        from qwen_decoder_b200.parts.attention import decode_rope_splits
+        splits = decode_rope_splits(T * G, ctx)
+        run = lambda: kernels.decode_attention_rope(part, bias, out, kv, bt, tr, pos, slots, H, G, d, ps,
+                                                    1 / math.sqrt(d), 0, splits, True, d, 0, cos, sin)
+        work = {"bytes": T * ctx * 2 * G * d * 2, "flops": 4 * T * ctx * H * d, "splits": splits}
     else:
         T = args.prefill_tokens
         kv = torch.randn(T // ps + 4, 2, G, ps, d, device=dev).bfloat16()
@@ -187,7 +206,7 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "prefill_attention"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention"],
                     help="time one kernel alone at the 3B shape (for profiles/), print one JSON line and exit")
     ap.add_argument("--micro-impl", default="stream", choices=["stream", "regs", "tc5", "cublas"])
     ap.add_argument("--micro-shape", default="lm_head", choices=["qkv", "o", "gate_up", "down", "lm_head"])
