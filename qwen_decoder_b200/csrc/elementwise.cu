@@ -284,6 +284,48 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int H, int G, int d, i
   }
 }
 
+// bfloat16, adjacent pairs, head size and rotated width multiples of 8: a thread takes 16 bytes (four pairs)
+// of q, k or v of one token, with its cosines and sines as two float4.
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int T, int H, int G, int d, int rotary_dim,
+                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         const int* __restrict__ positions, bf16* __restrict__ kv,
+                         const int* __restrict__ slot_map, int page_size, int write_kv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = (H + 2 * G) * d / 8;                 // 16-byte pieces per token
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * per_row) return;
+  const int t = (int)(idx / per_row), piece = (int)(idx - (long long)t * per_row);
+  const int head = piece / (d / 8), c8 = (piece - head * (d / 8)) * 8;      // element offset inside the head
+  if (head >= H && !write_kv) return;
+  bf16* src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d + c8;
+  uint4 raw = *reinterpret_cast<const uint4*>(src);
+  if (head < H + G && cos_t && c8 < rotary_dim) {
+    const int half = rotary_dim >> 1;
+    const size_t tab = (size_t)positions[t] * half + (c8 >> 1);
+    const float4 cv = *reinterpret_cast<const float4*>(cos_t + tab), sv = *reinterpret_cast<const float4*>(sin_t + tab);
+    const float cs[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
+    unsigned* u = reinterpret_cast<unsigned*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
+      float a = __low2float(v), b = __high2float(v);
+      __nv_bfloat162 r = __floats2bfloat162_rn(a * cs[i] - b * sn[i], a * sn[i] + b * cs[i]);
+      u[i] = *reinterpret_cast<unsigned*>(&r);
+    }
+  }
+  if (head < H) {
+    *reinterpret_cast<uint4*>(src) = raw;
+  } else {
+    const int slot = slot_map[t];
+    const int page = slot / page_size, off = slot - page * page_size;
+    const int g = head < H + G ? head - H : head - H - G;
+    const size_t base = (size_t)page * 2 * G * page_size * d + (head < H + G ? 0 : (size_t)G * page_size * d);
+    *reinterpret_cast<uint4*>(kv + base + ((size_t)g * page_size + off) * d + c8) = raw;
+  }
+}
+
 extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d, int rotary_dim,
                                 int pairing, const float* cos_t, const float* sin_t,
                                 const int* positions, void* kv, const int* slot_map, int page_size,
@@ -294,7 +336,12 @@ extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d
     qd_launch(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                        sin_t, positions, (float*)kv, slot_map,
                                                        page_size, write_kv);
-  else if (dtype == QD_BF16)
+  else if (dtype == QD_BF16 && pairing == 0 && d % 8 == 0 && rotary_dim % 8 == 0 && ((uintptr_t)qkv & 15) == 0 &&
+           (!write_kv || ((uintptr_t)kv & 15) == 0) && (!cos_t || (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0)) {
+    const long long pieces = (long long)T * (H + 2 * G) * d / 8;
+    qd_launch(rope_kv_write_vec_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream, (bf16*)qkv, T, H, G,
+              d, rotary_dim, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size, write_kv);
+  } else if (dtype == QD_BF16)
     qd_launch(rope_kv_write_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                       sin_t, positions, (bf16*)kv, slot_map,
                                                       page_size, write_kv);
