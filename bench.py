@@ -172,7 +172,8 @@ def micro(args):
         out = torch.empty(T, H * d, device=dev, dtype=torch.bfloat16)
         cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
         st = torch.tensor([0], dtype=torch.int32, device=dev)
-        run = lambda: kernels.prefill_attention(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0)
+        fn = kernels.prefill_attention if args.micro_impl == "regs" else kernels.prefill_attention_tc5
+        run = lambda: fn(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0)
         work = {"bytes": T * (H + 2 * G) * d * 2 * 2, "flops": 4 * d * H * (T * (T + 1) // 2)}
     for _ in range(3):
         run()
@@ -186,7 +187,7 @@ def micro(args):
         ts.append(e0.elapsed_time(e1) * 1e3)
     ts.sort()
     us = ts[len(ts) // 2]
-    print(json.dumps({"micro": args.micro, "impl": args.micro_impl if args.micro == "gemm" else "ours",
+    print(json.dumps({"micro": args.micro, "impl": args.micro_impl if args.micro == "gemm" else ("mma.sync" if args.micro == "prefill_attention" and args.micro_impl == "regs" else "ours"),
                       "shape": args.micro_shape if args.micro == "gemm" else None, "tokens": T, "us": round(us, 2),
                       "GB/s": round(work["bytes"] / us / 1e3, 1), "TFLOP/s": round(work["flops"] / us / 1e6, 2),
                       "note": "eager launch between CUDA events after an L2 flush; includes ~8 us of launch latency",

@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_generic": "attention_generic.cu",
     "attention_flash": "attention_flash.cu",
     "attention_decode_rope": "attention_decode_rope.cu",
+    "attention_tc5": "attention_tc5.cu",
     "sampling": "sampling.cu",
     "decode_fused": "decode_fused.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",

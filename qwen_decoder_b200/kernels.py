@@ -450,6 +450,34 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                                          _ptr(draws), _ptr(out), _stream()), "sample")
 
 
+def prefill_tc5_supported(dtype, H: int, G: int, d: int, page_size: int) -> bool:
+    """What the tcgen05 prefill attention takes: bfloat16, head size 64 or 128, 1, 2, 4, 8 or 16 query
+    heads per KV head, pages of a multiple of 16 tokens."""
+    return (dtype == torch.bfloat16 and d in (64, 128) and H % G == 0 and H // G in (1, 2, 4, 8, 16)
+            and page_size % 16 == 0)
+
+
+def prefill_attention_tc5(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
+                          block_table: torch.Tensor, cu_tokens: torch.Tensor, start_pos: torch.Tensor,
+                          n_requests: int, n_tokens: int, H: int, G: int, d: int, page_size: int, scale: float,
+                          window: int) -> None:
+    """``prefill_attention`` on tcgen05 tensor cores (accumulators in tensor memory, K/V tiles by TMA)."""
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
+    assert block_table.dtype == torch.int32 and block_table.shape[0] >= n_requests
+    assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
+    _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _check(library("attention_tc5").qd_prefill_attention_tc5(
+        _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _LL(kv.shape[0]), _ptr(block_table), _I(block_table.shape[1]),
+        _ptr(cu_tokens), _ptr(start_pos), _I(n_requests), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size),
+        _F(scale), _I(window), _stream()), "prefill_attention_tc5")
+
+
+def prefill_attention_tc5_status() -> int:
+    """0, or which bounded wait of the tcgen05 attention kernel ran out since the last call (synchronises)."""
+    return int(library("attention_tc5").qd_prefill_attention_tc5_status())
+
+
 # ------------------------------------------------------------------ a whole decode step in one kernel
 class FusedLayer(ctypes.Structure):
     """One schedule entry of the fused decode step (FdLayer in csrc/decode_fused.cu)."""

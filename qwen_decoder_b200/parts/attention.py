@@ -100,6 +100,10 @@ class GQAttention(Mixer):
                 qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
                 ctx.positions, ctx.num_tokens, H, G, d, ps, self.scale, window,
                 decode_splits(ctx.num_tokens * G, min(ctx.max_context, window or ctx.max_context)))
+        elif _PREFILL_TC5 and kernels.prefill_tc5_supported(x.dtype, H, G, d, ps):
+            kernels.prefill_attention_tc5(
+                qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
+                ctx.num_requests, ctx.num_tokens, H, G, d, ps, self.scale, window)
         elif kernels.flash_prefill_supported(x.dtype, H, G, d, ps):
             kernels.prefill_attention(
                 qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
@@ -114,6 +118,7 @@ class GQAttention(Mixer):
 import os as _os
 _TARGET_CTAS = int(_os.environ.get("QD_DECODE_ATTN_CTAS", "148"))
 _DECODE_ROPE = _os.environ.get("QD_DECODE_ROPE", "1") != "0"
+_PREFILL_TC5 = _os.environ.get("QD_PREFILL_TC5", "1") != "0"      # prompt portions on tcgen05 where its sizes allow
 _ROPE_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ROPE_CTAS", "148"))
 
 

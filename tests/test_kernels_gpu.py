@@ -264,6 +264,38 @@ def test_prefill_attention_tensor_cores(cfg):
         close(outc[int(cu[r]):int(cu[r + 1])], want, dt, scale=float(vs[r].abs().max()))
 
 
+@pytest.mark.parametrize("cfg", [(16, 2, 128, 16, None), (8, 8, 128, 32, None), (4, 1, 64, 16, None),
+                                 (16, 1, 64, 64, 40), (2, 1, 128, 16, 300)])
+def test_prefill_attention_tcgen05(cfg):
+    """The same portions through the tcgen05 kernel (tensor memory accumulators, K/V by TMA from the pages):
+    with and without history, one token up to hundreds, several requests, windows, tiles that end inside
+    a key tile of 128."""
+    from qwen_decoder_b200 import kernels
+    H, G, d, page_size, window = cfg
+    assert kernels.prefill_tc5_supported(torch.bfloat16, H, G, d, page_size)
+    dt = torch.bfloat16
+    plan = [(0, 150), (70, 45), (129, 1), (15, 2), (0, 1), (200, 330), (0, 128), (127, 129)]
+    lens = [a + b for a, b in plan]
+    kv, bt, ks, vs = _paged_setup(dt, lens, G, d, page_size, seed=13)
+    g = torch.Generator().manual_seed(14)
+    T = sum(b for _, b in plan)
+    q = torch.randn(T, H * d, generator=g).to(dt)
+    cu = torch.tensor([0] + list(torch.tensor([b for _, b in plan]).cumsum(0)), dtype=torch.int32)
+    start = torch.tensor([a for a, _ in plan], dtype=torch.int32)
+    out = torch.full((T, H * d), float("nan"), dtype=dt, device=DEV)
+    kernels.prefill_attention_tc5(q.to(DEV), H * d, out, kv.to(DEV), bt.to(DEV), cu.to(DEV), start.to(DEV), len(plan),
+                                  T, H, G, d, page_size, 1.0 / math.sqrt(d), window or 0)
+    assert kernels.prefill_attention_tc5_status() == 0
+    outc = out.cpu()
+    for r, (a, b) in enumerate(plan):
+        n = a + b
+        qq = torch.zeros(n, H * d, dtype=torch.float64)
+        qq[a:] = q[int(cu[r]):int(cu[r + 1])].double()
+        want = plain_model.attention(qq, ks[r].double().reshape(n, G * d), vs[r].double().reshape(n, G * d),
+                                     H, G, d, window)[a:]
+        close(outc[int(cu[r]):int(cu[r + 1])], want, dt, scale=float(vs[r].abs().max()))
+
+
 @pytest.mark.parametrize("shape", [(1, 48, 64), (7, 130, 72), (8, 2048, 2048), (9, 100, 136), (16, 64, 1000),
                                    (33, 257, 264), (64, 96, 512)])
 def test_gemm_skinny(shape):
