@@ -4,13 +4,15 @@
 //
 // A CTA takes 128 rows = (128 / gs) tokens x the gs query heads of one KV head (as attention_flash.cu
 // does with 64 or 128 rows), and walks key tiles of 128 through the request's block table.  Warps:
-//   4        producer: per key tile, 16-key boxes of K and of V (two 64-column halves each) from the pages
-//   5        issues the MMAs (one thread): S = Q K^T (both operands K-major), O' = P V (V is MN-major:
-//            its rows are keys, the contraction dimension)
-//   0..3     softmax: thread r owns row r (= TMEM lane r): loads S from tensor memory, scales, masks,
-//            keeps the running maximum and sum, writes P as bfloat16 into shared memory in the layout
-//            the MMA reads, then adds O' into its output row (held in registers, rescaled when the
-//            maximum moves).
+//   8        producer: per key tile, 16-key boxes of K and of V (two 64-column halves each) from the pages
+//   9        issues the MMAs (one thread): S = Q K^T (both operands K-major; S has two buffers in tensor
+//            memory, so the next tile's scores are computed while this tile's softmax runs), O' = P V (V is
+//            MN-major: its rows are keys, the contraction dimension)
+//   0..7     softmax: two threads per row (= TMEM lane), one for keys 0..63 and output columns 0..d/2-1,
+//            one for the rest: each loads its half of S from tensor memory in one go, scales, masks, shares
+//            the row maximum through shared memory, writes P as bfloat16 into shared memory in the layout
+//            the MMA reads, then adds its half of O' into its output columns (held in registers, rescaled
+//            when the maximum moves).
 // Formulas: gpu_kernels.cu:223-311 of the reference (scores q.k / sqrt(d), causal, softmax, weighted sum).
 // Keys past a row's position are masked on the scores; their V rows are whatever finite values the
 // pages hold (the cache starts as zeros and is only ever written with finite numbers), times zero.
@@ -21,7 +23,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
-#define AT_THREADS 192
+#define AT_THREADS 320
+#define AT_SOFTMAX_THREADS 256
 #define AT_ROWS 128
 #define AT_KEYS 128
 #define AT_SPIN_LIMIT (1u << 24)
@@ -103,6 +106,39 @@ __device__ __forceinline__ void at_tmem_ld16(unsigned taddr, float (&v)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
+// N consecutive columns of this thread's TMEM lane (N = 32 or 64) in one request
+template <int N>
+__device__ __forceinline__ void at_tmem_ld(unsigned taddr, float (&v)[N]) {
+  static_assert(N == 32 || N == 64, "32 or 64 columns");
+  unsigned r[N];
+  if (N == 32) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,"
+        "%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),
+          "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),
+          "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),
+          "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),
+          "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr));
+  }
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < N; i++) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void at_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -121,6 +157,12 @@ __device__ __forceinline__ unsigned at_swz(int r, int c) {
   return (unsigned)((c >> 3) * (AT_ROWS * 128) + (r >> 3) * 1024 + (r & 7) * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
+__device__ __forceinline__ long long at_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 struct AtParams {
   const bf16* q; long long q_stride; bf16* out;
   const int* block_table; int max_blocks;
@@ -128,20 +170,26 @@ struct AtParams {
   int R, H, G, page_size, window, tok_tile;
   float scale_log2e;
   int* status;
+  long long* timeline;     // null, or 16 x 8 nanosecond stamps of row 0's softmax thread and 16 x 4 of the MMA thread of one
+                           // CTA with 16 key tiles (for measurements)
 };
 
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 1)
 prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const AtParams p) {
   constexpr int NB = HD / 64;                       // 64-column blocks of a row
+  constexpr int DH = HD / 2;                        // output columns per softmax thread
   constexpr int TILE_BYTES = AT_ROWS * HD * 2;      // one [128][HD] bfloat16 tile
+  constexpr unsigned TMEM_COLS = 512;               // S buffer 0: 0..127, S buffer 1: 128..255, O': 256..256+HD-1
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* base = smem_raw + ((1024 - (at_smem(smem_raw) & 1023)) & 1023);
   unsigned char* q_s = base;                        // Q tile, K-major
   unsigned char* p_s = q_s + TILE_BYTES;            // P tile [128 rows][128 keys], K-major
   unsigned char* k_s = p_s + AT_ROWS * AT_KEYS * 2; // 2 stages of K [128 keys][HD], K-major
   unsigned char* v_s = k_s + 2 * TILE_BYTES;        // 2 stages of V [128 keys][HD], MN-major for the product
-  __shared__ unsigned long long k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, p_full, o_full, o_free, q_full;
+  __shared__ unsigned long long k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, o_full, o_free, q_full;
+  __shared__ float mx_s[2][2][AT_ROWS];             // [tile parity][half][row]: the halves' maxima
+  __shared__ float l_s[2][AT_ROWS];                 // the halves' sums, at the end
   __shared__ unsigned tmem_slot;
   __shared__ int dead;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -150,20 +198,22 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     dead = 0;
     for (int s = 0; s < 2; s++) {
       at_mbar_init(&k_full[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_empty[s], 1);
+      at_mbar_init(&s_full[s], 1);
     }
-    at_mbar_init(&s_full, 1); at_mbar_init(&o_full, 1);
-    at_mbar_init(&p_full, AT_ROWS); at_mbar_init(&o_free, AT_ROWS); at_mbar_init(&q_full, AT_ROWS);
+    at_mbar_init(&o_full, 1);
+    at_mbar_init(&p_full, AT_SOFTMAX_THREADS); at_mbar_init(&o_free, AT_SOFTMAX_THREADS);
+    at_mbar_init(&q_full, AT_SOFTMAX_THREADS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_slot)), "r"(256u)
-                 : "memory");
+  if (warp == 9) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_slot)),
+                 "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   at_fence_before();
   __syncthreads();
   at_fence_after();
-  const unsigned tmem = tmem_slot;                  // S: columns 0..127, O': columns 128..128+HD-1
+  const unsigned tmem = tmem_slot;
   pdl_wait();
 
   // ---- which request and which tokens (tiles numbered request by request, the longest histories first)
@@ -189,36 +239,38 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   const int kt_lo = key_lo_tile / AT_KEYS, kt_hi = idle ? kt_lo : (key_hi + AT_KEYS - 1) / AT_KEYS;
   const int n_kt = kt_hi - kt_lo;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ producer
+    // K and V tiles are asked for in the order the tensor cores take them: K(0), K(1), V(0), K(2), V(1), ...
+    // (the scores of tile j + 1 are computed before the product of tile j), so that a K stage is refilled as
+    // soon as its scores are done and does not wait for the V stage beside it.
     if (!idle) {
       const int* bt = p.block_table + (size_t)r * p.max_blocks;
-      for (int j = 0; j < n_kt; j++) {
+      auto load = [&](int j, int which) {             // which: 0 = K, 1 = V
         const int s = j & 1;
         const unsigned ph = (j >> 1) & 1;
-        if (!at_mbar_wait(&k_empty[s], ph ^ 1, &dead) && lane == 0) atomicExch(p.status, 1);
-        if (!at_mbar_wait(&v_empty[s], ph ^ 1, &dead) && lane == 0) atomicExch(p.status, 1);
-        if (lane == 0) {
-          at_mbar_expect_tx(&k_full[s], TILE_BYTES);
-          at_mbar_expect_tx(&v_full[s], TILE_BYTES);
-        }
+        unsigned long long* empty = which ? &v_empty[s] : &k_empty[s];
+        unsigned long long* full = which ? &v_full[s] : &k_full[s];
+        if (!at_mbar_wait(empty, ph ^ 1, &dead) && lane == 0) atomicExch(p.status, 1);
+        if (lane == 0) at_mbar_expect_tx(full, TILE_BYTES);
         __syncwarp();
         if (lane < AT_KEYS / 16) {                    // one 16-key box row per lane
           const int key0 = (kt_lo + j) * AT_KEYS + lane * 16;
           int page = key0 < key_hi ? bt[key0 / p.page_size] : -1;
           if (page < 0) page = 0;                     // no such keys: any page will do, the scores are masked
-          const int row_k = ((page * 2 + 0) * p.G + g) * p.page_size + key0 % p.page_size;
-          const int row_v = ((page * 2 + 1) * p.G + g) * p.page_size + key0 % p.page_size;
+          const int row0 = ((page * 2 + which) * p.G + g) * p.page_size + key0 % p.page_size;
+          unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES + lane * 2048;     // 16 keys = two groups of 8 rows
 #pragma unroll
-          for (int cb = 0; cb < NB; cb++) {
-            const unsigned off = (unsigned)(cb * (AT_KEYS * 128) + lane * 2048);     // 16 keys = two groups of 8 rows
-            at_tma_2d(k_s + s * TILE_BYTES + off, &kv_map, cb * 64, row_k, &k_full[s]);
-            at_tma_2d(v_s + s * TILE_BYTES + off, &kv_map, cb * 64, row_v, &v_full[s]);
-          }
+          for (int cb = 0; cb < NB; cb++) at_tma_2d(dst + cb * (AT_KEYS * 128), &kv_map, cb * 64, row0, full);
         }
+      };
+      if (n_kt > 0) load(0, 0);
+      for (int j = 0; j < n_kt; j++) {
+        if (j + 1 < n_kt) load(j + 1, 0);
+        load(j, 1);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && !idle) {
       const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_KEYS >> 3) << 17) | ((unsigned)(AT_ROWS >> 4) << 24);
@@ -235,16 +287,24 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
         for (int k = 0; k < HD / 16; k++) {
           // 16 columns = 32 bytes inside a 64-column block; the next block is 128 rows x 128 bytes further
           const unsigned long long adv = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
-          at_umma(tmem, dq + adv, dk + adv, idesc_qk, k ? 1u : 0u);
+          at_umma(tmem + s * AT_KEYS, dq + adv, dk + adv, idesc_qk, k ? 1u : 0u);
         }
         at_commit(&k_empty[s]);
-        at_commit(&s_full);
+        at_commit(&s_full[s]);
       };
+      const bool mstamp = p.timeline && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
       if (!at_mbar_wait(&q_full, 0, &dead)) atomicExch(p.status, 3);
+      at_fence_after();
       if (n_kt > 0) issue_qk(0);
       for (int j = 0; j < n_kt; j++) {
         const int s = j & 1;
+        // the next tile's scores go to the other S buffer while this tile's softmax runs (that buffer was
+        // read for tile j - 1, whose P has been waited for below)
+        if (mstamp) p.timeline[128 + j * 4 + 0] = at_now();
+        if (j + 1 < n_kt) issue_qk(j + 1);
+        if (mstamp) p.timeline[128 + j * 4 + 1] = at_now();
         if (!at_mbar_wait(&p_full, j & 1, &dead)) atomicExch(p.status, 4);
+        if (mstamp) p.timeline[128 + j * 4 + 2] = at_now();
         if (!at_mbar_wait(&v_full[s], (j >> 1) & 1, &dead)) atomicExch(p.status, 5);
         if (j > 0 && !at_mbar_wait(&o_free, (j - 1) & 1, &dead)) atomicExch(p.status, 6);
         at_fence_after();
@@ -254,25 +314,26 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
           const unsigned long long adv_p = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
           // 16 keys = two groups of 8 rows of V; the d columns 64.. lie one [128 keys][128 bytes] block further
           const unsigned long long dv = at_desc_mnmajor(v_addr + k * 2048, AT_KEYS * 128);
-          at_umma(tmem + 128, dp + adv_p, dv, idesc_pv, k ? 1u : 0u);
+          at_umma(tmem + 2 * AT_KEYS, dp + adv_p, dv, idesc_pv, k ? 1u : 0u);
         }
         at_commit(&v_empty[s]);
         at_commit(&o_full);
-        if (j + 1 < n_kt) issue_qk(j + 1);
+        if (mstamp) p.timeline[128 + j * 4 + 3] = at_now();
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: thread = row
-    const int row = threadIdx.x;                                   // 0..127, also the TMEM lane
+    // ------------------------------------------------------------------ softmax: two threads per row
+    const int row = (warp & 3) * 32 + lane;                        // 0..127, also the TMEM lane
+    const int h = warp >> 2;                                       // which half of the keys and of the columns
     const int t = row / gs, hh = row - t * gs;
     const bool ok = !idle && t < n_tok;
     const int pos = pos0 + t;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    // Q row into shared memory, in the layout the MMA reads
+    // this thread's half of the Q row into shared memory, in the layout the MMA reads
     {
       const bf16* qr = p.q + (size_t)(tok0 + t) * p.q_stride + (size_t)(g * gs + hh) * HD;
 #pragma unroll
-      for (int c = 0; c < HD / 8; c++) {
+      for (int c = h * (HD / 16); c < (h + 1) * (HD / 16); c++) {
         uint4 v = make_uint4(0, 0, 0, 0);
         if (ok) v = *reinterpret_cast<const uint4*>(qr + c * 8);
         *reinterpret_cast<uint4*>(q_s + at_swz(row, c)) = v;
@@ -280,75 +341,94 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       at_fence_async_smem();
       at_mbar_arrive(&q_full);
     }
-    float o[HD];
+    float o[DH];
 #pragma unroll
-    for (int i = 0; i < HD; i++) o[i] = 0.f;
+    for (int i = 0; i < DH; i++) o[i] = 0.f;
     float m = -INFINITY, l = 0.f;
-    const unsigned t_row = tmem + ((unsigned)(warp * 32) << 16);   // this warp's 32 lanes
-    for (int j = 0; j < n_kt; j++) {
-      const int key_base = (kt_lo + j) * AT_KEYS;
-      if (!at_mbar_wait(&s_full, j & 1, &dead) && lane == 0) atomicExch(p.status, 7);
+    const unsigned t_lane = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
+    const bool stamp = p.timeline && threadIdx.x == 0 && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
+    // keys every valid row of the tile sees need no test: all up to the first row's position and, with a
+    // window, from the last row's first visible key on
+    const int free_hi = pos0 + 1;
+    const int free_lo = (p.window > 0 && key_hi - p.window > 0) ? key_hi - p.window : 0;
+    auto add_partial = [&](int j) {          // O += O' of tile j, once the tensor cores have made it
+      if (!at_mbar_wait(&o_full, j & 1, &dead) && lane == 0) atomicExch(p.status, 8);
       at_fence_after();
-      // pass 1: the row's maximum over this tile
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < AT_KEYS; c += 16) {
-        float sv[16];
-        at_tmem_ld16(t_row + c, sv);
+      float ov[DH];
+      at_tmem_ld<DH>(t_lane + 2 * AT_KEYS + h * DH, ov);
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-          const int key = key_base + c + i;
+      for (int i = 0; i < DH; i++) o[i] += ov[i];
+      at_fence_before();
+    };
+    for (int j = 0; j < n_kt; j++) {
+      const int tile_base = (kt_lo + j) * AT_KEYS;
+      const int key_base = tile_base + h * 64;
+      if (stamp) p.timeline[j * 8 + 0] = at_now();
+      if (!at_mbar_wait(&s_full[j & 1], (j >> 1) & 1, &dead) && lane == 0) atomicExch(p.status, 7);
+      at_fence_after();
+      if (stamp) p.timeline[j * 8 + 1] = at_now();
+      float sv[64];
+      at_tmem_ld<64>(t_lane + (j & 1) * AT_KEYS + h * 64, sv);
+      if (stamp) p.timeline[j * 8 + 2] = at_now();
+      const bool interior = tile_base >= free_lo && tile_base + AT_KEYS <= free_hi && p.scale_log2e > 0.f;
+      float mx = -INFINITY;
+      if (interior) {
+#pragma unroll
+        for (int i = 0; i < 64; i++) mx = fmaxf(mx, sv[i]);
+        mx *= p.scale_log2e;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i++) {
+          const int key = key_base + i;
           const bool vis = ok && key <= pos && key >= lo;
-          mx = fmaxf(mx, vis ? sv[i] * p.scale_log2e : -INFINITY);
+          sv[i] = vis ? sv[i] * p.scale_log2e : -INFINITY;
+          mx = fmaxf(mx, sv[i]);
         }
       }
-      const float m_new = fmaxf(m, mx);
+      mx_s[j & 1][h][row] = mx;
+      asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_THREADS) : "memory");
+      if (stamp) p.timeline[j * 8 + 3] = at_now();
+      const float m_new = fmaxf(m, fmaxf(mx, mx_s[j & 1][h ^ 1][row]));
       const float ref = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = at_exp2(m - ref);
       m = m_new;
-      // pass 2: p = exp2(s - max), as bfloat16 into the P tile; the sum
+      // p = exp2(score - max) as bfloat16 pairs, kept in registers until the P tile is free
+      unsigned pk[32];
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < AT_KEYS; c += 16) {
-        float sv[16];
-        at_tmem_ld16(t_row + c, sv);
-        unsigned pk[8];
+      const float mul = interior ? p.scale_log2e : 1.0f;
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const int key = key_base + c + i;
-          const bool v0 = ok && key <= pos && key >= lo, v1 = ok && key + 1 <= pos && key + 1 >= lo;
-          const float p0 = v0 ? at_exp2(sv[i] * p.scale_log2e - ref) : 0.f;
-          const float p1 = v1 ? at_exp2(sv[i + 1] * p.scale_log2e - ref) : 0.f;
-          sum += p0 + p1;
-          pk[i >> 1] = at_pack(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(p_s + at_swz(row, c >> 3)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-        *reinterpret_cast<uint4*>(p_s + at_swz(row, (c >> 3) + 1)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      for (int i = 0; i < 32; i++) {
+        const float p0 = at_exp2(fmaf(sv[2 * i], mul, -ref)), p1 = at_exp2(fmaf(sv[2 * i + 1], mul, -ref));
+        sum += p0 + p1;
+        pk[i] = at_pack(p0, p1);
       }
       l = l * alpha + sum;
+      if (stamp) p.timeline[j * 8 + 4] = at_now();
+      // the product of the tile before ran under all of the above; its result joins the output row, which
+      // then moves to the new maximum
+      if (j > 0) {
+        add_partial(j - 1);
+        at_mbar_arrive(&o_free);
+      }
+      if (stamp) p.timeline[j * 8 + 5] = at_now();
+#pragma unroll
+      for (int i = 0; i < DH; i++) o[i] *= alpha;
+#pragma unroll
+      for (int c = 0; c < 8; c++)
+        *reinterpret_cast<uint4*>(p_s + at_swz(row, h * 8 + c)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       at_fence_before();
       at_fence_async_smem();
       at_mbar_arrive(&p_full);
-      // the output of the tiles so far moves to the new maximum while the tensor cores multiply P and V
-#pragma unroll
-      for (int i = 0; i < HD; i++) o[i] *= alpha;
-      if (!at_mbar_wait(&o_full, j & 1, &dead) && lane == 0) atomicExch(p.status, 8);
-      at_fence_after();
-#pragma unroll
-      for (int c = 0; c < HD; c += 16) {
-        float ov[16];
-        at_tmem_ld16(t_row + 128 + c, ov);
-#pragma unroll
-        for (int i = 0; i < 16; i++) o[c + i] += ov[i];
-      }
-      at_fence_before();
-      at_mbar_arrive(&o_free);
+      if (stamp) p.timeline[j * 8 + 6] = at_now();
     }
+    if (n_kt > 0) add_partial(n_kt - 1);
+    l_s[h][row] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_THREADS) : "memory");
     if (ok) {
-      const float inv = 1.f / l;
-      bf16* d = p.out + (size_t)(tok0 + t) * p.H * HD + (size_t)(g * gs + hh) * HD;
+      const float inv = 1.f / (l + l_s[h ^ 1][row]);
+      bf16* d = p.out + (size_t)(tok0 + t) * p.H * HD + (size_t)(g * gs + hh) * HD + h * DH;
 #pragma unroll
-      for (int c = 0; c < HD; c += 8) {
+      for (int c = 0; c < DH; c += 8) {
         uint4 v;
         v.x = at_pack(o[c] * inv, o[c + 1] * inv);
         v.y = at_pack(o[c + 2] * inv, o[c + 3] * inv);
@@ -361,9 +441,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   pdl_launch_dependents();
   at_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     at_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -415,7 +495,7 @@ static int at_launch(const CUtensorMap& map, const AtParams& p, int tiles, cudaS
 extern "C" int qd_prefill_attention_tc5(const void* q, long long q_stride, void* out, const void* kv, long long n_pages,
                                         const int* block_table, int max_blocks, const int* cu_tokens,
                                         const int* start_pos, int R, int T, int H, int G, int d, int page_size,
-                                        float scale, int window, cudaStream_t stream) {
+                                        float scale, int window, long long* timeline, cudaStream_t stream) {
   if (T <= 0 || R <= 0) return 0;
   if (G < 1 || H % G != 0 || page_size % 16 != 0 || (d != 64 && d != 128) || n_pages < 1) return QD_ERR_UNSUPPORTED;
   const int gs = H / G;
@@ -440,6 +520,7 @@ extern "C" int qd_prefill_attention_tc5(const void* q, long long q_stride, void*
   p.R = R; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.tok_tile = AT_ROWS / gs;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.status = status;
+  p.timeline = timeline;
   const int tiles = (T + p.tok_tile - 1) / p.tok_tile + R;      // upper bound on the tiles of R requests
   return d == 64 ? at_launch<64>(map, p, tiles, stream) : at_launch<128>(map, p, tiles, stream);
 }

@@ -460,7 +460,7 @@ def prefill_tc5_supported(dtype, H: int, G: int, d: int, page_size: int) -> bool
 def prefill_attention_tc5(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                           block_table: torch.Tensor, cu_tokens: torch.Tensor, start_pos: torch.Tensor,
                           n_requests: int, n_tokens: int, H: int, G: int, d: int, page_size: int, scale: float,
-                          window: int) -> None:
+                          window: int, timeline: Optional[torch.Tensor] = None) -> None:
     """``prefill_attention`` on tcgen05 tensor cores (accumulators in tensor memory, K/V tiles by TMA)."""
     assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
@@ -470,7 +470,7 @@ def prefill_attention_tc5(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv:
     _check(library("attention_tc5").qd_prefill_attention_tc5(
         _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _LL(kv.shape[0]), _ptr(block_table), _I(block_table.shape[1]),
         _ptr(cu_tokens), _ptr(start_pos), _I(n_requests), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size),
-        _F(scale), _I(window), _stream()), "prefill_attention_tc5")
+        _F(scale), _I(window), _ptr(timeline), _stream()), "prefill_attention_tc5")
 
 
 def prefill_attention_tc5_status() -> int:
