@@ -180,14 +180,14 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   constexpr int NB = HD / 64;                       // 64-column blocks of a row
   constexpr int DH = HD / 2;                        // output columns per softmax thread
   constexpr int TILE_BYTES = AT_ROWS * HD * 2;      // one [128][HD] bfloat16 tile
-  constexpr unsigned TMEM_COLS = 512;               // S buffer 0: 0..127, S buffer 1: 128..255, O': 256..256+HD-1
+  constexpr unsigned TMEM_COLS = 512;               // three S buffers of 128 columns, then O': 384..384+HD-1
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* base = smem_raw + ((1024 - (at_smem(smem_raw) & 1023)) & 1023);
   unsigned char* q_s = base;                        // Q tile, K-major
   unsigned char* p_s = q_s + TILE_BYTES;            // P tile [128 rows][128 keys], K-major
   unsigned char* k_s = p_s + AT_ROWS * AT_KEYS * 2; // 2 stages of K [128 keys][HD], K-major
   unsigned char* v_s = k_s + 2 * TILE_BYTES;        // 2 stages of V [128 keys][HD], MN-major for the product
-  __shared__ unsigned long long k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, o_full, o_free, q_full;
+  __shared__ unsigned long long k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[3], p_full, o_full, o_free, q_full;
   __shared__ float mx_s[2][2][AT_ROWS];             // [tile parity][half][row]: the halves' maxima
   __shared__ float l_s[2][AT_ROWS];                 // the halves' sums, at the end
   __shared__ unsigned tmem_slot;
@@ -198,8 +198,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     dead = 0;
     for (int s = 0; s < 2; s++) {
       at_mbar_init(&k_full[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_empty[s], 1);
-      at_mbar_init(&s_full[s], 1);
     }
+    for (int s = 0; s < 3; s++) at_mbar_init(&s_full[s], 1);
     at_mbar_init(&o_full, 1);
     at_mbar_init(&p_full, AT_SOFTMAX_THREADS); at_mbar_init(&o_free, AT_SOFTMAX_THREADS);
     at_mbar_init(&q_full, AT_SOFTMAX_THREADS);
@@ -241,9 +241,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
 
   if (warp == 8) {
     // ------------------------------------------------------------------ producer
-    // K and V tiles are asked for in the order the tensor cores take them: K(0), K(1), V(0), K(2), V(1), ...
-    // (the scores of tile j + 1 are computed before the product of tile j), so that a K stage is refilled as
-    // soon as its scores are done and does not wait for the V stage beside it.
+    // K and V tiles are asked for in the order the tensor cores take them: K(0), K(1), V(0), K(2), V(1), K(3), ...
+    // (the scores of tile j + 2 are computed together with the product of tile j), so that a K stage is
+    // refilled as soon as its scores are done and does not wait for the V stage beside it.
     if (!idle) {
       const int* bt = p.block_table + (size_t)r * p.max_blocks;
       auto load = [&](int j, int which) {             // which: 0 = K, 1 = V
@@ -264,10 +264,10 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
           for (int cb = 0; cb < NB; cb++) at_tma_2d(dst + cb * (AT_KEYS * 128), &kv_map, cb * 64, row0, full);
         }
       };
-      if (n_kt > 0) load(0, 0);
+      for (int j = 0; j < 2 && j < n_kt; j++) load(j, 0);
       for (int j = 0; j < n_kt; j++) {
-        if (j + 1 < n_kt) load(j + 1, 0);
         load(j, 1);
+        if (j + 2 < n_kt) load(j + 2, 0);
       }
     }
   } else if (warp == 9) {
@@ -278,46 +278,58 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
                                 ((unsigned)(AT_ROWS >> 4) << 24);
       const unsigned long long dq = at_desc_kmajor(at_smem(q_s));
       const unsigned long long dp = at_desc_kmajor(at_smem(p_s));
-      auto issue_qk = [&](int j) {
+      // MMAs into one accumulator wait for each other (some 200 cycles each), MMAs into different
+      // accumulators overlap: the product of tile j is issued step by step together with the scores of tile
+      // j + 2, which go to the third S buffer -- the scores of tile j + 1 are complete by then, so the
+      // softmax threads never wait for them.
+      auto qk_step = [&](int j, int k, unsigned long long dk) {
+        // 16 columns = 32 bytes inside a 64-column block; the next block is 128 rows x 128 bytes further
+        const unsigned long long adv = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
+        at_umma(tmem + (unsigned)(j % 3) * AT_KEYS, dq + adv, dk + adv, idesc_qk, k ? 1u : 0u);
+      };
+      auto k_ready = [&](int j) -> unsigned long long {
         const int s = j & 1;
         if (!at_mbar_wait(&k_full[s], (j >> 1) & 1, &dead)) atomicExch(p.status, 2);
         at_fence_after();
-        const unsigned long long dk = at_desc_kmajor(at_smem(k_s + s * TILE_BYTES));
-#pragma unroll
-        for (int k = 0; k < HD / 16; k++) {
-          // 16 columns = 32 bytes inside a 64-column block; the next block is 128 rows x 128 bytes further
-          const unsigned long long adv = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
-          at_umma(tmem + s * AT_KEYS, dq + adv, dk + adv, idesc_qk, k ? 1u : 0u);
-        }
-        at_commit(&k_empty[s]);
-        at_commit(&s_full[s]);
+        return at_desc_kmajor(at_smem(k_s + s * TILE_BYTES));
+      };
+      auto qk_done = [&](int j) {
+        at_commit(&k_empty[j & 1]);
+        at_commit(&s_full[j % 3]);
       };
       const bool mstamp = p.timeline && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
       if (!at_mbar_wait(&q_full, 0, &dead)) atomicExch(p.status, 3);
       at_fence_after();
-      if (n_kt > 0) issue_qk(0);
+      for (int j = 0; j < 2 && j < n_kt; j++) {         // the first two tiles' scores, alone
+        const unsigned long long dk = k_ready(j);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) qk_step(j, k, dk);
+        qk_done(j);
+      }
       for (int j = 0; j < n_kt; j++) {
         const int s = j & 1;
-        // the next tile's scores go to the other S buffer while this tile's softmax runs (that buffer was
-        // read for tile j - 1, whose P has been waited for below)
         if (mstamp) p.timeline[128 + j * 4 + 0] = at_now();
-        if (j + 1 < n_kt) issue_qk(j + 1);
+        const bool ahead = j + 2 < n_kt;
+        unsigned long long dk = 0;
+        if (ahead) dk = k_ready(j + 2);
         if (mstamp) p.timeline[128 + j * 4 + 1] = at_now();
         if (!at_mbar_wait(&p_full, j & 1, &dead)) atomicExch(p.status, 4);
-        if (mstamp) p.timeline[128 + j * 4 + 2] = at_now();
         if (!at_mbar_wait(&v_full[s], (j >> 1) & 1, &dead)) atomicExch(p.status, 5);
         if (j > 0 && !at_mbar_wait(&o_free, (j - 1) & 1, &dead)) atomicExch(p.status, 6);
         at_fence_after();
+        if (mstamp) p.timeline[128 + j * 4 + 2] = at_now();
         const unsigned v_addr = at_smem(v_s + s * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < AT_KEYS / 16; k++) {
           const unsigned long long adv_p = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
           // 16 keys = two groups of 8 rows of V; the d columns 64.. lie one [128 keys][128 bytes] block further
           const unsigned long long dv = at_desc_mnmajor(v_addr + k * 2048, AT_KEYS * 128);
-          at_umma(tmem + 2 * AT_KEYS, dp + adv_p, dv, idesc_pv, k ? 1u : 0u);
+          at_umma(tmem + 3 * AT_KEYS, dp + adv_p, dv, idesc_pv, k ? 1u : 0u);
+          if (ahead && k < HD / 16) qk_step(j + 2, k, dk);
         }
         at_commit(&v_empty[s]);
         at_commit(&o_full);
+        if (ahead) qk_done(j + 2);
         if (mstamp) p.timeline[128 + j * 4 + 3] = at_now();
       }
     }
@@ -355,7 +367,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       if (!at_mbar_wait(&o_full, j & 1, &dead) && lane == 0) atomicExch(p.status, 8);
       at_fence_after();
       float ov[DH];
-      at_tmem_ld<DH>(t_lane + 2 * AT_KEYS + h * DH, ov);
+      at_tmem_ld<DH>(t_lane + 3 * AT_KEYS + h * DH, ov);
 #pragma unroll
       for (int i = 0; i < DH; i++) o[i] += ov[i];
       at_fence_before();
@@ -364,11 +376,11 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       const int tile_base = (kt_lo + j) * AT_KEYS;
       const int key_base = tile_base + h * 64;
       if (stamp) p.timeline[j * 8 + 0] = at_now();
-      if (!at_mbar_wait(&s_full[j & 1], (j >> 1) & 1, &dead) && lane == 0) atomicExch(p.status, 7);
+      if (!at_mbar_wait(&s_full[j % 3], (j / 3) & 1, &dead) && lane == 0) atomicExch(p.status, 7);
       at_fence_after();
       if (stamp) p.timeline[j * 8 + 1] = at_now();
       float sv[64];
-      at_tmem_ld<64>(t_lane + (j & 1) * AT_KEYS + h * 64, sv);
+      at_tmem_ld<64>(t_lane + (unsigned)(j % 3) * AT_KEYS + h * 64, sv);
       if (stamp) p.timeline[j * 8 + 2] = at_now();
       const bool interior = tile_base >= free_lo && tile_base + AT_KEYS <= free_hi && p.scale_log2e > 0.f;
       float mx = -INFINITY;
