@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 # float32 differs from the float64 plain implementation by rounding of sums only;
 # bfloat16 rounds every activation to 8 bits of mantissa over a few layers.
 TOL = {"float32": 1e-5, "bfloat16": 3e-2}
-LENGTHS = {"A": [5, 17, 33, 70, 150], "B": [1, 9, 64, 130, 200], "C": [3, 40, 97, 180]}
+LENGTHS = {"A": [5, 17, 33, 70, 150], "B": [1, 9, 64, 130, 200], "C": [3, 40, 97, 180], "D": [2, 66, 129, 300, 515]}
 
 
 @pytest.fixture(scope="module")
@@ -44,7 +44,7 @@ def held(seqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole(models, name, dtype, tmp_path):
     folder, cfg, w, seqs, want = models[name]
     runner = make_runner(folder, dtype, held(seqs), page_size=32 if name == "B" else 16)
@@ -56,7 +56,7 @@ def test_whole(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_decode_tail(models, name, dtype, tmp_path):
     folder, cfg, w, seqs, want = models[name]
     runner = make_runner(folder, dtype, held(seqs))
@@ -66,7 +66,7 @@ def test_decode_tail(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions(models, name, dtype, tmp_path):
     folder, cfg, w, seqs, want = models[name]
     runner = make_runner(folder, dtype, held(seqs), page_size=32 if name == "B" else 16)
@@ -76,7 +76,7 @@ def test_portions(models, name, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_with_page_reuse(models, name, dtype, tmp_path):
     folder, cfg, w, seqs, want = models[name]
     # twice every request, in two orders, in a pool that holds about two of the longest

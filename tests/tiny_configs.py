@@ -1,5 +1,6 @@
-"""Two tiny configurations of the architecture that differ in every size and option,
-and a third with other head sizes; model folders are made in temporary folders."""
+"""Two tiny configurations of the architecture that differ in every size and option, a third with
+other head sizes and a fourth with the head size of the tensor-memory attention kernel; model
+folders are made in temporary folders."""
 import torch
 
 from qwen_decoder_b200.config import Qwen2Config
@@ -20,8 +21,14 @@ TINY_C = dict(
     max_position_embeddings=384, rope_theta=50000.0, rms_norm_eps=3e-6, tie_word_embeddings=False,
     rope_pairing="half")
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
+# head size 64 in groups of 2: the sizes the tcgen05 attention kernel and the 128-row tiles take
+TINY_D = dict(
+    architectures=["Qwen2ForCausalLM"], hidden_size=96, intermediate_size=264, num_hidden_layers=2,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=300,
+    max_position_embeddings=640, rope_theta=20000.0, rms_norm_eps=2e-6, tie_word_embeddings=True)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
 
 
 def make_folder(name: str, path: str) -> str:
