@@ -24,6 +24,18 @@ mode = os.environ.get("QD_BF16_GEMM", "auto")
 counters = {"own": 0, "library": 0}
 
 
+_bias_copies = {}     # (address of the float32 bias, dtype) -> (the bias itself, its copy in that dtype)
+
+
+def _bias_as(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The library product adds a bias of the output's dtype: convert each bias once, not every call."""
+    key = (bias.data_ptr(), dtype)
+    hit = _bias_copies.get(key)
+    if hit is None or hit[0] is not bias:
+        hit = _bias_copies[key] = (bias, bias.to(dtype))
+    return hit[1]
+
+
 def _cublas(x, w, bias, out):
     if out.dtype == torch.float32:
         y = torch.mm(x, w.t(), out_dtype=torch.float32)
@@ -31,7 +43,7 @@ def _cublas(x, w, bias, out):
             y += bias
         out.copy_(y)
     elif bias is not None:
-        torch.addmm(bias.to(out.dtype), x, w.t(), out=out)
+        torch.addmm(_bias_as(bias, out.dtype), x, w.t(), out=out)
     else:
         torch.mm(x, w.t(), out=out)
     counters["library"] += 1
