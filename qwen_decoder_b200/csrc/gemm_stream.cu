@@ -418,6 +418,228 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
   pdl_launch_dependents();
 }
 
+// ---------------------------------------------------------------------------------------------
+// The feed-forward of a few tokens as ONE launch of the resident-token streamer: gate/up with the SwiGLU
+// epilogue, a grid barrier, then the down projection as split-K partial sums.  The down projection needs
+// all of h, so every CTA waits for every other one -- but its producer warp does not: it goes on filling
+// the stages with the down projection's first weights while the barrier is waited for, so the second
+// product starts with its pipeline full and the first one's tail costs nothing.  All CTAs are resident
+// (the host launches no more than fit); the barrier's spin is bounded like every other wait.
+struct FfnArgs {
+  const bf16* w1; const bf16* x1; long long ldx1; int N1, K1, n_tiles1;        // [2F, D], tokens [T, D]
+  bf16* h; long long ldh;                                                       // [T, F]
+  const bf16* w2; int N2, K2, n_tiles2, splits2; float* part;                   // [D, F] -> [splits2, T, D]
+  int T;
+  unsigned* gbar;            // two words, zero before first use: arrivals, generation
+  int* status;
+};
+
+__global__ void __launch_bounds__(ST_THREADS)
+ffn_stream_kernel(const FfnArgs a) {
+  constexpr int NST = XR_STAGES;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* stages = smem_raw;
+  unsigned char* xres = smem_raw + NST * XR_STAGE_BYTES;
+  float* red = reinterpret_cast<float*>(xres + 8 * XR_ROW_BYTES);
+  __shared__ unsigned long long full_bar[NST], empty_bar[NST], x_bar, go_bar;
+  __shared__ int dead;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    dead = 0;
+    for (int s = 0; s < NST; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ST_CONSUMERS); }
+    mbar_init(&x_bar, 1);
+    mbar_init(&go_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int T = a.T;
+  const int F = a.N1 >> 1;
+  // phase 1: every CTA walks tiles b, b + grid, ... over the whole K1 (at most XR_KMAX)
+  const int chunks1 = (a.K1 + ST_KC - 1) / ST_KC;
+  // phase 2: CTA b keeps share b % splits2 of K2 and walks tiles b / splits2, + grid / splits2, ...
+  const int chunks2 = (a.K2 + ST_KC - 1) / ST_KC;
+  const int stride2 = (int)gridDim.x / a.splits2;
+  const int sp2 = (int)blockIdx.x % a.splits2;
+  const int first2 = (int)blockIdx.x / a.splits2;
+  const bool idle2 = first2 >= stride2;
+  const int cb2 = (int)((long long)chunks2 * sp2 / a.splits2), ce2 = (int)((long long)chunks2 * (sp2 + 1) / a.splits2);
+  const int k2_begin = cb2 * ST_KC, k2_end = min(a.K2, ce2 * ST_KC);
+  constexpr int RED_LD = 9;
+
+  if (warp == ST_CONSUMERS) {
+    // ------------------------------------------------------------ producer
+    unsigned it = 0;
+    bool waited = false;
+    auto tokens1 = [&]() {
+      pdl_wait();
+      waited = true;
+      const unsigned xb = (unsigned)(a.K1 * 2);
+      if (lane == 0) mbar_expect_tx(&x_bar, xb * T);
+      __syncwarp();
+      for (int t = lane; t < T; t += 32) bulk_copy(xres + (size_t)t * XR_ROW_BYTES, a.x1 + (size_t)t * a.ldx1, xb, &x_bar);
+    };
+    auto weights = [&](const bf16* W, long long row, int K, int c) {
+      const int s = it % NST;
+      const unsigned ph = (it / NST) & 1;
+      if (!mbar_wait(&empty_bar[s], ph ^ 1, &dead) && lane == 0) atomicExch(a.status, 1);
+      const int k0 = c * ST_KC;
+      const unsigned row_bytes = (unsigned)(min(ST_KC, K - k0) * 2);
+      if (lane == 0) mbar_expect_tx(&full_bar[s], row_bytes * 16);
+      __syncwarp();
+      if (lane < 16)
+        bulk_copy(stages + (size_t)s * XR_STAGE_BYTES + (size_t)lane * ST_ROW_BYTES, W + row * K + k0, row_bytes, &full_bar[s]);
+      it++;
+    };
+    for (int tile = blockIdx.x; tile < a.n_tiles1; tile += gridDim.x) {
+      int f = tile * 8 + (lane & 7);
+      if (f >= F) f = F - 1;
+      const long long row = (lane & 8) ? (long long)F + f : f;
+      for (int c = 0; c < chunks1; c++) {
+        if (it >= (unsigned)NST && !waited) tokens1();
+        weights(a.w1, row, a.K1, c);
+      }
+    }
+    if (!waited) tokens1();
+    // the down projection's weights follow at once; its tokens (h) only when every CTA has written its part
+    unsigned issued2 = 0;
+    bool have_h = false;
+    auto tokens2 = [&]() {
+      have_h = true;
+      if (!mbar_wait(&go_bar, 0, &dead) && lane == 0) atomicExch(a.status, 3);
+      asm volatile("fence.proxy.async;" ::: "memory");        // h was written by ordinary stores of other CTAs
+      if (idle2) return;
+      const unsigned xb = (unsigned)((k2_end - k2_begin) * 2);
+      if (lane == 0) mbar_expect_tx(&x_bar, xb * T);
+      __syncwarp();
+      for (int t = lane; t < T; t += 32)
+        bulk_copy(xres + (size_t)t * XR_ROW_BYTES, a.h + (size_t)t * a.ldh + k2_begin, xb, &x_bar);
+    };
+    if (!idle2) {
+      for (int tile = first2; tile < a.n_tiles2; tile += stride2) {
+        long long row = (long long)tile * 16 + (lane & 15);
+        if (row >= a.N2) row = a.N2 - 1;
+        for (int c = cb2; c < ce2; c++) {
+          if (issued2 >= (unsigned)NST && !have_h) tokens2();
+          weights(a.w2, row, a.K2, c);
+          issued2++;
+        }
+      }
+    }
+    if (!have_h) tokens2();
+    return;
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int j = lane & 3, r = lane >> 2;
+  unsigned it = 0;
+  auto stage_mma = [&](float (&acc)[4], int K, int c, int c_first) {
+    const int s = it % NST;
+    const unsigned ph = (it / NST) & 1;
+    if (!mbar_wait(&full_bar[s], ph, &dead) && lane == 0) atomicExch(a.status, 2);
+    const unsigned char* st = stages + (size_t)s * XR_STAGE_BYTES;
+    const unsigned char* xs = xres + (size_t)(c - c_first) * ST_KC * 2;
+#pragma unroll
+    for (int u = 0; u < ST_KC / 32 / ST_CONSUMERS; u++) {
+      const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
+      if (c * ST_KC + kq >= K) break;
+      const bool in = c * ST_KC + kq + 8 * j < K;
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      const size_t col = (size_t)(kq + 8 * j) * 2;
+      uint4 lo = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
+      uint4 hi = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
+      uint4 b = in ? *reinterpret_cast<const uint4*>(xs + (size_t)r * XR_ROW_BYTES + col) : zero;
+      mma16816(acc, lo.x, hi.x, lo.y, hi.y, b.x, b.y);
+      mma16816(acc, lo.z, hi.z, lo.w, hi.w, b.z, b.w);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+    it++;
+  };
+  auto to_red = [&](const float (&acc)[4]) {
+    float* base = red + (size_t)warp * 16 * RED_LD;
+    base[r * RED_LD + 2 * j] = acc[0];
+    base[r * RED_LD + 2 * j + 1] = acc[1];
+    base[(r + 8) * RED_LD + 2 * j] = acc[2];
+    base[(r + 8) * RED_LD + 2 * j + 1] = acc[3];
+    asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
+  };
+  // ---- phase 1: gate, up, SwiGLU
+  bool have_x = false;
+  for (int tile = blockIdx.x; tile < a.n_tiles1; tile += gridDim.x) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < chunks1; c++) {
+      if (!have_x) {
+        if (!mbar_wait(&x_bar, 0, &dead) && lane == 0) atomicExch(a.status, 2);
+        have_x = true;
+      }
+      stage_mma(acc, a.K1, c, 0);
+    }
+    to_red(acc);
+    for (int idx = threadIdx.x; idx < 8 * 8; idx += ST_CONSUMERS * 32) {
+      int row = idx & 7, tok = idx >> 3;
+      int f = tile * 8 + row;
+      if (tok >= T || f >= F) continue;
+      float gate = 0.f, up = 0.f;
+#pragma unroll
+      for (int w = 0; w < ST_CONSUMERS; w++) {
+        gate += red[((size_t)w * 16 + row) * RED_LD + tok];
+        up += red[((size_t)w * 16 + row + 8) * RED_LD + tok];
+      }
+      a.h[(size_t)tok * a.ldh + f] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
+  }
+  // ---- every CTA's part of h is written: meet the others
+  asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
+  if (threadIdx.x == 0) {
+    volatile unsigned* gen_p = a.gbar + 1;
+    const unsigned gen = *gen_p;
+    __threadfence();
+    const unsigned arrived = atomicAdd(a.gbar, 1u);
+    if (arrived == gridDim.x - 1) {
+      a.gbar[0] = 0;
+      __threadfence();
+      atomicAdd(a.gbar + 1, 1u);
+    } else if (!dead) {
+      unsigned long long start = 0;
+      bool ok = false;
+      for (unsigned spin = 0; spin < (1u << 26); spin++) {
+        if (*gen_p != gen) { ok = true; break; }
+        if ((spin & 1023) == 1023) {
+          unsigned long long now;
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+          if (start == 0) start = now;
+          else if (now - start > 2000000000ull) break;
+        }
+      }
+      if (!ok) { dead = 1; atomicExch(a.status, 4); }
+    }
+    __threadfence();
+    mbar_arrive(&go_bar);
+  }
+  // ---- phase 2: down projection, partial sums of this CTA's share of K
+  if (!idle2) {
+    if (!mbar_wait(&x_bar, 1, &dead) && lane == 0) atomicExch(a.status, 2);
+    for (int tile = first2; tile < a.n_tiles2; tile += stride2) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = cb2; c < ce2; c++) stage_mma(acc, a.K2, c, cb2);
+      to_red(acc);
+      for (int idx = threadIdx.x; idx < 16 * 8; idx += ST_CONSUMERS * 32) {
+        int row = idx & 15, tok = idx >> 4;
+        int n = tile * 16 + row;
+        if (tok >= T || n >= a.N2) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_CONSUMERS; w++) v += red[((size_t)w * 16 + row) * RED_LD + tok];
+        a.part[((size_t)sp2 * T + tok) * a.N2 + n] = v;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
+    }
+  }
+  pdl_launch_dependents();
+}
+
 static int* g_status[64];   // per device: one int of device memory for the kernels' error status
 
 static int* status_word() {
@@ -528,6 +750,47 @@ extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const
   if (T <= 16) return launch_stream<2>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 32) return launch_stream<4>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   return launch_stream<8>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
+}
+
+// The feed-forward of up to 8 tokens in one launch: h = silu(x Wg^T) * (x Wu^T) (w1 = [Wg; Wu], [2F, D]) and
+// part[s] = partial sums of h W2^T over `splits2` shares of F.  `gbar`: two zeroed words of device memory that
+// stay with the caller (the kernel leaves them ready for the next launch).  Refuses what it cannot take
+// (more than 8 tokens, D above 2,048, a share of F wider than 2,048, more CTAs than fit on the device at once).
+extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void* h, long long ldh, const void* w2,
+                             float* part, int T, int D, int F, int splits2, unsigned* gbar, int max_ctas,
+                             cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (T > 8 || D <= 0 || F <= 0 || D % 8 != 0 || F % 8 != 0 || ldx % 8 != 0 || ldh % 8 != 0 || D > XR_KMAX ||
+      splits2 < 1 || !gbar || !part)
+    return QD_ERR_UNSUPPORTED;
+  if (((uintptr_t)w1 & 15) || ((uintptr_t)w2 & 15) || ((uintptr_t)x & 15) || ((uintptr_t)h & 15)) return QD_ERR_UNSUPPORTED;
+  if (!xres_fits(T, F, splits2, max_ctas)) return QD_ERR_UNSUPPORTED;
+  int* status = status_word();
+  if (!status) return QD_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)XR_STAGES * XR_STAGE_BYTES + (size_t)8 * XR_ROW_BYTES + (size_t)ST_CONSUMERS * 16 * 9 * sizeof(float);
+  if (cudaFuncSetAttribute(ffn_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    cudaGetLastError();
+    return QD_ERR_UNSUPPORTED;
+  }
+  // every CTA waits for every other one: no more CTAs than the device holds at once
+  int per_sm = 0, dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ffn_stream_kernel, ST_THREADS, smem) != cudaSuccess || per_sm < 1) {
+    cudaGetLastError();
+    return QD_ERR_UNSUPPORTED;
+  }
+  FfnArgs a;
+  a.w1 = (const bf16*)w1; a.x1 = (const bf16*)x; a.ldx1 = ldx; a.N1 = 2 * F; a.K1 = D; a.n_tiles1 = (F + 7) / 8;
+  a.h = (bf16*)h; a.ldh = ldh;
+  a.w2 = (const bf16*)w2; a.N2 = D; a.K2 = F; a.n_tiles2 = (D + 15) / 16; a.splits2 = splits2; a.part = part;
+  a.T = T; a.gbar = gbar; a.status = status;
+  int grid = per_sm * sms;
+  if (grid > max_ctas) grid = max_ctas;
+  if (grid > a.n_tiles1) grid = a.n_tiles1;
+  if (grid < splits2) return QD_ERR_UNSUPPORTED;
+  qd_launch(ffn_stream_kernel, dim3(grid), dim3(ST_THREADS), smem, stream, a);
+  return qd_last_error();
 }
 
 // 0 if no kernel of this library has recorded a bounded-wait expiry on the current device

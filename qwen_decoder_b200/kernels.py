@@ -245,6 +245,7 @@ def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
 # csrc/gemm_stream.cu) or "regs" (one wave of CTAs loading straight into registers, csrc/gemm_skinny.cu).
 skinny_impl = _os.environ.get("QD_SKINNY_IMPL", "stream")
 STREAM_MAX_CTAS = 296          # two persistent CTAs on each of 148 SMs
+_FFN_FUSED = _os.environ.get("QD_FFN_FUSED", "1") != "0"      # gate/up and down of up to 8 tokens in one launch
 TC5_MAX_CTAS = int(_os.environ.get("QD_TC5_CTAS", "148"))   # the tcgen05 kernel runs one persistent CTA per SM
 
 
@@ -325,6 +326,37 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
     assert skinny_supported(x, w_gate_up, 1 << 30) and out.shape == (T, N // 2) and out.dtype == torch.bfloat16
     _contig(w_gate_up, "w"); _contig(out, "out")
     _skinny_call(x, w_gate_up, None, out, None, T, N, K, 1, EPI_SWIGLU, "gemm_skinny_swiglu")
+
+
+_ffn_barriers = {}
+
+
+def ffn_stream_supported(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+    """Whether the one-launch feed-forward (gate/up + SwiGLU, grid barrier, down) takes these sizes."""
+    T, D = x.shape
+    F = w_down.shape[1]
+    return (_FFN_FUSED and T <= 8 and D <= 2048 and few_token_impl(T) == "stream" and skinny_supported(x, w_gate_up)
+            and w_down.dtype == torch.bfloat16 and F % 8 == 0 and w_gate_up.shape[0] == 2 * F
+            and w_down.shape[0] == D)
+
+
+def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """float32 partial sums [splits, T, D] of (silu(x Wg^T) * (x Wu^T)) Wd^T for up to 8 tokens, in one
+    launch of the weight streamer: every CTA waits for all the others between the two products, its
+    producer warp meanwhile fetches the second product's first weights."""
+    T, D = x.shape
+    F = w_down.shape[1]
+    _contig(w_gate_up, "w_gate_up"); _contig(w_down, "w_down")
+    splits = skinny_splits(D, F, T)
+    h = torch.empty((T, F), dtype=torch.bfloat16, device=x.device)
+    part = torch.empty((splits, T, D), dtype=torch.float32, device=x.device)
+    bar = _ffn_barriers.get(x.device)
+    if bar is None:          # zero once; every launch leaves it ready for the next
+        bar = _ffn_barriers[x.device] = torch.zeros(2, dtype=torch.int32, device=x.device)
+    _check(library("gemm_stream").qd_ffn_stream(
+        _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(h), _LL(h.stride(0)), _ptr(w_down), _ptr(part), _I(T), _I(D),
+        _I(F), _I(splits), _ptr(bar), _I(STREAM_MAX_CTAS), _stream()), "ffn_stream")
+    return part
 
 
 # ------------------------------------------------------------------- attention

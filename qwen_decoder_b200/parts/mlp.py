@@ -37,6 +37,9 @@ class SwiGLU(FeedForward):
                 "wd": self.down.weight}
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        if matmul_backend.mode == "auto" and kernels.ffn_stream_supported(x, self.gate_up.weight, self.down.weight):
+            matmul_backend.counters["own"] += 1
+            return kernels.ffn_stream(x, self.gate_up.weight, self.down.weight)     # both products in one launch
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if matmul_backend.use_skinny(x, self.gate_up.weight):
             kernels.gemm_skinny_swiglu(x, self.gate_up.weight, h)       # gate, up and SwiGLU in one kernel

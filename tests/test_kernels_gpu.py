@@ -512,3 +512,30 @@ def test_fused_decode_step_matches_unfused(name, batch):
     a, b = outs
     assert torch.isfinite(b).all()
     assert (a - b).abs().max().item() <= 3e-2 * a.abs().max().item()
+
+
+@pytest.mark.parametrize("shape", [(8, 2048, 11008), (5, 96, 264), (1, 64, 176), (7, 1024, 2816), (3, 128, 1400)])
+def test_feed_forward_in_one_launch(shape):
+    """Gate/up with SwiGLU, a grid barrier, the down projection: against the two separate launches and
+    against float64; several times in a row (the barrier must be left ready for the next launch)."""
+    from qwen_decoder_b200 import kernels
+    T, D, F = shape
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn(T, D, generator=g)).to(torch.bfloat16).to(DEV)
+    w1 = (torch.randn(2 * F, D, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    w2 = (torch.randn(D, F, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    assert kernels.ffn_stream_supported(x, w1, w2)
+    h_ref = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_skinny_swiglu(x, w1, h_ref)
+    want = h_ref.double().cpu() @ w2.double().cpu().t()
+    gate_up = x.double().cpu() @ w1.double().cpu().t()
+    h64 = torch.nn.functional.silu(gate_up[:, :F]) * gate_up[:, F:]
+    for _ in range(3):
+        part = kernels.ffn_stream(x, w1, w2)
+        got = part.sum(0).double().cpu()
+        assert torch.isfinite(got).all()
+        # h is rounded to bfloat16 between the products in both paths: equal to the two-launch result up to
+        # the order of float32 sums, and close to float64 throughout
+        assert (got - want).abs().max() <= 1e-4 * want.abs().max() + 1e-6
+        assert (got - h64 @ w2.double().cpu().t()).abs().max() <= 2e-2 * want.abs().max()
+    assert kernels.gemm_stream_status() == 0
