@@ -328,9 +328,6 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
     _skinny_call(x, w_gate_up, None, out, None, T, N, K, 1, EPI_SWIGLU, "gemm_skinny_swiglu")
 
 
-_ffn_barriers = {}
-
-
 def ffn_stream_supported(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
     """Whether the one-launch feed-forward (gate/up + SwiGLU, grid barrier, down) takes these sizes."""
     T, D = x.shape
@@ -340,22 +337,22 @@ def ffn_stream_supported(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch
             and w_down.shape[0] == D)
 
 
-def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, barrier: torch.Tensor) -> torch.Tensor:
     """float32 partial sums [splits, T, D] of (silu(x Wg^T) * (x Wu^T)) Wd^T for up to 8 tokens, in one
     launch of the weight streamer: every CTA waits for all the others between the two products, its
-    producer warp meanwhile fetches the second product's first weights."""
+    producer warp meanwhile fetches the second product's first weights.  ``barrier``: two int32 words
+    on the device, zero before their first use, that belong to the caller (no two launches that may run
+    at the same time share them); every launch leaves them ready for the next."""
+    assert barrier.dtype == torch.int32 and barrier.numel() >= 2 and barrier.is_cuda
     T, D = x.shape
     F = w_down.shape[1]
     _contig(w_gate_up, "w_gate_up"); _contig(w_down, "w_down")
     splits = skinny_splits(D, F, T)
     h = torch.empty((T, F), dtype=torch.bfloat16, device=x.device)
     part = torch.empty((splits, T, D), dtype=torch.float32, device=x.device)
-    bar = _ffn_barriers.get(x.device)
-    if bar is None:          # zero once; every launch leaves it ready for the next
-        bar = _ffn_barriers[x.device] = torch.zeros(2, dtype=torch.int32, device=x.device)
     _check(library("gemm_stream").qd_ffn_stream(
         _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(h), _LL(h.stride(0)), _ptr(w_down), _ptr(part), _I(T), _I(D),
-        _I(F), _I(splits), _ptr(bar), _I(STREAM_MAX_CTAS), _stream()), "ffn_stream")
+        _I(F), _I(splits), _ptr(barrier), _I(STREAM_MAX_CTAS), _stream()), "ffn_stream")
     return part
 
 

@@ -24,6 +24,7 @@ class SwiGLU(FeedForward):
         self.gate_up = Linear(hidden_size, [(f"{prefix}gate_proj", intermediate_size),
                                             (f"{prefix}up_proj", intermediate_size)], bias=False)
         self.down = Linear(intermediate_size, [(f"{prefix}down_proj", hidden_size)], bias=False)
+        self._barrier = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         return self.gate_up.tensor_specs() + self.down.tensor_specs()
@@ -39,7 +40,9 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if matmul_backend.mode == "auto" and kernels.ffn_stream_supported(x, self.gate_up.weight, self.down.weight):
             matmul_backend.counters["own"] += 1
-            return kernels.ffn_stream(x, self.gate_up.weight, self.down.weight)     # both products in one launch
+            if self._barrier is None:       # this layer's own grid barrier words (zero once; each launch resets them)
+                self._barrier = torch.zeros(2, dtype=torch.int32, device=x.device)
+            return kernels.ffn_stream(x, self.gate_up.weight, self.down.weight, self._barrier)   # one launch
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if matmul_backend.use_skinny(x, self.gate_up.weight):
             kernels.gemm_skinny_swiglu(x, self.gate_up.weight, h)       # gate, up and SwiGLU in one kernel

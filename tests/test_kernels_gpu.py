@@ -530,8 +530,9 @@ def test_feed_forward_in_one_launch(shape):
     want = h_ref.double().cpu() @ w2.double().cpu().t()
     gate_up = x.double().cpu() @ w1.double().cpu().t()
     h64 = torch.nn.functional.silu(gate_up[:, :F]) * gate_up[:, F:]
+    barrier = torch.zeros(2, dtype=torch.int32, device=DEV)
     for _ in range(3):
-        part = kernels.ffn_stream(x, w1, w2)
+        part = kernels.ffn_stream(x, w1, w2, barrier)
         got = part.sum(0).double().cpu()
         assert torch.isfinite(got).all()
         # h is rounded to bfloat16 between the products in both paths: equal to the two-launch result up to
