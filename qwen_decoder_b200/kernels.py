@@ -424,9 +424,11 @@ def decode_attention_rope(part: torch.Tensor, bias: Optional[torch.Tensor], out:
                           slot_map: torch.Tensor, H: int, G: int, d: int, page_size: int, scale: float,
                           window: int, splits: int, write_kv: bool, rotary_dim: int, pairing: int,
                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
-                          timeline: Optional[torch.Tensor] = None) -> None:
+                          timeline: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
     """One decoded token per request, from the float32 partial sums part [n_parts, T, (H+2G)*d] of q, k, v:
-    bias, rotation by position, cache write and attention over the paged cache in one launch."""
+    bias, rotation by position, cache write and attention over the paged cache in one launch.  With
+    ``cluster`` and 2 to 8 splits the CTAs of a (token, kv head) form a thread-block cluster and combine
+    their partial results through distributed shared memory instead of scratch memory and tickets."""
     n_parts, T, W = part.shape
     assert part.dtype == torch.float32 and W == (H + 2 * G) * d and out.shape == (T, H * d)
     assert out.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and tuple(kv.shape[1:]) == (2, G, page_size, d)
@@ -447,7 +449,8 @@ def decode_attention_rope(part: torch.Tensor, bias: Optional[torch.Tensor], out:
         _ptr(part), _I(n_parts), _ptr(bias), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
         _ptr(token_req), _ptr(positions), _ptr(slot_map), _I(T), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
         _I(window), _I(splits), _I(1 if write_kv else 0), _ptr(cos), _ptr(sin), _I(rotary_dim), _I(pairing),
-        _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(timeline), _stream()), "decode_attention_rope")
+        _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(timeline), _I(1 if cluster else 0), _stream()),
+        "decode_attention_rope")
 
 
 def prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,

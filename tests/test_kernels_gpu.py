@@ -459,6 +459,13 @@ def test_decode_attention_from_partial_sums(cfg):
     kernels.decode_attention_rope(part.to(DEV), bias.to(DEV), out, dkv, bt.to(DEV), tr.to(DEV), pos.to(DEV),
                                   slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d), window or 0, splits, True,
                                   d, rot.pairing_code, rot.cos, rot.sin)
+    if 2 <= splits <= 8:
+        # the same with the splits of a (token, kv head) as a thread-block cluster: same numbers
+        out_c = torch.empty_like(out)
+        kernels.decode_attention_rope(part.to(DEV), bias.to(DEV), out_c, kv.to(DEV), bt.to(DEV), tr.to(DEV),
+                                      pos.to(DEV), slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d),
+                                      window or 0, splits, True, d, rot.pairing_code, rot.cos, rot.sin, cluster=True)
+        assert (out_c.float() - out.float()).abs().max() <= 2e-2 * float(out.float().abs().max())
     kvc = dkv.cpu()
     for i, n in enumerate(lens):
         page, off = int(slots[i]) // page_size, int(slots[i]) % page_size
