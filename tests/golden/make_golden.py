@@ -102,7 +102,9 @@ int main(int argc, char** argv) {
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QWEN_DECODER_REF", "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QWEN_DECODER_REF")
+    if not ref or not os.path.isfile(os.path.join(ref, "cpu_decoder.cpp")):
+        sys.exit("usage: make_golden.py <folder of the reference's sources>   (or QWEN_DECODER_REF=<folder>)")
     with tempfile.TemporaryDirectory() as tmp:
         gguf, wrap, exe, raw = (os.path.join(tmp, n) for n in ("m.gguf", "wrap.cpp", "golden", "out.bin"))
         write_gguf(gguf)
