@@ -239,11 +239,11 @@ def main():
     page = 16
     max_b = max(64, args.batch)
     span = args.context + 2 * (W + K) + 64
-    num_pages = max_b * ((span + page - 1) // page) + 64
+    num_pages = max(max_b * ((span + page - 1) // page), (args.prefill_tokens + page - 1) // page) + 64
     torch.manual_seed(0)
     engine = Engine(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_batch=max_b,
                     max_prefill_len=1 << 20, max_prefill_tokens_per_step=4096, max_total_tokens=8192,
-                    page_size=page, num_pages=num_pages, max_positions=span + 4096)
+                    page_size=page, num_pages=num_pages, max_positions=max(span, args.prefill_tokens) + 4096)
     runner = engine.runner
     dev = runner.device
     for kv in runner.cache.kv:                       # random cache contents stand in for real prompts
