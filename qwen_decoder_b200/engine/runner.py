@@ -136,11 +136,13 @@ class ModelRunner:
         elif device_tokens is not None:
             raise StepError("device_tokens: only a batch of single tokens that all want logits takes them")
         else:
+            from .. import kernels
             ctx = build_context(entries, self.cache, self.device, self.model.vocab_size, self.max_positions)
-            logits = self.model.forward(ctx)
-            tokens = None
-            if sampling is not None and ctx.num_wanted:
-                tokens = self.sampler.sample(logits, *sampling)
+            with kernels.step_stream():
+                logits = self.model.forward(ctx)
+                tokens = None
+                if sampling is not None and ctx.num_wanted:
+                    tokens = self.sampler.sample(logits, *sampling)
             n_tokens = ctx.num_tokens
         for e in entries:
             self.cache.commit(e.cache, len(e.tokens), e.tokens if device_tokens is None else None)
@@ -230,10 +232,11 @@ class _DecodeGraph:
 
     def _forward(self):
         from .. import kernels
-        self.logits = self.model.forward(self.ctx)
-        if self.with_sampling:
-            self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.device)
-            kernels.sample(self.logits, self.temps, self.top_ks, self.draws, self.tokens)
+        with kernels.step_stream():       # entered inside a capture too: the capturing stream is current then
+            self.logits = self.model.forward(self.ctx)
+            if self.with_sampling:
+                self.tokens = torch.empty(self.lay.T, dtype=torch.int32, device=self.device)
+                kernels.sample(self.logits, self.temps, self.top_ks, self.draws, self.tokens)
 
     def run(self) -> None:
         if self.graph is None:

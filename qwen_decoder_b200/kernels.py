@@ -50,9 +50,28 @@ def add_launches(n: int) -> None:
     _launch_count[0] += n
 
 
+_step_stream = [None]
+
+
+class step_stream:
+    """Within this context every launcher uses the stream that was current on entry, looked up once:
+    asking torch for the current stream costs several microseconds, a step has hundreds of launches.
+    (Nothing inside a step switches streams; a graph capture enters the context after it has begun.)"""
+
+    def __enter__(self):
+        self.previous = _step_stream[0]
+        _step_stream[0] = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        _step_stream[0] = self.previous
+        return False
+
+
 def _stream():
     _launch_count[0] += 1          # every launcher fetches the stream exactly once
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    s = _step_stream[0]
+    return s if s is not None else ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
 def _check(code: int, what: str) -> None:
