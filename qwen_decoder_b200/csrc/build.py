@@ -184,3 +184,9 @@ def build_all(verbose: bool = True, jobs: int = 0) -> Dict[str, str]:
 if __name__ == "__main__":
     for n, p in build_all().items():
         print(n, p)
+
+
+def loaded(name: str) -> bool:
+    """Whether the library ``name`` has been loaded in this process (no build, no load)."""
+    return name in _loaded
+

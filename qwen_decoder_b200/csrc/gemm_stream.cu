@@ -800,5 +800,6 @@ extern "C" int qd_gemm_stream_status() {
   if (!status) return -1;
   int v = 0;
   if (cudaMemcpy(&v, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(status, 0, sizeof(int));      // reported once
   return v;
 }

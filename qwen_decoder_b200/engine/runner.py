@@ -66,6 +66,8 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
 
+    STATUS_EVERY = 512       # steps between two looks at the kernels' status words (each look synchronises)
+
     # ---- construction ----------------------------------------------------
     @classmethod
     def from_folder(cls, model_dir: str, dtype="bfloat16", device="cuda:0", **kw) -> "ModelRunner":
@@ -148,6 +150,9 @@ class ModelRunner:
             self.cache.commit(e.cache, len(e.tokens), e.tokens if device_tokens is None else None)
         self.steps += 1
         self.tokens_run += n_tokens
+        if self.steps % self.STATUS_EVERY == 0:
+            from .. import kernels
+            kernels.check_status()       # a wait inside a kernel that ran out must not pass unnoticed
         return logits if sampling is None else (logits, tokens)
 
     def can_take_device_tokens(self, entries: Sequence[StepEntry]) -> bool:

@@ -12,7 +12,7 @@ from typing import Optional
 
 import torch
 
-from .csrc.build import library
+from .csrc.build import library, loaded as _library_loaded
 
 F32, BF16 = 0, 1
 ERR_UNSUPPORTED = 10001
@@ -527,6 +527,19 @@ def prefill_attention_tc5(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv:
 def prefill_attention_tc5_status() -> int:
     """0, or which bounded wait of the tcgen05 attention kernel ran out since the last call (synchronises)."""
     return int(library("attention_tc5").qd_prefill_attention_tc5_status())
+
+
+def check_status() -> None:
+    """Raise if a bounded wait inside one of the kernels with mbarrier or grid-barrier waits ran out since the
+    last call: the results of that launch were void.  Synchronises the device; asks only the libraries this
+    process has loaded."""
+    for name, fn in (("gemm_stream", "qd_gemm_stream_status"), ("gemm_tc5", "qd_gemm_tc5_status"),
+                     ("attention_tc5", "qd_prefill_attention_tc5_status")):
+        if _library_loaded(name):
+            code = int(getattr(library(name), fn)())
+            if code != 0:
+                raise KernelError(f"{name}: a bounded wait ran out inside a kernel (status {code}); results of "
+                                  "launches since the last check are invalid")
 
 
 # ------------------------------------------------------------------ a whole decode step in one kernel
