@@ -117,7 +117,7 @@ def micro(args):
     import torch
     from qwen_decoder_b200 import kernels
     dev = "cuda:0"
-    H, G, d, ps = 16, 2, 128, 16
+    H, G, d, ps = 16, 2, 128, args.page_size
     T = args.tokens
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     if args.micro == "gemm":
@@ -205,6 +205,7 @@ def main():
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=SHAPE_3B["num_hidden_layers"])
     ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (a multiple of 16)")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention"],
@@ -236,7 +237,7 @@ def main():
     cfgd = dict(SHAPE_3B, num_hidden_layers=args.layers)
     cfg = Qwen2Config.from_dict(cfgd)
     pk, pk_src = peaks()
-    page = 16
+    page = args.page_size
     max_b = max(64, args.batch)
     span = args.context + 2 * (W + K) + 64
     num_pages = max(max_b * ((span + page - 1) // page), (args.prefill_tokens + page - 1) // page) + 64
