@@ -9,7 +9,8 @@ with CUDA events over exactly K steps after W warm-up steps), ``e2e`` = the same
 through the Python entry point (``Engine.step``: host token ids in through pinned
 memory, sampled ids back to the host, every step), ``prefill`` = a 2,048-token
 prompt in one step, ``roofline`` = bytes a decode step must read / its time against
-the measured copy bandwidth, ``points`` = decode at batch 1 and 64.
+the measured copy bandwidth, ``points`` = decode at batch 1 and 64 and prompts of 128
+and 512 tokens in one step (tokens per second, host launching included).
 
 Weights are random (N(0, 0.02), seeded); the caches of the decode requests are filled
 with random values instead of running 2,048-token prompts first (decode time does not
@@ -295,22 +296,29 @@ def main():
             pms, _, _ = time_decode(b, min(K, 128), W)
             points[f"decode_b{b}"] = round(b * min(K, 128) / (pms / 1e3), 1)
 
-    # prefill: one prompt of T tokens in one step, logits at its last place
+    # prefill: one prompt of T tokens in one step, logits at its last place; the events span the host's
+    # launching too, so a portion that the host cannot launch as fast as the device runs it shows here
+    def time_prefill(T, tag):
+        pre_ms = []
+        for i in range(W + 3):
+            rc = runner.open(f"{tag}{i}")
+            prompt = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step([StepEntry(rc, prompt, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize(dev)
+            if i >= W:
+                pre_ms.append(e0.elapsed_time(e1))
+            runner.close(rc)
+        return sorted(pre_ms)[len(pre_ms) // 2]
+
     T = args.prefill_tokens
-    pre_ms = []
-    for i in range(W + 3):
-        rc = runner.open(f"p{i}")
-        prompt = torch.randint(0, cfg.vocab_size, (T,), generator=gen).tolist()
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        runner.step([StepEntry(rc, prompt, [T - 1])])
-        e1.record()
-        torch.cuda.synchronize(dev)
-        if i >= W:
-            pre_ms.append(e0.elapsed_time(e1))
-        runner.close(rc)
-    pre = sorted(pre_ms)[len(pre_ms) // 2]
+    pre = time_prefill(T, "p")
+    if not args.no_points:
+        for t in (128, 512):
+            points[f"prefill_{t}"] = round(t / (time_prefill(t, f"q{t}_") / 1e3), 1)
     pflops = prefill_flops(cfgd, args.layers, T)
     prefill = {"value": round(T / (pre / 1e3), 1), "tokens": T, "ms": round(pre, 3),
                "frac": round(pflops / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}

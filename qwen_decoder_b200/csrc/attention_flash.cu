@@ -13,6 +13,7 @@
 // 128); page sizes that are multiples of 16; groups of up to 16 heads (decode) / 64 heads
 // (prefill).  Anything else is refused and the caller takes the generic kernel.
 #include "common.cuh"
+#include "entry_points.h"
 #include <math.h>
 
 #define FA_PAD 8  // bf16 elements of padding per smem row: 16 bytes, keeps ldmatrix conflict-free

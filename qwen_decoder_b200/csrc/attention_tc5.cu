@@ -20,6 +20,7 @@
 // Every wait on an mbarrier is bounded in polls and in time; a wait that runs out marks the CTA dead:
 // nobody waits again, all roles run to their end, tensor memory is freed, and the host reads a status.
 #include "common.cuh"
+#include "entry_points.h"
 #include <cuda.h>
 #include <cudaTypedefs.h>
 

@@ -42,8 +42,9 @@ LIBRARIES: Dict[str, str] = {
     "sampling": "sampling.cu",
     "decode_fused": "decode_fused.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
+    "prompt_exec": "prompt_exec.cu",
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "entry_points.h"]
 # further files a library's source includes (hashed into its key)
 EXTRA_DEPS: Dict[str, List[str]] = {
     "decode_attention_noalloc": ["attention_flash.cu", "decode_attention_noalloc.h"],

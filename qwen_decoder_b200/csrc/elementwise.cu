@@ -7,6 +7,7 @@
 // residual_kernel + rmsnorm_kernel (gpu_kernels.cu:136-146, 32-67), rope_kernel +
 // kvcache_write_kernel (gpu_kernels.cu:82-133), swiglu_kernel (gpu_kernels.cu:149-160).
 #include "common.cuh"
+#include "entry_points.h"
 
 // ---------------------------------------------------------------- embedding
 // x[t, :] = table[tokens[t], :]; the residual stream x is float32 in both paths.
@@ -287,8 +288,8 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int H, int G, int d, i
 // bfloat16, adjacent pairs, head size and rotated width multiples of 8: a thread takes 16 bytes (four pairs)
 // of q, k or v of one token, with its cosines and sines as two float4.
 __global__ void __launch_bounds__(256)
-rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int T, int H, int G, int d, int rotary_dim,
-                         const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias, int T, int H, int G, int d,
+                         int rotary_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                          const int* __restrict__ positions, bf16* __restrict__ kv,
                          const int* __restrict__ slot_map, int page_size, int write_kv) {
   pdl_launch_dependents();
@@ -301,6 +302,18 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, int T, int H, int G, int d, int
   if (head >= H && !write_kv) return;
   bf16* src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d + c8;
   uint4 raw = *reinterpret_cast<const uint4*>(src);
+  if (bias) {          // the projection's bias, where the product before left it out
+    const float4 b0 = *reinterpret_cast<const float4*>(bias + (size_t)head * d + c8);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias + (size_t)head * d + c8 + 4);
+    const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    unsigned* u = reinterpret_cast<unsigned*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
+      __nv_bfloat162 r = __floats2bfloat162_rn(__low2float(v) + bs[2 * i], __high2float(v) + bs[2 * i + 1]);
+      u[i] = *reinterpret_cast<unsigned*>(&r);
+    }
+  }
   if (head < H + G && cos_t && c8 < rotary_dim) {
     const int half = rotary_dim >> 1;
     const size_t tab = (size_t)positions[t] * half + (c8 >> 1);
@@ -339,14 +352,34 @@ extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d
   else if (dtype == QD_BF16 && pairing == 0 && d % 8 == 0 && rotary_dim % 8 == 0 && ((uintptr_t)qkv & 15) == 0 &&
            (!write_kv || ((uintptr_t)kv & 15) == 0) && (!cos_t || (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0)) {
     const long long pieces = (long long)T * (H + 2 * G) * d / 8;
-    qd_launch(rope_kv_write_vec_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream, (bf16*)qkv, T, H, G,
-              d, rotary_dim, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size, write_kv);
+    qd_launch(rope_kv_write_vec_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream, (bf16*)qkv,
+              (const float*)nullptr, T, H, G, d, rotary_dim, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size,
+              write_kv);
   } else if (dtype == QD_BF16)
     qd_launch(rope_kv_write_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                       sin_t, positions, (bf16*)kv, slot_map,
                                                       page_size, write_kv);
   else
     return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// The vectorized kernel alone, with the projection's float32 bias [(H + 2G) d] added first (null: none):
+// bfloat16, adjacent pairs, head size and rotated width multiples of 8, 16-byte aligned pointers; refuses
+// anything else.  The sum is rounded to bfloat16 before the rotation, as a product with a bias epilogue
+// would leave it.
+extern "C" int qd_rope_kv_write_biased(void* qkv, const float* bias, int T, int H, int G, int d, int rotary_dim,
+                                       int pairing, const float* cos_t, const float* sin_t, const int* positions,
+                                       void* kv, const int* slot_map, int page_size, int write_kv,
+                                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (pairing != 0 || d % 8 != 0 || rotary_dim % 8 != 0 || rotary_dim > d || rotary_dim < 0) return QD_ERR_UNSUPPORTED;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)bias & 15) || (write_kv && ((uintptr_t)kv & 15)) ||
+      (cos_t && (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15)))
+    return QD_ERR_UNSUPPORTED;
+  const long long pieces = (long long)T * (H + 2 * G) * d / 8;
+  qd_launch(rope_kv_write_vec_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream, (bf16*)qkv, bias, T,
+            H, G, d, rotary_dim, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size, write_kv);
   return qd_last_error();
 }
 

@@ -1,0 +1,112 @@
+// The layers of a prompt step launched from native code.
+//
+// A step with a prompt portion is no replayed graph: its kernels are launched one by one, about nine
+// per layer, and from Python each launch costs some 15 us of interpreter, argument conversion and
+// tensor bookkeeping -- more than the device needs for portions of a few hundred tokens.  For a model
+// whose layers are all the common composition (pre-norm block, grouped-query attention with one
+// rotary table, SwiGLU, RMSNorm; bfloat16) this file runs the same kernels, in the same order, with
+// the same arguments as the parts do, from one C++ loop:
+//
+//   per layer:  h = rmsnorm(x += delta) ; qkv = h Wqkv^T ; bias, rotation, cache write ; attention over
+//               the pages ; delta = attn Wo^T ; h = rmsnorm(x += delta) ; gu = h Wgu^T ; act = silu(gate) * up ;
+//               delta = act Wd^T
+//   at the end: hrows = rmsnorm(x += delta) at the wanted rows          (the output projection stays outside)
+//
+// It holds no kernel of its own.  The launchers live in the other libraries of this directory and the
+// matrix products in cuBLAS (as the reference's do, gpu_kernels.cu:431-436); the caller hands over their
+// addresses, so this library links against none of them and uses whatever cuBLAS the process has loaded.
+// The reference launches its layers from C++ as well (gpu_decoder.cu:321-497).
+#include "common.cuh"
+#include "entry_points.h"
+#include <cublas_v2.h>
+
+struct PeLayer {
+  const float* norm1_w; const float* norm2_w;
+  const void* wqkv; const float* bqkv; const void* wo; const void* wgu; const void* wd;
+  void* kv;                        // this layer's pages [pages, 2, G, page_size, d]
+  float eps1, eps2;
+  int write_kv, pad;
+};
+
+// cublasGemmEx (the 32-bit form; the header overloads the name for C++)
+typedef cublasStatus_t (*PeGemmEx)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*,
+                                   const void*, cudaDataType, int, const void*, cudaDataType, int, const void*, void*,
+                                   cudaDataType, int, cublasComputeType_t, cublasGemmAlgo_t);
+
+struct PeFns {
+  decltype(&qd_add_rmsnorm) add_rmsnorm;
+  decltype(&qd_rope_kv_write_biased) rope_kv_write;
+  decltype(&qd_swiglu) swiglu;
+  decltype(&qd_prefill_attention) attention_regs;       // mma.sync, any supported head size
+  decltype(&qd_prefill_attention_tc5) attention_tc5;    // tcgen05, head size 64 or 128
+  PeGemmEx gemm_ex;
+  cublasHandle_t blas;             // the caller's handle, bound to ``stream``
+};
+
+struct PeParams {
+  PeFns fn;
+  const PeLayer* layers; int n_layers;
+  int T, R, D, H, G, d, F, page_size, window, rotary_dim, pairing, max_blocks, use_tc5, n_wanted;
+  float scale, final_eps;
+  long long n_pages;
+  const int* positions; const int* slot_map; const int* block_table; const int* cu_tokens; const int* start_pos;
+  const int* logit_rows;
+  const float* cos_t; const float* sin_t; const float* final_w;
+  float* x;                        // [T, D] residual sum, float32
+  const void* delta0;              // null: nothing pending on entry
+  void* h; void* qkv; void* attn; void* delta; void* gu; void* act;   // bfloat16 scratch: [T,D] [T,(H+2G)d] [T,Hd] [T,D] [T,2F] [T,F]
+  void* hrows;                     // [n_wanted, D] bfloat16
+};
+
+extern "C" int qd_prompt_exec_struct_sizes(int* layer_bytes, int* params_bytes) {
+  *layer_bytes = (int)sizeof(PeLayer);
+  *params_bytes = (int)sizeof(PeParams);
+  return 0;
+}
+
+// Y[T, N] = X[T, K] W[N, K]^T, all bfloat16 row-major, float32 accumulation
+static int product(const PeParams& p, const void* W, const void* X, void* Y, int T, int N, int K) {
+  const float one = 1.f, zero = 0.f;
+  cublasStatus_t st = p.fn.gemm_ex(p.fn.blas, CUBLAS_OP_T, CUBLAS_OP_N, N, T, K, &one, W, CUDA_R_16BF, K, X, CUDA_R_16BF,
+                                   K, &zero, Y, CUDA_R_16BF, N, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  return st == CUBLAS_STATUS_SUCCESS ? 0 : 20000 + (int)st;
+}
+
+#define PE_TRY(call)            \
+  do {                          \
+    int rc_ = (call);           \
+    if (rc_ != 0) return rc_;   \
+  } while (0)
+
+extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
+  const PeParams& p = *pp;
+  if (p.T <= 0 || p.n_layers < 0) return QD_ERR_UNSUPPORTED;
+  const int T = p.T, D = p.D, H = p.H, G = p.G, d = p.d, F = p.F;
+  const int n_qkv = (H + 2 * G) * d;
+  const long long xn = (long long)T * D;
+  const void* delta = p.delta0;
+  for (int l = 0; l < p.n_layers; l++) {
+    const PeLayer& L = p.layers[l];
+    PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? QD_BF16 : -1, L.norm1_w, p.h, QD_BF16, nullptr, T, D, L.eps1, 1, 1, xn,
+                            stream));
+    PE_TRY(product(p, L.wqkv, p.h, p.qkv, T, n_qkv, D));
+    PE_TRY(p.fn.rope_kv_write(p.qkv, L.bqkv, T, H, G, d, p.rotary_dim, p.pairing, p.cos_t, p.sin_t, p.positions, L.kv,
+                              p.slot_map, p.page_size, L.write_kv, stream));
+    if (p.use_tc5)
+      PE_TRY(p.fn.attention_tc5(p.qkv, n_qkv, p.attn, L.kv, p.n_pages, p.block_table, p.max_blocks, p.cu_tokens,
+                                p.start_pos, p.R, T, H, G, d, p.page_size, p.scale, p.window, nullptr, stream));
+    else
+      PE_TRY(p.fn.attention_regs(p.qkv, n_qkv, p.attn, L.kv, p.block_table, p.max_blocks, p.cu_tokens, p.start_pos, p.R,
+                                 T, H, G, d, p.page_size, p.scale, p.window, stream));
+    PE_TRY(product(p, L.wo, p.attn, p.delta, T, D, H * d));
+    PE_TRY(p.fn.add_rmsnorm(p.x, p.delta, QD_BF16, L.norm2_w, p.h, QD_BF16, nullptr, T, D, L.eps2, 1, 1, xn, stream));
+    PE_TRY(product(p, L.wgu, p.h, p.gu, T, 2 * F, D));
+    PE_TRY(p.fn.swiglu(p.gu, p.act, QD_BF16, T, F, stream));
+    PE_TRY(product(p, L.wd, p.act, p.delta, T, D, F));
+    delta = p.delta;
+  }
+  if (p.n_wanted > 0)
+    PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? QD_BF16 : -1, p.final_w, p.hrows, QD_BF16, p.logit_rows, p.n_wanted, D,
+                            p.final_eps, 0, 1, xn, stream));       // only the wanted rows: x itself stays as it is
+  return 0;
+}

@@ -542,6 +542,79 @@ def check_status() -> None:
                                   "launches since the last check are invalid")
 
 
+# ------------------------------------------------------------------ the layers of a prompt step from native code
+class PromptLayer(ctypes.Structure):
+    """One schedule entry of the native prompt step (PeLayer in csrc/prompt_exec.cu)."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("norm1_w", "norm2_w", "wqkv", "bqkv", "wo", "wgu", "wd", "kv")] + \
+        [("eps1", ctypes.c_float), ("eps2", ctypes.c_float), ("write_kv", ctypes.c_int), ("pad", ctypes.c_int)]
+
+
+class PromptFns(ctypes.Structure):
+    """Addresses of the launchers and of the library product that the native prompt step calls."""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("add_rmsnorm", "rope_kv_write", "swiglu", "attention_regs",
+                                               "attention_tc5", "gemm_ex", "blas")]
+
+
+class PromptParams(ctypes.Structure):
+    """Arguments of the native prompt step (PeParams in csrc/prompt_exec.cu)."""
+    _fields_ = [("fn", PromptFns), ("layers", ctypes.c_void_p), ("n_layers", ctypes.c_int)] + \
+        [(n, ctypes.c_int) for n in ("T", "R", "D", "H", "G", "d", "F", "page_size", "window", "rotary_dim",
+                                     "pairing", "max_blocks", "use_tc5", "n_wanted")] + \
+        [("scale", ctypes.c_float), ("final_eps", ctypes.c_float), ("n_pages", ctypes.c_longlong)] + \
+        [(n, ctypes.c_void_p) for n in ("positions", "slot_map", "block_table", "cu_tokens", "start_pos",
+                                        "logit_rows", "cos_t", "sin_t", "final_w", "x", "delta0", "h", "qkv",
+                                        "attn", "delta", "gu", "act", "hrows")]
+
+
+def prompt_exec_struct_sizes_match() -> bool:
+    a, b = ctypes.c_int(0), ctypes.c_int(0)
+    library("prompt_exec").qd_prompt_exec_struct_sizes(ctypes.byref(a), ctypes.byref(b))
+    return a.value == ctypes.sizeof(PromptLayer) and b.value == ctypes.sizeof(PromptParams)
+
+
+def _loaded_cublas() -> ctypes.CDLL:
+    """The cuBLAS that this process has loaded already (torch's), found among the mapped files: the native
+    prompt step must call the same copy whose handle it is given."""
+    torch.cuda.current_blas_handle()          # makes torch load and initialise it
+    with open("/proc/self/maps") as f:
+        for line in f:
+            path = line.split(None, 5)[-1].strip() if line.count("/") else ""
+            if "/libcublas.so" in path:
+                return ctypes.CDLL(path)
+    raise KernelError("no libcublas is loaded in this process")
+
+
+_prompt_fns: list = []
+
+
+def prompt_fns() -> PromptFns:
+    """The launchers' addresses (the libraries are built and loaded on the first call); ``blas`` is filled
+    in per step."""
+    if not _prompt_fns:
+        addr = lambda f: ctypes.cast(f, ctypes.c_void_p).value
+        ew, fl, t5 = library("elementwise"), library("attention_flash"), library("attention_tc5")
+        fns = PromptFns()
+        fns.add_rmsnorm = addr(ew.qd_add_rmsnorm)
+        fns.rope_kv_write = addr(ew.qd_rope_kv_write_biased)
+        fns.swiglu = addr(ew.qd_swiglu)
+        fns.attention_regs = addr(fl.qd_prefill_attention)
+        fns.attention_tc5 = addr(t5.qd_prefill_attention_tc5)
+        fns.gemm_ex = addr(_loaded_cublas().cublasGemmEx)
+        _prompt_fns.append(fns)
+    return _prompt_fns[0]
+
+
+def prompt_exec(params: PromptParams, n_launches: int) -> None:
+    """All layers of a prompt step and the final norm at the wanted rows, launched from one native loop on
+    the step's stream (``params.fn.blas`` must be a cuBLAS handle bound to that stream)."""
+    stream = _stream()
+    _launch_count[0] += n_launches - 1
+    code = library("prompt_exec").qd_prompt_exec(ctypes.byref(params), stream)
+    if code >= 20000:
+        raise KernelError(f"prompt_exec: cuBLAS status {code - 20000}")
+    _check(code, "prompt_exec")
+
+
 # ------------------------------------------------------------------ a whole decode step in one kernel
 class FusedLayer(ctypes.Structure):
     """One schedule entry of the fused decode step (FdLayer in csrc/decode_fused.cu)."""

@@ -63,6 +63,7 @@ class DecoderModel:
             Linear(spec.hidden_size, [(spec.lm_head_tensor[:-len(".weight")], spec.vocab_size)], bias=False)
         self.embedding: Optional[torch.Tensor] = None
         self.fused_decode = None     # parts.fused_decode.FusedDecode once bound, if the parts allow it
+        self.native_prompt = None    # parts.native_prompt.NativePrompt once bound, if the parts allow it
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
 
@@ -94,6 +95,8 @@ class DecoderModel:
         self.prepared_positions = min(max_positions, self.max_positions)
         from .fused_decode import FusedDecode
         self.fused_decode = FusedDecode.try_build(self)
+        from .native_prompt import NativePrompt
+        self.native_prompt = NativePrompt.try_build(self)
 
     # ---- cache -------------------------------------------------------------
     def cache_layout(self) -> CacheLayout:
@@ -117,6 +120,12 @@ class DecoderModel:
             return self.fused_decode.forward(ctx)
         x = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=self.device)
         kernels.embedding(x, self.embedding, ctx.tokens)
+        if self.native_prompt is not None and self.native_prompt.takes(ctx):
+            # the common composition, many tokens: the layers' launches come from one native loop
+            h = self.native_prompt.forward(ctx, x)
+            if h is None:
+                return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+            return self.lm_head.forward(h, out_dtype=torch.float32)
         stream = ResidualStream(x)
         for i, e in enumerate(self.schedule):
             self.layers[e.layer].forward(stream, ctx, self._cache_view(i, ctx))
