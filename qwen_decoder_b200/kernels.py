@@ -584,24 +584,27 @@ def _loaded_cublas() -> ctypes.CDLL:
     raise KernelError("no libcublas is loaded in this process")
 
 
-_prompt_fns: list = []
+_prompt_fns: dict = {}
 
 
-def prompt_fns() -> PromptFns:
-    """The launchers' addresses (the libraries are built and loaded on the first call); ``blas`` is filled
-    in per step."""
-    if not _prompt_fns:
+def prompt_fns(use_tc5: bool) -> PromptFns:
+    """The launchers' addresses (their libraries are built and loaded on the first call; the attention
+    kernel that the model does not use stays unbuilt); ``blas`` is filled in per step."""
+    fns = _prompt_fns.get(use_tc5)
+    if fns is None:
         addr = lambda f: ctypes.cast(f, ctypes.c_void_p).value
-        ew, fl, t5 = library("elementwise"), library("attention_flash"), library("attention_tc5")
+        ew = library("elementwise")
         fns = PromptFns()
         fns.add_rmsnorm = addr(ew.qd_add_rmsnorm)
         fns.rope_kv_write = addr(ew.qd_rope_kv_write_biased)
         fns.swiglu = addr(ew.qd_swiglu)
-        fns.attention_regs = addr(fl.qd_prefill_attention)
-        fns.attention_tc5 = addr(t5.qd_prefill_attention_tc5)
+        if use_tc5:
+            fns.attention_tc5 = addr(library("attention_tc5").qd_prefill_attention_tc5)
+        else:
+            fns.attention_regs = addr(library("attention_flash").qd_prefill_attention)
         fns.gemm_ex = addr(_loaded_cublas().cublasGemmEx)
-        _prompt_fns.append(fns)
-    return _prompt_fns[0]
+        _prompt_fns[use_tc5] = fns
+    return fns
 
 
 def prompt_exec(params: PromptParams, n_launches: int) -> None:

@@ -133,7 +133,8 @@ class NativePrompt:
         group = ctx.groups[0]
         pos = c["position_obj"]
         p = kernels.PromptParams()
-        p.fn = kernels.prompt_fns()
+        use_tc5 = self.attention_impl(group.page_size)
+        p.fn = kernels.prompt_fns(bool(use_tc5))
         p.fn.blas = torch.cuda.current_blas_handle()
         p.layers = ctypes.cast(self._layer_array(ctx.cache), ctypes.c_void_p)
         p.n_layers = len(self.entries)
@@ -141,7 +142,7 @@ class NativePrompt:
         p.page_size, p.window = group.page_size, c["window"] or 0
         p.rotary_dim, p.pairing = c["rotary_dim"], c["pairing"]
         p.max_blocks = group.block_table.shape[1]
-        p.use_tc5 = self.attention_impl(group.page_size)
+        p.use_tc5 = use_tc5
         p.n_wanted = ctx.num_wanted
         p.scale, p.final_eps = c["scale"], c["final"]["eps"]
         p.n_pages = ctx.cache.layer_kv(0).shape[0]
