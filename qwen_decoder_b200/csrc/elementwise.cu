@@ -285,11 +285,43 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int H, int G, int d, i
   }
 }
 
-// bfloat16, adjacent pairs, head size and rotated width multiples of 8: a thread takes 16 bytes (four pairs)
-// of q, k or v of one token, with its cosines and sines as two float4.
+// bfloat16, head size a multiple of 8: a thread takes 16 bytes (8 elements) of q, k or v of one token.
+// pairing 0 (adjacent pairs, rotated width a multiple of 8): the piece holds four pairs, their cosines and
+// sines are two float4.  pairing 1 (element i with i + rotary_dim / 2, rotated width a multiple of 16): the
+// thread of a piece in the first half takes the partner piece of the second half as well; the partner's own
+// thread has nothing to do.  ``bias`` (float32 [(H + 2G) d] or null) is added first and the sum rounded to
+// bfloat16, as a product with a bias epilogue would leave it.
+__device__ __forceinline__ void rkv_unpack(const uint4& raw, float (&f)[8]) {
+  const unsigned* u = reinterpret_cast<const unsigned*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&u[i]);
+    f[2 * i] = __low2float(v);
+    f[2 * i + 1] = __high2float(v);
+  }
+}
+__device__ __forceinline__ uint4 rkv_pack(const float (&f)[8]) {
+  uint4 raw;
+  unsigned* u = reinterpret_cast<unsigned*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    __nv_bfloat162 r = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    u[i] = *reinterpret_cast<unsigned*>(&r);
+  }
+  return raw;
+}
+__device__ __forceinline__ uint4 rkv_add_bias(const uint4& raw, const float* __restrict__ b) {
+  float f[8];
+  rkv_unpack(raw, f);
+  const float4 b0 = *reinterpret_cast<const float4*>(b), b1 = *reinterpret_cast<const float4*>(b + 4);
+  f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+  f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+  return rkv_pack(f);
+}
+
 __global__ void __launch_bounds__(256)
 rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias, int T, int H, int G, int d,
-                         int rotary_dim, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         int rotary_dim, int pairing, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                          const int* __restrict__ positions, bf16* __restrict__ kv,
                          const int* __restrict__ slot_map, int page_size, int write_kv) {
   pdl_launch_dependents();
@@ -300,43 +332,71 @@ rope_kv_write_vec_kernel(bf16* __restrict__ qkv, const float* __restrict__ bias,
   const int t = (int)(idx / per_row), piece = (int)(idx - (long long)t * per_row);
   const int head = piece / (d / 8), c8 = (piece - head * (d / 8)) * 8;      // element offset inside the head
   if (head >= H && !write_kv) return;
+  const int half = rotary_dim >> 1;
+  const bool rotated = head < H + G && cos_t && c8 < rotary_dim;
+  if (rotated && pairing == 1 && c8 >= half) return;       // the thread of the first-half piece writes this one
   bf16* src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d + c8;
-  uint4 raw = *reinterpret_cast<const uint4*>(src);
-  if (bias) {          // the projection's bias, where the product before left it out
-    const float4 b0 = *reinterpret_cast<const float4*>(bias + (size_t)head * d + c8);
-    const float4 b1 = *reinterpret_cast<const float4*>(bias + (size_t)head * d + c8 + 4);
-    const float bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-    unsigned* u = reinterpret_cast<unsigned*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
-      __nv_bfloat162 r = __floats2bfloat162_rn(__low2float(v) + bs[2 * i], __high2float(v) + bs[2 * i + 1]);
-      u[i] = *reinterpret_cast<unsigned*>(&r);
-    }
-  }
-  if (head < H + G && cos_t && c8 < rotary_dim) {
-    const int half = rotary_dim >> 1;
-    const size_t tab = (size_t)positions[t] * half + (c8 >> 1);
-    const float4 cv = *reinterpret_cast<const float4*>(cos_t + tab), sv = *reinterpret_cast<const float4*>(sin_t + tab);
-    const float cs[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
-    unsigned* u = reinterpret_cast<unsigned*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u[i]);
-      float a = __low2float(v), b = __high2float(v);
-      __nv_bfloat162 r = __floats2bfloat162_rn(a * cs[i] - b * sn[i], a * sn[i] + b * cs[i]);
-      u[i] = *reinterpret_cast<unsigned*>(&r);
-    }
-  }
-  if (head < H) {
-    *reinterpret_cast<uint4*>(src) = raw;
-  } else {
+  // where the piece at offset c goes: q in place, k and v to the token's slot of the cache
+  bf16* dst = src;
+  if (head >= H) {
     const int slot = slot_map[t];
     const int page = slot / page_size, off = slot - page * page_size;
     const int g = head < H + G ? head - H : head - H - G;
     const size_t base = (size_t)page * 2 * G * page_size * d + (head < H + G ? 0 : (size_t)G * page_size * d);
-    *reinterpret_cast<uint4*>(kv + base + ((size_t)g * page_size + off) * d + c8) = raw;
+    dst = kv + base + ((size_t)g * page_size + off) * d + c8;
   }
+  uint4 raw = *reinterpret_cast<const uint4*>(src);
+  if (bias) raw = rkv_add_bias(raw, bias + (size_t)head * d + c8);
+  if (!rotated) {
+    *reinterpret_cast<uint4*>(dst) = raw;
+    return;
+  }
+  if (pairing == 0) {
+    const size_t tab = (size_t)positions[t] * half + (c8 >> 1);
+    const float4 cv = *reinterpret_cast<const float4*>(cos_t + tab), sv = *reinterpret_cast<const float4*>(sin_t + tab);
+    const float cs[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
+    float f[8];
+    rkv_unpack(raw, f);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float a = f[2 * i], b = f[2 * i + 1];
+      f[2 * i] = a * cs[i] - b * sn[i];
+      f[2 * i + 1] = a * sn[i] + b * cs[i];
+    }
+    *reinterpret_cast<uint4*>(dst) = rkv_pack(f);
+    return;
+  }
+  // pairing 1: elements c8 .. c8+7 with c8+half .. c8+half+7, angles c8 .. c8+7
+  uint4 raw2 = *reinterpret_cast<const uint4*>(src + half);
+  if (bias) raw2 = rkv_add_bias(raw2, bias + (size_t)head * d + c8 + half);
+  const size_t tab = (size_t)positions[t] * half + c8;
+  const float4 c0 = *reinterpret_cast<const float4*>(cos_t + tab), c1 = *reinterpret_cast<const float4*>(cos_t + tab + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sin_t + tab), s1 = *reinterpret_cast<const float4*>(sin_t + tab + 4);
+  const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  float fa[8], fb[8];
+  rkv_unpack(raw, fa);
+  rkv_unpack(raw2, fb);
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const float a = fa[i], b = fb[i];
+    fa[i] = a * cs[i] - b * sn[i];
+    fb[i] = a * sn[i] + b * cs[i];
+  }
+  *reinterpret_cast<uint4*>(dst) = rkv_pack(fa);
+  *reinterpret_cast<uint4*>(dst + half) = rkv_pack(fb);
+}
+
+// what the vectorized kernel takes
+static bool rope_vec_ok(const void* qkv, const float* bias, int d, int rotary_dim, int pairing, const float* cos_t,
+                        const float* sin_t, const void* kv, int write_kv) {
+  if (d % 8 != 0 || rotary_dim > d || rotary_dim < 0) return false;
+  if (pairing == 0 ? rotary_dim % 8 != 0 : (pairing != 1 || rotary_dim % 16 != 0)) return false;
+  if (((uintptr_t)qkv & 15) || ((uintptr_t)bias & 15) || (write_kv && ((uintptr_t)kv & 15))) return false;
+  if (cos_t && (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15)) return false;
+  // pairing 1 reads eight table entries from an offset that is a multiple of 8 floats: rows of rotary_dim / 2
+  // floats keep that 16-byte aligned only when rotary_dim / 2 is a multiple of 4 (it is a multiple of 8 here)
+  return true;
 }
 
 extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d, int rotary_dim,
@@ -349,12 +409,11 @@ extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d
     qd_launch(rope_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                        sin_t, positions, (float*)kv, slot_map,
                                                        page_size, write_kv);
-  else if (dtype == QD_BF16 && pairing == 0 && d % 8 == 0 && rotary_dim % 8 == 0 && ((uintptr_t)qkv & 15) == 0 &&
-           (!write_kv || ((uintptr_t)kv & 15) == 0) && (!cos_t || (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15) == 0)) {
+  else if (dtype == QD_BF16 && rope_vec_ok(qkv, nullptr, d, rotary_dim, pairing, cos_t, sin_t, kv, write_kv)) {
     const long long pieces = (long long)T * (H + 2 * G) * d / 8;
     qd_launch(rope_kv_write_vec_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream, (bf16*)qkv,
-              (const float*)nullptr, T, H, G, d, rotary_dim, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size,
-              write_kv);
+              (const float*)nullptr, T, H, G, d, rotary_dim, pairing, cos_t, sin_t, positions, (bf16*)kv, slot_map,
+              page_size, write_kv);
   } else if (dtype == QD_BF16)
     qd_launch(rope_kv_write_kernel<bf16>, dim3(T), dim3(256), 0, stream, (bf16*)qkv, H, G, d, rotary_dim, pairing, cos_t,
                                                       sin_t, positions, (bf16*)kv, slot_map,
@@ -365,21 +424,17 @@ extern "C" int qd_rope_kv_write(void* qkv, int dtype, int T, int H, int G, int d
 }
 
 // The vectorized kernel alone, with the projection's float32 bias [(H + 2G) d] added first (null: none):
-// bfloat16, adjacent pairs, head size and rotated width multiples of 8, 16-byte aligned pointers; refuses
-// anything else.  The sum is rounded to bfloat16 before the rotation, as a product with a bias epilogue
-// would leave it.
+// bfloat16, head size a multiple of 8, rotated width a multiple of 8 (adjacent pairs) or 16 (half-split pairs),
+// 16-byte aligned pointers; refuses anything else.
 extern "C" int qd_rope_kv_write_biased(void* qkv, const float* bias, int T, int H, int G, int d, int rotary_dim,
                                        int pairing, const float* cos_t, const float* sin_t, const int* positions,
                                        void* kv, const int* slot_map, int page_size, int write_kv,
                                        cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (pairing != 0 || d % 8 != 0 || rotary_dim % 8 != 0 || rotary_dim > d || rotary_dim < 0) return QD_ERR_UNSUPPORTED;
-  if (((uintptr_t)qkv & 15) || ((uintptr_t)bias & 15) || (write_kv && ((uintptr_t)kv & 15)) ||
-      (cos_t && (((uintptr_t)cos_t | (uintptr_t)sin_t) & 15)))
-    return QD_ERR_UNSUPPORTED;
+  if (!rope_vec_ok(qkv, bias, d, rotary_dim, pairing, cos_t, sin_t, kv, write_kv)) return QD_ERR_UNSUPPORTED;
   const long long pieces = (long long)T * (H + 2 * G) * d / 8;
   qd_launch(rope_kv_write_vec_kernel, dim3((unsigned)((pieces + 255) / 256)), dim3(256), 0, stream, (bf16*)qkv, bias, T,
-            H, G, d, rotary_dim, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size, write_kv);
+            H, G, d, rotary_dim, pairing, cos_t, sin_t, positions, (bf16*)kv, slot_map, page_size, write_kv);
   return qd_last_error();
 }
 

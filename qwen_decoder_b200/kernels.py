@@ -176,6 +176,25 @@ def rope_kv_write(qkv: torch.Tensor, H: int, G: int, d: int, rotary_dim: int, pa
         _I(1 if write_kv else 0), _stream()), "rope_kv_write")
 
 
+def rope_kv_write_biased(qkv: torch.Tensor, bias: Optional[torch.Tensor], H: int, G: int, d: int, rotary_dim: int,
+                         pairing: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                         positions: torch.Tensor, kv: Optional[torch.Tensor], slot_map: Optional[torch.Tensor],
+                         page_size: int, write_kv: bool) -> None:
+    """``rope_kv_write`` with the projection's float32 bias [(H+2G)*d] added first (rounded to bfloat16 before
+    the rotation); bfloat16 and the vectorized kernel's sizes only (KernelError otherwise)."""
+    T = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.shape[1] == (H + 2 * G) * d and positions.dtype == torch.int32
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == (H + 2 * G) * d)
+    _contig(qkv, "qkv")
+    if write_kv:
+        assert kv is not None and kv.dtype == qkv.dtype and tuple(kv.shape[1:]) == (2, G, page_size, d)
+        _contig(kv, "kv")
+    _check(library("elementwise").qd_rope_kv_write_biased(
+        _ptr(qkv), _ptr(bias), _I(T), _I(H), _I(G), _I(d), _I(rotary_dim), _I(pairing), _ptr(cos), _ptr(sin),
+        _ptr(positions), _ptr(kv), _ptr(slot_map), _I(page_size), _I(1 if write_kv else 0), _stream()),
+        "rope_kv_write_biased")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
     T, F = out.shape

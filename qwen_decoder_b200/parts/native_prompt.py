@@ -4,7 +4,7 @@ A step with a prompt portion is launched kernel by kernel.  From Python that is 
 15 us of host time per launch, 5 ms for 36 layers, while the device needs 3 ms for a
 portion of 512 tokens: the device waits for the interpreter.  When every layer of the
 schedule is the common composition -- pre-norm block, grouped-query attention with one
-rotary table (adjacent pairs), SwiGLU, RMSNorm, bfloat16 -- the same launchers are called,
+rotary table, SwiGLU, RMSNorm, bfloat16 -- the same launchers are called,
 in the same order and with the same arguments, from one C++ loop instead.  The embedding
 before it and the output projection after it stay with the model.
 
@@ -73,7 +73,9 @@ class NativePrompt:
         c = common
         n_qkv = (c["H"] + 2 * c["G"]) * c["d"]
         # what the vectorized rotation kernel and the library product take
-        if c["pairing"] != 0 or c["d"] % 8 or c["rotary_dim"] % 8 or c["D"] % 8 or c["F"] % 8 or n_qkv % 8:
+        if c["pairing"] not in (0, 1) or c["rotary_dim"] % (8 if c["pairing"] == 0 else 16):
+            return None
+        if c["d"] % 8 or c["D"] % 8 or c["F"] % 8 or n_qkv % 8:
             return None
         if not kernels.prompt_exec_struct_sizes_match():
             raise kernels.KernelError("prompt_exec: the argument structures of the library and of the "

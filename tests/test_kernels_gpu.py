@@ -163,6 +163,49 @@ def test_rope_kv_write(dt, pairing):
         close(kvc[page, 1, :, off, :].reshape(-1), wv[t], dt)
 
 
+@pytest.mark.parametrize("pairing", ["adjacent", "half"])
+@pytest.mark.parametrize("sizes", [(6, 2, 48, 48), (4, 1, 128, 128), (3, 3, 64, 32), (2, 1, 40, 40)])
+def test_rope_kv_write_with_bias(pairing, sizes):
+    """The vectorized kernel with the projection's bias, both pairings, partly rotated heads; sizes it does
+    not take are refused, not computed wrongly."""
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.parts.rotary import Rotary
+    H, G, d, rd = sizes
+    page_size, T, base = 16, 37, 20000.0
+    dt = torch.bfloat16
+    rot = Rotary(d, rd, base, pairing)
+    rot.prepare(400, torch.device(DEV))
+    g = torch.Generator().manual_seed(15)
+    qkv = torch.randn(T, (H + 2 * G) * d, generator=g).to(dt)
+    bias = torch.randn((H + 2 * G) * d, generator=g)
+    positions = torch.randint(0, 400, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(4 * page_size, generator=g)[:T].to(torch.int32)
+    kv = torch.zeros(4, 2, G, page_size, d, dtype=dt, device=DEV)
+    dq = qkv.to(DEV).clone()
+    call = lambda: kernels.rope_kv_write_biased(dq, bias.to(DEV), H, G, d, rd, rot.pairing_code, rot.cos, rot.sin,
+                                                positions.to(DEV), kv, slots.to(DEV), page_size, True)
+    if rd % (8 if pairing == "adjacent" else 16):
+        with pytest.raises(kernels.KernelError):
+            call()
+        return
+    call()
+    x = (qkv.float() + bias).to(dt).double()           # the sum is rounded to bfloat16 before the rotation
+
+    def rotate(part, heads):
+        part = part.reshape(T, heads, d)
+        turned = plain_model.rope(part[:, :, :rd].reshape(T, heads * rd), positions, heads, rd, base, pairing)
+        return torch.cat([turned.reshape(T, heads, rd), part[:, :, rd:]], dim=2).reshape(T, heads * d)
+
+    wq, wk = rotate(x[:, :H * d], H), rotate(x[:, H * d:(H + G) * d], G)
+    wv = x[:, (H + G) * d:]
+    close(dq[:, :H * d], wq, dt)
+    kvc = kv.cpu()
+    for t in range(T):
+        page, off = int(slots[t]) // page_size, int(slots[t]) % page_size
+        close(kvc[page, 0, :, off, :].reshape(-1), wk[t], dt)
+        close(kvc[page, 1, :, off, :].reshape(-1), wv[t], dt)
+
+
 @pytest.mark.parametrize("dt", DTYPES)
 def test_swiglu(dt):
     from qwen_decoder_b200 import kernels

@@ -45,7 +45,7 @@ def run_portions(runner, seqs, cuts):
     return out
 
 
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_native_prompt_steps_match_the_parts(name, tmp_path):
     folder = make_folder(name, str(tmp_path))
     cfg, w = plain_model.read_folder(folder)
@@ -67,12 +67,9 @@ def test_native_prompt_steps_match_the_parts(name, tmp_path):
     native.cache.check()
 
 
-def test_native_prompt_declines_other_compositions(tmp_path):
-    """Half-split rotary pairing is not what the vectorized rotation kernel takes: the parts' path stays."""
+def test_native_prompt_declines_float32(tmp_path):
+    """The native loop is for bfloat16; the float32 path keeps the parts' own launches."""
     from qwen_decoder_b200.engine import ModelRunner
-    folder = make_folder("C", str(tmp_path))
-    r = ModelRunner.from_folder(folder, dtype="bfloat16", device="cuda:0", num_pages=16, page_size=16, max_requests=2)
-    assert r.model.native_prompt is None
-    r32 = ModelRunner.from_folder(make_folder("A", str(tmp_path / "a")), dtype="float32", device="cuda:0",
+    r32 = ModelRunner.from_folder(make_folder("A", str(tmp_path)), dtype="float32", device="cuda:0",
                                   num_pages=16, page_size=16, max_requests=2)
     assert r32.model.native_prompt is None
