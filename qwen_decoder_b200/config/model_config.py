@@ -73,9 +73,11 @@ class Qwen2Config:
     rms_norm_eps: float
     tie_word_embeddings: bool = False
     hidden_act: str = "silu"
-    # The reference rotates adjacent element pairs (2p, 2p+1)
-    # (gpu_kernels.cu:94-100, cpu_decoder.cpp:135-146).  "half" pairs (p, p + d/2).
-    rope_pairing: str = "adjacent"
+    # Which elements of a head rotate together.  "half" pairs (p, p + d/2): what checkpoints of this
+    # architecture in safetensors form are trained with, hence the default.  "adjacent" pairs (2p, 2p+1),
+    # as the reference rotates the tensors of its own file format (gpu_kernels.cu:94-100,
+    # cpu_decoder.cpp:135-146); the optional key ``rope_pairing`` selects it.
+    rope_pairing: str = "half"
     attention_bias: bool = True  # q, k, v carry a bias (gpu_decoder.cu:347-349)
     eos_token_ids: tuple = ()
     torch_dtype: str = "bfloat16"
@@ -126,7 +128,7 @@ class Qwen2Config:
         act = _get(d, "hidden_act", str, "silu")
         if act != "silu":
             raise ConfigError(f"config.json: 'hidden_act' must be 'silu', got {act!r}")
-        pairing = _get(d, "rope_pairing", str, "adjacent")
+        pairing = _get(d, "rope_pairing", str, "half")
         if pairing not in ("adjacent", "half"):
             raise ConfigError(f"config.json: 'rope_pairing' must be 'adjacent' or 'half', got {pairing!r}")
         eos = d.get("eos_token_id")

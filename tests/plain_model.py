@@ -62,7 +62,7 @@ def rope(x: torch.Tensor, positions: torch.Tensor, n_heads: int, head_dim: int, 
     """Per head, pair p: theta = 1 / base^(2p / head_dim); angle = theta * pos;
     (x0, x1) -> (x0 cos - x1 sin, x0 sin + x1 cos)  (cpu_decoder.cpp:135-157;
     gpu_kernels.cu:94-100).  The reference pairs adjacent elements (2p, 2p+1); ``half``
-    pairs (p, p + head_dim/2) and is here for the engine's other pairing option only."""
+    pairs (p, p + head_dim/2), the convention of this architecture's safetensors checkpoints."""
     T = x.shape[0]
     x = x.reshape(T, n_heads, head_dim).clone()
     p = torch.arange(head_dim // 2, dtype=F64)
@@ -128,7 +128,7 @@ def attention_block(x, w: Dict[str, torch.Tensor], prefix: str, cfg, positions, 
     q = linear(x, w[f"{prefix}self_attn.q_proj.weight"], bias("q"))
     k = linear(x, w[f"{prefix}self_attn.k_proj.weight"], bias("k"))
     v = linear(x, w[f"{prefix}self_attn.v_proj.weight"], bias("v"))
-    pairing = cfg.get("rope_pairing", "adjacent")
+    pairing = cfg.get("rope_pairing", "half")      # the configuration's default; the reference's is "adjacent"
     q = rope(q, positions, H, d, cfg["rope_theta"], pairing)
     k = rope(k, positions, G, d, cfg["rope_theta"], pairing)
     a = attention(q, k, v, H, G, d, window)

@@ -16,15 +16,16 @@ def test_reads_every_key():
     assert c.rope_theta == 1e6 and c.rms_norm_eps == 1e-5 and c.tie_word_embeddings is False
     assert c.group_size == 4 and c.kv_dim == 32 and c.q_dim == 128
     c = Qwen2Config.from_dict(TINY_C)
-    assert c.head_dim == 48 and c.q_dim == 288 and c.rope_pairing == "half"
+    assert c.head_dim == 48 and c.q_dim == 288 and c.rope_pairing == "adjacent"
 
 
 def test_defaults_and_eos():
     d = dict(TINY_A)
     del d["num_key_value_heads"]
+    del d["rope_pairing"]
     d["eos_token_id"] = [3, 5]
     c = Qwen2Config.from_dict(d)
-    assert c.num_key_value_heads == 4 and c.eos_token_ids == (3, 5) and c.rope_pairing == "adjacent"
+    assert c.num_key_value_heads == 4 and c.eos_token_ids == (3, 5) and c.rope_pairing == "half"
     d["eos_token_id"] = 7
     assert Qwen2Config.from_dict(d).eos_token_ids == (7,)
 

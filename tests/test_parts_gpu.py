@@ -106,7 +106,7 @@ def attention_setup(dtype, H, G, d, D, window, page_size=16):
 
 def plain_attention(x, w, H, G, d, window):
     cfg = {"num_attention_heads": H, "num_key_value_heads": G, "head_dim": d, "hidden_size": x.shape[1],
-           "rope_theta": 30000.0}
+           "rope_theta": 30000.0, "rope_pairing": "adjacent"}
     ww = {k.replace("a.", "L.self_attn."): v for k, v in w.items()}
     return plain_model.attention_block(x, ww, "L.", cfg, torch.arange(x.shape[0]), window)
 
