@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include <cooperative_groups.h>
 #include <math.h>
+#include <stdlib.h>
 
 #define AR_WARPS 8
 #define AR_THREADS (AR_WARPS * 32)
@@ -66,15 +67,19 @@ __device__ __forceinline__ float ar_exp2(float x) {
   return y;
 }
 
-template <int HD>
-__global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(const ArParams p) {
+// NS: chunks a warp keeps in flight (stages of its own K/V ring).  With 3 a CTA needs nearly all of an SM's
+// shared memory, which costs nothing while the grid has no more CTAs than the GPU has SMs; 1 leaves room for
+// two CTAs per SM.
+template <int HD, int NS>
+__global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_rope_kernel(const ArParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int LD = HD + AR_PAD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = p.H, G = p.G, gs = H / G, Nqkv = (H + 2 * G) * HD;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);                       // [16][LD] rotated q of the group
   bf16* kvs = qs + 16 * LD;                                           // per warp: K chunk, V chunk [16][LD] each
-  float* mm = reinterpret_cast<float*>(kvs + (size_t)AR_WARPS * 2 * 16 * LD);   // merge: [warps][16]
+  constexpr int STAGE = 2 * 16 * LD;                                  // elements of a stage: K chunk, V chunk
+  float* mm = reinterpret_cast<float*>(kvs + (size_t)AR_WARPS * NS * STAGE);     // merge: [warps][16]
   float* ml = mm + AR_WARPS * 16;                                     // [warps][16]
   float* fac = ml + AR_WARPS * 16;                                    // combine: [16][64] x 3
   bf16* newkv = reinterpret_cast<bf16*>(fac + 3 * 16 * 64);          // the token's own k and v: [2][HD]
@@ -98,12 +103,13 @@ __global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(co
     const size_t k_off = (size_t)g * p.page_size * HD, v_off = ((size_t)G + g) * p.page_size * HD;
 
     // ---- before waiting for the kernel that makes q, k, v: ask for this warp's first chunk of old keys
-    bf16* ks = kvs + (size_t)warp * 2 * 16 * LD;
-    bf16* vs = ks + 16 * LD;
+    bf16* wbuf = kvs + (size_t)warp * NS * STAGE;
     constexpr int CPR = HD / 8;
     constexpr int ROWS_PER_IT = 32 / CPR > 0 ? 32 / CPR : 1;
     const int l_row = lane / CPR, l_col = (lane % CPR) * 8;
-    auto request_chunk = [&](int c) {
+    auto request_chunk = [&](int c, int stage) {
+      bf16* ks = wbuf + (size_t)stage * STAGE;
+      bf16* vs = ks + 16 * LD;
       const int key0 = c * 16;
       const int page = bt[key0 / p.page_size];
       const int in_page = key0 % p.page_size;
@@ -116,11 +122,14 @@ __global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(co
         ar_cp_async16(ks + row * LD + l_col, kg + (bytes ? row * HD + l_col : 0), bytes);
         ar_cp_async16(vs + row * LD + l_col, vg + (bytes ? row * HD + l_col : 0), bytes);
       }
-      asm volatile("cp.async.commit_group;\n" ::);
     };
+    // the first NS chunks of this warp: all of them hold keys of earlier steps only
     const int c_first = c0 + warp;
-    const bool early = c_first < c1;
-    if (early) request_chunk(c_first);
+#pragma unroll
+    for (int j = 0; j < NS; j++) {
+      if (c_first + j * AR_WARPS < c1) request_chunk(c_first + j * AR_WARPS, j);
+      asm volatile("cp.async.commit_group;\n" ::);
+    }
     ar_stamp(p, 1);
     pdl_wait();
     ar_stamp(p, 2);
@@ -190,10 +199,13 @@ __global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(co
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    for (int c = c_first; c < c1; c += AR_WARPS) {
+    int it = 0;
+    for (int c = c_first; c < c1; c += AR_WARPS, it++) {
       const int key0 = c * 16;
-      if (!(early && c == c_first)) request_chunk(c);
-      asm volatile("cp.async.wait_group 0;\n" ::);
+      const int stage = it % NS;
+      bf16* ks = wbuf + (size_t)stage * STAGE;
+      bf16* vs = ks + 16 * LD;
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(NS - 1));     // NS groups are out: the oldest is this chunk's
       __syncwarp();
       if (p.write_kv && c == chunk_hi - 1) {
         // the token's own k and v, made above: into this warp's copy of the chunk (no trip through memory)
@@ -252,20 +264,23 @@ __global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(co
         ar_mma(o[2 * dn + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
       }
       __syncwarp();
+      if (c + NS * AR_WARPS < c1) request_chunk(c + NS * AR_WARPS, stage);       // the stage is free again
+      asm volatile("cp.async.commit_group;\n" ::);
     }
+    asm volatile("cp.async.wait_group 0;\n" ::);
     ar_stamp(p, 4);
     pdl_launch_dependents();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     // ---- merge the 8 warps; a warp's partial output [16][HD] float32 lies over its own K/V chunk buffers
-    // (2 * 16 * LD bfloat16 = 16 * (HD + 8) floats), which it no longer reads
+    // (a stage is 2 * 16 * LD bfloat16 = 16 * (HD + 8) floats), which it no longer reads
     {
       const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
       __syncwarp();
 #pragma unroll
       for (int n = 0; n < HD / 8; n++) {
-        float* d0 = reinterpret_cast<float*>(ks) + (size_t)r0 * HD + n * 8 + cq;
-        float* d1 = reinterpret_cast<float*>(ks) + (size_t)r1 * HD + n * 8 + cq;
+        float* d0 = reinterpret_cast<float*>(wbuf) + (size_t)r0 * HD + n * 8 + cq;
+        float* d1 = reinterpret_cast<float*>(wbuf) + (size_t)r1 * HD + n * 8 + cq;
         d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
       }
       if ((lane & 3) == 0) {
@@ -285,7 +300,7 @@ __global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(co
         for (int w = 0; w < AR_WARPS; w++) {
           float f = ar_exp2(mm[w * 16 + row] - M);
           Lsum += ml[w * 16 + row] * f;
-          O += reinterpret_cast<const float*>(kvs + (size_t)w * 2 * 16 * LD)[(size_t)row * HD + dim] * f;
+          O += reinterpret_cast<const float*>(kvs + (size_t)w * NS * STAGE)[(size_t)row * HD + dim] * f;
         }
       }
       int hd = g * gs + row;
@@ -426,12 +441,12 @@ __global__ void __launch_bounds__(AR_THREADS, 2) decode_attention_rope_kernel(co
 }
 
 
-template <int HD>
-static int ar_launch(const ArParams& p, cudaStream_t stream) {
-  size_t smem = (size_t)16 * (HD + AR_PAD) * sizeof(bf16) + (size_t)AR_WARPS * 2 * 16 * (HD + AR_PAD) * sizeof(bf16) +
+template <int HD, int NS>
+static int ar_launch_ns(const ArParams& p, cudaStream_t stream) {
+  size_t smem = (size_t)16 * (HD + AR_PAD) * sizeof(bf16) + (size_t)AR_WARPS * NS * 2 * 16 * (HD + AR_PAD) * sizeof(bf16) +
                 (size_t)AR_WARPS * 16 * 2 * sizeof(float) + (size_t)3 * 16 * 64 * sizeof(float) +
                 (size_t)2 * HD * sizeof(bf16);
-  auto kernel = decode_attention_rope_kernel<HD>;
+  auto kernel = decode_attention_rope_kernel<HD, NS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();
     return QD_ERR_UNSUPPORTED;
@@ -449,6 +464,23 @@ static int ar_launch(const ArParams& p, cudaStream_t stream) {
   }
   qd_launch(kernel, dim3((unsigned)(p.T * p.G * p.splits)), dim3(AR_THREADS), smem, stream, p);
   return (int)cudaGetLastError();
+}
+
+static int ar_sm_count() {
+  static int sms[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+  return sms[dev] > 0 ? sms[dev] : 1;
+}
+
+// Three chunks in flight per warp while every CTA has an SM of its own, else one (two CTAs per SM).
+template <int HD>
+static int ar_launch(const ArParams& p, cudaStream_t stream) {
+  int stages = (long long)p.T * p.G * p.splits <= ar_sm_count() ? 3 : 1;
+  if (const char* e = getenv("QD_DECODE_ROPE_STAGES")) stages = atoi(e);
+  if (stages >= 3) return ar_launch_ns<HD, 3>(p, stream);
+  return ar_launch_ns<HD, 1>(p, stream);
 }
 
 // One decoded token per request: q, k, v from partial sums, rotation, cache write and attention.
