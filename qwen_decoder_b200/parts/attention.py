@@ -55,7 +55,7 @@ class GQAttention(Mixer):
         self.qkv.bind(source, dtype, device)
         self.out.bind(source, dtype, device)
 
-    def fused_decode_params(self):
+    def native_params(self):
         from .rotary import Rotary
         pos = self.position
         if self.out.bias is not None or not (pos is None or type(pos) is Rotary):

@@ -33,9 +33,10 @@ class Part:
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
         pass
 
-    def fused_decode_params(self) -> Optional[dict]:
-        """The part's tensors and constants, if a fused decode kernel may stand in for its
-        ``forward`` (see ``parts/fused_decode.py``); None, the default, keeps the part's own path."""
+    def native_params(self) -> Optional[dict]:
+        """The part's tensors and constants, if native code may stand in for its ``forward``: the native
+        prompt loop (``parts/native_prompt.py``) and the fused decode step (``parts/fused_decode.py``) run a
+        model only when every part of it answers.  None, the default, keeps the part's own path."""
         return None
 
 

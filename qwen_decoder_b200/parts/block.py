@@ -37,9 +37,9 @@ class PreNormBlock(Block):
         for p in self.parts():
             p.bind(source, dtype, device)
 
-    def fused_decode_params(self):
-        n1, mx = self.input_norm.fused_decode_params(), self.mixer.fused_decode_params()
-        n2, ff = self.post_mixer_norm.fused_decode_params(), self.feed_forward.fused_decode_params()
+    def native_params(self):
+        n1, mx = self.input_norm.native_params(), self.mixer.native_params()
+        n2, ff = self.post_mixer_norm.native_params(), self.feed_forward.native_params()
         if None in (n1, mx, n2, ff) or not all(k in mx for k in ("wqkv", "wo", "H", "G", "d")) \
                 or not all(k in ff for k in ("wgu", "wd", "F")) or "weight" not in n1 or "weight" not in n2:
             return None

@@ -9,7 +9,7 @@ dependent launch (its grid barriers cost what the kernel boundaries cost), so it
 with ``QD_FUSED_DECODE=1`` in the environment; it stays as the base for further work and
 as a second implementation that the tests compare the first with.
 
-Parts stay ignorant of it: a block that can take part answers ``fused_decode_params()``
+Parts stay ignorant of it: a block that can take part answers ``native_params()``
 with its tensors and constants (None otherwise, the default), and this module only
 collects the answers.  A model with any other part keeps the unfused path.
 """
@@ -75,7 +75,7 @@ class FusedDecode:
         for e in model.schedule:
             if e.cache_of is not None:
                 return None
-            answer = getattr(model.layers[e.layer], "fused_decode_params", lambda: None)()
+            answer = getattr(model.layers[e.layer], "native_params", lambda: None)()
             if answer is None:
                 return None
             key = {k: answer[k] for k in ("D", "H", "G", "d", "F", "window", "scale", "rotary_dim", "pairing")}
@@ -87,7 +87,7 @@ class FusedDecode:
             entries.append(answer)
         if common is None or model.hidden_size != common["D"]:
             return None
-        final = getattr(model.final_norm, "fused_decode_params", lambda: None)()
+        final = getattr(model.final_norm, "native_params", lambda: None)()
         if final is None or model.lm_head.bias is not None:
             return None
         c = common

@@ -33,7 +33,7 @@ class SwiGLU(FeedForward):
         self.gate_up.bind(source, dtype, device)
         self.down.bind(source, dtype, device)
 
-    def fused_decode_params(self):
+    def native_params(self):
         return {"D": self.hidden_size, "F": self.intermediate_size, "wgu": self.gate_up.weight,
                 "wd": self.down.weight}
 

@@ -8,7 +8,7 @@ rotary table, SwiGLU, RMSNorm, bfloat16 -- the same launchers are called,
 in the same order and with the same arguments, from one C++ loop instead.  The embedding
 before it and the output projection after it stay with the model.
 
-Parts stay ignorant of it: a block that can take part answers ``fused_decode_params()``
+Parts stay ignorant of it: a block that can take part answers ``native_params()``
 with its tensors and constants (None otherwise, the default), and this module only
 collects the answers.  A model with any other part or another dtype keeps the parts' own
 path, and so does a step of single tokens (it replays as a CUDA graph); so does everything
@@ -55,7 +55,7 @@ class NativePrompt:
             return None
         entries, common = [], None
         for e in model.schedule:
-            answer = getattr(model.layers[e.layer], "fused_decode_params", lambda: None)()
+            answer = getattr(model.layers[e.layer], "native_params", lambda: None)()
             if answer is None:
                 return None
             key = {k: answer[k] for k in ("D", "H", "G", "d", "F", "window", "scale", "rotary_dim", "pairing")}
@@ -67,7 +67,7 @@ class NativePrompt:
             entries.append(answer)
         if common is None or model.hidden_size != common["D"]:
             return None
-        final = getattr(model.final_norm, "fused_decode_params", lambda: None)()
+        final = getattr(model.final_norm, "native_params", lambda: None)()
         if final is None or "weight" not in final:
             return None
         c = common

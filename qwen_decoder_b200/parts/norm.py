@@ -32,7 +32,7 @@ class RMSNorm(Norm):
         # norm scales are used in float32 whatever they are stored in
         self.weight = source.get(f"{self.prefix}weight").to(device=device, dtype=torch.float32).contiguous()
 
-    def fused_decode_params(self) -> Optional[dict]:
+    def native_params(self) -> Optional[dict]:
         return {"weight": self.weight, "eps": self.eps, "size": self.size}
 
     def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
