@@ -8,7 +8,8 @@
 // the same arguments as the parts do, from one C++ loop:
 //
 //   per layer:  h = rmsnorm(x += delta) ; qkv = h Wqkv^T ; bias, rotation, cache write ; attention over
-//               the pages ; delta = attn Wo^T ; h = rmsnorm(x += delta) ; gu = h Wgu^T ; act = silu(gate) * up ;
+//               the pages (the decode kernel for the single tokens of a mixed step, a prompt kernel for the
+//               rest) ; delta = attn Wo^T ; h = rmsnorm(x += delta) ; gu = h Wgu^T ; act = silu(gate) * up ;
 //               delta = act Wd^T
 //   at the end: hrows = rmsnorm(x += delta) at the wanted rows          (the output projection stays outside)
 //
@@ -39,6 +40,7 @@ struct PeFns {
   decltype(&qd_swiglu) swiglu;
   decltype(&qd_prefill_attention) attention_regs;       // mma.sync, any supported head size
   decltype(&qd_prefill_attention_tc5) attention_tc5;    // tcgen05, head size 64 or 128
+  decltype(&qd_decode_attention) attention_decode;      // split-KV, for the single tokens of a mixed step
   PeGemmEx gemm_ex;
   cublasHandle_t blas;             // the caller's handle, bound to ``stream``
 };
@@ -56,6 +58,9 @@ struct PeParams {
   const void* delta0;              // null: nothing pending on entry
   void* h; void* qkv; void* attn; void* delta; void* gu; void* act;   // bfloat16 scratch: [T,D] [T,(H+2G)d] [T,Hd] [T,D] [T,2F] [T,F]
   void* hrows;                     // [n_wanted, D] bfloat16
+  // a mixed step: requests and tokens 0 .. n_decode-1 are single tokens and go to the decode kernel
+  int n_decode, decode_splits;
+  const int* token_req; float* part_o; float* part_ml; unsigned* tickets;
 };
 
 extern "C" int qd_prompt_exec_struct_sizes(int* layer_bytes, int* params_bytes) {
@@ -80,7 +85,7 @@ static int product(const PeParams& p, const void* W, const void* X, void* Y, int
 
 extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
   const PeParams& p = *pp;
-  if (p.T <= 0 || p.n_layers < 0) return QD_ERR_UNSUPPORTED;
+  if (p.T <= 0 || p.n_layers < 0 || p.n_decode < 0 || p.n_decode >= p.R) return QD_ERR_UNSUPPORTED;
   const int T = p.T, D = p.D, H = p.H, G = p.G, d = p.d, F = p.F;
   const int n_qkv = (H + 2 * G) * d;
   const long long xn = (long long)T * D;
@@ -92,12 +97,19 @@ extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
     PE_TRY(product(p, L.wqkv, p.h, p.qkv, T, n_qkv, D));
     PE_TRY(p.fn.rope_kv_write(p.qkv, L.bqkv, T, H, G, d, p.rotary_dim, p.pairing, p.cos_t, p.sin_t, p.positions, L.kv,
                               p.slot_map, p.page_size, L.write_kv, stream));
+    const int nd = p.n_decode;
+    if (nd > 0)
+      PE_TRY(p.fn.attention_decode(p.qkv, n_qkv, p.attn, L.kv, p.block_table, p.max_blocks, p.token_req, p.positions,
+                                   nd, H, G, d, p.page_size, p.scale, p.window, p.decode_splits, p.part_o, p.part_ml,
+                                   p.tickets, stream));
+    const int* bt = p.block_table + (size_t)nd * p.max_blocks;
     if (p.use_tc5)
-      PE_TRY(p.fn.attention_tc5(p.qkv, n_qkv, p.attn, L.kv, p.n_pages, p.block_table, p.max_blocks, p.cu_tokens,
-                                p.start_pos, p.R, T, H, G, d, p.page_size, p.scale, p.window, nullptr, stream));
+      PE_TRY(p.fn.attention_tc5(p.qkv, n_qkv, p.attn, L.kv, p.n_pages, bt, p.max_blocks, p.cu_tokens + nd,
+                                p.start_pos + nd, p.R - nd, T - nd, H, G, d, p.page_size, p.scale, p.window, nullptr,
+                                stream));
     else
-      PE_TRY(p.fn.attention_regs(p.qkv, n_qkv, p.attn, L.kv, p.block_table, p.max_blocks, p.cu_tokens, p.start_pos, p.R,
-                                 T, H, G, d, p.page_size, p.scale, p.window, stream));
+      PE_TRY(p.fn.attention_regs(p.qkv, n_qkv, p.attn, L.kv, bt, p.max_blocks, p.cu_tokens + nd, p.start_pos + nd,
+                                 p.R - nd, T - nd, H, G, d, p.page_size, p.scale, p.window, stream));
     PE_TRY(product(p, L.wo, p.attn, p.delta, T, D, H * d));
     PE_TRY(p.fn.add_rmsnorm(p.x, p.delta, QD_BF16, L.norm2_w, p.h, QD_BF16, nullptr, T, D, L.eps2, 1, 1, xn, stream));
     PE_TRY(product(p, L.wgu, p.h, p.gu, T, 2 * F, D));

@@ -10,6 +10,8 @@ buffer and copied to the device in one transfer.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -61,6 +63,15 @@ class StepContext:
     max_context: int = 0
     num_wanted: int = 0
     all_decode: bool = False      # every entry is one token (the kernels may take a decode path)
+    # In a step that mixes single tokens with longer portions the single tokens come first in the flat
+    # batch (entries are reordered inside the step; logits keep the caller's order): requests and tokens
+    # 0 .. num_decode-1 are those, and a mixer may give them to its decode kernel.  0 when not mixed.
+    num_decode: int = 0
+    decode_max_context: int = 0   # most keys any of them reads
+
+
+# single tokens first in a mixed step, for the mixers' decode kernels (QD_MIXED_SPLIT=0: entries as given)
+_SPLIT_MIXED = os.environ.get("QD_MIXED_SPLIT", "1") != "0"
 
 
 def _pad4(n: int) -> int:
@@ -135,9 +146,10 @@ def validate(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: int,
 
 
 def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: CacheManager, lens, starts,
-         slots, vocab_size: int):
+         slots, vocab_size: int, want_order: Optional[Sequence[int]] = None):
     """Write the step's arrays into the host buffer ``h`` (int32) at ``lay``'s places.  When ``lay``
-    is larger than the batch (a padded decode batch), the padding repeats entry 0."""
+    is larger than the batch (a padded decode batch), the padding repeats entry 0.  ``want_order``: the
+    order of the entries in which their wanted rows are listed (default: as given)."""
     R = len(entries)
     T = sum(lens)
     cu = np.zeros(R + 1, dtype=np.int64)
@@ -156,7 +168,8 @@ def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: Ca
     else:
         token_req = np.repeat(np.arange(R, dtype=np.int64), lens)
         positions = np.arange(T, dtype=np.int64) - cu[:-1][token_req] + starts_a[token_req]
-    want = [cu[i] + np.asarray(e.want, dtype=np.int64).reshape(-1) for i, e in enumerate(entries) if len(e.want)]
+    want = [cu[i] + np.asarray(entries[i].want, dtype=np.int64).reshape(-1)
+            for i in (range(R) if want_order is None else want_order) if len(entries[i].want)]
     want = np.concatenate(want) if want else np.zeros(0, dtype=np.int64)
     padded = lay.T != T or lay.R != R
     if padded and not (T == R and lay.T == lay.R and len(want) == R):
@@ -203,11 +216,22 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, device, voc
     """Validate ``entries`` and make the step's device metadata (one host-to-device copy)."""
     lens, starts, slots = validate(entries, cache, vocab_size, max_positions)
     R, T = len(entries), sum(lens)
+    # single tokens first when the step mixes them with longer portions (stable otherwise)
+    n_single = sum(1 for n in lens if n == 1)
+    want_order = None
+    if 0 < n_single < R and _SPLIT_MIXED:
+        order = [i for i in range(R) if lens[i] == 1] + [i for i in range(R) if lens[i] != 1]
+        place = [0] * R
+        for new_i, old_i in enumerate(order):
+            place[old_i] = new_i
+        want_order = place                      # the caller's entry i is entry place[i] of the step
+        entries = [entries[i] for i in order]
+        lens, starts, slots = [lens[i] for i in order], [starts[i] for i in order], [slots[i] for i in order]
     n_want = sum(len(e.want) for e in entries)
     max_blocks = [max(1, max(len(e.cache.tables[g]) for e in entries)) for g in range(len(cache.pools))]
     lay = MetaLayout(T, R, n_want, max_blocks)
     host = torch.empty(lay.total, dtype=torch.int32, pin_memory=torch.device(device).type == "cuda")
-    cu, _ = fill(host.numpy(), lay, entries, cache, lens, starts, slots, vocab_size)
+    cu, _ = fill(host.numpy(), lay, entries, cache, lens, starts, slots, vocab_size, want_order)
     dev = host.to(device, non_blocking=True)
     ctx = lay.context(dev, cache, device)
     ctx.host_cu_tokens = [int(c) for c in cu]
@@ -216,5 +240,8 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, device, voc
     ctx.max_portion = max(lens)
     ctx.max_context = max(s + n for s, n in zip(starts, lens))
     ctx.all_decode = T == R
+    if want_order is not None:
+        ctx.num_decode = n_single
+        ctx.decode_max_context = max(starts[i] + 1 for i in range(n_single))
     ctx._host_buffer = host  # keep the pinned buffer alive until the copy has run
     return ctx

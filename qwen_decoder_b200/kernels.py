@@ -498,7 +498,8 @@ def prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: tor
     """Portions of ``n_requests`` requests (tokens cu_tokens[r]..cu_tokens[r+1]-1 at positions
     start_pos[r]..) over their cached keys, causal, on tensor cores."""
     assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-    assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
+    # cu_tokens holds rows of q and out: they may start past row 0 (the rows before belong to another kernel)
+    assert out.shape[0] >= n_tokens and out.shape[1] == H * d and tuple(kv.shape[1:]) == (2, G, page_size, d)
     assert block_table.dtype == torch.int32 and block_table.shape[0] >= n_requests
     assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
     _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
@@ -533,7 +534,7 @@ def prefill_attention_tc5(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv:
                           window: int, timeline: Optional[torch.Tensor] = None) -> None:
     """``prefill_attention`` on tcgen05 tensor cores (accumulators in tensor memory, K/V tiles by TMA)."""
     assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
-    assert out.shape == (n_tokens, H * d) and tuple(kv.shape[1:]) == (2, G, page_size, d)
+    assert out.shape[0] >= n_tokens and out.shape[1] == H * d and tuple(kv.shape[1:]) == (2, G, page_size, d)
     assert block_table.dtype == torch.int32 and block_table.shape[0] >= n_requests
     assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
     _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
@@ -571,7 +572,7 @@ class PromptLayer(ctypes.Structure):
 class PromptFns(ctypes.Structure):
     """Addresses of the launchers and of the library product that the native prompt step calls."""
     _fields_ = [(n, ctypes.c_void_p) for n in ("add_rmsnorm", "rope_kv_write", "swiglu", "attention_regs",
-                                               "attention_tc5", "gemm_ex", "blas")]
+                                               "attention_tc5", "attention_decode", "gemm_ex", "blas")]
 
 
 class PromptParams(ctypes.Structure):
@@ -582,7 +583,9 @@ class PromptParams(ctypes.Structure):
         [("scale", ctypes.c_float), ("final_eps", ctypes.c_float), ("n_pages", ctypes.c_longlong)] + \
         [(n, ctypes.c_void_p) for n in ("positions", "slot_map", "block_table", "cu_tokens", "start_pos",
                                         "logit_rows", "cos_t", "sin_t", "final_w", "x", "delta0", "h", "qkv",
-                                        "attn", "delta", "gu", "act", "hrows")]
+                                        "attn", "delta", "gu", "act", "hrows")] + \
+        [("n_decode", ctypes.c_int), ("decode_splits", ctypes.c_int)] + \
+        [(n, ctypes.c_void_p) for n in ("token_req", "part_o", "part_ml", "tickets")]
 
 
 def prompt_exec_struct_sizes_match() -> bool:
@@ -606,10 +609,10 @@ def _loaded_cublas() -> ctypes.CDLL:
 _prompt_fns: dict = {}
 
 
-def prompt_fns(use_tc5: bool) -> PromptFns:
-    """The launchers' addresses (their libraries are built and loaded on the first call; the attention
+def prompt_fns(use_tc5: bool, with_decode: bool = False) -> PromptFns:
+    """The launchers' addresses (their libraries are built and loaded on the first call; an attention
     kernel that the model does not use stays unbuilt); ``blas`` is filled in per step."""
-    fns = _prompt_fns.get(use_tc5)
+    fns = _prompt_fns.get((use_tc5, with_decode))
     if fns is None:
         addr = lambda f: ctypes.cast(f, ctypes.c_void_p).value
         ew = library("elementwise")
@@ -621,9 +624,25 @@ def prompt_fns(use_tc5: bool) -> PromptFns:
             fns.attention_tc5 = addr(library("attention_tc5").qd_prefill_attention_tc5)
         else:
             fns.attention_regs = addr(library("attention_flash").qd_prefill_attention)
+        if with_decode:
+            fns.attention_decode = addr(library("attention_flash").qd_decode_attention)
         fns.gemm_ex = addr(_loaded_cublas().cublasGemmEx)
-        _prompt_fns[use_tc5] = fns
+        _prompt_fns[(use_tc5, with_decode)] = fns
     return fns
+
+
+def decode_scratch(n_tokens: int, H: int, d: int, G: int, splits: int, device):
+    """(part_o, part_ml, tickets) for a split-KV decode attention launch of ``n_tokens`` tokens."""
+    if splits <= 1:
+        return None, None, None
+    part_o = torch.empty((n_tokens * H * splits, d), dtype=torch.float32, device=device)
+    part_ml = torch.empty((n_tokens * H * splits, 2), dtype=torch.float32, device=device)
+    tickets = None
+    if n_tokens * G <= _TICKETS:
+        tickets = _tickets.get(device)
+        if tickets is None:     # zero once; every launch leaves them zero again
+            tickets = _tickets[device] = torch.zeros(_TICKETS, dtype=torch.int32, device=device)
+    return part_o, part_ml, tickets
 
 
 def prompt_exec(params: PromptParams, n_launches: int) -> None:

@@ -100,14 +100,22 @@ class GQAttention(Mixer):
                 qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
                 ctx.positions, ctx.num_tokens, H, G, d, ps, self.scale, window,
                 decode_splits(ctx.num_tokens * G, min(ctx.max_context, window or ctx.max_context)))
-        elif _PREFILL_TC5 and kernels.prefill_tc5_supported(x.dtype, H, G, d, ps):
-            kernels.prefill_attention_tc5(
-                qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
-                ctx.num_requests, ctx.num_tokens, H, G, d, ps, self.scale, window)
-        elif kernels.flash_prefill_supported(x.dtype, H, G, d, ps):
-            kernels.prefill_attention(
-                qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.cu_tokens, ctx.start_pos,
-                ctx.num_requests, ctx.num_tokens, H, G, d, ps, self.scale, window)
+        elif kernels.flash_prefill_supported(x.dtype, H, G, d, ps) or \
+                (_PREFILL_TC5 and kernels.prefill_tc5_supported(x.dtype, H, G, d, ps)):
+            # a mixed step: its single tokens (first in the batch) go to the decode kernel, which shares
+            # a request's keys among CTAs; a prompt kernel would walk them with one CTA per request
+            nd = getattr(ctx, "num_decode", 0)
+            if nd and not kernels.flash_decode_supported(x.dtype, H, G, d, ps):
+                nd = 0
+            if nd:
+                kernels.decode_attention(
+                    qkv, qkv.stride(0), attn[:nd], cache.kv, cache.group.block_table, ctx.token_request[:nd],
+                    ctx.positions[:nd], nd, H, G, d, ps, self.scale, window,
+                    decode_splits(nd * G, min(ctx.decode_max_context, window or ctx.decode_max_context)))
+            fn = kernels.prefill_attention_tc5 \
+                if _PREFILL_TC5 and kernels.prefill_tc5_supported(x.dtype, H, G, d, ps) else kernels.prefill_attention
+            fn(qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table[nd:], ctx.cu_tokens[nd:],
+               ctx.start_pos[nd:], ctx.num_requests - nd, ctx.num_tokens - nd, H, G, d, ps, self.scale, window)
         else:
             kernels.paged_attention_generic(
                 qkv, qkv.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,

@@ -136,7 +136,18 @@ class NativePrompt:
         pos = c["position_obj"]
         p = kernels.PromptParams()
         use_tc5 = self.attention_impl(group.page_size)
-        p.fn = kernels.prompt_fns(bool(use_tc5))
+        # a mixed step: its single tokens (first in the batch) go to the split-KV decode kernel
+        nd = ctx.num_decode if kernels.flash_decode_supported(bf, H, G, d, group.page_size) else 0
+        p.fn = kernels.prompt_fns(bool(use_tc5), nd > 0)
+        keep = None
+        if nd:
+            from .attention import decode_splits
+            window = c["window"] or 0
+            p.n_decode = nd
+            p.decode_splits = decode_splits(nd * G, min(ctx.decode_max_context, window or ctx.decode_max_context))
+            keep = kernels.decode_scratch(nd, H, d, G, p.decode_splits, dev)
+            p.token_req = ctx.token_request.data_ptr()
+            p.part_o, p.part_ml, p.tickets = (t.data_ptr() if t is not None else None for t in keep)
         p.fn.blas = torch.cuda.current_blas_handle()
         p.layers = ctypes.cast(self._layer_array(ctx.cache), ctypes.c_void_p)
         p.n_layers = len(self.entries)
@@ -158,7 +169,7 @@ class NativePrompt:
         p.x, p.delta0 = x.data_ptr(), None
         p.h, p.qkv, p.attn, p.delta, p.gu, p.act = (base + 2 * o for o in offs)
         p.hrows = hrows.data_ptr() if hrows is not None else None
-        n_launches = len(self.entries) * OWN_LAUNCHES_PER_LAYER + (1 if ctx.num_wanted else 0)
+        n_launches = len(self.entries) * (OWN_LAUNCHES_PER_LAYER + (1 if nd else 0)) + (1 if ctx.num_wanted else 0)
         kernels.prompt_exec(p, n_launches)
         self.steps += 1
         matmul_backend.counters["library"] += 4 * len(self.entries)
