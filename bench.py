@@ -354,7 +354,11 @@ def main():
         wall = time.perf_counter() - t0
         n1 = sum(len(r.output) for r in reqs)
         g = next(iter(runner._graphs.values())) if runner._graphs else None
-        h2d = max((gr.lay.total * 4 for gr in runner._graphs.values()), default=0)
+        bp = 1
+        while bp < args.batch:
+            bp *= 2
+        # the packed metadata of this batch size's graphs (other sizes' graphs, made for ``points``, are larger)
+        h2d = max((gr.lay.total * 4 for gr in runner._graphs.values() if gr.lay.T == bp), default=0)
         e2e = {"value": round((n1 - n0) / max(wall, e0.elapsed_time(e1) / 1e3), 1), "unit": "tokens/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(wall / K * 1e3, 4)}
     ck = clocks.stop()
