@@ -47,3 +47,42 @@ def test_steps_that_are_not_mixed_keep_the_given_order():
     assert ctx.num_decode == 0 and ctx.tokens.tolist() == [1, 2, 3, 4] and ctx.logit_rows.tolist() == [1, 2, 3]
     ctx = build_context([StepEntry(a, [5], [0]), StepEntry(b, [6], [0])], m, "cpu", 100, 1000)
     assert ctx.all_decode and ctx.num_decode == 0 and ctx.tokens.tolist() == [5, 6]
+
+
+def test_random_batches_keep_every_token_with_its_request():
+    """Random mixes of single tokens and portions: whatever the order inside the step, every wanted row is
+    the token the caller meant, at its position, in a slot of its own request's pages."""
+    import random
+    rng = random.Random(4)
+    for trial in range(60):
+        m = manager()
+        n = rng.randint(1, 6)
+        held = [rng.randint(0, 30) for _ in range(n)]
+        rcs = [opened(m, f"r{i}", held[i]) for i in range(n)]
+        entries, next_token = [], 1
+        for i, rc in enumerate(rcs):
+            k = 1 if rng.random() < 0.5 else rng.randint(2, 9)
+            toks = list(range(next_token, next_token + k))
+            next_token += k
+            want = sorted(rng.sample(range(k), rng.randint(0, min(k, 2))))
+            m.ensure(rc, held[i] + k)
+            entries.append(StepEntry(rc, toks, want))
+        ctx = build_context(entries, m, "cpu", 1000, 1000)
+        tokens, positions = ctx.tokens.tolist(), ctx.positions.tolist()
+        req, slots = ctx.token_request.tolist(), ctx.groups[0].slot_map.tolist()
+        table = ctx.groups[0].block_table.tolist()
+        rows = ctx.logit_rows.tolist()
+        expect = [(e, w) for e in entries for w in e.want]
+        assert len(rows) == len(expect)
+        for row, (e, w) in zip(rows, expect):
+            assert tokens[row] == e.tokens[w] and positions[row] == e.cache.num_tokens + w
+        assert sorted(tokens) == list(range(1, next_token))
+        for t in range(ctx.num_tokens):
+            owner = next(e for e in entries if tokens[t] in e.tokens)
+            page, off = divmod(positions[t], 16)
+            assert slots[t] == owner.cache.tables[0].pages[page] * 16 + off
+            assert table[req[t]][:len(owner.cache.tables[0].pages)] == owner.cache.tables[0].pages
+        singles = sum(1 for e in entries if len(e.tokens) == 1)
+        assert ctx.num_decode == (singles if 0 < singles < n else 0)
+        if ctx.num_decode:
+            assert all(ctx.cu_tokens.tolist()[i + 1] - ctx.cu_tokens.tolist()[i] == 1 for i in range(singles))
