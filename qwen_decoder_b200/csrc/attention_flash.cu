@@ -14,7 +14,10 @@
 // (prefill).  Anything else is refused and the caller takes the generic kernel.
 #include "common.cuh"
 #include "entry_points.h"
+#include <cuda.h>
 #include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
 
 #define FA_PAD 8  // bf16 elements of padding per smem row: 16 bytes, keeps ldmatrix conflict-free
 
@@ -65,6 +68,111 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #define DEC_WARPS 4
 #define DEC_STAGES 3
 #define DEC_CHUNK 16  // keys per warp iteration; a chunk never straddles a page
+
+// The end of a decode attention CTA, shared by the kernels below: the warps' partial results (o, running
+// maxima m and denominators l of 16 rows each) are merged in shared memory; with one split the result is
+// written, otherwise it goes to scratch and the CTA that finishes last for its (token, kv head) adds up all
+// splits.  Every warp must be done with the stage buffers that start at smem_raw.
+template <int HD>
+__device__ __forceinline__ void dec_finish(float (&o)[HD / 8][4], float m0, float m1, float l0, float l1,
+                                           unsigned char* smem_raw, int warp, int lane, int gs, int g, int t, int s,
+                                           int H, int G, int splits, bf16* __restrict__ out,
+                                           float* __restrict__ part_o, float* __restrict__ part_ml,
+                                           unsigned* __restrict__ tickets) {
+  l0 = quad_sum(l0);
+  l1 = quad_sum(l1);
+  __syncthreads();  // every warp is done with its stage buffers: reuse them for the merge
+
+  float* mo = reinterpret_cast<float*>(smem_raw);             // [warps][16][HD]
+  float* mm = mo + DEC_WARPS * 16 * HD;                       // [warps][16]
+  float* ml = mm + DEC_WARPS * 16;                            // [warps][16]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) {
+      float* d0 = mo + ((size_t)warp * 16 + r0) * HD + n * 8 + cq;
+      float* d1 = mo + ((size_t)warp * 16 + r1) * HD + n * 8 + cq;
+      d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+      mm[warp * 16 + r0] = m0; mm[warp * 16 + r1] = m1;
+      ml[warp * 16 + r0] = l0; ml[warp * 16 + r1] = l1;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < gs * HD; idx += DEC_WARPS * 32) {
+    int row = idx / HD, dim = idx - row * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mm[w * 16 + row]);
+    float L = 0.f, O = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < DEC_WARPS; w++) {
+        float f = exp2f(mm[w * 16 + row] - M);
+        L += ml[w * 16 + row] * f;
+        O += mo[((size_t)w * 16 + row) * HD + dim] * f;
+      }
+    }
+    int h = g * gs + row;
+    if (splits == 1) {
+      out[(size_t)t * H * HD + (size_t)h * HD + dim] = __float2bfloat16_rn(O / L);
+    } else {
+      size_t pi = ((size_t)t * H + h) * splits + s;
+      part_o[pi * HD + dim] = O;
+      if (dim == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+    }
+  }
+  if (splits == 1 || tickets == nullptr) return;   // without tickets a combine kernel follows
+  // the CTA that finishes last for this (token, kv head) adds up all partial results
+  __shared__ unsigned s_ticket;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[(size_t)t * G + g], 1u);
+  __syncthreads();
+  if (s_ticket != (unsigned)splits - 1) return;
+  __threadfence();
+  // weights of the partial results: f[row][sp] = 2^(m_sp - M) / sum_sp l_sp 2^(m_sp - M), in smem
+  // (reusing the merge area: [16 rows][splits] after the (m, l) pairs have been read)
+  float* fac = reinterpret_cast<float*>(smem_raw);                 // [gs][splits]
+  float* pm = fac + 16 * 64;                                       // [gs][splits] maxima
+  float* pl = pm + 16 * 64;                                        // [gs][splits] denominators
+  for (int idx = threadIdx.x; idx < gs * splits; idx += DEC_WARPS * 32) {
+    int row = idx / splits, sp = idx - row * splits;
+    size_t pi = ((size_t)t * H + (size_t)g * gs + row) * splits + sp;
+    float2 ml2 = __ldcg(reinterpret_cast<const float2*>(part_ml) + pi);
+    pm[row * 64 + sp] = ml2.x;
+    pl[row * 64 + sp] = ml2.y;
+  }
+  __syncthreads();
+  if (threadIdx.x < gs) {
+    int row = threadIdx.x;
+    float M = -INFINITY;
+    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, pm[row * 64 + sp]);
+    float L = 0.f;
+    for (int sp = 0; sp < splits; sp++) L += pl[row * 64 + sp] * exp2f(pm[row * 64 + sp] - M);
+    float invL = 1.f / L;
+    for (int sp = 0; sp < splits; sp++) fac[row * 64 + sp] = exp2f(pm[row * 64 + sp] - M) * invL;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < gs * (HD / 4); idx += DEC_WARPS * 32) {
+    int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
+    size_t base = ((size_t)t * H + (size_t)g * gs + row) * splits;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int sp = 0; sp < splits; sp++) {
+      float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + sp) * HD) + d4);
+      float f = fac[row * 64 + sp];
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    }
+    bf16* dst = out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
+    uint2 raw;
+    raw.x = pack_bf16(acc.x, acc.y);
+    raw.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(dst) = raw;
+  }
+  if (threadIdx.x == 0) tickets[(size_t)t * G + g] = 0;   // ready for the next launch
+}
 
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -218,99 +326,204 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   }
   cp_async_wait<0>();
   pdl_launch_dependents();
-  l0 = quad_sum(l0);
-  l1 = quad_sum(l1);
-  __syncthreads();  // every warp is done with its stage buffers: reuse them for the merge
+  dec_finish<HD>(o, m0, m1, l0, l1, smem_raw, warp, lane, gs, g, t, s, H, G, splits, out, part_o, part_ml, tickets);
+}
 
-  float* mo = reinterpret_cast<float*>(smem_raw);             // [warps][16][HD]
-  float* mm = mo + DEC_WARPS * 16 * HD;                       // [warps][16]
-  float* ml = mm + DEC_WARPS * 16;                            // [warps][16]
+// ------------------------------------------------------------------ the same with K/V through TMA
+// Head sizes 64 and 128.  A chunk's K and V arrive as TMA tensor copies (boxes of 16 keys x 64 columns,
+// 128-byte swizzle: the 16-byte unit u of row r lies at unit u ^ (r & 7)) onto an mbarrier per (warp, stage);
+// one lane issues them, nobody computes addresses per row.  Waits are bounded: a wait that runs out sets the
+// status word and the CTA runs on to its end.
+#define DEC_SPIN_LIMIT (1u << 22)
+__device__ __forceinline__ unsigned fa_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool fa_mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
+  const unsigned addr = fa_smem(bar);
+  if (*dead) return false;
+  unsigned long long start = 0;
+  for (unsigned spin = 0; spin < DEC_SPIN_LIMIT; spin++) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((spin & 255) == 255) {              // also bounded in time: one second
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (start == 0) start = now;
+      else if (now - start > 1000000000ull) break;
+    }
+  }
+  *dead = 1;
+  return false;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, long long q_stride,
+                            bf16* __restrict__ out, const int* __restrict__ block_table, int max_blocks,
+                            const int* __restrict__ token_req, const int* __restrict__ positions, int H, int G,
+                            int page_size, float scale_log2e, int window, int splits,
+                            float* __restrict__ part_o, float* __restrict__ part_ml,
+                            unsigned* __restrict__ tickets, int* __restrict__ status) {
+  static_assert(HD % 64 == 0, "boxes of 64 columns");
+  constexpr int NB = HD / 64;                      // boxes per K or V chunk
+  constexpr int BOX = 16 * 64;                     // elements of a box (2 KB)
+  constexpr int STAGE = 2 * NB * BOX;              // elements of a stage: K boxes, then V boxes
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ unsigned long long bars[DEC_WARPS][DEC_STAGES];
+  __shared__ int dead;
+  __shared__ int page_ring[DEC_WARPS][64];
+  // the swizzle pattern follows address bits 7-9: stages start on 1024-byte boundaries
+  bf16* smem = reinterpret_cast<bf16*>(smem_raw + ((1024 - (fa_smem(smem_raw) & 1023)) & 1023));
+  const int s = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gs = H / G;
+  if (threadIdx.x == 0) {
+    dead = 0;
+    for (int w = 0; w < DEC_WARPS; w++)
+      for (int st = 0; st < DEC_STAGES; st++)
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(fa_smem(&bars[w][st])), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int pos = positions[t];
+  const int n_keys = pos + 1;
+  const int key_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int chunk_lo = key_lo / DEC_CHUNK, chunk_hi = (n_keys + DEC_CHUNK - 1) / DEC_CHUNK;
+  const int per = (chunk_hi - chunk_lo + splits - 1) / splits;
+  const int c0 = chunk_lo + s * per;
+  const int c1 = min(chunk_hi, c0 + per);
+  const int* bt = block_table + (size_t)token_req[t] * max_blocks;
+  bf16* wbuf = smem + (size_t)warp * DEC_STAGES * STAGE;
+  const int first = c0 + warp;
+  const int n_my = first < c1 ? (c1 - first + DEC_WARPS - 1) / DEC_WARPS : 0;
+  auto fill_ring = [&](int from) {      // page ids of chunks [from, from + 32) of this warp's sequence
+    int i = from + lane;
+    if (i < n_my) page_ring[warp][i & 63] = bt[((first + i * DEC_WARPS) * DEC_CHUNK) / page_size];
+  };
+  fill_ring(0);
+  fill_ring(32);
+  __syncwarp();
+  auto load_chunk = [&](int i, int stage) {          // i-th chunk of this warp; one lane asks for its four boxes
+    if (lane != 0) return;
+    unsigned long long* bar = &bars[warp][stage];
+    const int key0 = (first + i * DEC_WARPS) * DEC_CHUNK;
+    int page = page_ring[warp][i & 63];
+    if (page < 0) page = 0;                          // no such keys: any page will do, the scores are masked
+    const int in_page = key0 % page_size;
+    const int row_k = ((page * 2 + 0) * G + g) * page_size + in_page;
+    const int row_v = ((page * 2 + 1) * G + g) * page_size + in_page;
+    bf16* ks = wbuf + (size_t)stage * STAGE;
+    bf16* vs = ks + NB * BOX;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(fa_smem(bar)),
+                 "r"((unsigned)(STAGE * sizeof(bf16))) : "memory");
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                   ::"r"(fa_smem(ks + b * BOX)), "l"(&kv_map), "r"(fa_smem(bar)), "r"(b * 64), "r"(row_k) : "memory");
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                   ::"r"(fa_smem(vs + b * BOX)), "l"(&kv_map), "r"(fa_smem(bar)), "r"(b * 64), "r"(row_v) : "memory");
+    }
+  };
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+
+  // before the dependency wait only chunks of earlier steps' keys; the chunk that holds this step's own key after it
+  const int hot = chunk_hi - 1;
+  int deferred = -1;
+#pragma unroll
+  for (int p = 0; p < DEC_STAGES - 1; p++) {
+    if (p < n_my) {
+      if (first + p * DEC_WARPS == hot) deferred = p; else load_chunk(p, p);
+    }
+  }
+  pdl_wait();
+  if (deferred >= 0) load_chunk(deferred, deferred);
+  unsigned qa[HD / 16][4];
   {
     const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
+    const bf16* q0 = q + (size_t)t * q_stride + (size_t)(g * gs + r0) * HD + cq;
+    const bf16* q1 = q + (size_t)t * q_stride + (size_t)(g * gs + r1) * HD + cq;
 #pragma unroll
-    for (int n = 0; n < HD / 8; n++) {
-      float* d0 = mo + ((size_t)warp * 16 + r0) * HD + n * 8 + cq;
-      float* d1 = mo + ((size_t)warp * 16 + r1) * HD + n * 8 + cq;
-      d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
-    }
-    if ((lane & 3) == 0) {
-      mm[warp * 16 + r0] = m0; mm[warp * 16 + r1] = m1;
-      ml[warp * 16 + r0] = l0; ml[warp * 16 + r1] = l1;
+    for (int kk = 0; kk < HD / 16; kk++) {
+      qa[kk][0] = r0 < gs ? *reinterpret_cast<const unsigned*>(q0 + kk * 16) : 0u;
+      qa[kk][1] = r1 < gs ? *reinterpret_cast<const unsigned*>(q1 + kk * 16) : 0u;
+      qa[kk][2] = r0 < gs ? *reinterpret_cast<const unsigned*>(q0 + kk * 16 + 8) : 0u;
+      qa[kk][3] = r1 < gs ? *reinterpret_cast<const unsigned*>(q1 + kk * 16 + 8) : 0u;
     }
   }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < gs * HD; idx += DEC_WARPS * 32) {
-    int row = idx / HD, dim = idx - row * HD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mm[w * 16 + row]);
-    float L = 0.f, O = 0.f;
-    if (M != -INFINITY) {
-#pragma unroll
-      for (int w = 0; w < DEC_WARPS; w++) {
-        float f = exp2f(mm[w * 16 + row] - M);
-        L += ml[w * 16 + row] * f;
-        O += mo[((size_t)w * 16 + row) * HD + dim] * f;
+  // element offset of the 16-byte unit `unit` (0 .. HD/8-1) of row r inside a K or V chunk
+  auto sw = [](int r, int unit) { return (unit >> 3) * BOX + r * 64 + (((unit & 7) ^ (r & 7)) << 3); };
+  for (int i = 0; i < n_my; i++) {
+    const int nx = i + DEC_STAGES - 1;
+    if ((i & 31) == 0 && i > 0) { fill_ring(i + 32); __syncwarp(); }
+    if (nx < n_my) load_chunk(nx, nx % DEC_STAGES);      // its stage was read in iteration i - 1 (syncwarp below)
+    const int stage = i % DEC_STAGES;
+    if (!fa_mbar_wait(&bars[warp][stage], (i / DEC_STAGES) & 1, &dead) && lane == 0) atomicExch(status, 1);
+    __syncwarp();
+    bf16* ks = wbuf + (size_t)stage * STAGE;
+    bf16* vs = ks + NB * BOX;
+    const int c = first + i * DEC_WARPS;
+    const int rows_ok = n_keys - c * DEC_CHUNK;
+    if (rows_ok < DEC_CHUNK) {        // a request's last chunk: rows past its keys hold whatever the page held
+      for (int idx = lane; idx < (DEC_CHUNK - rows_ok) * (HD / 8); idx += 32) {
+        const int r = rows_ok + idx / (HD / 8), unit = idx % (HD / 8);
+        *reinterpret_cast<uint4*>(vs + sw(r, unit)) = make_uint4(0u, 0u, 0u, 0u);
       }
+      __syncwarp();
     }
-    int h = g * gs + row;
-    if (splits == 1) {
-      out[(size_t)t * H * HD + (size_t)h * HD + dim] = __float2bfloat16_rn(O / L);
-    } else {
-      size_t pi = ((size_t)t * H + h) * splits + s;
-      part_o[pi * HD + dim] = O;
-      if (dim == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+    float sc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+      unsigned b[4];
+      ldmatrix_x4(b, ks + sw((lane & 7) + 8 * (lane >> 4), kk * 2 + ((lane >> 3) & 1)));
+      mma_bf16(sc[0], qa[kk], b[0], b[1]);
+      mma_bf16(sc[1], qa[kk], b[2], b[3]);
     }
-  }
-  if (splits == 1 || tickets == nullptr) return;   // without tickets a combine kernel follows
-  // the CTA that finishes last for this (token, kv head) adds up all partial results
-  __shared__ unsigned s_ticket;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[(size_t)t * G + g], 1u);
-  __syncthreads();
-  if (s_ticket != (unsigned)splits - 1) return;
-  __threadfence();
-  // weights of the partial results: f[row][sp] = 2^(m_sp - M) / sum_sp l_sp 2^(m_sp - M), in smem
-  // (reusing the merge area: [16 rows][splits] after the (m, l) pairs have been read)
-  float* fac = reinterpret_cast<float*>(smem_raw);                 // [gs][splits]
-  float* pm = fac + 16 * 64;                                       // [gs][splits] maxima
-  float* pl = pm + 16 * 64;                                        // [gs][splits] denominators
-  for (int idx = threadIdx.x; idx < gs * splits; idx += DEC_WARPS * 32) {
-    int row = idx / splits, sp = idx - row * splits;
-    size_t pi = ((size_t)t * H + (size_t)g * gs + row) * splits + sp;
-    float2 ml2 = __ldcg(reinterpret_cast<const float2*>(part_ml) + pi);
-    pm[row * 64 + sp] = ml2.x;
-    pl[row * 64 + sp] = ml2.y;
-  }
-  __syncthreads();
-  if (threadIdx.x < gs) {
-    int row = threadIdx.x;
-    float M = -INFINITY;
-    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, pm[row * 64 + sp]);
-    float L = 0.f;
-    for (int sp = 0; sp < splits; sp++) L += pl[row * 64 + sp] * exp2f(pm[row * 64 + sp] - M);
-    float invL = 1.f / L;
-    for (int sp = 0; sp < splits; sp++) fac[row * 64 + sp] = exp2f(pm[row * 64 + sp] - M) * invL;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < gs * (HD / 4); idx += DEC_WARPS * 32) {
-    int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
-    size_t base = ((size_t)t * H + (size_t)g * gs + row) * splits;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int sp = 0; sp < splits; sp++) {
-      float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + sp) * HD) + d4);
-      float f = fac[row * 64 + sp];
-      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+#pragma unroll
+    for (int n = 0; n < 2; n++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        int key = c * DEC_CHUNK + n * 8 + (lane & 3) * 2 + (j & 1);
+        bool ok = key >= key_lo && key < n_keys;
+        sc[n][j] = ok ? sc[n][j] * scale_log2e : -INFINITY;
+      }
+    float mx0 = quad_max(fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1])));
+    float mx1 = quad_max(fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3])));
+    float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+    float a0 = fast_exp2(m0 - ref0), a1 = fast_exp2(m1 - ref1);
+    m0 = mn0; m1 = mn1;
+    float p[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; n++) {
+      p[n][0] = fast_exp2(sc[n][0] - ref0); p[n][1] = fast_exp2(sc[n][1] - ref0);
+      p[n][2] = fast_exp2(sc[n][2] - ref1); p[n][3] = fast_exp2(sc[n][3] - ref1);
     }
-    bf16* dst = out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
-    uint2 raw;
-    raw.x = pack_bf16(acc.x, acc.y);
-    raw.y = pack_bf16(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(dst) = raw;
+    l0 = l0 * a0 + p[0][0] + p[0][1] + p[1][0] + p[1][1];
+    l1 = l1 * a1 + p[0][2] + p[0][3] + p[1][2] + p[1][3];
+    unsigned pa[4] = {pack_bf16(p[0][0], p[0][1]), pack_bf16(p[0][2], p[0][3]),
+                      pack_bf16(p[1][0], p[1][1]), pack_bf16(p[1][2], p[1][3])};
+    if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+      for (int n = 0; n < HD / 8; n++) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+    }
+#pragma unroll
+    for (int dn = 0; dn < HD / 16; dn++) {
+      unsigned b[4];
+      ldmatrix_x4_trans(b, vs + sw((lane & 7) + 8 * ((lane >> 3) & 1), dn * 2 + (lane >> 4)));
+      mma_bf16(o[2 * dn], pa, b[0], b[1]);
+      mma_bf16(o[2 * dn + 1], pa, b[2], b[3]);
+    }
+    __syncwarp();
   }
-  if (threadIdx.x == 0) tickets[(size_t)t * G + g] = 0;   // ready for the next launch
+  pdl_launch_dependents();
+  dec_finish<HD>(o, m0, m1, l0, l1, smem_raw, warp, lane, gs, g, t, s, H, G, splits, out, part_o, part_ml, tickets);
 }
 
 // out[t, h, :] = sum_s O_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
@@ -382,6 +595,95 @@ extern "C" int qd_decode_attention(const void* q, long long q_stride, void* out,
     default: return QD_ERR_UNSUPPORTED;
   }
 #undef CASE
+}
+
+// ---- host side of the TMA variant
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static FaEncodeFn fa_encode_fn() {
+  static FaEncodeFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (FaEncodeFn)p;
+  }
+  return fn;
+}
+static int* fa_status_word() {
+  static int* words[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!words[dev]) {
+    int* w = nullptr;
+    if (cudaMalloc(&w, sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(w, 0, sizeof(int));
+    words[dev] = w;
+  }
+  return words[dev];
+}
+
+template <int HD>
+static int launch_decode_tma(const CUtensorMap& map, const bf16* q, long long q_stride, bf16* out, const int* block_table,
+                             int max_blocks, const int* token_req, const int* positions, int T, int H, int G,
+                             int page_size, float scale, int window, int splits, float* part_o, float* part_ml,
+                             unsigned* tickets, int* status, cudaStream_t stream) {
+  size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_CHUNK * HD * sizeof(bf16) + 1024;
+  if (cudaFuncSetAttribute(decode_attention_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return QD_ERR_UNSUPPORTED;
+  }
+  dim3 grid(splits, G, T);
+  qd_launch(decode_attention_tma_kernel<HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, map, q, q_stride, out,
+            block_table, max_blocks, token_req, positions, H, G, page_size, scale * 1.4426950408889634f, window, splits,
+            part_o, part_ml, tickets, status);
+  return qd_last_error();
+}
+
+// As qd_decode_attention with K/V fetched by TMA tensor copies: head size 64 or 128, tickets required when
+// splits > 1, the cache 16-byte aligned; ``n_pages`` = pages of ``kv``.  Anything else is refused.
+extern "C" int qd_decode_attention_tma(const void* q, long long q_stride, void* out, const void* kv, long long n_pages,
+                                       const int* block_table, int max_blocks, const int* token_req,
+                                       const int* positions, int T, int H, int G, int d, int page_size, float scale,
+                                       int window, int splits, float* part_o, float* part_ml, unsigned* tickets,
+                                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (G <= 0 || H % G != 0 || H / G > 16 || page_size % DEC_CHUNK != 0 || splits < 1 || splits > 64 || T > 65535 ||
+      G > 65535 || (d != 64 && d != 128) || n_pages < 1)
+    return QD_ERR_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml || !tickets)) return QD_ERR_UNSUPPORTED;
+  if (((uintptr_t)kv & 15) || q_stride % 2 != 0) return QD_ERR_UNSUPPORTED;
+  FaEncodeFn fn = fa_encode_fn();
+  int* status = fa_status_word();
+  if (!fn || !status) return QD_ERR_UNSUPPORTED;
+  // the cache as rows of d: [pages * 2 * G * page_size][d]; a box is 16 rows x 64 columns
+  CUtensorMap map;
+  cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)(n_pages * 2 * G * page_size)};
+  cuuint64_t strides[1] = {(cuuint64_t)d * 2};
+  cuuint32_t box[2] = {64, 16};
+  cuuint32_t estr[2] = {1, 1};
+  if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(kv), dims, strides, box, estr,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return QD_ERR_UNSUPPORTED;
+  if (d == 64)
+    return launch_decode_tma<64>(map, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, token_req, positions,
+                                 T, H, G, page_size, scale, window, splits, part_o, part_ml, tickets, status, stream);
+  return launch_decode_tma<128>(map, (const bf16*)q, q_stride, (bf16*)out, block_table, max_blocks, token_req, positions,
+                                T, H, G, page_size, scale, window, splits, part_o, part_ml, tickets, status, stream);
+}
+
+// 0 if no bounded wait of the TMA decode kernel has run out on the current device (reported once).  Synchronises.
+extern "C" int qd_decode_attention_tma_status() {
+  int* status = fa_status_word();
+  if (!status) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (v) cudaMemset(status, 0, sizeof(int));
+  return v;
 }
 
 // ==================================================================== prefill

@@ -426,6 +426,9 @@ def flash_prefill_supported(dtype, H: int, G: int, d: int, page_size: int) -> bo
 
 _TICKETS = 1 << 16
 _tickets = {}
+# split-KV decode attention fed by TMA tensor copies at head sizes 64 and 128 (batch 64 at context 2,176: 43.0
+# against 47.1 us a launch; QD_DECODE_TMA=0 keeps the cp.async kernel)
+_DECODE_TMA = _os.environ.get("QD_DECODE_TMA", "1") != "0"
 
 
 def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
@@ -446,6 +449,14 @@ def decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torc
             tickets = _tickets.get(q.device)
             if tickets is None:     # zero once; every launch leaves them zero again
                 tickets = _tickets[q.device] = torch.zeros(_TICKETS, dtype=torch.int32, device=q.device)
+    if _DECODE_TMA and d in (64, 128) and splits <= 64 and (splits == 1 or tickets is not None):
+        # K/V chunks by TMA tensor copies instead of 16-byte cp.async
+        _check(library("attention_flash").qd_decode_attention_tma(
+            _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _LL(kv.shape[0]), _ptr(block_table),
+            _I(block_table.shape[1]), _ptr(token_req), _ptr(positions), _I(n_tokens), _I(H), _I(G), _I(d),
+            _I(page_size), _F(scale), _I(window), _I(splits), _ptr(part_o), _ptr(part_ml), _ptr(tickets),
+            _stream()), "decode_attention_tma")
+        return
     _check(library("attention_flash").qd_decode_attention(
         _ptr(q), _LL(q_stride), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
         _ptr(token_req), _ptr(positions), _I(n_tokens), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
@@ -554,7 +565,8 @@ def check_status() -> None:
     last call: the results of that launch were void.  Synchronises the device; asks only the libraries this
     process has loaded."""
     for name, fn in (("gemm_stream", "qd_gemm_stream_status"), ("gemm_tc5", "qd_gemm_tc5_status"),
-                     ("attention_tc5", "qd_prefill_attention_tc5_status")):
+                     ("attention_tc5", "qd_prefill_attention_tc5_status"),
+                     ("attention_flash", "qd_decode_attention_tma_status")):
         if _library_loaded(name):
             code = int(getattr(library(name), fn)())
             if code != 0:

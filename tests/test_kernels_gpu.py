@@ -254,6 +254,20 @@ def _plain_attention_row(q_row, k, v, H, G, d, p, window):
 def test_decode_attention_tensor_cores(cfg):
     """One query token per request; contexts that end inside a page, at a page's edge, of one key;
     a window; keys split over several CTAs; one far key made to stand out."""
+    _decode_attention_case(cfg)
+
+
+@pytest.mark.parametrize("cfg", [(16, 2, 128, 16, None, 1), (16, 2, 128, 16, None, 7), (14, 2, 64, 64, 300, 5),
+                                 (8, 8, 64, 32, None, 3), (32, 2, 128, 16, 50, 2)])
+def test_decode_attention_fed_by_tma(cfg, monkeypatch):
+    """The same cases through the kernel that fetches K/V with TMA tensor copies (head sizes 64 and 128)."""
+    from qwen_decoder_b200 import kernels
+    monkeypatch.setattr(kernels, "_DECODE_TMA", True)
+    _decode_attention_case(cfg)
+    assert kernels.library("attention_flash").qd_decode_attention_tma_status() == 0
+
+
+def _decode_attention_case(cfg):
     from qwen_decoder_b200 import kernels
     H, G, d, page_size, window, splits = cfg
     dt = torch.bfloat16
