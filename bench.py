@@ -393,7 +393,6 @@ def main():
         torch.cuda.synchronize(dev)
         wall = time.perf_counter() - t0
         n1 = sum(len(r.output) for r in reqs)
-        g = next(iter(runner._graphs.values())) if runner._graphs else None
         bp = 1
         while bp < args.batch:
             bp *= 2
