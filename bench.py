@@ -411,7 +411,7 @@ def main():
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "tied": True, "global_batch": args.batch, "seq_len": args.context, "new_tokens": W + K,
-                   "page": page, "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 6.2 GB/step)",
+                   "page": page, "parallelism": "single GPU", "l2": f"inputs larger than L2 (weights {decode_bytes(cfgd, args.layers, 0, 0) / 1e9:.1f} GB/step)",
                    "bf16_gemm": matmul_backend.mode, "peaks": pk_src},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
