@@ -275,3 +275,40 @@ def test_planning_ahead_declines_when_the_usual_path_has_to_decide():
     p = s2.schedule(); s2.cache.commit(r.cache, 3); s2.update(p, [4])
     p = s2.schedule(); s2.cache.commit(r.cache, 1)
     assert s2.plan_ahead(p) is None
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_random_arrivals_keep_every_rule(seed):
+    """Requests of random lengths arriving while others run, in a pool small enough to force preemption:
+    every plan keeps the budgets, every request ends with the output it would have had alone, and the pool
+    is whole again at the end."""
+    import random
+    rng = random.Random(seed)
+    budget, total, max_batch = rng.choice([16, 24, 40]), 48, rng.choice([2, 3, 5])
+    cache = manager(rng.choice([10, 14, 24]), page_size=16, max_requests=max_batch)
+    s = Scheduler(cache, max_batch=max_batch, max_prefill_tokens_per_step=budget, max_total_tokens=total)
+    specs = [([rng.randrange(1000) for _ in range(rng.randint(1, 70))], rng.randint(1, 30)) for _ in range(12)]
+    reqs = [Request(i, p, SamplingParams(max_new_tokens=n, ignore_eos=True)) for i, (p, n) in enumerate(specs)]
+    waiting = list(reqs)
+    steps = 0
+    while waiting or s.has_work():
+        for _ in range(rng.randint(0, 2)):
+            if waiting:
+                s.add_request(waiting.pop(0))
+        if not s.has_work():
+            continue
+        plan = s.schedule()
+        portions = [e for e in plan.entries if len(e.tokens) > 1]
+        assert sum(len(e.tokens) for e in portions) <= budget
+        assert sum(len(e.tokens) for e in plan.entries) <= total
+        assert len({id(e.request) for e in plan.entries}) == len(plan.entries) <= max_batch
+        fake_step(s, plan)
+        cache.check()
+        steps += 1
+        assert steps < 5000
+    for r, (p, n) in zip(reqs, specs):
+        if r.finish_reason == "too_long_for_cache":          # could never fit this pool, even alone
+            assert (len(p) + n + 15) // 16 > cache.num_pages
+            continue
+        assert r.output == expected_output(p, n), (r.request_id, r.finish_reason)
+    assert cache.free_pages() == [cache.num_pages] * len(cache.pools)
