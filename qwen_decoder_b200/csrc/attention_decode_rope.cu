@@ -6,7 +6,6 @@
 // the kernel waits for its predecessor.  Formulas: gpu_kernels.cu:82-133 (rotation, cache write) and
 // :223-311 (attention) of the reference; softmax, rotation and sums in float32.
 #include "common.cuh"
-#include <cooperative_groups.h>
 #include <math.h>
 #include <stdlib.h>
 
@@ -25,8 +24,6 @@ struct ArParams {
   const float* cos_t; const float* sin_t; int rotary_dim, pairing; float scale_log2e;
   float* part_o; float* part_ml; unsigned* tickets;
   long long* timeline;                 // null, or 16 nanosecond stamps per CTA (for measurements)
-  int cluster;                         // the `splits` CTAs of a (token, kv head) are one thread-block cluster:
-                                       // they combine through distributed shared memory, not through scratch
 };
 
 __device__ __forceinline__ void ar_stamp(const ArParams& p, int i) {
@@ -123,15 +120,26 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
         ar_cp_async16(vs + row * LD + l_col, vg + (bytes ? row * HD + l_col : 0), bytes);
       }
     };
-    // the first NS chunks of this warp: all of them hold keys of earlier steps only
+    // The first NS chunks of this warp hold keys of earlier steps only -- except, when this run reads another
+    // run's cache (write_kv = 0), the chunk with the token's own position: its owner wrote that key earlier in
+    // this very step, so it is asked for only after the wait.
     const int c_first = c0 + warp;
+    int deferred = -1;
 #pragma unroll
     for (int j = 0; j < NS; j++) {
-      if (c_first + j * AR_WARPS < c1) request_chunk(c_first + j * AR_WARPS, j);
+      const int c = c_first + j * AR_WARPS;
+      if (c < c1) {
+        if (!p.write_kv && c == chunk_hi - 1) deferred = j;
+        else request_chunk(c, j);
+      }
       asm volatile("cp.async.commit_group;\n" ::);
     }
     ar_stamp(p, 1);
     pdl_wait();
+    if (deferred >= 0) {
+      request_chunk(chunk_hi - 1, deferred);
+      asm volatile("cp.async.commit_group;\n" ::);
+    }
     ar_stamp(p, 2);
 
     // ---- q of the group (gs heads) and, in the CTA that holds the chunk of the token's own position, its
@@ -205,7 +213,8 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
       const int stage = it % NS;
       bf16* ks = wbuf + (size_t)stage * STAGE;
       bf16* vs = ks + 16 * LD;
-      asm volatile("cp.async.wait_group %0;\n" ::"n"(NS - 1));     // NS groups are out: the oldest is this chunk's
+      if (!p.write_kv && c == chunk_hi - 1) asm volatile("cp.async.wait_group 0;\n" ::);   // asked for late: all
+      else asm volatile("cp.async.wait_group %0;\n" ::"n"(NS - 1));     // NS groups are out: the oldest is this chunk's
       __syncwarp();
       if (p.write_kv && c == chunk_hi - 1) {
         // the token's own k and v, made above: into this warp's copy of the chunk (no trip through memory)
@@ -306,9 +315,6 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
       int hd = g * gs + row;
       if (p.splits == 1) {
         p.out[(size_t)t * H * HD + (size_t)hd * HD + dim] = __float2bfloat16_rn(O / Lsum);
-      } else if (p.cluster) {
-        fac[row * HD + dim] = O;                                  // this CTA's partial output, for its cluster
-        if (dim == 0) { fac[16 * HD + row] = M; fac[16 * HD + 16 + row] = Lsum; }
       } else {
         size_t pi = ((size_t)t * H + hd) * p.splits + s;
         p.part_o[pi * HD + dim] = O;
@@ -316,50 +322,7 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
       }
     }
     ar_stamp(p, 5);
-    if (p.splits > 1 && p.cluster) {
-      // ---- combine inside the cluster: every CTA reads the others' partial results from their shared memory
-      // and finishes its share of the (row, 4 columns) pieces
-      namespace cg = cooperative_groups;
-      cg::cluster_group cluster = cg::this_cluster();
-      cluster.sync();
-      ar_stamp(p, 6);
-      const int S = p.splits;                                       // at most 8 here
-      for (int it = s + S * (int)threadIdx.x; it < gs * (HD / 4); it += S * AR_THREADS) {
-        const int row = it / (HD / 4), d4 = it - row * (HD / 4);
-        float mq[8], lq[8];
-        float4 oq[8];
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-          if (q < S) {
-            const float* rf = cluster.map_shared_rank(fac, q);
-            mq[q] = rf[16 * HD + row];
-            lq[q] = rf[16 * HD + 16 + row];
-            oq[q] = reinterpret_cast<const float4*>(rf + row * HD)[d4];
-          } else {
-            mq[q] = -INFINITY; lq[q] = 0.f; oq[q] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-        float M = -INFINITY;
-#pragma unroll
-        for (int q = 0; q < 8; q++) M = fmaxf(M, mq[q]);
-        float Lsum = 0.f;
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int q = 0; q < 8; q++) {
-          const float f = q < S ? ar_exp2(mq[q] - M) : 0.f;
-          Lsum += lq[q] * f;
-          a.x += oq[q].x * f; a.y += oq[q].y * f; a.z += oq[q].z * f; a.w += oq[q].w * f;
-        }
-        const float inv = 1.f / Lsum;
-        bf16* dst = p.out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
-        uint2 raw;
-        raw.x = ar_pack(a.x * inv, a.y * inv);
-        raw.y = ar_pack(a.z * inv, a.w * inv);
-        *reinterpret_cast<uint2*>(dst) = raw;
-      }
-      cluster.sync();          // nobody leaves while its shared memory may still be read
-      ar_stamp(p, 7);
-    } else if (p.splits > 1) {
+    if (p.splits > 1) {
       __threadfence();
       __syncthreads();
       if (threadIdx.x == 0) s_ticket = atomicAdd(&p.tickets[(size_t)t * G + g], 1u);
@@ -451,17 +414,6 @@ static int ar_launch_ns(const ArParams& p, cudaStream_t stream) {
     cudaGetLastError();
     return QD_ERR_UNSUPPORTED;
   }
-  if (p.cluster) {
-    cudaError_t e = qd_launch_cluster(kernel, dim3((unsigned)(p.T * p.G * p.splits)), dim3(AR_THREADS), smem, stream,
-                                      (unsigned)p.splits, p);
-    if (e == cudaSuccess) return (int)cudaGetLastError();
-    cudaGetLastError();            // the cluster could not be launched: the scratch path takes over
-    ArParams q = p;
-    q.cluster = 0;
-    if (!q.part_o || !q.part_ml || !q.tickets) return QD_ERR_UNSUPPORTED;
-    qd_launch(kernel, dim3((unsigned)(q.T * q.G * q.splits)), dim3(AR_THREADS), smem, stream, q);
-    return (int)cudaGetLastError();
-  }
   qd_launch(kernel, dim3((unsigned)(p.T * p.G * p.splits)), dim3(AR_THREADS), smem, stream, p);
   return (int)cudaGetLastError();
 }
@@ -492,19 +444,18 @@ extern "C" int qd_decode_attention_rope(const float* part, int n_parts, const fl
                                         int page_size, float scale, int window, int splits, int write_kv,
                                         const float* cos_t, const float* sin_t, int rotary_dim, int pairing,
                                         float* part_o, float* part_ml, unsigned* tickets, long long* timeline,
-                                        int cluster, cudaStream_t stream) {
+                                        cudaStream_t stream) {
   if (T < 1 || G < 1 || H % G != 0 || H / G > 16 || page_size % 16 != 0 || splits < 1 || splits > 64 || n_parts < 1)
     return QD_ERR_UNSUPPORTED;
   if ((rotary_dim & 1) || rotary_dim > d || (rotary_dim > 0 && (!cos_t || !sin_t))) return QD_ERR_UNSUPPORTED;
-  if (cluster && (splits < 2 || splits > 8)) cluster = 0;
-  if (splits > 1 && !cluster && (!part_o || !part_ml || !tickets)) return QD_ERR_UNSUPPORTED;
+  if (splits > 1 && (!part_o || !part_ml || !tickets)) return QD_ERR_UNSUPPORTED;
   ArParams p;
   p.part = part; p.n_parts = n_parts; p.bias = bias; p.out = out; p.kv = kv;
   p.block_table = block_table; p.max_blocks = max_blocks; p.token_req = token_req; p.positions = positions;
   p.slot_map = slot_map; p.T = T; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.splits = splits;
   p.write_kv = write_kv; p.cos_t = rotary_dim > 0 ? cos_t : nullptr; p.sin_t = sin_t; p.rotary_dim = rotary_dim;
   p.pairing = pairing; p.scale_log2e = scale * 1.4426950408889634f;
-  p.part_o = part_o; p.part_ml = part_ml; p.tickets = tickets; p.timeline = timeline; p.cluster = cluster;
+  p.part_o = part_o; p.part_ml = part_ml; p.tickets = tickets; p.timeline = timeline;
   switch (d) {
     case 16: return ar_launch<16>(p, stream);
     case 32: return ar_launch<32>(p, stream);

@@ -40,7 +40,6 @@ LIBRARIES: Dict[str, str] = {
     "attention_decode_rope": "attention_decode_rope.cu",
     "attention_tc5": "attention_tc5.cu",
     "sampling": "sampling.cu",
-    "decode_fused": "decode_fused.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
     "prompt_exec": "prompt_exec.cu",
 }
@@ -153,6 +152,14 @@ def build_library(name: str, verbose: bool = True, extra_flags=()) -> str:
             pass
         raise BuildError(f"nvcc failed on {LIBRARIES[name]} (exit {proc.returncode}):\n{out}")
     os.replace(tmp, path)
+    # builds of older sources of this library are of no use any more (a process that still has one mapped keeps it)
+    prefix = f"libqd_{name}-"
+    for f in os.listdir(os.path.dirname(path)):
+        if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(path):
+            try:
+                os.unlink(os.path.join(os.path.dirname(path), f))
+            except OSError:
+                pass
     if verbose:
         _log(f"  built {os.path.basename(path)} in {time.time() - t0:.1f} s")
     return path

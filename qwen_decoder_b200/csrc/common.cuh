@@ -89,25 +89,3 @@ static inline void qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   cfg.numAttrs = qd_pdl_enabled() ? 1 : 0;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
-
-// The same with the CTAs grouped into thread-block clusters of ``cluster_x`` along x (the grid's x must be a
-// multiple of it).  Returns the launch's error code: a cluster that cannot be scheduled is reported here.
-template <typename... KArgs, typename... Args>
-static inline cudaError_t qd_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                            cudaStream_t stream, unsigned cluster_x, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cluster_x;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = qd_pdl_enabled() ? 2 : 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}

@@ -112,10 +112,15 @@ class MetaLayout:
             logit_rows=seg("want", nw), groups=groups, cache=cache, num_wanted=nw)
 
 
-def validate(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: int, max_positions: int):
+def validate(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: int, max_positions: int,
+             max_step_tokens: Optional[int] = None):
     """Check a batch; returns (lens, starts, slots)."""
     if not entries:
         raise StepError("a step needs at least one entry")
+    if max_step_tokens is not None:
+        total = sum(len(e.tokens) for e in entries)
+        if total > max_step_tokens:
+            raise StepError(f"the step holds {total} tokens, more than max_step_tokens = {max_step_tokens}")
     lens, starts, slots = [], [], []
     seen = set()
     for e in entries:
@@ -212,9 +217,9 @@ def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: Ca
 
 
 def build_context(entries: Sequence[StepEntry], cache: CacheManager, device, vocab_size: int,
-                  max_positions: int) -> StepContext:
+                  max_positions: int, max_step_tokens: Optional[int] = None) -> StepContext:
     """Validate ``entries`` and make the step's device metadata (one host-to-device copy)."""
-    lens, starts, slots = validate(entries, cache, vocab_size, max_positions)
+    lens, starts, slots = validate(entries, cache, vocab_size, max_positions, max_step_tokens)
     R, T = len(entries), sum(lens)
     # single tokens first when the step mixes them with longer portions (stable otherwise)
     n_single = sum(1 for n in lens if n == 1)

@@ -59,6 +59,7 @@ class Engine:
                                    max_total_tokens=max_total_tokens,
                                    max_positions=self.runner.max_positions,
                                    stop_ids=getattr(self.config, "eos_token_ids", ()))
+        self.runner.max_step_tokens = self.scheduler.max_total_tokens
         self._next_id = 0
         self._keys: Dict[int, int] = {}
         self.run_ahead = run_ahead
@@ -134,6 +135,8 @@ class Engine:
                 if e.request.cache is not None:
                     self.runner.cache.log_tokens(e.request.cache, [t])
         finished += self.scheduler.update(cur.plan, tokens)
+        if finished:
+            self.runner.check_status()       # before results leave: no kernel's wait ran out on the way
         return finished
 
     # ---- batch use -----------------------------------------------------------
@@ -145,6 +148,7 @@ class Engine:
         reqs = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         while self.has_work():
             self.step()
+        self.runner.check_status()
         return [r.output for r in reqs]
 
     @property

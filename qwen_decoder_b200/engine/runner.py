@@ -47,7 +47,7 @@ class ModelRunner:
 
     def __init__(self, model: DecoderModel, config, num_pages: int, page_size: int = 16,
                  max_requests: int = 64, max_positions: Optional[int] = None, use_graphs: bool = True,
-                 prefix_cache: bool = False):
+                 prefix_cache: bool = False, max_step_tokens: Optional[int] = None):
         self.model = model
         self.config = config
         self.device = model.device
@@ -62,11 +62,12 @@ class ModelRunner:
         from ..sampling import Sampler
         self.sampler = Sampler(self.device)
         self.use_graphs = use_graphs
+        self.max_step_tokens = max_step_tokens     # most tokens one step may hold (None: no limit of its own)
         self._graphs = {}
         self.steps = 0
         self.tokens_run = 0
 
-    STATUS_EVERY = 512       # steps between two looks at the kernels' status words (each look synchronises)
+    STATUS_EVERY = 512       # steps between two routine looks at the kernels' status words (each look synchronises)
 
     # ---- construction ----------------------------------------------------
     @classmethod
@@ -139,7 +140,8 @@ class ModelRunner:
             raise StepError("device_tokens: only a batch of single tokens that all want logits takes them")
         else:
             from .. import kernels
-            ctx = build_context(entries, self.cache, self.device, self.model.vocab_size, self.max_positions)
+            ctx = build_context(entries, self.cache, self.device, self.model.vocab_size, self.max_positions,
+                                self.max_step_tokens)
             with kernels.step_stream():
                 logits = self.model.forward(ctx)
                 tokens = None
@@ -151,9 +153,26 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += n_tokens
         if self.steps % self.STATUS_EVERY == 0:
-            from .. import kernels
-            kernels.check_status()       # a wait inside a kernel that ran out must not pass unnoticed
+            self.check_status()          # a wait inside a kernel that ran out must not pass unnoticed
         return logits if sampling is None else (logits, tokens)
+
+    def check_status(self) -> None:
+        """Raise ``KernelError`` if a bounded wait inside a kernel ran out since the last look: what the
+        steps since then returned is void.  Synchronises the device.  Callers look before they hand
+        results out: ``Engine`` whenever requests finish, trace replay after every step that writes
+        logits, and every ``STATUS_EVERY`` steps in between.  After a fault the parts put the words their
+        kernels share between launches (a grid barrier's arrival count) back to their starting values."""
+        from .. import kernels
+        try:
+            kernels.check_status()
+        except kernels.KernelError:
+            torch.cuda.synchronize(self.device)
+            for layer in self.model.layers:
+                for part in layer.parts() if hasattr(layer, "parts") else ():
+                    reset = getattr(part, "reset_after_fault", None)
+                    if reset is not None:
+                        reset()
+            raise
 
     def can_take_device_tokens(self, entries: Sequence[StepEntry]) -> bool:
         """True if this batch runs as a replayed graph: single tokens that all want logits."""
@@ -163,7 +182,8 @@ class ModelRunner:
     # ---- decode steps as CUDA graphs ---------------------------------------------
     def _graph_step(self, entries: Sequence[StepEntry], sampling, device_tokens=None):
         import numpy as np
-        lens, starts, slots = validate(entries, self.cache, self.model.vocab_size, self.max_positions)
+        lens, starts, slots = validate(entries, self.cache, self.model.vocab_size, self.max_positions,
+                                       self.max_step_tokens)
         R = len(entries)
         Bp = 1
         while Bp < R:

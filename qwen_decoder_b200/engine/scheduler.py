@@ -185,20 +185,25 @@ class Scheduler:
                 self._finish(req, "too_long_for_cache")
                 plan.finished.append(req)
                 continue
-            n = min(total, prompt_budget, budget)
-            # room for the first portion, and one page of growth for every running request
-            need = (n + ps - 1) // ps + len(self.running)
-            if any(need > free for free in self.cache.free_pages()) or self.cache.slots.num_free == 0:
+            if self.cache.slots.num_free == 0:
+                break
+            tokens = req.all_tokens()
+            # Open first: with the prefix cache a known beginning takes its pages off the free list, so the
+            # room that counts is what is free afterwards.  Room for the first portion, and one page of
+            # growth for every running request; if it is not there the request goes back where it was.
+            rc = self.cache.open(req.request_id, tokens)
+            n = min(total - rc.num_tokens, prompt_budget, budget)
+            missing = self.cache.pages_missing(rc, rc.num_tokens + n)
+            if any(m + len(self.running) > free for m, free in zip(missing, self.cache.free_pages())):
+                self.cache.close(rc)
                 break
             self.waiting.popleft()
-            tokens = req.all_tokens()
-            req.cache = self.cache.open(req.request_id, tokens)    # with the prefix cache: pages of a known beginning
-            req.num_computed = req.cache.num_tokens
+            req.cache = rc
+            req.num_computed = rc.num_tokens
             req.admitted_at = self._admissions
             self._admissions += 1
             self.running.append(req)
-            n = min(total - req.num_computed, n)
-            self.cache.ensure(req.cache, req.num_computed + n)
+            self.cache.ensure(rc, req.num_computed + n)
             self.stats["prefix_hit_tokens"] = self.stats.get("prefix_hit_tokens", 0) + req.num_computed
             plan.entries.append(PlannedEntry(req, tokens[req.num_computed:req.num_computed + n],
                                              req.num_computed + n == total))

@@ -20,13 +20,18 @@ from ..cache import RequestCache
 from .batch import StepEntry
 from .runner import ModelRunner
 
-PAGE_SIZE = 16
-MAX_LIVE = 8
+DEFAULT_PAGE_SIZE = 16
+DEFAULT_MAX_LIVE = 8
 
 
-def pool_pages(max_tokens: int, page_size: int = PAGE_SIZE) -> int:
-    """Pages for ``max_tokens`` held at once (each request's count a multiple of 64, so of the page)."""
-    return max(1, (max_tokens + page_size - 1) // page_size)
+def pool_pages(max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE, max_live: int = DEFAULT_MAX_LIVE) -> int:
+    """Pages for ``max_tokens`` held at once.  The caller counts each request's tokens rounded up to a
+    multiple of 64; a page that is no divisor of 64 rounds each request up to its own size instead, which
+    may take up to one page more per live request."""
+    pages = (max_tokens + page_size - 1) // page_size
+    if 64 % page_size:
+        pages += max_live
+    return max(1, pages)
 
 
 def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: IO[str]) -> int:
@@ -49,6 +54,7 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: IO[str]) -> 
             logits = runner.step(entries)
             if logits.shape[0] > 0:
                 arr = logits.to("cpu").numpy().astype("<f4", copy=False)
+                runner.check_status()        # logits of a step in which a kernel's wait ran out are not written
                 with open(os.path.join(out_dir, f"{step['step']}.f32"), "wb") as f:
                     f.write(arr.tobytes())
         for rid in step.get("end", []):
@@ -58,6 +64,7 @@ def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: IO[str]) -> 
         done.write(f"done {step['step']}\n")
         done.flush()
         n_steps += 1
+    runner.check_status()
     return n_steps
 
 
@@ -69,10 +76,15 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder the <step>.f32 files go to")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (sizes the cache pool)")
+    ap.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE,
+                    help="tokens in a page of the cache (a multiple of 16 for the bfloat16 kernels)")
+    ap.add_argument("--max-live", type=int, default=DEFAULT_MAX_LIVE, help="most requests live at a time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
+    if args.page_size < 1 or args.max_live < 1:
+        ap.error("--page-size and --max-live must be at least 1")
     runner = ModelRunner.from_folder(args.model, dtype=args.dtype, device=args.device,
-                                     num_pages=pool_pages(args.max_tokens), page_size=PAGE_SIZE,
-                                     max_requests=MAX_LIVE)
+                                     num_pages=pool_pages(args.max_tokens, args.page_size, args.max_live),
+                                     page_size=args.page_size, max_requests=args.max_live)
     replay(runner, sys.stdin, args.out, sys.stdout)
     return 0

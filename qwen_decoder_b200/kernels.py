@@ -473,11 +473,10 @@ def decode_attention_rope(part: torch.Tensor, bias: Optional[torch.Tensor], out:
                           slot_map: torch.Tensor, H: int, G: int, d: int, page_size: int, scale: float,
                           window: int, splits: int, write_kv: bool, rotary_dim: int, pairing: int,
                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
-                          timeline: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
+                          timeline: Optional[torch.Tensor] = None) -> None:
     """One decoded token per request, from the float32 partial sums part [n_parts, T, (H+2G)*d] of q, k, v:
-    bias, rotation by position, cache write and attention over the paged cache in one launch.  With
-    ``cluster`` and 2 to 8 splits the CTAs of a (token, kv head) form a thread-block cluster and combine
-    their partial results through distributed shared memory instead of scratch memory and tickets."""
+    bias, rotation by position, cache write and attention over the paged cache in one launch; the splits
+    of a (token, kv head) combine through scratch memory, the last CTA to finish doing the sum."""
     n_parts, T, W = part.shape
     assert part.dtype == torch.float32 and W == (H + 2 * G) * d and out.shape == (T, H * d)
     assert out.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and tuple(kv.shape[1:]) == (2, G, page_size, d)
@@ -498,7 +497,7 @@ def decode_attention_rope(part: torch.Tensor, bias: Optional[torch.Tensor], out:
         _ptr(part), _I(n_parts), _ptr(bias), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]),
         _ptr(token_req), _ptr(positions), _ptr(slot_map), _I(T), _I(H), _I(G), _I(d), _I(page_size), _F(scale),
         _I(window), _I(splits), _I(1 if write_kv else 0), _ptr(cos), _ptr(sin), _I(rotary_dim), _I(pairing),
-        _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(timeline), _I(1 if cluster else 0), _stream()),
+        _ptr(part_o), _ptr(part_ml), _ptr(tickets), _ptr(timeline), _stream()),
         "decode_attention_rope")
 
 
@@ -666,43 +665,3 @@ def prompt_exec(params: PromptParams, n_launches: int) -> None:
     if code >= 20000:
         raise KernelError(f"prompt_exec: cuBLAS status {code - 20000}")
     _check(code, "prompt_exec")
-
-
-# ------------------------------------------------------------------ a whole decode step in one kernel
-class FusedLayer(ctypes.Structure):
-    """One schedule entry of the fused decode step (FdLayer in csrc/decode_fused.cu)."""
-    _fields_ = [("norm1_w", ctypes.c_void_p), ("eps1", ctypes.c_float),
-                ("wqkv", ctypes.c_void_p), ("bqkv", ctypes.c_void_p), ("wo", ctypes.c_void_p),
-                ("norm2_w", ctypes.c_void_p), ("eps2", ctypes.c_float),
-                ("wgu", ctypes.c_void_p), ("wd", ctypes.c_void_p), ("kv", ctypes.c_void_p)]
-
-
-class FusedParams(ctypes.Structure):
-    """Arguments of the fused decode step (FdParams in csrc/decode_fused.cu)."""
-    _fields_ = [(n, ctypes.c_int) for n in ("T", "D", "H", "G", "d", "F", "V", "L")] + \
-        [(n, ctypes.c_void_p) for n in ("x", "qkv", "attn_out", "h", "part_o", "part_ml", "tickets",
-                                        "scratch", "gemm_tickets")] + \
-        [("scratch_floats", ctypes.c_int), ("n_gemm_tickets", ctypes.c_int)] + \
-        [(n, ctypes.c_void_p) for n in ("positions", "token_req", "block_table", "slot_map")] + \
-        [(n, ctypes.c_int) for n in ("max_blocks", "page_size", "splits", "window")] + \
-        [("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p), ("rotary_dim", ctypes.c_int),
-         ("pairing", ctypes.c_int), ("scale_log2e", ctypes.c_float), ("layers", ctypes.c_void_p),
-         ("final_w", ctypes.c_void_p), ("final_eps", ctypes.c_float), ("lm_head", ctypes.c_void_p),
-         ("logits", ctypes.c_void_p), ("barrier", ctypes.c_void_p), ("status", ctypes.c_void_p),
-         ("host_status", ctypes.c_void_p), ("timeline", ctypes.c_void_p)]
-
-
-def fused_decode_struct_sizes_match() -> bool:
-    lib = library("decode_fused")
-    return (lib.qd_decode_fused_param_bytes() == ctypes.sizeof(FusedParams)
-            and lib.qd_decode_fused_layer_bytes() == ctypes.sizeof(FusedLayer))
-
-
-_FUSED_MAX_CTAS = int(_os.environ.get("QD_FUSED_CTAS", "100000"))
-
-
-def decode_step_fused(params: FusedParams) -> None:
-    """All layers, the final norm and the output projection of a decode step of at most 16 tokens in
-    one cooperative launch; raises KernelError(unsupported) for sizes the kernel does not take."""
-    _check(library("decode_fused").qd_decode_step_fused(ctypes.byref(params), _I(_FUSED_MAX_CTAS), _stream()),
-           "decode_step_fused")

@@ -60,7 +60,7 @@ class GQAttention(Mixer):
         pos = self.position
         if self.out.bias is not None or not (pos is None or type(pos) is Rotary):
             return None
-        return {"D": self.hidden_size, "H": self.num_heads, "G": self.num_kv_heads, "d": self.head_dim,
+        return {"kind": "gq_attention", "D": self.hidden_size, "H": self.num_heads, "G": self.num_kv_heads, "d": self.head_dim,
                 "window": self.window, "scale": self.scale, "position": pos,
                 "rotary_dim": pos.rotary_dim if pos is not None else 0,
                 "pairing": pos.pairing_code if pos is not None else 0,
@@ -84,7 +84,7 @@ class GQAttention(Mixer):
                     part, self.qkv.bias, attn, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions,
                     cache.group.slot_map, H, G, d, ps, self.scale, window,
                     decode_rope_splits(ctx.num_tokens * G, min(ctx.max_context, window or ctx.max_context)),
-                    cache.write, *rope, cluster=_DECODE_CLUSTER)
+                    cache.write, *rope)
                 return self.out.forward_partial(attn)
             qkv = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)       # q only
             kernels.rope_kv_write_partial(part, self.qkv.bias, qkv, H, G, d, *rope, ctx.positions, cache.kv,
@@ -128,10 +128,6 @@ _TARGET_CTAS = int(_os.environ.get("QD_DECODE_ATTN_CTAS", "148"))
 _DECODE_ROPE = _os.environ.get("QD_DECODE_ROPE", "1") != "0"
 _PREFILL_TC5 = _os.environ.get("QD_PREFILL_TC5", "1") != "0"      # prompt portions on tcgen05 where its sizes allow
 _ROPE_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ROPE_CTAS", "148"))
-# The splits of a (token, kv head) as one thread-block cluster that combines through distributed shared memory:
-# measured slower in whole decode steps (batch 8: 56.8 against 54.9 us per layer; batch 1: 52.5 against 51.0) --
-# a cluster of 8 CTAs of 88 KB has to find room on one GPC before it starts, and holds at most 8 splits.  Off.
-_DECODE_CLUSTER = _os.environ.get("QD_DECODE_CLUSTER", "0") == "1"
 
 
 def decode_rope_splits(ctas_without_split: int, max_keys: int) -> int:
@@ -140,8 +136,7 @@ def decode_rope_splits(ctas_without_split: int, max_keys: int) -> int:
     never more than that, and none with fewer than eight 16-key chunks, one per warp."""
     by_fill = max(1, _ROPE_TARGET_CTAS // max(1, ctas_without_split))      # never a second wave
     by_work = max(1, (max_keys + 127) // 128)
-    # a thread-block cluster holds at most 8 CTAs: its combine through shared memory beats more splits
-    return max(1, min(by_fill, by_work, 8 if _DECODE_CLUSTER else 64))
+    return max(1, min(by_fill, by_work, 64))
 
 
 def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = _TARGET_CTAS) -> int:

@@ -35,8 +35,8 @@ class Part:
 
     def native_params(self) -> Optional[dict]:
         """The part's tensors and constants, if native code may stand in for its ``forward``: the native
-        prompt loop (``parts/native_prompt.py``) and the fused decode step (``parts/fused_decode.py``) run a
-        model only when every part of it answers.  None, the default, keeps the part's own path."""
+        prompt loop (``parts/native_prompt.py``) runs a model only when every part of it answers.  None,
+        the default, keeps the part's own path."""
         return None
 
 

@@ -38,6 +38,8 @@ class PreNormBlock(Block):
             p.bind(source, dtype, device)
 
     def native_params(self):
+        if type(self) is not PreNormBlock:
+            return None          # a subclass may run its parts in another order: it answers for itself
         n1, mx = self.input_norm.native_params(), self.mixer.native_params()
         n2, ff = self.post_mixer_norm.native_params(), self.feed_forward.native_params()
         if None in (n1, mx, n2, ff) or not all(k in mx for k in ("wqkv", "wo", "H", "G", "d")) \
@@ -46,6 +48,9 @@ class PreNormBlock(Block):
         if not (n1["size"] == n2["size"] == mx["D"] == ff["D"]):
             return None
         out = dict(mx)
+        # what runs in which order: native code that restates one composition takes that one only
+        out["composition"] = "/".join(["pre_norm", str(mx.get("kind")), str(ff.get("kind")), str(n1.get("kind")),
+                                       str(n2.get("kind"))])
         out.update(F=ff["F"], wgu=ff["wgu"], wd=ff["wd"], norm1_w=n1["weight"], eps1=n1["eps"],
                    norm2_w=n2["weight"], eps2=n2["eps"])
         return out

@@ -34,8 +34,13 @@ class SwiGLU(FeedForward):
         self.down.bind(source, dtype, device)
 
     def native_params(self):
-        return {"D": self.hidden_size, "F": self.intermediate_size, "wgu": self.gate_up.weight,
+        return {"kind": "swiglu", "D": self.hidden_size, "F": self.intermediate_size, "wgu": self.gate_up.weight,
                 "wd": self.down.weight}
+
+    def reset_after_fault(self) -> None:
+        """A launch whose grid barrier ran out may have left arrivals counted: start from zero again."""
+        if self._barrier is not None:
+            self._barrier.zero_()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if matmul_backend.mode == "auto" and kernels.ffn_stream_supported(x, self.gate_up.weight, self.down.weight):

@@ -62,7 +62,6 @@ class DecoderModel:
             if spec.lm_head_tensor is None else \
             Linear(spec.hidden_size, [(spec.lm_head_tensor[:-len(".weight")], spec.vocab_size)], bias=False)
         self.embedding: Optional[torch.Tensor] = None
-        self.fused_decode = None     # parts.fused_decode.FusedDecode once bound, if the parts allow it
         self.native_prompt = None    # parts.native_prompt.NativePrompt once bound, if the parts allow it
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
@@ -93,8 +92,6 @@ class DecoderModel:
         for p in self.positions.values():
             p.prepare(min(max_positions, self.max_positions), self.device)
         self.prepared_positions = min(max_positions, self.max_positions)
-        from .fused_decode import FusedDecode
-        self.fused_decode = FusedDecode.try_build(self)
         from .native_prompt import NativePrompt
         self.native_prompt = NativePrompt.try_build(self)
 
@@ -116,8 +113,6 @@ class DecoderModel:
     # ---- forward -------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [n_wanted, vocab]."""
-        if self.fused_decode is not None and self.fused_decode.takes(ctx):
-            return self.fused_decode.forward(ctx)
         x = torch.empty((ctx.num_tokens, self.hidden_size), dtype=torch.float32, device=self.device)
         kernels.embedding(x, self.embedding, ctx.tokens)
         if self.native_prompt is not None and self.native_prompt.takes(ctx):

@@ -31,6 +31,9 @@ from . import matmul_backend
 
 _ENABLED = os.environ.get("QD_NATIVE_PROMPT", "1") != "0"
 _MIN_TOKENS = int(os.environ.get("QD_NATIVE_PROMPT_MIN", "1"))   # measured faster at every length: 4 tokens 3.2 against 4.4 ms
+# the one arrangement of parts whose order of kernels csrc/prompt_exec.cu restates: a block that answers
+# ``native_params()`` with any other ``composition`` (another order, another part) keeps the parts' own path
+COMPOSITION = "pre_norm/gq_attention/swiglu/rmsnorm/rmsnorm"
 OWN_LAUNCHES_PER_LAYER = 5    # norm, rotation, attention, norm, SwiGLU; the four products are the library's
 
 
@@ -56,7 +59,7 @@ class NativePrompt:
         entries, common = [], None
         for e in model.schedule:
             answer = getattr(model.layers[e.layer], "native_params", lambda: None)()
-            if answer is None:
+            if answer is None or answer.get("composition") != COMPOSITION:
                 return None
             key = {k: answer[k] for k in ("D", "H", "G", "d", "F", "window", "scale", "rotary_dim", "pairing")}
             key["position"] = id(answer["position"])
@@ -68,7 +71,7 @@ class NativePrompt:
         if common is None or model.hidden_size != common["D"]:
             return None
         final = getattr(model.final_norm, "native_params", lambda: None)()
-        if final is None or "weight" not in final:
+        if final is None or final.get("kind") != "rmsnorm" or "weight" not in final:
             return None
         c = common
         n_qkv = (c["H"] + 2 * c["G"]) * c["d"]

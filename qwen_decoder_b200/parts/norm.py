@@ -33,7 +33,7 @@ class RMSNorm(Norm):
         self.weight = source.get(f"{self.prefix}weight").to(device=device, dtype=torch.float32).contiguous()
 
     def native_params(self) -> Optional[dict]:
-        return {"weight": self.weight, "eps": self.eps, "size": self.size}
+        return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
 
     def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -6,9 +6,12 @@ gpu_decoder.cu:15-61); shapes and dtypes are never checked (common.cpp:104-112).
 Here every tensor the model declares is checked against the folder first, and all
 faults come out in one error: missing names, unexpected names, wrong shapes.
 
-Storage rule: a tensor is kept as it is stored if that is bfloat16 or a 32-bit
-type; float16 and float64 become bfloat16 / float32; integer tables become int32.
-What precision a part computes in is the part's business (``bind``).
+Storage rule: a tensor is kept as it is stored if that is bfloat16, float16 or a
+32-bit type (float16 is the reference's own weight format, decoded exactly by its
+float32 forward, common.cpp:104-112, cpu_decoder.cpp:55-62: a part that computes in
+float32 gets every stored bit, one that computes in bfloat16 rounds once);
+float64 becomes float32; integer tables become int32.  What precision a part
+computes in is the part's business (``bind``).
 """
 from __future__ import annotations
 
@@ -41,10 +44,8 @@ class TensorSpec:
 
 def storage_dtype(dt: torch.dtype) -> torch.dtype:
     """The dtype a loaded tensor is kept in (see the module's storage rule)."""
-    if dt in (torch.bfloat16, torch.float32, torch.int32):
+    if dt in (torch.bfloat16, torch.float16, torch.float32, torch.int32):
         return dt
-    if dt == torch.float16:
-        return torch.bfloat16
     if dt == torch.float64:
         return torch.float32
     if dt in (torch.int64, torch.int16, torch.int8, torch.uint8, torch.bool):

@@ -1,5 +1,6 @@
 """A plain, slow implementation of the Qwen2.5 dense decoder: whole sequences, no
-cache, one function per part, float64 on the CPU.  It is written from the formulas of
+cache, one function per part, float64, on whatever device its weights lie (the CPU unless
+a test moves them: float64 has no reduced-precision mode on any device).  It is written from the formulas of
 the reference project nature-li/qwen-decoder (each function cites file:line there) and
 shares no code with the engine: it reads a model folder with the ``safetensors``
 package and ``json``.
@@ -40,7 +41,7 @@ def head_dim_of(cfg) -> int:
 # ------------------------------------------------------------------------ parts
 def embedding(table: torch.Tensor, tokens: Sequence[int]) -> torch.Tensor:
     """x[t, :] = table[tokens[t], :]  (gpu_kernels.cu:18-29; cpu_decoder.cpp:118-119)."""
-    return table[torch.as_tensor(list(tokens), dtype=torch.long)]
+    return table[torch.as_tensor(list(tokens), dtype=torch.long, device=table.device)]
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -65,9 +66,9 @@ def rope(x: torch.Tensor, positions: torch.Tensor, n_heads: int, head_dim: int, 
     pairs (p, p + head_dim/2), the convention of this architecture's safetensors checkpoints."""
     T = x.shape[0]
     x = x.reshape(T, n_heads, head_dim).clone()
-    p = torch.arange(head_dim // 2, dtype=F64)
-    theta = 1.0 / torch.pow(torch.tensor(base, dtype=F64), 2.0 * p / head_dim)
-    ang = positions.to(F64)[:, None] * theta[None, :]          # [T, d/2]
+    p = torch.arange(head_dim // 2, dtype=F64, device=x.device)
+    theta = 1.0 / torch.pow(torch.tensor(base, dtype=F64, device=x.device), 2.0 * p / head_dim)
+    ang = positions.to(device=x.device, dtype=F64)[:, None] * theta[None, :]          # [T, d/2]
     c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
     if pairing == "adjacent":
         x0, x1 = x[..., 0::2].clone(), x[..., 1::2].clone()
@@ -94,8 +95,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n
     q = q.reshape(T, n_heads, head_dim)
     k = k.reshape(T, n_kv_heads, head_dim)
     v = v.reshape(T, n_kv_heads, head_dim)
-    out = torch.zeros(T, n_heads, head_dim, dtype=F64)
-    idx = torch.arange(T)
+    out = torch.zeros(T, n_heads, head_dim, dtype=F64, device=q.device)
+    idx = torch.arange(T, device=q.device)
     for h in range(n_heads):
         g = h // kv_mul
         scores = (q[:, h, :] @ k[:, g, :].t()) * scale                  # [T, T]
@@ -144,14 +145,19 @@ def decoder_layer(x, w, prefix: str, cfg, positions) -> torch.Tensor:
                           w[f"{prefix}mlp.down_proj.weight"])
 
 
-def forward(cfg, w: Dict[str, torch.Tensor], tokens: Sequence[int]) -> torch.Tensor:
+def forward(cfg, w: Dict[str, torch.Tensor], tokens: Sequence[int],
+            rows: Optional[Sequence[int]] = None) -> torch.Tensor:
     """Logits [len(tokens), vocab] of one whole sequence from position 0
     (cpu_decoder.cpp:111-220; final norm :216, output projection :219; with
-    ``tie_word_embeddings`` the output matrix is the embedding table)."""
+    ``tie_word_embeddings`` the output matrix is the embedding table).  With ``rows`` only the
+    logits at those positions, [len(rows), vocab] (a large vocabulary times a long sequence is
+    more than a test needs)."""
     x = embedding(w["model.embed_tokens.weight"], tokens)
-    positions = torch.arange(len(tokens))
+    positions = torch.arange(len(tokens), device=x.device)
     for l in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, f"model.layers.{l}.", cfg, positions)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long, device=x.device)]
     x = rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return linear(x, head)

@@ -86,3 +86,27 @@ def test_random_batches_keep_every_token_with_its_request():
         assert ctx.num_decode == (singles if 0 < singles < n else 0)
         if ctx.num_decode:
             assert all(ctx.cu_tokens.tolist()[i + 1] - ctx.cu_tokens.tolist()[i] == 1 for i in range(singles))
+
+
+def test_a_step_refuses_what_it_cannot_run():
+    """Limits checked by the step function itself: tokens in a step, positions, pages, token ids, wanted places."""
+    import pytest
+    from qwen_decoder_b200.engine.batch import StepError
+    m = manager()
+    a, b = opened(m, "a", 0), opened(m, "b", 20)
+    m.ensure(a, 8)
+    m.ensure(b, 21)
+    ok = [StepEntry(a, [1, 2, 3, 4, 5], [4]), StepEntry(b, [9], [0])]
+    build_context(ok, m, "cpu", 100, 1000, max_step_tokens=6)
+    with pytest.raises(StepError, match="more than max_step_tokens = 5"):
+        build_context(ok, m, "cpu", 100, 1000, max_step_tokens=5)
+    with pytest.raises(StepError, match="exceed the model's 21 positions"):
+        build_context([StepEntry(b, [9, 9], [0])], m, "cpu", 100, 21)
+    with pytest.raises(StepError, match="pages for its 30 new tokens are missing"):
+        build_context([StepEntry(a, list(range(30)), [])], m, "cpu", 100, 1000)
+    with pytest.raises(StepError, match="token id 100 is outside the vocabulary"):
+        build_context([StepEntry(a, [1, 100], [])], m, "cpu", 100, 1000)
+    with pytest.raises(StepError, match="wanted place 2 is outside its 2 tokens"):
+        build_context([StepEntry(a, [1, 2], [2])], m, "cpu", 100, 1000)
+    with pytest.raises(StepError, match="appears twice"):
+        build_context([StepEntry(a, [1], []), StepEntry(a, [2], [])], m, "cpu", 100, 1000)

@@ -516,13 +516,6 @@ def test_decode_attention_from_partial_sums(cfg):
     kernels.decode_attention_rope(part.to(DEV), bias.to(DEV), out, dkv, bt.to(DEV), tr.to(DEV), pos.to(DEV),
                                   slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d), window or 0, splits, True,
                                   d, rot.pairing_code, rot.cos, rot.sin)
-    if 2 <= splits <= 8:
-        # the same with the splits of a (token, kv head) as a thread-block cluster: same numbers
-        out_c = torch.empty_like(out)
-        kernels.decode_attention_rope(part.to(DEV), bias.to(DEV), out_c, kv.to(DEV), bt.to(DEV), tr.to(DEV),
-                                      pos.to(DEV), slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d),
-                                      window or 0, splits, True, d, rot.pairing_code, rot.cos, rot.sin, cluster=True)
-        assert (out_c.float() - out.float()).abs().max() <= 2e-2 * float(out.float().abs().max())
     kvc = dkv.cpu()
     for i, n in enumerate(lens):
         page, off = int(slots[i]) // page_size, int(slots[i]) % page_size
@@ -538,44 +531,13 @@ def test_decode_attention_from_partial_sums(cfg):
                                   slots.to(DEV), H, G, d, page_size, 1.0 / math.sqrt(d), window or 0, splits, False,
                                   d, rot.pairing_code, rot.cos, rot.sin)
     assert torch.equal(dkv2.cpu(), kv)
-    i, n = 3, lens[3]
-    k_all = torch.cat([ks[i][:n - 1].reshape(n - 1, G, d), torch.full((1, G, d), 7.0, dtype=dt)])
-    v_all = torch.cat([vs[i][:n - 1].reshape(n - 1, G, d), torch.full((1, G, d), 7.0, dtype=dt)])
-    want = _plain_attention_row(wq[i], k_all, v_all, H, G, d, n - 1, window)
-    close(out[i], want, dt, scale=7.0)
-
-
-# ---- the whole decode step as one cooperative kernel (opt-in path) against the unfused kernels
-@pytest.mark.gpu
-@pytest.mark.parametrize("name", ["A", "B", "C"])
-@pytest.mark.parametrize("batch", [1, 5, 13])
-def test_fused_decode_step_matches_unfused(name, batch):
-    from tiny_configs import TINY
-    from qwen_decoder_b200.config import Qwen2Config
-    from qwen_decoder_b200.engine.batch import StepEntry
-    from qwen_decoder_b200.engine.runner import ModelRunner
-    from qwen_decoder_b200.parts.fused_decode import FusedDecode
-    cfg = Qwen2Config.from_dict(TINY[name])
-    outs = []
-    for fused in (False, True):
-        r = ModelRunner.from_random(cfg, seed=3, dtype="bfloat16", num_pages=128, page_size=16,
-                                    max_requests=16, use_graphs=False)
-        r.model.fused_decode = FusedDecode.try_build(r.model, force=True) if fused else None
-        assert (r.model.fused_decode is not None) == fused
-        g = torch.Generator().manual_seed(batch)
-        rcs = [r.open(i) for i in range(batch)]
-        prompts = [torch.randint(0, cfg.vocab_size, (7 + 5 * i,), generator=g).tolist() for i in range(batch)]
-        r.step([StepEntry(rc, p, []) for rc, p in zip(rcs, prompts)])
-        seq = []
-        for _ in range(20):          # crosses page edges (16) for several requests
-            toks = torch.randint(0, cfg.vocab_size, (batch,), generator=g).tolist()
-            seq.append(r.step([StepEntry(rc, [t], [0]) for rc, t in zip(rcs, toks)]).float().cpu())
-        if fused:
-            r.model.fused_decode.check_status()
-        outs.append(torch.stack(seq))
-    a, b = outs
-    assert torch.isfinite(b).all()
-    assert (a - b).abs().max().item() <= 3e-2 * a.abs().max().item()
+    # every row, the short ones too: there the chunk with the token's own slot is among the first that a warp
+    # asks for, and it may be read only after the kernel before this one has ended
+    for i, n in enumerate(lens):
+        k_all = torch.cat([ks[i][:n - 1].reshape(n - 1, G, d), torch.full((1, G, d), 7.0, dtype=dt)])
+        v_all = torch.cat([vs[i][:n - 1].reshape(n - 1, G, d), torch.full((1, G, d), 7.0, dtype=dt)])
+        want = _plain_attention_row(wq[i], k_all, v_all, H, G, d, n - 1, window)
+        close(out[i], want, dt, scale=7.0)
 
 
 @pytest.mark.parametrize("shape", [(8, 2048, 11008), (5, 96, 264), (1, 64, 176), (7, 1024, 2816), (3, 128, 1400)])

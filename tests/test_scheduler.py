@@ -180,6 +180,50 @@ def test_prefix_cache_skips_known_beginnings_and_keeps_the_output():
     assert s1.cache.free_pages() == [64]
 
 
+def test_prefix_hit_in_a_nearly_full_pool_waits_instead_of_failing():
+    """A known beginning takes its pages off the free list when the request is opened: the room check has
+    to count what is free after that.  Pool of 256 pages; a finished request left 200 recorded pages on
+    the free list; a running request holds 30; a request with the recorded beginning plus 512 tokens
+    then finds 26 free pages where its first portion needs 32: it must wait, not raise."""
+    layout = CacheLayout.from_needs([PagedKV(2, 16)], [None])
+    cache = CacheManager(layout, 256, 16, 8, prefix_cache=True)
+    s = Scheduler(cache, max_batch=4, max_prefill_tokens_per_step=512, max_total_tokens=1024)
+
+    def step():
+        plan = s.schedule()
+        sampled = []
+        for e in plan.entries:
+            cache.commit(e.request.cache, len(e.tokens), e.tokens)
+            if e.samples:
+                sampled.append(next_token(e.request.all_tokens()))
+        s.update(plan, sampled)
+        cache.check()
+        return plan
+
+    stem = [(7 * i) % 991 + 1 for i in range(3200)]
+    first = Request("first", stem + [5], SamplingParams(max_new_tokens=1))
+    s.add_request(first)
+    while s.has_work():
+        step()
+    assert first.finished and cache.free_pages() == [256]
+    holder = Request("holder", [900 - (i % 50) for i in range(30 * 16 - 8)], SamplingParams(max_new_tokens=1000))
+    s.add_request(holder)
+    step()
+    assert len(holder.cache.tables[0]) == 30
+    again = Request("again", stem + [(11 * i) % 977 + 1 for i in range(512)], SamplingParams(max_new_tokens=2))
+    s.add_request(again)
+    plan = step()                        # would raise OutOfPages out of schedule() before
+    assert again.cache is None and list(s.waiting) == [again] and "again" not in cache.live
+    assert [e.request for e in plan.entries] == [holder]
+    assert cache.free_pages() == [256 - 30]
+    # once the holder is gone the request runs, and finds its beginning
+    s._finish(holder, "cancelled")
+    while s.has_work():
+        step()
+    assert again.finished and again.finish_reason == "length" and len(again.output) == 2
+    assert s.stats["prefix_hit_tokens"] >= 3200 and cache.free_pages() == [256]
+
+
 def run_ahead(sched, reqs, max_steps=10000):
     """The engine's pipelined loop with a fake step: a step's sampled tokens are handed to ``update`` only
     after the next step has been planned (``plan_ahead``) and committed."""

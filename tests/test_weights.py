@@ -50,11 +50,11 @@ def test_truncated_and_malformed_files(tmp_path):
 def test_storage_rule():
     assert storage_dtype(torch.bfloat16) == torch.bfloat16      # kept
     assert storage_dtype(torch.float32) == torch.float32        # a tensor stored in 32-bit stays so
-    assert storage_dtype(torch.float16) == torch.bfloat16
+    assert storage_dtype(torch.float16) == torch.float16        # kept exactly: bind rounds once, or not at all
     assert storage_dtype(torch.int64) == torch.int32            # integer tables
     src = TensorSource.from_dict({"a": torch.ones(2, dtype=torch.float16), "b": torch.ones(2),
                                   "i": torch.ones(2, dtype=torch.int64)})
-    assert src.get("a").dtype == torch.bfloat16 and src.get("b").dtype == torch.float32
+    assert src.get("a").dtype == torch.float16 and src.get("b").dtype == torch.float32
     assert src.get("i").dtype == torch.int32
 
 

@@ -32,20 +32,26 @@ class Trace:
         return "".join(json.dumps(s) + "\n" for s in self.steps)
 
 
-def whole(seqs: Sequence[Sequence[int]]) -> Trace:
+def _wanted(keep, r, p0, n):
+    """Places 0..n-1 of a portion that starts at position p0 of request r; ``keep(r, position)`` thins them
+    (a model with a large vocabulary wants logits at chosen positions, not at all of them)."""
+    return range(n) if keep is None else [i for i in range(n) if keep(r, p0 + i)]
+
+
+def whole(seqs: Sequence[Sequence[int]], keep=None) -> Trace:
     """Each request alone, whole, logits everywhere."""
     t = Trace()
     for r, seq in enumerate(seqs):
-        t.add([(r, 0, seq, range(len(seq)))], end=[r])
+        t.add([(r, 0, seq, _wanted(keep, r, 0, len(seq)))], end=[r])
     return t
 
 
-def decode_tail(seqs, tail=32) -> Trace:
+def decode_tail(seqs, tail=32, keep=None) -> Trace:
     """Most of a request in one step, its last ``tail`` tokens one by one."""
     t = Trace()
     for r, seq in enumerate(seqs):
         n0 = max(1, len(seq) - tail)
-        t.add([(r, 0, seq[:n0], range(n0))])
+        t.add([(r, 0, seq[:n0], _wanted(keep, r, 0, n0))])
         for p in range(n0, len(seq)):
             t.add([(r, p, seq[p:p + 1], [0])], end=[r] if p == len(seq) - 1 else [])
         if n0 == len(seq):
@@ -53,7 +59,7 @@ def decode_tail(seqs, tail=32) -> Trace:
     return t
 
 
-def portions(seqs, sizes=(7, 2, 24, 3, 2, 16, 5, 2, 31, 2)) -> Trace:
+def portions(seqs, sizes=(7, 2, 24, 3, 2, 16, 5, 2, 31, 2), keep=None) -> Trace:
     """Each request in portions of changing size, down to two tokens."""
     t = Trace()
     for r, seq in enumerate(seqs):
@@ -62,12 +68,13 @@ def portions(seqs, sizes=(7, 2, 24, 3, 2, 16, 5, 2, 31, 2)) -> Trace:
             n = min(sizes[i % len(sizes)], len(seq) - p)
             i += 1
             last = p + n == len(seq)
-            t.add([(r, p, seq[p:p + n], range(n))], end=[r] if last else [])
+            t.add([(r, p, seq[p:p + n], _wanted(keep, r, p, n))], end=[r] if last else [])
             p += n
     return t
 
 
-def mixed(seqs, max_tokens: int, seed: int, max_live=4, prompt_frac=0.6) -> Trace:
+def mixed(seqs, max_tokens: int, seed: int, max_live=4, prompt_frac=0.6, keep=None,
+          portion_sizes=(2, 3, 5, 8, 13, 24)) -> Trace:
     """Up to ``max_live`` live requests; some get portions of their prompt (2..24 tokens), others
     single tokens, some sit a step out; a request starts only when the pool (``max_tokens``, each
     request's length rounded up to 64) has room, so pages of finished requests are used again."""
@@ -87,10 +94,10 @@ def mixed(seqs, max_tokens: int, seed: int, max_live=4, prompt_frac=0.6) -> Trac
             p = live[r]
             prompt_len = int(len(seqs[r]) * prompt_frac)
             if p < prompt_len:
-                n = min(rng.choice([2, 3, 5, 8, 13, 24]), len(seqs[r]) - p)
+                n = min(rng.choice(list(portion_sizes)), len(seqs[r]) - p)
             else:
                 n = 1
-            entries.append((r, p, seqs[r][p:p + n], range(n)))
+            entries.append((r, p, seqs[r][p:p + n], _wanted(keep, r, p, n) if n > 1 else [0]))
             live[r] = p + n
             if live[r] == len(seqs[r]):
                 end.append(r)
@@ -118,9 +125,12 @@ def read_outputs(trace: Trace, out_dir: str, vocab: int) -> Dict[int, np.ndarray
     return out
 
 
-def compare(trace: Trace, got: Dict[int, np.ndarray], want_logits: List[np.ndarray], rel_tol: float):
-    """Every replayed row against the plain implementation's row; the first wrong place is named."""
-    scale = max(float(np.abs(w).max()) for w in want_logits)
+def compare(trace: Trace, got: Dict[int, np.ndarray], want_logits, rel_tol: float):
+    """Every replayed row against the plain implementation's row; the first wrong place is named.
+    ``want_logits[r]`` is indexed by position: an array [positions, vocab] or a dict position -> row."""
+    def largest(w):
+        return max(float(np.abs(v).max()) for v in w.values()) if isinstance(w, dict) else float(np.abs(w).max())
+    scale = max(largest(w) for w in want_logits)
     worst = 0.0
     for s in sorted(trace.expect):
         for i, (r, p) in enumerate(trace.expect[s]):
