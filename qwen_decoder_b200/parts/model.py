@@ -76,6 +76,11 @@ class DecoderModel:
             specs += self.lm_head.tensor_specs()
         return specs
 
+    def ignorable_tensors(self) -> List[str]:
+        """Tensors a folder may hold although this model does not use them: with tied embeddings the output
+        projection reads the embedding table, and a stored output matrix is left aside."""
+        return ["lm_head.weight"] if self.spec.lm_head_tensor is None else []
+
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
         self.dtype, self.device = dtype, device
         self.embedding = source.get(self.spec.embedding_tensor).to(device=device, dtype=dtype).contiguous()

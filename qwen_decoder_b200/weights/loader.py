@@ -53,13 +53,22 @@ def storage_dtype(dt: torch.dtype) -> torch.dtype:
     raise WeightError(f"unsupported tensor dtype {dt}")
 
 
-def check_tensors(specs: Iterable[TensorSpec], found: Mapping[str, Tuple[int, ...]], where: str = "") -> None:
-    """Raise one ``WeightError`` that lists every fault, or return."""
+def check_tensors(specs: Iterable[TensorSpec], found: Mapping[str, Tuple[int, ...]], where: str = "",
+                  ignorable: Iterable[str] = ()) -> None:
+    """Raise one ``WeightError`` that lists every fault, or return.  Tensors named in ``ignorable`` may be
+    present without being used (a warning says so): a model with tied embeddings whose file still
+    carries an output matrix."""
     want = {}
     for s in specs:
         want[s.name] = tuple(s.shape)
     missing = sorted(n for n in want if n not in found)
-    unexpected = sorted(n for n in found if n not in want)
+    ignorable = set(ignorable)
+    ignored = sorted(n for n in found if n not in want and n in ignorable)
+    if ignored:
+        import warnings
+        warnings.warn(f"weights{' in ' + where if where else ''}: tensors present but not used by this "
+                      f"configuration: {', '.join(ignored)}")
+    unexpected = sorted(n for n in found if n not in want and n not in ignorable)
     wrong = sorted((n, want[n], tuple(found[n])) for n in want if n in found and tuple(found[n]) != want[n])
     if not (missing or unexpected or wrong):
         return
@@ -102,5 +111,6 @@ class TensorSource:
 
 def load_into(model, source: TensorSource, dtype: torch.dtype, device) -> None:
     """Check ``source`` against ``model.tensor_specs()`` and bind every part."""
-    check_tensors(model.tensor_specs(), source.shapes, source.where)
+    check_tensors(model.tensor_specs(), source.shapes, source.where,
+                  getattr(model, "ignorable_tensors", lambda: ())())
     model.bind(source, dtype, torch.device(device))

@@ -1,7 +1,10 @@
 #!/usr/bin/env python3
-"""Makes tests/golden/reference_cpu_logits.npy: logits of the reference project's own CPU forward
-(nature-li/qwen-decoder, cpu_decoder.cpp:111-220, compiled unmodified from its source tree) for the
-tiny model of golden_model.py, one row per token of golden_model.TOKENS fed at positions 0, 1, 2, ...
+"""Makes tests/golden/reference_cpu_logits.npy and reference_cpu_logits_b.npy: logits of the reference
+project's own CPU forward (nature-li/qwen-decoder, cpu_decoder.cpp:111-220, compiled unmodified from its
+source tree) for the two tiny models of golden_model.py, one row per token fed at positions 0, 1, 2, ...
+The second model reaches the reference as an equivalent model with adjacent rotary pairs and eps 1e-6
+(golden_model.weights_b_reference), and so pins half-split pairs, another eps, one key/value head and
+an output matrix of its own on the reference's code.
 
 Usage: python tests/golden/make_golden.py [path to the reference source tree]
 
@@ -33,9 +36,7 @@ def gstr(s: str) -> bytes:
     return struct.pack("<Q", len(b)) + b
 
 
-def write_gguf(path: str) -> None:
-    c = golden_model.CONFIG
-    w = golden_model.weights()
+def write_gguf(path: str, c: dict, w: dict) -> None:
     L = c["num_hidden_layers"]
     kv = [
         ("qwen2.embedding_length", U32, c["hidden_size"]), ("qwen2.feed_forward_length", U32, c["intermediate_size"]),
@@ -107,16 +108,20 @@ def main():
         sys.exit("usage: make_golden.py <folder of the reference's sources>   (or QWEN_DECODER_REF=<folder>)")
     with tempfile.TemporaryDirectory() as tmp:
         gguf, wrap, exe, raw = (os.path.join(tmp, n) for n in ("m.gguf", "wrap.cpp", "golden", "out.bin"))
-        write_gguf(gguf)
         open(wrap, "w").write(WRAPPER)
         subprocess.check_call(["g++", "-std=c++17", "-O1", "-ffp-contract=off", f"-I{ref}", "-I/usr/local/cuda/include",
                                wrap, os.path.join(ref, "common.cpp"), os.path.join(ref, "gguf_loader.cpp"),
                                "-o", exe])
-        V = golden_model.CONFIG["vocab_size"]
-        subprocess.check_call([exe, gguf, raw, str(V)] + [str(t) for t in golden_model.TOKENS])
-        logits = np.fromfile(raw, dtype="<f4").reshape(len(golden_model.TOKENS), V)
-    np.save(os.path.join(HERE, "reference_cpu_logits.npy"), logits)
-    print("wrote reference_cpu_logits.npy", logits.shape, float(np.abs(logits).max()))
+        for out_name, config, weights, tokens in (
+                ("reference_cpu_logits.npy", golden_model.CONFIG, golden_model.weights(), golden_model.TOKENS),
+                ("reference_cpu_logits_b.npy", golden_model.CONFIG_B, golden_model.weights_b_reference(),
+                 golden_model.TOKENS_B)):
+            write_gguf(gguf, config, weights)
+            V = config["vocab_size"]
+            subprocess.check_call([exe, gguf, raw, str(V)] + [str(t) for t in tokens])
+            logits = np.fromfile(raw, dtype="<f4").reshape(len(tokens), V)
+            np.save(os.path.join(HERE, out_name), logits)
+            print("wrote", out_name, logits.shape, float(np.abs(logits).max()))
 
 
 if __name__ == "__main__":

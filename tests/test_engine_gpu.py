@@ -120,3 +120,22 @@ def test_long_decoding_and_first_tokens(models, dtype, tmp_path):
     tr = trace_tools.decode_tail([seq], tail=250)
     got = trace_tools.run_inprocess(runner, tr, str(tmp_path))
     trace_tools.compare(tr, got, expect, TOL[dtype])
+
+
+def test_float16_weights_are_exact_in_float32_and_rounded_once_in_bfloat16(tmp_path):
+    """A folder stored in float16, the reference's own weight format (common.cpp:104-112), which its
+    float32 forward decodes exactly (cpu_decoder.cpp:55-62): the float32 engine must use every stored
+    bit, the bfloat16 engine rounds each weight once."""
+    from qwen_decoder_b200.config import Qwen2Config
+    from qwen_decoder_b200.weights import write_random_model
+    folder = write_random_model(Qwen2Config.from_dict(TINY["A"]), str(tmp_path / "f16"), 5, dtype=torch.float16)
+    cfg, w = plain_model.read_folder(folder)
+    assert any((t.float().bfloat16().double() != t).any() for t in w.values())     # bits that bfloat16 would lose
+    rng = random.Random(9)
+    seqs = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (9, 60)]
+    want = [plain_model.forward(cfg, w, s).numpy() for s in seqs]
+    for dtype in ("float32", "bfloat16"):
+        runner = make_runner(folder, dtype, held(seqs))
+        tr = trace_tools.portions(seqs)
+        got = trace_tools.run_inprocess(runner, tr, str(tmp_path / dtype))
+        trace_tools.compare(tr, got, want, TOL[dtype])

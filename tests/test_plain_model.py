@@ -28,6 +28,24 @@ def test_plain_forward_equals_the_reference_cpu_decoder():
     assert (got.argmax(-1) == want.argmax(-1)).all()
 
 
+def test_half_split_pairs_another_eps_and_one_kv_head_on_the_reference_cpu_decoder():
+    """reference_cpu_logits_b.npy: the reference's CPU forward on a model that is equivalent, by a reordering
+    of the rows of Wq and Wk and a scaling of the matrices that write to the residual sum, to one with
+    half-split rotary pairs and eps 1e-5 (golden_model.py says why).  The plain implementation computes
+    that model directly, with ``rope_pairing`` "half" and its own eps."""
+    want = np.load(os.path.join(GOLDEN, "reference_cpu_logits_b.npy"))
+    cfg = golden_model.CONFIG_B
+    assert cfg["rope_pairing"] == "half" and cfg["rms_norm_eps"] == 1e-5 and cfg["num_key_value_heads"] == 1
+    w = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in golden_model.weights_b().items()}
+    got = plain_model.forward(cfg, w, golden_model.TOKENS_B).numpy()
+    assert got.shape == want.shape
+    err = np.abs(got - want).max()
+    assert err <= 2e-6 * np.abs(want).max(), err
+    # and it does pin them: the other pairing or the reference's eps on the same tensors is another function
+    for other in (dict(cfg, rope_pairing="adjacent"), dict(cfg, rms_norm_eps=1e-6)):
+        assert np.abs(plain_model.forward(other, w, golden_model.TOKENS_B).numpy() - want).max() > 1e-4
+
+
 def test_half_pairing_is_a_different_function():
     w = {k: torch.from_numpy(v) for k, v in golden_model.weights().items()}
     want = np.load(os.path.join(GOLDEN, "reference_cpu_logits.npy"))

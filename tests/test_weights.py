@@ -87,6 +87,19 @@ def test_tied_model_has_no_output_matrix(tmp_path):
     assert "model.layers.1.self_attn.q_proj.bias" in names and "model.layers.0.self_attn.o_proj.bias" not in names
 
 
+def test_tied_model_leaves_a_stored_output_matrix_aside(tmp_path):
+    cfg = Qwen2Config.from_dict(TINY_A)
+    model = build_model(describe_model(cfg))
+    shapes = {s.name: tuple(s.shape) for s in model.tensor_specs()}
+    shapes["lm_head.weight"] = (cfg.vocab_size, cfg.hidden_size)
+    with pytest.warns(UserWarning, match="not used by this configuration: lm_head.weight"):
+        check_tensors(model.tensor_specs(), shapes, "test", model.ignorable_tensors())
+    shapes["model.extra.weight"] = (1,)
+    with pytest.raises(WeightError) as ei, pytest.warns(UserWarning):
+        check_tensors(model.tensor_specs(), shapes, "test", model.ignorable_tensors())
+    assert ei.value.unexpected == ["model.extra.weight"]
+
+
 def test_random_mode_is_seeded_and_order_free(tmp_path):
     cfg = Qwen2Config.from_dict(TINY_A)
     a = write_random_model(cfg, str(tmp_path / "a"), seed=0)
@@ -101,3 +114,35 @@ def test_random_mode_is_seeded_and_order_free(tmp_path):
     nw = fa.tensor("model.layers.1.input_layernorm.weight").float()
     assert abs(float(nw.mean()) - 1.0) < 0.1
     assert json.load(open(os.path.join(a, "config.json")))["architectures"] == ["Qwen2ForCausalLM"]
+
+
+def test_a_folder_of_shards_with_an_index(tmp_path):
+    """model.safetensors.index.json + shards: every tensor is found in the shard the index names, the
+    model binds from it as from a single file, and an index that names a wrong shard is an error."""
+    cfg = Qwen2Config.from_dict(TINY_B)
+    single = write_random_model(cfg, str(tmp_path / "single"), seed=1)
+    f = SafetensorsFile(os.path.join(single, "model.safetensors"))
+    names = sorted(f.names())
+    sharded = tmp_path / "sharded"
+    sharded.mkdir()
+    with open(os.path.join(single, "config.json")) as src, open(sharded / "config.json", "w") as dst:
+        dst.write(src.read())
+    cut = len(names) // 2
+    parts = {"model-00001-of-00002.safetensors": names[:cut], "model-00002-of-00002.safetensors": names[cut:]}
+    weight_map = {}
+    for fname, ns in parts.items():
+        save_safetensors(str(sharded / fname), {n: f.tensor(n) for n in ns})
+        weight_map.update({n: fname for n in ns})
+    with open(sharded / "model.safetensors.index.json", "w") as fh:
+        json.dump({"metadata": {}, "weight_map": weight_map}, fh)
+    src = TensorSource.from_folder(str(sharded))
+    model = build_model(describe_model(cfg))
+    check_tensors(model.tensor_specs(), src.shapes)
+    for n in names:
+        assert torch.equal(src.get(n), f.tensor(n))
+    # an index entry that points at the other shard
+    weight_map[names[0]] = "model-00002-of-00002.safetensors"
+    with open(sharded / "model.safetensors.index.json", "w") as fh:
+        json.dump({"weight_map": weight_map}, fh)
+    with pytest.raises(SafetensorsError, match="is not in shard"):
+        TensorSource.from_folder(str(sharded))
