@@ -233,6 +233,84 @@ def micro(args):
     return 0
 
 
+def reference_arm(args):
+    """The same metric from the reference's own program (baseline/reference_arm.py says how it is built and
+    fed): decode tokens per second at ``--batch`` with ``--context``-token prompts from its per-step lines,
+    batch 1 and 64 and the 2,048-token prompt step beside it.  Its weights are float16 where ours are
+    bfloat16: the same bytes per step."""
+    import tempfile
+    from baseline import reference_arm as ra
+    if args.gpus != 1:
+        print(f"bench.py: the reference's gpu_decoder_main runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    cfgd = dict(SHAPE_3B, num_hidden_layers=args.layers)
+    W = max(3, args.warmup)
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    try:
+        os.makedirs(out_dir, exist_ok=True)
+    except OSError:
+        out_dir = tempfile.gettempdir()
+    clocks = ClockSampler()
+    try:
+        ra.ensure_binary()
+        with tempfile.TemporaryDirectory(prefix="qd_ref_") as tmp:
+            model = os.path.join(tmp, "model.gguf")
+            ra.write_gguf(model, cfgd, seed=0, context_length=4096)
+            clocks.start()
+            main_rec = ra.run(model, args.batch, args.context, log_path=os.path.join(out_dir, f"reference_b{args.batch}.log"))
+            ck = clocks.stop()
+            recs = {args.batch: main_rec}
+            if not args.no_points:
+                for b in (1, 64):
+                    if b not in recs:
+                        recs[b] = ra.run(model, b, args.context, log_path=os.path.join(out_dir, f"reference_b{b}.log"))
+    except ra.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    ms = main_rec["decode_ms"][W:]
+    if not ms:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference's run printed no decode steps of the full batch"}))
+        return 0
+    K = len(ms)
+    ms_per_step = sum(ms) / K
+    value = args.batch / (ms_per_step / 1e3)
+    pk, pk_src = peaks()
+    ctx_mean = args.context + W + K / 2.0
+    achieved = decode_bytes(cfgd, args.layers, args.batch, ctx_mean) / (ms_per_step / 1e3) / 1e9
+    points = {}
+    for b, rec in recs.items():
+        if b != args.batch and rec["decode_ms"][W:]:
+            d = rec["decode_ms"][W:]
+            points[f"decode_b{b}"] = round(b / (sum(d) / len(d) / 1e3), 1)
+    prefill = None
+    one = recs.get(1, main_rec)["prefill_steps"]
+    whole = [(n, t) for n, n_dec, t in one if n == args.context and n_dec == 0]
+    if whole:
+        n, t = whole[0]
+        prefill = {"value": round(n / (t / 1e3), 1), "tokens": n, "ms": round(t, 3),
+                   "frac": round(prefill_flops(cfgd, args.layers, n) / (t / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    V = cfgd["vocab_size"]
+    print(json.dumps({
+        "metric": "decode tok/s at batch 8 (3B, bf16); prefill tok/s at 2,048 tokens and batch 1/64 beside it",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp16", "data": "synthetic: random weights N(0,0.02) in a GGUF file, random prompt characters",
+        "config": {"model": "Qwen2.5-3B shape", "layers": args.layers, "layers_full": SHAPE_3B["num_hidden_layers"],
+                   "global_batch": args.batch, "seq_len": args.context, "new_tokens": ra.NEW_TOKENS, "page": 16,
+                   "parallelism": "single GPU", "program": "gpu_decoder_main, unmodified, nvcc -O3 -arch=sm_100",
+                   "timing": "the program's own per-step wall-clock lines: batch building, copies, forward, "
+                             "logits to the host and sampling there", "peaks": pk_src},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * 5 * args.batch,
+                "d2h_bytes_per_step": 4 * V * args.batch, "ms_per_step": round(ms_per_step, 4)},
+        "total_line": {"tokens": main_rec.get("total_tokens"), "seconds": main_rec.get("total_s")},
+        "clocks": ck, "impl": "reference"}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -258,11 +336,7 @@ def main():
     if args.micro:
         return micro(args)
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "nature-li/qwen-decoder is a CMake project of executables (no setup.py/pyproject, "
-                          "pip cannot install it) that needs Drogon, gRPC and MPI, which this image lacks, and a "
-                          "GGUF checkpoint with tokenizer to run at all"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
