@@ -198,18 +198,21 @@ def run(model_path: str, batch: int, prompt_tokens: int, max_prefill_step: int =
     stdin = "\n".join(lines) + "\n\n"
     cmd = [exe, model_path, str(batch), "4096", str(max_prefill_step), str(max_prefill_step + batch), "0"]
     t0 = time.time()
-    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    # bytes, not text: the program prints the decoded output of random weights, which is no valid UTF-8
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+    text = lambda b: b.decode("utf-8", errors="replace")
     try:
-        out, err = proc.communicate(stdin, timeout=timeout_s)
+        out, err = (text(b) for b in proc.communicate(stdin.encode(), timeout=timeout_s))
     except subprocess.TimeoutExpired:
         proc.kill()
-        out, err = proc.communicate()
+        out, err = (text(b) for b in proc.communicate())
         if log_path:
             open(log_path, "w").write(out[-20000:] + "\n---- stderr ----\n" + err[-5000:])
         raise Unavailable(f"the reference's gpu_decoder_main did not finish batch {batch} within {timeout_s:.0f} s")
     if log_path:
         # the step lines and the totals; the echoed prompts and outputs are left out
-        keep = [ln for ln in out.splitlines() if ln.startswith(("between", "BlockPool"))]
+        keep = [ln[ln.find("between"):] if "between" in ln else ln for ln in out.splitlines()
+                if "between" in ln or ln.startswith("BlockPool")]
         open(log_path, "w").write("\n".join(keep) + "\n---- stderr ----\n" + err[-5000:])
     if proc.returncode != 0:
         last = (err.strip().splitlines() or ["no message"])[-1][:200]

@@ -142,9 +142,15 @@ class CacheManager:
                 self.kv[g] = torch.zeros(
                     (len(grp.entries), num_pages, 2, n.num_kv_heads, page_size, n.head_dim),
                     dtype=dtype, device=self.device)
+            # one slot more than requests: the padding rows of a padded decode batch update that one
             for i, need in enumerate(layout.fixed_needs):
-                self.states[i] = torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype,
+                self.states[i] = torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype,
                                              device=self.device)
+
+    @property
+    def scratch_slot(self) -> int:
+        """The state slot that belongs to no request: rows that pad a batch read and write it."""
+        return self.max_requests
 
     # ---- sizes ---------------------------------------------------------
     @staticmethod

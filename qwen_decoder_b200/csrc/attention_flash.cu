@@ -336,25 +336,9 @@ decode_attention_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 // status word and the CTA runs on to its end.
 #define DEC_SPIN_LIMIT (1u << 22)
 __device__ __forceinline__ unsigned fa_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool fa_mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
-  const unsigned addr = fa_smem(bar);
-  if (*dead) return false;
-  unsigned long long start = 0;
-  for (unsigned spin = 0; spin < DEC_SPIN_LIMIT; spin++) {
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((spin & 255) == 255) {              // also bounded in time: one second
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (start == 0) start = now;
-      else if (now - start > 1000000000ull) break;
-    }
-  }
-  *dead = 1;
-  return false;
+__device__ __forceinline__ bool fa_mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead,
+                                             unsigned poll_limit = DEC_SPIN_LIMIT) {
+  return qd_mbar_wait_bounded(fa_smem(bar), parity, dead, poll_limit, 1000000000ull);
 }
 
 template <int HD>
@@ -677,6 +661,8 @@ extern "C" int qd_decode_attention_tma(const void* q, long long q_stride, void* 
 }
 
 // 0 if no bounded wait of the TMA decode kernel has run out on the current device (reported once).  Synchronises.
+QD_DEFINE_WAIT_PROBE(qd_decode_attention_tma_wait_probe, fa_mbar_wait(bar, 0, dead, poll_limit), fa_status_word, 99)
+
 extern "C" int qd_decode_attention_tma_status() {
   int* status = fa_status_word();
   if (!status) return -1;

@@ -40,25 +40,9 @@ __device__ __forceinline__ void at_mbar_arrive(unsigned long long* bar) {
 __device__ __forceinline__ void at_mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool at_mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
-  unsigned addr = at_smem(bar);
-  if (*dead) return false;
-  unsigned long long start = 0;
-  for (unsigned spin = 0; spin < AT_SPIN_LIMIT; spin++) {
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((spin & 255) == 255) {              // also bounded in time: two seconds
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (start == 0) start = now;
-      else if (now - start > 2000000000ull) break;
-    }
-  }
-  *dead = 1;
-  return false;
+__device__ __forceinline__ bool at_mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead,
+                                             unsigned poll_limit = AT_SPIN_LIMIT) {
+  return qd_mbar_wait_bounded(at_smem(bar), parity, dead, poll_limit, 2000000000ull);
 }
 // x = column in elements (0 or 64 here: a multiple of 128 bytes), y = row of the cache seen as [rows][d]
 __device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
@@ -539,6 +523,8 @@ extern "C" int qd_prefill_attention_tc5(const void* q, long long q_stride, void*
 }
 
 // 0 if no kernel of this library has recorded a bounded-wait expiry on the current device.  Synchronises.
+QD_DEFINE_WAIT_PROBE(qd_prefill_attention_tc5_wait_probe, at_mbar_wait(bar, 0, dead, poll_limit), at_status_word, 99)
+
 extern "C" int qd_prefill_attention_tc5_status() {
   int* status = at_status_word();
   if (!status) return -1;

@@ -89,3 +89,55 @@ static inline void qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   cfg.numAttrs = qd_pdl_enabled() ? 1 : 0;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// ---- bounded waits -----------------------------------------------------------------
+// Every wait on an mbarrier in these kernels has a limit in polls and in time.  When it runs out the
+// waiter sets ``*dead`` (no wait of its CTA spins again), the caller records which wait it was in the
+// library's status word, and the kernel runs on to its end with void results: the host reads the
+// status word (qd_<library>_status) and raises.  A kernel never hangs on a copy that did not arrive.
+__device__ __forceinline__ bool qd_mbar_wait_bounded(unsigned bar_smem_addr, unsigned parity, volatile int* dead,
+                                                     unsigned poll_limit, unsigned long long time_limit_ns,
+                                                     unsigned backoff_ns = 0) {
+  if (*dead) return false;
+  unsigned long long start = 0;
+  for (unsigned spin = 0; spin < poll_limit; spin++) {
+    if (backoff_ns && spin) __nanosleep(backoff_ns);     // long waits of many threads: leave the issue slots alone
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar_smem_addr), "r"(parity) : "memory");
+    if (ok) return true;
+    if ((spin & 255) == 255) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (start == 0) start = now;
+      else if (now - start > time_limit_ns) break;
+    }
+  }
+  *dead = 1;
+  return false;
+}
+
+// A probe of a library's wait, for tests: one warp waits, with ``poll_limit`` polls, on an mbarrier that
+// nobody arrives at, through the library's own wait function; the wait must run out, the kernel must end
+// and the library's status word must read ``code`` afterwards.  ``wait_expr`` may use ``bar`` (the
+// barrier), ``dead`` and ``poll_limit``; ``status_fn`` returns the library's status word on the device.
+#define QD_DEFINE_WAIT_PROBE(entry, wait_expr, status_fn, code)                                          \
+  __global__ void entry##_kernel(int* status, unsigned poll_limit) {                                      \
+    __shared__ unsigned long long bar_word;                                                               \
+    __shared__ int dead_word;                                                                             \
+    unsigned long long* bar = &bar_word;                                                                  \
+    volatile int* dead = &dead_word;                                                                      \
+    if (threadIdx.x == 0) {                                                                               \
+      dead_word = 0;                                                                                      \
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(bar)), "r"(1u)); \
+    }                                                                                                     \
+    __syncthreads();                                                                                      \
+    if (!(wait_expr) && threadIdx.x == 0) atomicExch(status, code);                                       \
+  }                                                                                                       \
+  extern "C" int entry(unsigned poll_limit, cudaStream_t stream) {                                        \
+    int* status = status_fn();                                                                            \
+    if (!status) return QD_ERR_UNSUPPORTED;                                                               \
+    entry##_kernel<<<1, 32, 0, stream>>>(status, poll_limit);                                             \
+    return (int)cudaGetLastError();                                                                       \
+  }

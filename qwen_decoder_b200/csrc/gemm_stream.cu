@@ -48,27 +48,11 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
 __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// true when the phase with the given parity has completed; false after ST_SPIN_LIMIT polls (or at
+// true when the phase with the given parity has completed; false after ST_SPIN_LIMIT polls or two seconds (or at
 // once when a wait of this CTA has already run out: *dead is then set and nobody waits any more)
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead) {
-  unsigned addr = smem_u32(bar);
-  if (*dead) return false;
-  unsigned long long start = 0;
-  for (unsigned spin = 0; spin < ST_SPIN_LIMIT; spin++) {
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((spin & 255) == 255) {              // also bounded in time: two seconds
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (start == 0) start = now;
-      else if (now - start > 2000000000ull) break;
-    }
-  }
-  *dead = 1;
-  return false;
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead,
+                                          unsigned poll_limit = ST_SPIN_LIMIT) {
+  return qd_mbar_wait_bounded(smem_u32(bar), parity, dead, poll_limit, 2000000000ull);
 }
 __device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, unsigned long long* bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -795,6 +779,8 @@ extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void*
 
 // 0 if no kernel of this library has recorded a bounded-wait expiry on the current device
 // (1: producer gave up waiting for a free stage, 2: a consumer gave up waiting for data).  Synchronises.
+QD_DEFINE_WAIT_PROBE(qd_gemm_stream_wait_probe, mbar_wait(bar, 0, dead, poll_limit), status_word, 99)
+
 extern "C" int qd_gemm_stream_status() {
   int* status = status_word();
   if (!status) return -1;

@@ -52,26 +52,8 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
 // when a wait of this CTA has already run out (*dead set): then nobody spins again, every role runs
 // on to its end without leaving early, the kernel ends and the host sees a non-zero status.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, volatile int* dead,
-                                          unsigned backoff_ns = 0) {
-  unsigned addr = smem_u32(bar);
-  if (*dead) return false;
-  unsigned long long start = 0;
-  for (unsigned spin = 0; spin < TC_SPIN_LIMIT; spin++) {
-    if (backoff_ns && spin) __nanosleep(backoff_ns);     // long waits of many threads: leave the issue slots alone
-    unsigned ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((spin & 255) == 255) {              // also bounded in time: two seconds
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (start == 0) start = now;
-      else if (now - start > 2000000000ull) break;
-    }
-  }
-  *dead = 1;
-  return false;
+                                          unsigned backoff_ns = 0, unsigned poll_limit = TC_SPIN_LIMIT) {
+  return qd_mbar_wait_bounded(smem_u32(bar), parity, dead, poll_limit, 2000000000ull, backoff_ns);
 }
 // x = innermost coordinate (k, in elements; always a multiple of 64 here: 128 bytes), y = row
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, unsigned long long* bar) {
@@ -467,6 +449,8 @@ extern "C" int qd_gemm_tc5(const void* W, const void* X, long long ldx, const fl
 // 0 if no bounded wait of this library's kernels has run out on the current device (1: producer waiting
 // for a free stage, 2: MMA issuer waiting for data, 3: MMA issuer waiting for a drained accumulator,
 // 4: epilogue waiting for a complete accumulator).  Synchronises the device.
+QD_DEFINE_WAIT_PROBE(qd_gemm_tc5_wait_probe, mbar_wait(bar, 0, dead, 0, poll_limit), status_word, 99)
+
 extern "C" int qd_gemm_tc5_status() {
   int* status = status_word();
   if (!status) return -1;

@@ -194,6 +194,11 @@ def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: Ca
     h[o:o + lay.R + 1] = np.arange(lay.R + 1) if padded else cu
     put("start", starts_a, R, lay.R)
     put("slots", np.asarray(slots, dtype=np.int64), R, lay.R)
+    if lay.R > R:
+        # padding rows repeat entry 0 where that is harmless (the same K/V written twice); a state of fixed
+        # size would be updated twice, so they get the slot that belongs to no request
+        o = lay.off["slots"]
+        h[o + R:o + lay.R] = cache.scratch_slot
     o = lay.off["want"]
     h[o:o + lay.n_want] = np.arange(lay.n_want) if padded else want
     ps = cache.page_size

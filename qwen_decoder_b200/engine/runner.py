@@ -61,7 +61,9 @@ class ModelRunner:
                                   device=self.device, prefix_cache=prefix_cache)
         from ..sampling import Sampler
         self.sampler = Sampler(self.device)
-        self.use_graphs = use_graphs
+        # decode steps replay as CUDA graphs unless a part has to see the step's metadata on the host
+        self.use_graphs = use_graphs and not any(
+            getattr(part, "needs_host_metadata", False) for part in model.all_parts())
         self.max_step_tokens = max_step_tokens     # most tokens one step may hold (None: no limit of its own)
         self._graphs = {}
         self.steps = 0
@@ -176,8 +178,7 @@ class ModelRunner:
 
     def can_take_device_tokens(self, entries: Sequence[StepEntry]) -> bool:
         """True if this batch runs as a replayed graph: single tokens that all want logits."""
-        return self.use_graphs and not self.layout.fixed and all(
-            len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+        return self.use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
 
     # ---- decode steps as CUDA graphs ---------------------------------------------
     def _graph_step(self, entries: Sequence[StepEntry], sampling, device_tokens=None):
@@ -216,6 +217,16 @@ class ModelRunner:
         return g.logits[:R], (g.tokens[:R] if g.tokens is not None else None)
 
 
+class _NotOnHost:
+    """Stands where a step's host copies of the metadata would be when the step replays as a graph."""
+
+    def _refuse(self, *a, **k):
+        raise StepError("this step replays as a CUDA graph and has no host copies of its metadata; a part whose "
+                        "forward reads ctx.host_* must set needs_host_metadata = True")
+
+    __getitem__ = __iter__ = __len__ = _refuse
+
+
 class _DecodeGraph:
     """One captured decode step for a padded batch size and block-table widths."""
 
@@ -234,6 +245,8 @@ class _DecodeGraph:
         self.ctx = self.lay.context(self.dev, runner.cache, runner.device)
         self.ctx.all_decode = True
         self.ctx.max_portion = 1
+        # nothing of a replayed step runs on the host: there are no host copies of its metadata
+        self.ctx.host_cu_tokens = self.ctx.host_start_pos = self.ctx.host_state_slots = _NotOnHost()
         self.ctx.max_context = min(runner.max_positions, max(mbs) * runner.cache.page_size) if mbs else 1
         o = self.lay.off["extra"]
         self.temps = self.dev[o:o + Bp].view(torch.float32)

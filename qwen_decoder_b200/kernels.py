@@ -559,18 +559,33 @@ def prefill_attention_tc5_status() -> int:
     return int(library("attention_tc5").qd_prefill_attention_tc5_status())
 
 
+# library -> (its status function, its wait probe): the kernels with bounded waits on mbarriers or a grid barrier
+_STATUS = {"gemm_stream": ("qd_gemm_stream_status", "qd_gemm_stream_wait_probe"),
+           "gemm_tc5": ("qd_gemm_tc5_status", "qd_gemm_tc5_wait_probe"),
+           "attention_tc5": ("qd_prefill_attention_tc5_status", "qd_prefill_attention_tc5_wait_probe"),
+           "attention_flash": ("qd_decode_attention_tma_status", "qd_decode_attention_tma_wait_probe")}
+
+
 def check_status() -> None:
     """Raise if a bounded wait inside one of the kernels with mbarrier or grid-barrier waits ran out since the
     last call: the results of that launch were void.  Synchronises the device; asks only the libraries this
-    process has loaded."""
-    for name, fn in (("gemm_stream", "qd_gemm_stream_status"), ("gemm_tc5", "qd_gemm_tc5_status"),
-                     ("attention_tc5", "qd_prefill_attention_tc5_status"),
-                     ("attention_flash", "qd_decode_attention_tma_status")):
+    process has loaded; a status is reported once."""
+    bad = []
+    for name, (fn, _) in _STATUS.items():
         if _library_loaded(name):
             code = int(getattr(library(name), fn)())
             if code != 0:
-                raise KernelError(f"{name}: a bounded wait ran out inside a kernel (status {code}); results of "
-                                  "launches since the last check are invalid")
+                bad.append(f"{name} (status {code})")
+    if bad:
+        raise KernelError("a bounded wait ran out inside a kernel of " + ", ".join(bad) +
+                          "; results of launches since the last check are invalid")
+
+
+def wait_probe(name: str, poll_limit: int = 2048) -> None:
+    """Launch library ``name``'s probe: one warp waits ``poll_limit`` polls, through the library's own wait
+    function, on an mbarrier that nobody arrives at.  The wait runs out, the kernel ends, and the next
+    ``check_status`` raises.  For tests of that chain; it harms nothing else."""
+    _check(getattr(library(name), _STATUS[name][1])(ctypes.c_uint(poll_limit), _stream()), f"{name} wait probe")
 
 
 # ------------------------------------------------------------------ the layers of a prompt step from native code

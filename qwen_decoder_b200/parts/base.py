@@ -27,6 +27,12 @@ from ..weights.loader import TensorSource, TensorSpec
 class Part:
     """Base of every part: tensors by name, bound once, then ``forward``."""
 
+    # True if ``forward`` reads the host copies of the step's metadata (``ctx.host_cu_tokens``,
+    # ``ctx.host_start_pos``, ``ctx.host_state_slots``): a loop over requests in Python.  A step that is
+    # replayed as a CUDA graph has no such copies (nothing of it runs on the host), so a model with such
+    # a part runs every step eagerly.  Parts that work from the device tensors alone leave it False.
+    needs_host_metadata = False
+
     def tensor_specs(self) -> List[TensorSpec]:
         return []
 

@@ -100,6 +100,15 @@ class DecoderModel:
         from .native_prompt import NativePrompt
         self.native_prompt = NativePrompt.try_build(self)
 
+    def all_parts(self):
+        """Every part of the model: position encodings, each layer and what it is made of, the final norm."""
+        out = list(self.positions.values())
+        for layer in self.layers:
+            out.append(layer)
+            out += list(layer.parts()) if hasattr(layer, "parts") else []
+        out.append(self.final_norm)
+        return out
+
     # ---- cache -------------------------------------------------------------
     def cache_layout(self) -> CacheLayout:
         needs = [self.layers[e.layer].mixer.cache_need() for e in self.schedule]

@@ -43,6 +43,7 @@ class ToyConfig:
     num_experts: int = 3
     expert_size: int = 40
     gain_period: float = 9.0
+    block: str = "pre_norm"
     eos_token_ids: tuple = ()
 
     @classmethod
@@ -67,16 +68,17 @@ def describe_toy(c: ToyConfig) -> ModelSpec:
     norm = {"size": c.hidden_size, "eps": c.eps}
     layers = []
     for i, kind in enumerate(c.kinds):
-        if kind in ("ema", "ema_gain"):
-            mixer = PartSpec("toy_ema", {"hidden_size": c.hidden_size, "prefix": "mix.",
-                                         "position": "gain" if kind == "ema_gain" else None})
+        if kind in ("ema", "ema_gain", "ema_dev"):
+            mixer = PartSpec("toy_ema_device" if kind == "ema_dev" else "toy_ema",
+                             {"hidden_size": c.hidden_size, "prefix": "mix.",
+                              "position": "gain" if kind == "ema_gain" else None})
         else:
             mixer = PartSpec("gq_attention", {
                 "hidden_size": c.hidden_size, "num_heads": c.num_heads, "num_kv_heads": c.num_kv_heads,
                 "head_dim": c.head_dim, "qkv_bias": True, "out_bias": False, "position": "rope",
                 "window": c.window if kind == "window" else None, "prefix": "self_attn."})
         layers.append(LayerSpec(
-            prefix=f"model.layers.{i}.", block="pre_norm", mixer=mixer,
+            prefix=f"model.layers.{i}.", block=c.block, mixer=mixer,
             feed_forward=PartSpec("toy_routed", {"hidden_size": c.hidden_size, "expert_size": c.expert_size,
                                                  "num_experts": c.num_experts, "prefix": "moe."})
             if i in c.routed_layers else
@@ -96,9 +98,30 @@ def describe_toy(c: ToyConfig) -> ModelSpec:
         final_norm_prefix="model.norm.", lm_head_tensor="lm_head.weight")
 
 
+# ------------------------------------------------------------ another arrangement of the same parts
+from qwen_decoder_b200.parts.block import PreNormBlock  # noqa: E402
+
+
+class ToyParallelBlock(PreNormBlock):
+    """x += mixer(norm1(x)) + feed_forward(norm2(x)), both branches from the same x: the parts and tensor
+    names of the pre-norm block in another order.  It inherits ``native_params`` and changes nothing there:
+    native code that restates the pre-norm order must not take it."""
+
+    def forward(self, stream, ctx, cache):
+        h1 = self.input_norm.forward(stream, self.dtype)          # adds what is pending, normalises
+        h2 = self.post_mixer_norm.forward(stream, self.dtype)     # nothing pending: the same x
+        a = self.mixer.forward(h1, ctx, cache)
+        f = self.feed_forward.forward(h2, ctx)
+        stream.push(a)
+        stream.push(f)
+
+
 # ------------------------------------------------------------ a toy mixer with its own state
 class ToyEma(Mixer):
-    """y_t = (s_t) W^T with s_t = 0.75 s_{t-1} + 0.25 x_t, s kept per request between steps."""
+    """y_t = (s_t) W^T with s_t = 0.75 s_{t-1} + 0.25 x_t, s kept per request between steps.
+    Written as a loop over requests on the host, so it says so: its model runs every step eagerly."""
+
+    needs_host_metadata = True
 
     def __init__(self, hidden_size, prefix="mix.", position=None):
         self.hidden_size, self.prefix, self.position = hidden_size, prefix, position
@@ -129,6 +152,32 @@ class ToyEma(Mixer):
                 cache.state[ctx.host_state_slots[r]] = s
             out[a:b] = (torch.stack(rows) @ self.w.t()).to(x.dtype)
         return out
+
+
+class ToyEmaDevice(ToyEma):
+    """The same mixer computed from the step's device tensors alone (no loop over requests on the host):
+    decode steps of its model replay as CUDA graphs like any other model's."""
+
+    needs_host_metadata = False
+
+    def forward(self, x, ctx, cache):
+        T, R = ctx.num_tokens, ctx.num_requests
+        slots = ctx.state_slots.long()
+        cu = ctx.cu_tokens.long()
+        s = cache.state[slots]                                   # [R, D]
+        rows = torch.zeros((T + 1, x.shape[1]), dtype=torch.float32, device=x.device)   # row T: for nobody
+        xf = x.float()
+        for j in range(ctx.max_portion):                        # token j of every request that has one
+            idx = cu[:-1] + j
+            valid = idx < cu[1:]
+            xt = xf[idx.clamp(max=T - 1)]
+            if self.position is not None:
+                xt = xt * self.position.table[(ctx.start_pos.long() + j).clamp(max=self.position.table.numel() - 1)][:, None]
+            s = torch.where(valid[:, None], 0.75 * s + 0.25 * xt, s)
+            rows.index_put_((torch.where(valid, idx, torch.full_like(idx, T)),), s)
+        if cache.write:
+            cache.state.index_put_((slots,), s)
+        return (rows[:T] @ self.w.t()).to(x.dtype)
 
 
 # ------------------------------------------------------------ another position encoding
@@ -181,12 +230,16 @@ class ToyRouted(FeedForward):
 @pytest.fixture(scope="module", autouse=True)
 def toy_registration():
     register_part("mixer", "toy_ema")(ToyEma)
+    register_part("mixer", "toy_ema_device")(ToyEmaDevice)
+    register_part("block", "toy_parallel")(ToyParallelBlock)
     register_part("position", "toy_gain")(ToyGain)
     register_part("feed_forward", "toy_routed")(ToyRouted)
     register_architecture("ToyLM", ToyConfig, describe_toy)
     yield
     unregister_architecture("ToyLM")
     unregister_part("mixer", "toy_ema")
+    unregister_part("mixer", "toy_ema_device")
+    unregister_part("block", "toy_parallel")
     unregister_part("position", "toy_gain")
     unregister_part("feed_forward", "toy_routed")
 
@@ -202,7 +255,7 @@ def toy_plain(cfg: ToyConfig, w, tokens):
         p = f"model.layers.{l}."
         h = plain_model.rmsnorm(x, w[p + "input_layernorm.weight"], cfg.eps)
         kind = cfg.kinds[l]
-        if kind in ("ema", "ema_gain"):
+        if kind in ("ema", "ema_gain", "ema_dev"):
             s = torch.zeros(cfg.hidden_size, dtype=torch.float64)
             gain = gain_table(T, cfg.gain_period) if kind == "ema_gain" else torch.ones(T, dtype=torch.float64)
             rows = []
@@ -221,8 +274,9 @@ def toy_plain(cfg: ToyConfig, w, tokens):
                 kv_of[e] = (k, v)
             a = plain_model.attention(q, k, v, H, G, d, cfg.window if kind == "window" else None)
             a = plain_model.linear(a, w[p + "self_attn.o_proj.weight"])
+        h = plain_model.rmsnorm(x if cfg.block == "toy_parallel" else x + a,
+                                w[p + "post_attention_layernorm.weight"], cfg.eps)
         x = x + a
-        h = plain_model.rmsnorm(x, w[p + "post_attention_layernorm.weight"], cfg.eps)
         if l in cfg.routed_layers:
             choice = (h @ w[p + "moe.router.weight"].t()).argmax(-1)
             y = torch.zeros_like(h)
@@ -288,7 +342,9 @@ def test_a_layer_named_twice_and_a_run_that_reads_another_runs_cache(tmp_path, d
 def test_a_toy_mixer_with_state_of_its_own(tmp_path, dtype):
     cfg = ToyConfig("ToyLM", kinds=("ema", "full", "ema"))
     runner = run_all_cuttings(cfg, tmp_path, dtype)
-    assert len(runner.cache.states) == 2 and runner.cache.states[0].shape == (8, 48)
+    # a slot per request and one for the rows that pad a batch
+    assert len(runner.cache.states) == 2 and runner.cache.states[0].shape == (8 + 1, 48)
+    assert not runner.use_graphs and not runner._graphs        # its forward loops over requests on the host
 
 
 def test_a_toy_feed_forward_with_routing(tmp_path):
@@ -311,3 +367,30 @@ def test_another_position_encoding(tmp_path, dtype):
     model = runner.model
     assert type(model.positions["gain"]).__name__ == "ToyGain"
     assert model.layers[0].mixer.position is model.positions["gain"] and model.layers[1].mixer.position is model.positions["rope"]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_mixer_with_state_replays_as_graphs_when_it_works_on_the_device(tmp_path, dtype):
+    """The same toy mixer written with device tensors only: batches of single tokens run as replayed CUDA
+    graphs (padded batches too: the padding rows use the state slot that belongs to no request), and every
+    way of cutting gives the plain implementation's logits."""
+    cfg = ToyConfig("ToyLM", kinds=("ema_dev", "full", "ema_dev"))
+    runner = run_all_cuttings(cfg, tmp_path, dtype)
+    assert runner.use_graphs and runner._graphs
+    assert any(g.lay.T > 1 for g in runner._graphs.values())           # the mixed trace decodes several at once
+    assert 3 in {len(s["entries"]) for s in trace_tools.mixed([[1] * 40] * 6, 384, seed=5).steps}
+
+
+def test_another_order_of_the_same_parts_keeps_the_parts_path(tmp_path):
+    """A block with the pre-norm block's parts and tensor names in another order (both branches read the same
+    x): the native prompt loop, which restates the pre-norm order, must decline it, and the logits are the
+    plain implementation's."""
+    cfg = ToyConfig("ToyLM", kinds=("full", "full"), block="toy_parallel")
+    runner = run_all_cuttings(cfg, tmp_path, "bfloat16")
+    assert runner.model.native_prompt is None
+    from qwen_decoder_b200.engine import ModelRunner
+    usual = ModelRunner.from_folder(str(tmp_path / "model"), dtype="bfloat16", device="cuda:0", num_pages=8)
+    assert type(usual.model.layers[0]).__name__ == "ToyParallelBlock"
+    plain_cfg = ToyConfig("ToyLM", kinds=("full", "full"))
+    folder = write_random_model(plain_cfg, str(tmp_path / "prenorm"), seed=11)
+    assert ModelRunner.from_folder(folder, dtype="bfloat16", device="cuda:0", num_pages=8).model.native_prompt is not None

@@ -2,6 +2,7 @@
 models do not use (odd widths, other head sizes, other page sizes)."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -566,3 +567,72 @@ def test_feed_forward_in_one_launch(shape):
         assert (got - want).abs().max() <= 1e-4 * want.abs().max() + 1e-6
         assert (got - h64 @ w2.double().cpu().t()).abs().max() <= 2e-2 * want.abs().max()
     assert kernels.gemm_stream_status() == 0
+
+
+# ---- a wait that runs out: the kernel ends, the status word says so, the host raises
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["gemm_stream", "gemm_tc5", "attention_tc5", "attention_flash"])
+def test_a_wait_that_runs_out_ends_the_kernel_and_is_reported_once(name):
+    """Each library's own wait function, on an mbarrier nobody arrives at, with a limit of a few thousand
+    polls: the launch returns, the library's status word is set, ``check_status`` raises once, and the
+    device goes on working."""
+    from qwen_decoder_b200 import kernels
+    kernels.check_status()                      # clean before
+    kernels.wait_probe(name, 4096)
+    torch.cuda.synchronize()
+    with pytest.raises(kernels.KernelError, match=name):
+        kernels.check_status()
+    kernels.check_status()                      # reported once
+    x = torch.arange(1000, device=DEV, dtype=torch.float32)
+    assert float((x * 2).sum()) == 999000.0
+
+
+@pytest.mark.gpu
+def test_a_grid_barrier_that_runs_out_is_reported_and_repaired(tmp_path):
+    """The one-launch feed-forward meets all its CTAs at a grid barrier whose spin is bounded.  With a
+    barrier word that no arrival count can satisfy the spin runs out (two seconds), the step's results are
+    void, the runner's look at the status raises and puts the barrier words back; the steps after it are
+    right again."""
+    import plain_model
+    from tiny_configs import make_folder
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.engine import ModelRunner, StepEntry
+    folder = make_folder("D", str(tmp_path))
+    cfg, w = plain_model.read_folder(folder)
+    runner = ModelRunner.from_folder(folder, dtype="bfloat16", device=DEV, num_pages=8, use_graphs=False)
+    seq = [5, 17, 3, 250, 99, 7, 1, 64, 12, 33]
+    want = plain_model.forward(cfg, w, seq).numpy()
+    rc = runner.open("r")
+    runner.step([StepEntry(rc, seq[:7], [6])])
+    runner.step([StepEntry(rc, seq[7:8], [0])])
+    ff = runner.model.layers[0].feed_forward
+    assert ff._barrier is not None, "the decode step did not run the one-launch feed-forward"
+    runner.check_status()
+    ff._barrier[0] = 1 << 30                    # arrivals counted from here never reach the grid's size
+    runner.step([StepEntry(rc, seq[8:9], [0])])
+    with pytest.raises(kernels.KernelError, match="gemm_stream"):
+        runner.check_status()
+    assert ff._barrier.tolist() == [0, 0]
+    logits = runner.step([StepEntry(rc, seq[9:10], [0])])
+    runner.check_status()
+    # position 8 was computed by the void step: its cache entries are suspect, so compare a fresh request
+    rc2 = runner.open("again")
+    logits = runner.step([StepEntry(rc2, seq, [9])])
+    runner.check_status()
+    assert float((logits[0].float().cpu() - torch.from_numpy(want[9])).abs().max()) <= 3e-2 * float(np.abs(want).max())
+
+
+@pytest.mark.gpu
+def test_generate_raises_when_a_wait_ran_out(tmp_path):
+    """A short generation (far fewer steps than the routine look at the status words) does not hand out
+    tokens of a run in which a kernel's wait ran out."""
+    from tiny_configs import make_folder
+    from qwen_decoder_b200 import kernels
+    from qwen_decoder_b200.engine import Engine, SamplingParams
+    folder = make_folder("A", str(tmp_path))
+    eng = Engine(folder, dtype="bfloat16", device=DEV, num_pages=16)
+    assert len(eng.generate([[1, 2, 3]], SamplingParams(max_new_tokens=4, ignore_eos=True))[0]) == 4
+    kernels.wait_probe("gemm_stream", 4096)
+    with pytest.raises(kernels.KernelError):
+        eng.generate([[4, 5, 6]], SamplingParams(max_new_tokens=4, ignore_eos=True))
+    kernels.check_status()
