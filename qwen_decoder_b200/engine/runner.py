@@ -279,8 +279,13 @@ class _DecodeGraph:
     def run(self) -> None:
         if self.graph is None:
             # the first step of this shape runs eagerly (loads every kernel), then is captured; the
-            # eager run and the first replay write the same values to the same cache slots
+            # eager run and the first replay write the same values to the same cache slots.  A state of
+            # fixed size is another matter: its update is no plain write, so the eager run's is undone
+            states = [st.clone() for st in self.ctx.cache.states if st is not None]
             self._forward()
+            for st, saved in zip((st for st in self.ctx.cache.states if st is not None), states):
+                st.copy_(saved)
+            del states
             torch.cuda.synchronize(self.device)
             import gc
             from .. import kernels
