@@ -32,6 +32,16 @@ SHAPE_3B = dict(
     architectures=["Qwen2ForCausalLM"], hidden_size=2048, intermediate_size=11008, num_hidden_layers=36,
     num_attention_heads=16, num_key_value_heads=2, vocab_size=151936, max_position_embeddings=32768,
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+# the two other GPU-sized shapes of the survey's measurement table (their own workloads: see --workload)
+SHAPE_7B = dict(
+    architectures=["Qwen2ForCausalLM"], hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+    num_attention_heads=28, num_key_value_heads=4, vocab_size=152064, max_position_embeddings=32768,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+SHAPE_32B = dict(
+    architectures=["Qwen2ForCausalLM"], hidden_size=5120, intermediate_size=27648, num_hidden_layers=64,
+    num_attention_heads=40, num_key_value_heads=8, vocab_size=152064, max_position_embeddings=32768,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+SHAPES = {"3B": SHAPE_3B, "7B": SHAPE_7B, "32B": SHAPE_32B}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -98,7 +108,7 @@ def decode_bytes(cfg, layers, batch, ctx_mean):
     H, G = cfg["num_attention_heads"], cfg["num_key_value_heads"]
     d = D // H
     per_layer = (H * d + 2 * G * d) * D + D * H * d + 3 * F * D
-    weights = (layers * per_layer + V * D) * 2          # every matrix once; the tied table once (output product)
+    weights = (layers * per_layer + V * D) * 2          # every matrix once; the output matrix (tied or not) once
     kv = batch * ctx_mean * layers * 2 * G * d * 2
     return weights + kv
 
@@ -120,7 +130,7 @@ def serve(args):
     from qwen_decoder_b200 import kernels
     from qwen_decoder_b200.config import Qwen2Config
     from qwen_decoder_b200.engine import Engine, SamplingParams
-    cfg = Qwen2Config.from_dict(dict(SHAPE_3B, num_hidden_layers=args.layers))
+    cfg = Qwen2Config.from_dict(dict(SHAPES[args.shape], num_hidden_layers=args.layers))
     n, plen, new = args.batch, args.context, args.steps
     page = args.page_size
     engine = Engine(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_batch=max(64, n),
@@ -319,7 +329,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
-    ap.add_argument("--layers", type=int, default=SHAPE_3B["num_hidden_layers"])
+    ap.add_argument("--shape", default="3B", choices=sorted(SHAPES), help="layer sizes: Qwen2.5-3B (the headline), 7B or 32B")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (config names both numbers)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (a multiple of 16)")
     ap.add_argument("--no-points", action="store_true")
@@ -333,6 +344,9 @@ def main():
     ap.add_argument("--micro-shape", default="lm_head", choices=["qkv", "o", "gate_up", "down", "lm_head"])
     ap.add_argument("--tokens", type=int, default=8)
     args = ap.parse_args()
+    shape = SHAPES[args.shape]
+    if args.layers is None:
+        args.layers = shape["num_hidden_layers"]
     if args.micro:
         return micro(args)
     if args.impl == "reference":
@@ -349,7 +363,7 @@ def main():
     from qwen_decoder_b200.engine import Engine, SamplingParams, StepEntry
     from qwen_decoder_b200.parts import matmul_backend
 
-    cfgd = dict(SHAPE_3B, num_hidden_layers=args.layers)
+    cfgd = dict(shape, num_hidden_layers=args.layers)
     cfg = Qwen2Config.from_dict(cfgd)
     pk, pk_src = peaks()
     page = args.page_size
@@ -477,14 +491,15 @@ def main():
     ck = clocks.stop()
 
     out = {
-        "metric": "decode tok/s at batch 8 (3B, bf16); prefill tok/s at 2,048 tokens and batch 1/64 beside it",
+        "metric": f"decode tok/s at batch {args.batch} ({args.shape}, bf16); prefill tok/s at {args.prefill_tokens:,} tokens and "
+                  "batch 1/64 beside it",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), random token ids, random cache contents",
-        "config": {"model": "Qwen2.5-3B shape", "layers": args.layers, "layers_full": SHAPE_3B["num_hidden_layers"],
+        "config": {"model": f"Qwen2.5-{args.shape} shape", "layers": args.layers, "layers_full": shape["num_hidden_layers"],
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "tied": True, "global_batch": args.batch, "seq_len": args.context, "new_tokens": W + K,
+                   "tied": bool(cfgd["tie_word_embeddings"]), "global_batch": args.batch, "seq_len": args.context, "new_tokens": W + K,
                    "page": page, "parallelism": "single GPU", "l2": f"inputs larger than L2 (weights {decode_bytes(cfgd, args.layers, 0, 0) / 1e9:.1f} GB/step)",
                    "bf16_gemm": matmul_backend.mode, "peaks": pk_src},
         "prefill": prefill,

@@ -137,15 +137,21 @@ class CacheManager:
         self.kv: List[Optional[torch.Tensor]] = [None] * len(layout.groups)
         self.states: List[Optional[torch.Tensor]] = [None] * len(layout.fixed_needs)
         if self.device is not None:
+            # one page more than the pool hands out: the rows that pad a batch write their keys and values there
             for g, grp in enumerate(layout.groups):
                 n = grp.need
                 self.kv[g] = torch.zeros(
-                    (len(grp.entries), num_pages, 2, n.num_kv_heads, page_size, n.head_dim),
+                    (len(grp.entries), num_pages + 1, 2, n.num_kv_heads, page_size, n.head_dim),
                     dtype=dtype, device=self.device)
             # one slot more than requests: the padding rows of a padded decode batch update that one
             for i, need in enumerate(layout.fixed_needs):
                 self.states[i] = torch.zeros((max_requests + 1,) + tuple(need.shape), dtype=need.dtype,
                                              device=self.device)
+
+    @property
+    def scratch_page(self) -> int:
+        """The page (of every group) that belongs to no request: rows that pad a batch write to it."""
+        return self.num_pages
 
     @property
     def scratch_slot(self) -> int:

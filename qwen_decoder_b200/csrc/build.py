@@ -34,7 +34,6 @@ LIBRARIES: Dict[str, str] = {
     "gemm_generic": "gemm_generic.cu",
     "gemm_skinny": "gemm_skinny.cu",
     "gemm_stream": "gemm_stream.cu",
-    "decode_stream": "decode_stream.cu",
     "gemm_tc5": "gemm_tc5.cu",
     "attention_generic": "attention_generic.cu",
     "attention_flash": "attention_flash.cu",

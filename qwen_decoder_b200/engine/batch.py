@@ -153,7 +153,8 @@ def validate(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: int,
 def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: CacheManager, lens, starts,
          slots, vocab_size: int, want_order: Optional[Sequence[int]] = None):
     """Write the step's arrays into the host buffer ``h`` (int32) at ``lay``'s places.  When ``lay``
-    is larger than the batch (a padded decode batch), the padding repeats entry 0.  ``want_order``: the
+    is larger than the batch (a padded decode batch), the padding repeats entry 0's token, position and
+    block table, and writes to the cache's scratch page and scratch state slot.  ``want_order``: the
     order of the entries in which their wanted rows are listed (default: as given)."""
     R = len(entries)
     T = sum(lens)
@@ -216,7 +217,9 @@ def fill(h: np.ndarray, lay: MetaLayout, entries: Sequence[StepEntry], cache: Ca
         put_arr = phys * ps + positions % ps
         h[so:so + T] = put_arr
         if lay.T > T:
-            h[so + T:so + lay.T] = put_arr[0]
+            # padding rows read what entry 0 reads, but what they compute may differ from entry 0's (a state of
+            # their own): their keys and values go to the page that belongs to no request
+            h[so + T:so + lay.T] = cache.scratch_page * ps
         h[bo:bo + lay.R * mb] = bt.reshape(-1)
     return cu, want
 

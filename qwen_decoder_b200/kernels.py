@@ -394,136 +394,6 @@ def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, b
     return part
 
 
-# ---------------------------------------------------------------- the products of a small decode step
-# csrc/decode_stream.cu: up to 8 tokens, the norm before a product and the residual add after it inside the
-# product's own launch
-DS_MAX_TOKENS = 8
-_U = ctypes.c_uint
-
-
-_ds_ctas: dict = {}
-_ds_splits: dict = {}
-
-
-def ds_ctas(k_resident: int) -> int:
-    """CTAs the streamer of csrc/decode_stream.cu runs when its resident token rows are ``k_resident`` elements
-    wide (two per SM while they fit beside two stages each, else one); 0 if that does not fit at all."""
-    key = (torch.cuda.current_device(), k_resident)
-    n = _ds_ctas.get(key)
-    if n is None:
-        n = _ds_ctas[key] = int(library("decode_stream").qd_decode_stream_ctas(_I(k_resident)))
-    return n
-
-
-def ds_pick_splits(N: int, K: int, resident_min: int = 0, cap: int = 32) -> int:
-    """Shares of K for a product whose shares are added up inside the launch: the number whose busiest CTA
-    streams least (rounds over its tiles x stages of its share); fewer shares win a tie.  ``resident_min``:
-    the resident rows are at least this wide whatever the share (another product of the same launch)."""
-    key = (torch.cuda.current_device(), N, K, resident_min, cap)
-    if key not in _ds_splits:
-        _ds_splits[key] = _ds_pick_splits(N, K, resident_min, cap)
-    return _ds_splits[key]
-
-
-def _ds_pick_splits(N: int, K: int, resident_min: int, cap: int) -> int:
-    tiles, chunks = (N + 15) // 16, (K + 1023) // 1024
-    best = (None, 1)
-    for sp in range(1, min(chunks, cap) + 1):
-        widest = max(chunks * (i + 1) // sp - chunks * i // sp for i in range(sp))
-        ctas = ds_ctas(max(resident_min, min(K, widest * 1024)))
-        if ctas < sp:
-            continue
-        cost = -(-tiles // max(1, min(ctas // sp, tiles))) * widest
-        if best[0] is None or cost < best[0]:
-            best = (cost, sp)
-    return best[1]
-
-
-def ds_supported(T: int, *weights: torch.Tensor) -> bool:
-    return (1 <= T <= DS_MAX_TOKENS and all(w.dtype == torch.bfloat16 and w.is_cuda and w.is_contiguous()
-                                            and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0 for w in weights)
-            and all(ds_ctas(w.shape[1]) > 0 for w in weights))
-
-
-def ds_gemm(w: torch.Tensor, T: int, *, x: Optional[torch.Tensor] = None, resid_in: Optional[torch.Tensor] = None,
-            norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
-            add_to: Optional[torch.Tensor] = None, tickets: Optional[torch.Tensor] = None) -> None:
-    """Y = X W^T for T <= 8 tokens.  X is either ``x`` (bfloat16 rows) or the RMSNorm of rows of the float32
-    residual sum ``resid_in`` (``norm_w``, ``eps``; row t is ``rows[t]`` or t).  Y goes (+ ``bias``) to ``out``
-    (bfloat16 or float32), or is added to ``add_to`` (float32 [T, N]; ``tickets``: int32 zeros, one per 16
-    columns, left zero)."""
-    N, K = w.shape
-    _contig(w, "w")
-    pro = 0 if x is not None else 1
-    if pro == 0:
-        assert x.dtype == torch.bfloat16 and x.shape == (T, K) and x.stride(1) == 1
-    else:
-        assert resid_in.dtype == torch.float32 and resid_in.shape[1] == K and resid_in.is_contiguous()
-        assert norm_w.dtype == torch.float32 and norm_w.numel() == K
-        assert rows is None or (rows.dtype == torch.int32 and rows.numel() == T)
-    part = None
-    splits = 1
-    if add_to is not None:
-        assert add_to.dtype == torch.float32 and add_to.shape == (T, N) and add_to.is_contiguous()
-        splits = ds_pick_splits(N, K)
-        if splits > 1:
-            assert tickets is not None and tickets.dtype == torch.int32 and tickets.numel() >= (N + 15) // 16
-            part = torch.empty((splits, T, N), dtype=torch.float32, device=w.device)
-        epi = 3
-    else:
-        assert out.shape == (T, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
-        epi = 0
-    _check(library("decode_stream").qd_ds_gemm(
-        _ptr(w), _I(N), _I(K), _I(T), _I(splits), _I(pro), _ptr(x), _LL(x.stride(0) if x is not None else 0),
-        _ptr(resid_in), _ptr(norm_w), _F(eps), _ptr(rows), _I(epi), _ptr(bias), _ptr(out),
-        _LL(out.stride(0) if out is not None else 0), _I(1 if out is not None and out.dtype == torch.float32 else 0),
-        _ptr(part), _ptr(add_to), _ptr(tickets), _stream()), "ds_gemm")
-
-
-def ds_qkv_supported(H: int, G: int, d: int, rotary_dim: int, pairing: int) -> bool:
-    """What the q/k/v product with rotation and cache write in its epilogue takes."""
-    return d % 16 == 0 and rotary_dim % 2 == 0 and rotary_dim <= d and (pairing == 0 or rotary_dim in (0, d))
-
-
-def ds_qkv(w: torch.Tensor, T: int, resid_in: torch.Tensor, norm_w: torch.Tensor, eps: float,
-           bias: Optional[torch.Tensor], q_out: torch.Tensor, kv: Optional[torch.Tensor], positions: torch.Tensor,
-           slot_map: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], H: int, G: int,
-           d: int, page_size: int, rotary_dim: int, pairing: int, write_kv: bool) -> None:
-    """q, k, v of T <= 8 tokens from the residual sum in one launch: RMSNorm, product with w [(H+2G)d, K], bias,
-    rotation of q and k, k and v to their cache slots, q to ``q_out`` [T, H d] bfloat16."""
-    N, K = w.shape
-    assert N == (H + 2 * G) * d and resid_in.dtype == torch.float32 and resid_in.shape == (T, K)
-    assert q_out.dtype == torch.bfloat16 and q_out.shape == (T, H * d) and q_out.is_contiguous()
-    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
-    if write_kv:
-        assert kv.dtype == torch.bfloat16 and tuple(kv.shape[1:]) == (2, G, page_size, d) and kv.is_contiguous()
-    _contig(w, "w"); _contig(resid_in, "resid_in")
-    _check(library("decode_stream").qd_ds_qkv(
-        _ptr(w), _I(K), _I(T), _ptr(resid_in), _ptr(norm_w), _F(eps), _ptr(bias), _ptr(q_out), _ptr(kv),
-        _ptr(positions), _ptr(slot_map), _ptr(cos), _ptr(sin), _I(H), _I(G), _I(d), _I(page_size), _I(rotary_dim),
-        _I(pairing), _I(1 if write_kv else 0), _stream()), "ds_qkv")
-
-
-def ds_ffn(w_gate_up: torch.Tensor, w_down: torch.Tensor, T: int, resid: torch.Tensor, norm_w: torch.Tensor,
-           eps: float, tickets: torch.Tensor, barrier: torch.Tensor) -> None:
-    """resid += (silu(h Wg^T) * (h Wu^T)) Wd^T with h = RMSNorm(resid), for T <= 8 tokens, in one launch
-    (gate/up, a grid barrier, down, the shares of the down projection added up by the last CTA of each tile).
-    ``tickets`` (int32 zeros, one per 16 columns of resid) and ``barrier`` (two int32 zeros) belong to the
-    caller and are left as found."""
-    D, F = w_down.shape
-    assert w_gate_up.shape == (2 * F, D) and resid.dtype == torch.float32 and resid.shape == (T, D)
-    assert barrier.dtype == torch.int32 and barrier.numel() >= 2 and tickets.dtype == torch.int32
-    _contig(w_gate_up, "w_gate_up"); _contig(w_down, "w_down"); _contig(resid, "resid")
-    splits = ds_pick_splits(D, F, resident_min=D)
-    assert tickets.numel() >= (D + 15) // 16
-    act = torch.empty((T, F), dtype=torch.bfloat16, device=resid.device)
-    part = torch.empty((splits, T, D), dtype=torch.float32, device=resid.device) if splits > 1 else None
-    _check(library("decode_stream").qd_ds_ffn(
-        _ptr(w_gate_up), _ptr(w_down), _I(D), _I(F), _I(T), _ptr(resid), _ptr(norm_w), _F(eps), _ptr(act), _ptr(part),
-        _I(splits), _ptr(tickets), _ptr(barrier), _stream()), "ds_ffn")
-
-
 # ------------------------------------------------------------------- attention
 def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv: torch.Tensor,
                             block_table: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
@@ -691,7 +561,6 @@ def prefill_attention_tc5_status() -> int:
 
 # library -> (its status function, its wait probe): the kernels with bounded waits on mbarriers or a grid barrier
 _STATUS = {"gemm_stream": ("qd_gemm_stream_status", "qd_gemm_stream_wait_probe"),
-           "decode_stream": ("qd_decode_stream_status", "qd_decode_stream_wait_probe"),
            "gemm_tc5": ("qd_gemm_tc5_status", "qd_gemm_tc5_wait_probe"),
            "attention_tc5": ("qd_prefill_attention_tc5_status", "qd_prefill_attention_tc5_wait_probe"),
            "attention_flash": ("qd_decode_attention_tma_status", "qd_decode_attention_tma_wait_probe")}

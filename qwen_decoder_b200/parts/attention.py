@@ -44,7 +44,6 @@ class GQAttention(Mixer):
                                         (f"{prefix}k_proj", num_kv_heads * head_dim),
                                         (f"{prefix}v_proj", num_kv_heads * head_dim)], bias=qkv_bias)
         self.out = Linear(num_heads * head_dim, [(f"{prefix}o_proj", hidden_size)], bias=out_bias)
-        self._tickets = None        # one word per 16 output columns for the output projection's in-kernel sum
 
     def cache_need(self):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
@@ -66,42 +65,6 @@ class GQAttention(Mixer):
                 "rotary_dim": pos.rotary_dim if pos is not None else 0,
                 "pairing": pos.pairing_code if pos is not None else 0,
                 "wqkv": self.qkv.weight, "bqkv": self.qkv.bias, "wo": self.out.weight}
-
-    def forward_fused(self, norm, stream, ctx, cache: PagedCacheView) -> bool:
-        """A decode step of up to 8 tokens in three launches: RMSNorm + q/k/v product + bias + rotation + cache
-        write; split-KV attention over the pages; output projection added to the residual sum."""
-        from .rotary import Rotary
-        H, G, d = self.num_heads, self.num_kv_heads, self.head_dim
-        pos = self.position
-        T = ctx.num_tokens
-        if not (_DECODE_STREAM and ctx.all_decode and matmul_backend.mode == "auto" and hasattr(norm, "pending")
-                and self.out.bias is None and (pos is None or type(pos) is Rotary)
-                and self.qkv.weight.dtype == torch.bfloat16 and cache.kv.dtype == torch.bfloat16
-                and kernels.ds_supported(T, self.qkv.weight, self.out.weight)):
-            return False
-        rd, pairing = (pos.rotary_dim, pos.pairing_code) if pos is not None else (0, 0)
-        ps, window = cache.group.page_size, self.window or 0
-        if not (kernels.ds_qkv_supported(H, G, d, rd, pairing) and kernels.flash_decode_supported(torch.bfloat16, H, G, d, ps)):
-            return False
-        pn = norm.pending(stream)
-        dev = stream.x.device
-        q = torch.empty((T, H * d), dtype=torch.bfloat16, device=dev)
-        kernels.ds_qkv(self.qkv.weight, T, pn.x, pn.weight, pn.eps, self.qkv.bias, q, cache.kv, ctx.positions,
-                       cache.group.slot_map, pos.cos if pos is not None else None, pos.sin if pos is not None else None,
-                       H, G, d, ps, rd, pairing, cache.write)
-        attn = torch.empty((T, H * d), dtype=torch.bfloat16, device=dev)
-        kernels.decode_attention(q, q.stride(0), attn, cache.kv, cache.group.block_table, ctx.token_request,
-                                 ctx.positions, T, H, G, d, ps, self.scale, window,
-                                 decode_splits(T * G, min(ctx.max_context, window or ctx.max_context)))
-        if self._tickets is None:
-            self._tickets = torch.zeros((self.hidden_size + 15) // 16, dtype=torch.int32, device=dev)
-        kernels.ds_gemm(self.out.weight, T, x=attn, add_to=stream.x, tickets=self._tickets)
-        matmul_backend.counters["own"] += 2
-        return True
-
-    def reset_after_fault(self) -> None:
-        if self._tickets is not None:
-            self._tickets.zero_()
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
         H, G, d = self.num_heads, self.num_kv_heads, self.head_dim
@@ -163,8 +126,6 @@ class GQAttention(Mixer):
 import os as _os
 _TARGET_CTAS = int(_os.environ.get("QD_DECODE_ATTN_CTAS", "148"))
 _DECODE_ROPE = _os.environ.get("QD_DECODE_ROPE", "1") != "0"
-# decode steps of up to 8 tokens: the norm before and the residual add after each product inside its launch
-_DECODE_STREAM = _os.environ.get("QD_DECODE_STREAM", "1") != "0"
 _PREFILL_TC5 = _os.environ.get("QD_PREFILL_TC5", "1") != "0"      # prompt portions on tcgen05 where its sizes allow
 _ROPE_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ROPE_CTAS", "148"))
 

@@ -88,21 +88,10 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         raise NotImplementedError
 
-    def forward_fused(self, norm, stream: "ResidualStream", ctx, cache) -> bool:
-        """Optional fast path: run the norm before this part and the residual add after it inside the part's
-        own kernels (``norm.pending(stream)`` hands the norm over; the result is added to ``stream.x`` in
-        place).  Return False, the default, to be called the usual way: ``forward`` on the normalised rows,
-        its result pushed on the stream."""
-        return False
-
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
-
-    def forward_fused(self, norm, stream: "ResidualStream", ctx) -> bool:
-        """As ``Mixer.forward_fused``."""
-        return False
 
 
 class Norm(Part):

@@ -56,10 +56,7 @@ class PreNormBlock(Block):
         return out
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
-        # a part may take the norm before it and the add after it into its own kernels (small decode steps)
-        if not self.mixer.forward_fused(self.input_norm, stream, ctx, cache):
-            h = self.input_norm.forward(stream, self.dtype)
-            stream.push(self.mixer.forward(h, ctx, cache))
-        if not self.feed_forward.forward_fused(self.post_mixer_norm, stream, ctx):
-            h = self.post_mixer_norm.forward(stream, self.dtype)
-            stream.push(self.feed_forward.forward(h, ctx))
+        h = self.input_norm.forward(stream, self.dtype)
+        stream.push(self.mixer.forward(h, ctx, cache))
+        h = self.post_mixer_norm.forward(stream, self.dtype)
+        stream.push(self.feed_forward.forward(h, ctx))

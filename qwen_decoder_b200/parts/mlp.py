@@ -25,7 +25,6 @@ class SwiGLU(FeedForward):
                                             (f"{prefix}up_proj", intermediate_size)], bias=False)
         self.down = Linear(intermediate_size, [(f"{prefix}down_proj", hidden_size)], bias=False)
         self._barrier = None
-        self._tickets = None
 
     def tensor_specs(self) -> List[TensorSpec]:
         return self.gate_up.tensor_specs() + self.down.tensor_specs()
@@ -40,26 +39,8 @@ class SwiGLU(FeedForward):
 
     def reset_after_fault(self) -> None:
         """A launch whose grid barrier ran out may have left arrivals counted: start from zero again."""
-        for words in (self._barrier, self._tickets):
-            if words is not None:
-                words.zero_()
-
-    def forward_fused(self, norm, stream, ctx) -> bool:
-        """A decode step of up to 8 tokens: RMSNorm, gate/up, SwiGLU, down and the residual add in one launch."""
-        from .attention import _DECODE_STREAM
-        T = ctx.num_tokens
-        if not (_DECODE_STREAM and ctx.all_decode and matmul_backend.mode == "auto" and hasattr(norm, "pending")
-                and kernels.ds_supported(T, self.gate_up.weight, self.down.weight)
-                and self.intermediate_size % 8 == 0):
-            return False
-        pn = norm.pending(stream)
-        if self._barrier is None:       # this layer's own words (zero once; each launch leaves them zero)
-            self._barrier = torch.zeros(2, dtype=torch.int32, device=stream.x.device)
-        if self._tickets is None:
-            self._tickets = torch.zeros((self.hidden_size + 15) // 16, dtype=torch.int32, device=stream.x.device)
-        kernels.ds_ffn(self.gate_up.weight, self.down.weight, T, pn.x, pn.weight, pn.eps, self._tickets, self._barrier)
-        matmul_backend.counters["own"] += 1
-        return True
+        if self._barrier is not None:
+            self._barrier.zero_()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if matmul_backend.mode == "auto" and kernels.ffn_stream_supported(x, self.gate_up.weight, self.down.weight):

@@ -20,7 +20,6 @@ from ..config.spec import ModelSpec, PartSpec
 from ..weights.loader import TensorSource, TensorSpec
 from .base import PagedCacheView, ResidualStream, StateCacheView
 from .linear import Linear
-from . import matmul_backend as _matmul
 # importing the part modules registers them
 from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, rotary as _rotary  # noqa: F401
 
@@ -141,14 +140,6 @@ class DecoderModel:
             self.layers[e.layer].forward(stream, ctx, self._cache_view(i, ctx))
         if ctx.num_wanted == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        w = self.lm_head.weight
-        if hasattr(self.final_norm, "pending") and w.dtype == torch.bfloat16 and self.lm_head.bias is None \
-                and _matmul.mode == "auto" and kernels.ds_supported(ctx.num_wanted, w):
-            # few wanted rows: the final norm inside the output projection's launch
-            pn = self.final_norm.pending(stream, rows=ctx.logit_rows)
-            logits = torch.empty((ctx.num_wanted, self.vocab_size), dtype=torch.float32, device=self.device)
-            kernels.ds_gemm(w, ctx.num_wanted, resid_in=pn.x, norm_w=pn.weight, eps=pn.eps, rows=pn.rows, out=logits)
-            return logits
         h = self.final_norm.forward(stream, self.dtype, rows=ctx.logit_rows)
         return self.lm_head.forward(h, out_dtype=torch.float32)
 

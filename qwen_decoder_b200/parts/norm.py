@@ -7,7 +7,6 @@ still pending on the stream, which the reference does in a separate residual_ker
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import List, Optional
 
 import torch
@@ -16,16 +15,6 @@ from .. import kernels
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
 from .base import Norm, ResidualStream
-
-
-@dataclass
-class PendingRMSNorm:
-    """An RMSNorm that has not run: the rows of ``x`` (float32 residual sum, nothing pending on it) that a
-    product's kernel will normalise in its own prologue instead of a launch of the norm's."""
-    x: torch.Tensor
-    weight: torch.Tensor
-    eps: float
-    rows: Optional[torch.Tensor] = None
 
 
 @register_part("norm", "rmsnorm")
@@ -45,12 +34,6 @@ class RMSNorm(Norm):
 
     def native_params(self) -> Optional[dict]:
         return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
-
-    def pending(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> PendingRMSNorm:
-        """This norm as something a product's kernel applies itself (``kernels.ds_*``): the stream's pending
-        branch output, if any, is added first; nothing is normalised here."""
-        stream.flush()
-        return PendingRMSNorm(stream.x, self.weight, self.eps, rows)
 
     def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

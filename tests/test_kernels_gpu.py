@@ -571,7 +571,7 @@ def test_feed_forward_in_one_launch(shape):
 
 # ---- a wait that runs out: the kernel ends, the status word says so, the host raises
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["gemm_stream", "decode_stream", "gemm_tc5", "attention_tc5", "attention_flash"])
+@pytest.mark.parametrize("name", ["gemm_stream", "gemm_tc5", "attention_tc5", "attention_flash"])
 def test_a_wait_that_runs_out_ends_the_kernel_and_is_reported_once(name):
     """Each library's own wait function, on an mbarrier nobody arrives at, with a limit of a few thousand
     polls: the launch returns, the library's status word is set, ``check_status`` raises once, and the
@@ -610,7 +610,7 @@ def test_a_grid_barrier_that_runs_out_is_reported_and_repaired(tmp_path):
     runner.check_status()
     ff._barrier[0] = 1 << 30                    # arrivals counted from here never reach the grid's size
     runner.step([StepEntry(rc, seq[8:9], [0])])
-    with pytest.raises(kernels.KernelError, match="decode_stream"):
+    with pytest.raises(kernels.KernelError, match="gemm_stream"):
         runner.check_status()
     assert ff._barrier.tolist() == [0, 0]
     logits = runner.step([StepEntry(rc, seq[9:10], [0])])
@@ -635,136 +635,4 @@ def test_generate_raises_when_a_wait_ran_out(tmp_path):
     kernels.wait_probe("gemm_stream", 4096)
     with pytest.raises(kernels.KernelError):
         eng.generate([[4, 5, 6]], SamplingParams(max_new_tokens=4, ignore_eos=True))
-    kernels.check_status()
-
-
-# ---- the products of a small decode step with the norm before and the add after them inside (csrc/decode_stream.cu)
-def _plain_rmsnorm(x, w, eps):
-    return plain_model.rmsnorm(x.double(), w.double(), eps)
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(8, 2048, 2048), (5, 2560, 2048), (1, 96, 264), (7, 3584, 18944), (3, 1000, 96),
-                                   (8, 5120, 5120), (2, 176, 1400)])
-def test_decode_stream_product_with_norm_before_and_add_after(shape):
-    """Y = X W^T with X given as bfloat16 rows or as rows of the float32 residual sum that the kernel normalises
-    itself (all rows, or gathered ones), and Y stored (bfloat16 with bias, float32) or added to the residual sum
-    through the in-kernel sum over shares of K; several launches in a row (the tickets are left as found)."""
-    from qwen_decoder_b200 import kernels
-    T, N, K = shape
-    g = torch.Generator().manual_seed(N + K)
-    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    xb = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
-    assert kernels.ds_supported(T, w)
-    w64, eps = w.double().cpu(), 3e-6
-    # rows in, stored with a bias
-    bias = torch.randn(N, generator=g).to(DEV)
-    out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    kernels.ds_gemm(w, T, x=xb, out=out, bias=bias)
-    close(out, xb.double().cpu() @ w64.t() + bias.double().cpu(), torch.bfloat16)
-    # normalised rows of a larger residual sum (gathered), float32 out
-    resid = torch.randn(T + 3, K, generator=g).to(DEV) * 2.0
-    nw = (1.0 + 0.1 * torch.randn(K, generator=g)).to(DEV)
-    rows = torch.tensor([(3 * t + 1) % (T + 3) for t in range(T)], dtype=torch.int32, device=DEV)
-    h64 = _plain_rmsnorm(resid.cpu()[rows.cpu().long()], nw.cpu(), eps)
-    out32 = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
-    kernels.ds_gemm(w, T, resid_in=resid, norm_w=nw, eps=eps, rows=rows, out=out32)
-    want = h64.to(torch.bfloat16).double() @ w64.t()
-    close(out32, want, TENSOR_F32)
-    assert (out32.double().cpu() - h64 @ w64.t()).abs().max() <= 1e-2 * float(want.abs().max())
-    # rows in, added to the residual sum: three times, the sum must grow by the same product each time
-    if N == K or True:
-        target = torch.randn(T, N, generator=g).to(DEV)
-        before = target.clone()
-        tickets = torch.zeros((N + 15) // 16, dtype=torch.int32, device=DEV)
-        prod = xb.double().cpu() @ w64.t()
-        for i in range(3):
-            kernels.ds_gemm(w, T, x=xb, add_to=target, tickets=tickets)
-            err = (target.double().cpu() - (before.double().cpu() + (i + 1) * prod)).abs().max()
-            assert err <= 2e-5 * (i + 1) * float(prod.abs().max()) + 1e-6, (i, float(err))
-        assert int(tickets.abs().sum()) == 0
-    kernels.check_status()
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("cfg", [(16, 2, 128, 2048, 16, "half"), (16, 2, 128, 2048, 16, "adjacent"),
-                                 (28, 4, 128, 3584, 16, "half"), (6, 2, 48, 72, 32, "adjacent"),
-                                 (4, 1, 32, 128, 32, "half"), (5, 5, 96, 480, 16, "half"), (4, 2, 16, 64, 16, "adjacent")])
-def test_decode_stream_qkv_with_rotation_and_cache_write(cfg):
-    """RMSNorm, q/k/v product, bias, rotation by position and the cache write in one launch against the plain
-    formulas; tokens at different positions and slots; with write_kv off the cache stays untouched."""
-    from qwen_decoder_b200 import kernels
-    from qwen_decoder_b200.parts.rotary import Rotary
-    H, G, d, D, page_size, pairing = cfg
-    base, eps, T = 50000.0, 1e-5, 7
-    g = torch.Generator().manual_seed(H * d + D)
-    W = (H + 2 * G) * d
-    w = (torch.randn(W, D, generator=g) * 0.06).to(torch.bfloat16).to(DEV)
-    bias = (torch.randn(W, generator=g) * 0.3).to(DEV)
-    resid = (torch.randn(T, D, generator=g) * 1.5).to(DEV)
-    nw = (1.0 + 0.1 * torch.randn(D, generator=g)).to(DEV)
-    rot = Rotary(d, d, base, pairing)
-    rot.prepare(900, torch.device(DEV))
-    pos = torch.tensor([0, 1, 15, 16, 333, 640, 899], dtype=torch.int32)
-    n_pages = 64
-    slots = torch.tensor([5, 17 * page_size + 1, 3 * page_size + page_size - 1, 40 * page_size, 63 * page_size + 2,
-                          9 * page_size + 7, 2], dtype=torch.int32)
-    kv0 = torch.randn(n_pages, 2, G, page_size, d, generator=g).to(torch.bfloat16)
-    h = _plain_rmsnorm(resid.cpu(), nw.cpu(), eps).to(torch.bfloat16).double()
-    qkv = h @ w.double().cpu().t() + bias.double().cpu()
-    wq = plain_model.rope(qkv[:, :H * d], pos, H, d, base, pairing)
-    wk = plain_model.rope(qkv[:, H * d:(H + G) * d], pos, G, d, base, pairing)
-    wv = qkv[:, (H + G) * d:]
-    for write in (True, False):
-        kv = kv0.clone().to(DEV)
-        q = torch.full((T, H * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-        kernels.ds_qkv(w, T, resid, nw, eps, bias, q, kv, pos.to(DEV), slots.to(DEV), rot.cos, rot.sin, H, G, d,
-                       page_size, d, rot.pairing_code, write)
-        close(q, wq, torch.bfloat16)
-        kvc = kv.cpu()
-        if not write:
-            assert torch.equal(kvc, kv0)
-            continue
-        touched = torch.zeros(n_pages, page_size, dtype=torch.bool)
-        for i in range(T):
-            page, off = int(slots[i]) // page_size, int(slots[i]) % page_size
-            close(kvc[page, 0, :, off, :].reshape(-1), wk[i], torch.bfloat16)
-            close(kvc[page, 1, :, off, :].reshape(-1), wv[i], torch.bfloat16, scale=float(wv.abs().max()))
-            touched[page, off] = True
-        keep = ~touched[:, None, None, :, None].expand_as(kvc)
-        assert torch.equal(kvc[keep], kv0[keep])            # nothing else was written
-    kernels.check_status()
-
-
-@pytest.mark.gpu
-@pytest.mark.parametrize("shape", [(8, 2048, 11008), (5, 96, 264), (1, 64, 176), (7, 3584, 18944), (3, 128, 1400),
-                                   (6, 5120, 3072)])
-def test_decode_stream_feed_forward_on_the_residual_sum(shape):
-    """resid += down(silu(gate(h)) * up(h)) with h = RMSNorm(resid), one launch, against float64; several times
-    in a row (barrier and tickets must be left ready for the next launch)."""
-    from qwen_decoder_b200 import kernels
-    T, D, F = shape
-    g = torch.Generator().manual_seed(D + F)
-    resid = (torch.randn(T, D, generator=g) * 1.5).to(DEV)
-    nw = (1.0 + 0.1 * torch.randn(D, generator=g)).to(DEV)
-    w1 = (torch.randn(2 * F, D, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    w2 = (torch.randn(D, F, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    assert kernels.ds_supported(T, w1, w2)
-    barrier = torch.zeros(2, dtype=torch.int32, device=DEV)
-    tickets = torch.zeros((D + 15) // 16, dtype=torch.int32, device=DEV)
-    eps = 2e-6
-    x64 = resid.double().cpu()
-    for i in range(3):
-        h = _plain_rmsnorm(x64, nw.cpu(), eps).to(torch.bfloat16).double()
-        gu = h @ w1.double().cpu().t()
-        act = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]).to(torch.bfloat16).double()
-        delta = act @ w2.double().cpu().t()
-        kernels.ds_ffn(w1, w2, T, resid, nw, eps, tickets, barrier)
-        got = resid.double().cpu()
-        assert torch.isfinite(got).all()
-        # h and the activation are rounded to bfloat16 in both; a rounding that falls the other way moves one
-        # term by 2^-9 of itself
-        assert (got - (x64 + delta)).abs().max() <= 4e-3 * float(delta.abs().max()), i
-        x64 = got
-    assert int(tickets.abs().sum()) == 0 and int(barrier[0]) == 0
     kernels.check_status()
