@@ -27,7 +27,7 @@ class Engine:
                  max_prefill_tokens_per_step: int = 512, max_total_tokens: int = 4096,
                  page_size: int = 16, num_pages: Optional[int] = None, kv_memory_fraction: float = 0.8,
                  max_positions: Optional[int] = None, use_graphs: bool = True,
-                 enable_prefix_cache: bool = False, run_ahead: bool = True):
+                 enable_prefix_cache: bool = False, run_ahead: bool = True, record_steps: bool = False):
         """``model``: a folder with config.json and model.safetensors; or give ``config`` (a typed
         configuration) and ``random_seed`` for random weights made on the device.
 
@@ -41,7 +41,10 @@ class Engine:
         part (the reference's generate_continuous argument, decoder.h:148-154).
         ``run_ahead``: while a decode step runs on the device, the next one is already planned and
         launched with the tokens it needs taken from the device; the host reads a step's tokens one
-        step late.  The tokens are the same; a request that ends on a stop token costs one wasted row."""
+        step late.  The tokens are the same; a request that ends on a stop token costs one wasted row.
+        ``record_steps``: keep one record per step (``step_records()``): tokens, how many of them prompt and
+        decoded tokens, requests, device time by CUDA events, free pages, queue lengths -- what the reference
+        prints per step (decoder.cpp:178-185) and more; each step is also an NVTX range then."""
         self.max_prefill_len = max_prefill_len
         make = dict(dtype=dtype, device=device, page_size=page_size, max_requests=max_batch,
                     max_positions=max_positions, use_graphs=use_graphs, prefix_cache=enable_prefix_cache)
@@ -67,6 +70,7 @@ class Engine:
         self._host_tokens = [torch.empty(self.scheduler.max_batch, dtype=torch.int32, pin_memory=True)
                              for _ in range(2)]
         self._turn = 0
+        self._records: Optional[list] = [] if record_steps else None
 
     # ---- streaming use -----------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -90,14 +94,17 @@ class Engine:
                    for e in plan.entries]
         sampling = [e.request for e in plan.entries if e.samples]
         flight = _InFlight(plan, len(sampling), device_tokens is not None)
+        rec = self._begin_record(plan, device_tokens is not None)
         if not sampling:
             self.runner.step(entries, ensure_pages=False)
+            self._end_record(rec)
             return flight
         ahead = 1 if device_tokens is not None else 0       # a step planned ahead samples one token later
         _, ids = self.runner.step(entries, ensure_pages=False, device_tokens=device_tokens, sampling=(
             [r.params.temperature for r in sampling], [r.params.top_k for r in sampling],
             [uniform_draw(r.params.seed, r.sample_key, len(r.output) + ahead) if r.params.temperature else 0.0
              for r in sampling]))
+        self._end_record(rec)
         self._turn ^= 1
         flight.host = self._host_tokens[self._turn][:len(sampling)]
         flight.host.copy_(ids, non_blocking=True)
@@ -150,6 +157,39 @@ class Engine:
             self.step()
         self.runner.check_status()
         return [r.output for r in reqs]
+
+    # ---- per-step records ------------------------------------------------------
+    def _begin_record(self, plan: StepPlan, ahead: bool) -> Optional[dict]:
+        if self._records is None:
+            return None
+        decode = sum(1 for e in plan.entries if len(e.tokens) == 1 and e.request.output)
+        rec = {"step": len(self._records), "tokens": plan.num_tokens, "decode_tokens": decode,
+               "prompt_tokens": plan.num_tokens - decode, "requests": len(plan.entries),
+               "prompt_requests": len(plan.entries) - decode, "planned_ahead": ahead,
+               "preempted": len(plan.preempted), "running": len(self.scheduler.running),
+               "waiting": len(self.scheduler.waiting), "pages_free": self.runner.cache.free_pages(),
+               "_events": (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))}
+        torch.cuda.nvtx.range_push(f"step {rec['step']}: {rec['prompt_tokens']} prompt + {decode} decode tokens")
+        rec["_events"][0].record()
+        return rec
+
+    def _end_record(self, rec: Optional[dict]) -> None:
+        if rec is None:
+            return
+        rec["_events"][1].record()
+        torch.cuda.nvtx.range_pop()
+        self._records.append(rec)
+
+    def step_records(self) -> List[dict]:
+        """The records kept with ``record_steps`` (device times read now: waits for the last recorded step)."""
+        out = []
+        for rec in self._records or []:
+            if "_events" in rec:
+                e0, e1 = rec.pop("_events")
+                e1.synchronize()
+                rec["ms"] = round(e0.elapsed_time(e1), 4)
+            out.append(rec)
+        return out
 
     @property
     def stats(self) -> dict:

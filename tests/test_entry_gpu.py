@@ -113,6 +113,68 @@ def test_command_line(folders):
         assert len(got) == 6 and check_greedy(cfg, w, p, got, "float32") >= 4
 
 
+def test_command_line_options_beyond_the_reference(folders, tmp_path):
+    """--random-weights on a folder with config.json only, prompts from --prompt-ids, a file and --random-prompts,
+    --stats: a line per step in the reference's words, and prompt / decode tokens per second apart."""
+    import json
+    import shutil
+    only_config = tmp_path / "cfg"
+    only_config.mkdir()
+    shutil.copy(os.path.join(folders["A"], "config.json"), only_config / "config.json")
+    pf = tmp_path / "prompts.txt"
+    pf.write_text("5 6 7 8 9\n10,11,12\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "decoder_main"), str(only_config), "4", "4096", "8",
+                        "64", "0", "--random-weights", "--weights-seed", "3", "--prompt-ids", "1,2,3", "--prompt-file",
+                        str(pf), "--random-prompts", "2", "--len", "3:20", "--max-new-tokens", "5", "--num-pages", "24",
+                        "--ignore-eos", "--stats"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert len(lines) == 5 and all(len(l.split(")", 1)[1].split()) == 5 for l in lines)
+    steps = [l for l in r.stderr.splitlines() if l.startswith("step ")]
+    assert steps and all("total_tokens=" in l and "n_decode=" in l and "prefill_tokens=" in l and "ms=" in l for l in steps)
+    # prompts are cut under the budget of 8 prompt tokens a step
+    assert all(int(l.split("prefill_tokens=")[1].split()[0]) <= 8 for l in steps)
+    assert any(l.startswith("prompt: ") and "decode: " in l and "tokens/s" in l for l in r.stderr.splitlines())
+    # the same seed gives the same weights: the same tokens again
+    r2 = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "decoder_main"), str(only_config), "4", "4096", "64",
+                         "64", "0", "--random-weights", "--weights-seed", "3", "--prompt-ids", "1,2,3",
+                         "--max-new-tokens", "5", "--num-pages", "24", "--ignore-eos"], capture_output=True, text=True,
+                        timeout=600)
+    assert r2.returncode == 0, r2.stderr
+    assert [l for l in r2.stdout.splitlines() if l.startswith("[")][0] == lines[0]
+
+
+def test_step_records(folders):
+    from qwen_decoder_b200.engine import Engine, SamplingParams
+    cfg, _ = plain_model.read_folder(folders["A"])
+    eng = Engine(folders["A"], dtype="bfloat16", num_pages=32, max_prefill_tokens_per_step=16, record_steps=True)
+    prompts = prompts_for(cfg, [40, 5, 23], seed=8)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True))
+    recs = eng.step_records()
+    assert sum(r["prompt_tokens"] for r in recs) == 68 and sum(r["decode_tokens"] for r in recs) == 3 * 5
+    assert all(r["prompt_tokens"] <= 16 and r["ms"] > 0 and r["tokens"] == r["prompt_tokens"] + r["decode_tokens"]
+               for r in recs)
+    assert any(r["planned_ahead"] for r in recs) and recs[-1]["pages_free"][0] < 32
+    assert [len(o) for o in outs] == [6, 6, 6]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program_with_pages_of_32(folders, dtype, tmp_path):
+    """Tiny B's page of 32 tokens through the program itself (--page-size), four requests live at most."""
+    cfg, w = plain_model.read_folder(folders["B"])
+    seqs = prompts_for(cfg, [1, 9, 64, 130, 70], seed=4)
+    want = [plain_model.forward(cfg, w, s).numpy() for s in seqs]
+    tr = trace_tools.mixed(seqs, max_tokens=320, seed=2)
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders["B"], "--dtype",
+                        dtype, "--out", str(out), "--max-tokens", "320", "--page-size", "32", "--max-live", "4"],
+                       input=tr.lines(), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.splitlines() == [f"done {s['step']}" for s in tr.steps]
+    got = trace_tools.read_outputs(tr, str(out), cfg["vocab_size"])
+    trace_tools.compare(tr, got, want, 1e-5 if dtype == "float32" else 3e-2)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(folders, dtype, tmp_path):
     """bin/trace_run as a separate process: steps on stdin, one `done` line per step, .f32 files."""
