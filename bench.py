@@ -123,36 +123,62 @@ def prefill_flops(cfg, layers, T):
 
 
 def serve(args):
-    """A whole serving run through the entry point at the 3B shape: ``--batch`` requests arrive at once, each
-    with a random prompt of ``--context`` tokens, and generate ``--steps`` tokens each (greedy, no stop token);
-    continuous batching, prompt portions under the default budget mixed with decode steps.  Wall clock."""
+    """A whole serving run through the entry point: ``--batch`` requests arrive at once, each with a random
+    prompt of ``--context`` tokens (or, with ``--context-range A:B``, of a length drawn uniformly from [A, B])
+    and generate ``--steps`` tokens each (greedy, no stop token); continuous batching, prompt portions of at
+    most ``--prefill-budget`` tokens a step mixed with decode tokens (the reference's loop: decoder.cpp:35-239,
+    its budget decoder.cpp:90-96).  Wall clock of the second round, and from the engine's step records the
+    device time of its steps: prompt and output tokens per second and the spread of the step times."""
+    import random
     import torch
     from qwen_decoder_b200 import kernels
     from qwen_decoder_b200.config import Qwen2Config
     from qwen_decoder_b200.engine import Engine, SamplingParams
-    cfg = Qwen2Config.from_dict(dict(SHAPES[args.shape], num_hidden_layers=args.layers))
-    n, plen, new = args.batch, args.context, args.steps
+    shape = SHAPES[args.shape]
+    cfg = Qwen2Config.from_dict(dict(shape, num_hidden_layers=args.layers))
+    n, new = args.batch, args.steps
+    lo, hi = args.context, args.context
+    if args.context_range:
+        a, _, b = args.context_range.partition(":")
+        lo, hi = int(a), int(b or a)
     page = args.page_size
+    rng = random.Random(3)
+    lengths = [[rng.randint(lo, hi) for _ in range(n)] for _ in range(2)]
+    most = max(sum((p + new + page) // page + 1 for p in ls) for ls in lengths)
     engine = Engine(config=cfg, random_seed=0, dtype="bfloat16", device="cuda:0", max_batch=max(64, n),
-                    max_prefill_len=1 << 20, page_size=page, num_pages=n * ((plen + new + page) // page + 1) + 64,
-                    max_positions=plen + new + 64, max_prefill_tokens_per_step=args.prefill_budget,
-                    max_total_tokens=max(4096, args.prefill_budget + n))
+                    max_prefill_len=1 << 20, page_size=page, num_pages=most + 64,
+                    max_positions=hi + new + 64, max_prefill_tokens_per_step=args.prefill_budget,
+                    max_total_tokens=max(4096, args.prefill_budget + n), record_steps=True)
     gen = torch.Generator().manual_seed(3)
     sp = SamplingParams(max_new_tokens=new, ignore_eos=True)
     rounds = []
     for rnd in range(2):                 # the first round builds libraries and captures graphs
-        prompts = [torch.randint(0, cfg.vocab_size, (plen,), generator=gen).tolist() for _ in range(n)]
+        prompts = [torch.randint(0, cfg.vocab_size, (p,), generator=gen).tolist() for p in lengths[rnd]]
         torch.cuda.synchronize()
+        r0 = len(engine.step_records())
         s0, l0, t0 = engine.runner.steps, kernels.launches(), time.perf_counter()
         outs = engine.generate(prompts, sp)
         torch.cuda.synchronize()
         rounds.append((time.perf_counter() - t0, engine.runner.steps - s0, kernels.launches() - l0,
-                       sum(len(o) for o in outs)))
-    sec, steps, launches, made = rounds[-1]
-    print(json.dumps({"micro": "serve", "requests": n, "prompt_tokens": plen, "new_tokens": new,
-                      "prefill_budget": args.prefill_budget, "layers": args.layers, "seconds": round(sec, 4),
-                      "engine_steps": steps, "generated": made, "generated_tok_s": round(made / sec, 1),
-                      "total_tok_s": round((made + n * plen) / sec, 1), "gpu_launches": launches,
+                       sum(len(o) for o in outs), engine.step_records()[r0:]))
+    sec, steps, launches, made, recs = rounds[-1]
+    n_prompt = sum(lengths[1])
+    pct = lambda xs, q: round(sorted(xs)[min(len(xs) - 1, int(q * len(xs)))], 3) if xs else None
+    mixed = [r["ms"] for r in recs if r["prompt_tokens"] and r["decode_tokens"]]
+    prompt_only = [r["ms"] for r in recs if r["prompt_tokens"] and not r["decode_tokens"]]
+    decode_only = [r["ms"] for r in recs if not r["prompt_tokens"]]
+    print(json.dumps({"micro": "serve", "shape": args.shape, "requests": n,
+                      "prompt_tokens": n_prompt, "prompt_lengths": [lo, hi], "new_tokens": new,
+                      "prefill_budget": args.prefill_budget, "layers": args.layers, "layers_full": shape["num_hidden_layers"],
+                      "seconds": round(sec, 4), "engine_steps": steps, "generated": made,
+                      "prompt_tok_s": round(n_prompt / sec, 1), "generated_tok_s": round(made / sec, 1),
+                      "total_tok_s": round((made + n_prompt) / sec, 1), "gpu_launches": launches,
+                      "step_ms": {"all": {"n": len(recs), "p50": pct([r["ms"] for r in recs], 0.5),
+                                          "p90": pct([r["ms"] for r in recs], 0.9), "max": pct([r["ms"] for r in recs], 1.0)},
+                                  "prompt_and_decode": {"n": len(mixed), "p50": pct(mixed, 0.5), "p90": pct(mixed, 0.9)},
+                                  "prompt_only": {"n": len(prompt_only), "p50": pct(prompt_only, 0.5)},
+                                  "decode_only": {"n": len(decode_only), "p50": pct(decode_only, 0.5), "p90": pct(decode_only, 0.9)}},
+                      "device_seconds_of_steps": round(sum(r["ms"] for r in recs) / 1e3, 4),
                       "first_round_seconds": round(rounds[0][0], 3)}))
     return 0
 
@@ -340,6 +366,8 @@ def main():
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")
     ap.add_argument("--prefill-budget", type=int, default=512, help="serve: prompt tokens per step")
+    ap.add_argument("--context-range", default=None, metavar="A:B", help="serve: prompt lengths uniform in [A, B]")
+    ap.add_argument("--points", default="1,64", help="other decode batch sizes measured beside --batch")
     ap.add_argument("--micro-impl", default="stream", choices=["stream", "regs", "tc5", "cublas"])
     ap.add_argument("--micro-shape", default="lm_head", choices=["qkv", "o", "gate_up", "down", "lm_head"])
     ap.add_argument("--tokens", type=int, default=8)
@@ -367,7 +395,8 @@ def main():
     cfg = Qwen2Config.from_dict(cfgd)
     pk, pk_src = peaks()
     page = args.page_size
-    max_b = max(64, args.batch)
+    point_batches = [int(b) for b in args.points.split(",") if b] if not args.no_points else []
+    max_b = max([args.batch] + point_batches)
     span = args.context + 2 * (W + K) + 64
     num_pages = max(max_b * ((span + page - 1) // page), (args.prefill_tokens + page - 1) // page) + 64
     torch.manual_seed(0)
@@ -420,7 +449,9 @@ def main():
 
     points = {}
     if not args.no_points:
-        for b in (1, 64):
+        for b in point_batches:
+            if b == args.batch:
+                continue
             pms, _, _ = time_decode(b, min(K, 128), W)
             points[f"decode_b{b}"] = round(b * min(K, 128) / (pms / 1e3), 1)
 

@@ -487,8 +487,10 @@ static int at_launch(const CUtensorMap& map, const AtParams& p, int tiles, cudaS
 }
 
 // Arguments as qd_prefill_attention (attention_flash.cu) plus the number of pages of `kv`
-// ([pages, 2, G, page_size, d], bfloat16).  Takes head sizes 64 and 128, groups of 1, 2, 4, 8 or 16 query
-// heads per KV head, page sizes that are multiples of 16; refuses the rest (the caller has another kernel).
+// ([pages, 2, G, page_size, d], bfloat16).  Takes head sizes 64 and 128, groups of 1 to 16 query heads per KV
+// head (a tile's 128 rows hold floor(128 / group) tokens x the group's heads; with a group that does not
+// divide 128 the last rows of a tile stay empty: 2 of 128 at 7 heads, 3 at 5), page sizes that are multiples
+// of 16; refuses the rest (the caller has another kernel).
 extern "C" int qd_prefill_attention_tc5(const void* q, long long q_stride, void* out, const void* kv, long long n_pages,
                                         const int* block_table, int max_blocks, const int* cu_tokens,
                                         const int* start_pos, int R, int T, int H, int G, int d, int page_size,
@@ -496,7 +498,7 @@ extern "C" int qd_prefill_attention_tc5(const void* q, long long q_stride, void*
   if (T <= 0 || R <= 0) return 0;
   if (G < 1 || H % G != 0 || page_size % 16 != 0 || (d != 64 && d != 128) || n_pages < 1) return QD_ERR_UNSUPPORTED;
   const int gs = H / G;
-  if (AT_ROWS % gs != 0 || gs > 16) return QD_ERR_UNSUPPORTED;
+  if (gs > 16) return QD_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || ((uintptr_t)kv & 15) || ((uintptr_t)out & 15) || q_stride % 8 != 0) return QD_ERR_UNSUPPORTED;
   AtEncodeFn fn = at_encode_fn();
   int* status = at_status_word();

@@ -532,9 +532,9 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 
 def prefill_tc5_supported(dtype, H: int, G: int, d: int, page_size: int) -> bool:
-    """What the tcgen05 prefill attention takes: bfloat16, head size 64 or 128, 1, 2, 4, 8 or 16 query
-    heads per KV head, pages of a multiple of 16 tokens."""
-    return (dtype == torch.bfloat16 and d in (64, 128) and H % G == 0 and H // G in (1, 2, 4, 8, 16)
+    """What the tcgen05 prefill attention takes: bfloat16, head size 64 or 128, up to 16 query heads per KV
+    head, pages of a multiple of 16 tokens."""
+    return (dtype == torch.bfloat16 and d in (64, 128) and H % G == 0 and 1 <= H // G <= 16
             and page_size % 16 == 0)
 
 

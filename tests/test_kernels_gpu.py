@@ -323,7 +323,11 @@ def test_prefill_attention_tensor_cores(cfg):
 
 
 @pytest.mark.parametrize("cfg", [(16, 2, 128, 16, None), (8, 8, 128, 32, None), (4, 1, 64, 16, None),
-                                 (16, 1, 64, 64, 40), (2, 1, 128, 16, 300)])
+                                 (16, 1, 64, 64, 40), (2, 1, 128, 16, 300),
+                                 # groups that do not divide the tile's 128 rows: 7 heads per KV head (Qwen2.5-7B),
+                                 # 5 (32B), 6, 3, 12
+                                 (28, 4, 128, 16, None), (40, 8, 128, 16, None), (12, 2, 128, 16, 100), (3, 1, 64, 32, None),
+                                 (12, 1, 64, 16, None)])
 def test_prefill_attention_tcgen05(cfg):
     """The same portions through the tcgen05 kernel (tensor memory accumulators, K/V by TMA from the pages):
     with and without history, one token up to hundreds, several requests, windows, tiles that end inside
