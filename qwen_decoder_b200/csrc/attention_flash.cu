@@ -926,12 +926,6 @@ static int launch_prefill_v(const bf16* q, long long q_stride, bf16* out, const 
   return qd_last_error();
 }
 
-static int pf_variant() {
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("QD_PF_VARIANT"); v = e ? atoi(e) : 0; }
-  return v;
-}
-
 template <int HD>
 static int launch_prefill(const bf16* q, long long q_stride, bf16* out, const bf16* kv, const int* block_table,
                           int max_blocks, const int* cu_tokens, const int* start_pos, int R, int T, int H, int G,
@@ -941,13 +935,7 @@ static int launch_prefill(const bf16* q, long long q_stride, bf16* out, const bf
   int gs = H / G;
   // eight warps (128 rows) halve the K/V traffic per row, but only pay with enough tokens per request
   bool big = T / R >= 128 && gs <= 128;
-  switch (pf_variant()) {
-    case 1: return PFV(4, 2);
-    case 2: return PFV(4, 3);
-    case 3: return PFV(8, 2);
-    case 4: return PFV(8, 3);
-    default: return big && gs <= 64 ? PFV(8, 2) : PFV(4, 2);
-  }
+  return big && gs <= 64 ? PFV(8, 2) : PFV(4, 2);       // three stages measured no better with either
 #undef PFV
 }
 

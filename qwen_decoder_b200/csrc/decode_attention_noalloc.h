@@ -24,6 +24,13 @@
 //    in it has to start at zero: every partial result is written by the call before the
 //    same call reads it.  Two calls that overlap on the GPU (different streams, or
 //    graphs replayed concurrently) race on the array; keep calls on one device ordered.
+//  * The kernels are launched so that they may begin while the kernel before them on the stream
+//    is still finishing (programmatic stream serialization), and they read `positions`,
+//    `token_req`, `block_table` and the cache rows of earlier positions before they wait for that
+//    kernel.  So the kernel that precedes this call on the stream must not still be writing
+//    those when it lets its dependents start early.  Kernels that never trigger their dependents
+//    early (every ordinary launch) are always safe; `q` and the newest cache row of each request
+//    may be written by the preceding kernel in any case: they are read after the wait.
 //  * Everything else (arguments, sizes accepted, result) is as qd_decode_attention.
 #pragma once
 #include <cuda_runtime.h>

@@ -728,7 +728,7 @@ extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const
   if (epi != EPI_PARTIAL && splits != 1) return QD_ERR_UNSUPPORTED;
   const bf16* w = (const bf16*)W;
   const bf16* x = (const bf16*)X;
-  if (xres_fits(T, K, splits, max_ctas) && !getenv("QD_STREAM_NO_XRES"))
+  if (xres_fits(T, K, splits, max_ctas))
     return launch_stream_xres(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 8) return launch_stream<1>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 16) return launch_stream<2>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);

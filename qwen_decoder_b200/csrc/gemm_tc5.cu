@@ -395,8 +395,6 @@ extern "C" int qd_gemm_tc5(const void* W, const void* X, long long ldx, const fl
   p.kbs = T <= 64 ? 4 : 1;
   int min_stages = 3;
   int smem_budget = 200 * 1024;
-  if (const char* e = getenv("QD_TC5_KBS")) { p.kbs = atoi(e); min_stages = 1; }
-  if (const char* e = getenv("QD_TC5_SMEM_KB")) smem_budget = atoi(e) * 1024;
   if (p.kbs > (kb_total + splits - 1) / splits) p.kbs = (kb_total + splits - 1) / splits;
   while (p.kbs > 1 && smem_budget / (p.kbs * blk_bytes) < min_stages) p.kbs /= 2;     // keep at least three stages
   const int stage_bytes = p.kbs * blk_bytes;
@@ -405,7 +403,6 @@ extern "C" int qd_gemm_tc5(const void* W, const void* X, long long ldx, const fl
   if (p.stages < 1) return QD_ERR_UNSUPPORTED;
   p.set_cols = a_tiles * p.BN;
   p.nacc = 4;
-  if (const char* e = getenv("QD_TC5_NACC")) p.nacc = atoi(e);
   while (p.nacc > 1 && 2 * p.nacc * p.set_cols > 512) p.nacc /= 2;
   if (p.nacc < 1) p.nacc = 1;
   p.acc_cols = p.nacc * p.set_cols < 32 ? 32 : p.nacc * p.set_cols;

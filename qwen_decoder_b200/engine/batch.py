@@ -70,8 +70,8 @@ class StepContext:
     decode_max_context: int = 0   # most keys any of them reads
 
 
-# single tokens first in a mixed step, for the mixers' decode kernels (QD_MIXED_SPLIT=0: entries as given)
-_SPLIT_MIXED = os.environ.get("QD_MIXED_SPLIT", "1") != "0"
+# single tokens first in a mixed step, for the mixers' decode kernels
+_SPLIT_MIXED = True
 
 
 def _pad4(n: int) -> int:

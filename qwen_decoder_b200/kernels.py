@@ -220,9 +220,11 @@ def gemm_generic(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 
 
 SKINNY_MAX_TOKENS = 64      # what the mma.sync few-token kernels take
-SKINNY_POLICY_TOKENS = int(_os.environ.get("QD_SKINNY_TOKENS", "16"))   # up to here they are the faster choice
-STREAM_POLICY_TOKENS = int(_os.environ.get("QD_STREAM_TOKENS", "8"))     # the streaming kernel up to here
-TC5_POLICY_TOKENS = int(_os.environ.get("QD_TC5_TOKENS", "16"))   # from there up to here the tcgen05 kernel; 16 = never:
+# Who takes a product of T tokens was settled by measurement in whole decode steps (profiles/); the numbers are
+# module attributes so that a measurement can move them, not switches of the environment.
+SKINNY_POLICY_TOKENS = 16      # up to here the few-token kernels are the faster choice
+STREAM_POLICY_TOKENS = 8       # the streaming kernel up to here
+TC5_POLICY_TOKENS = 16         # from there up to here the tcgen05 kernel; 16 = never:
 # on row-major weights it reads 128-byte pieces of 128 rows per copy and stays below the library product
 EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
 
@@ -249,13 +251,15 @@ def skinny_supported(x: torch.Tensor, w: torch.Tensor, limit: Optional[int] = No
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
+def skinny_splits(N: int, K: int, T: int = 1, target_ctas: Optional[int] = None) -> int:
     """Shares of K over the grid: enough CTAs (16 rows of W each) for four per SM, every warp at
     least one group of 128 k.  The tcgen05 kernel has tiles of 128 rows and one CTA per SM."""
     impl = few_token_impl(T) or "tc5"
+    if target_ctas is None:
+        target_ctas = 4 * sm_count()
     if impl == "tc5":
         tiles = (N + 127) // 128
-        return max(1, min((TC5_MAX_CTAS + tiles - 1) // tiles, ((K + 63) // 64) // 8, 16))
+        return max(1, min((tc5_max_ctas() + tiles - 1) // tiles, ((K + 63) // 64) // 8, 16))
     tiles = (N + 15) // 16
     if impl == "stream":
         chunks = (K + 1023) // 1024          # the streaming kernel splits K in whole stages of 1024
@@ -265,7 +269,7 @@ def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
             # whose busiest CTA reads least (rounds over the tiles x stages per share).
             best = None
             for sp in range((chunks + 1) // 2, min(chunks, 16) + 1):
-                per_share = max(1, min(STREAM_MAX_CTAS // sp, tiles))
+                per_share = max(1, min(stream_max_ctas() // sp, tiles))
                 widest = max(chunks * (i + 1) // sp - chunks * i // sp for i in range(sp))
                 if widest > 2:
                     continue
@@ -281,10 +285,30 @@ def skinny_splits(N: int, K: int, T: int = 1, target_ctas: int = 592) -> int:
 
 # Which few-token kernel runs: "stream" (persistent CTAs fed by bulk asynchronous copies,
 # csrc/gemm_stream.cu) or "regs" (one wave of CTAs loading straight into registers, csrc/gemm_skinny.cu).
-skinny_impl = _os.environ.get("QD_SKINNY_IMPL", "stream")
-STREAM_MAX_CTAS = 296          # two persistent CTAs on each of 148 SMs
+skinny_impl = "stream"
 _FFN_FUSED = _os.environ.get("QD_FFN_FUSED", "1") != "0"      # gate/up and down of up to 8 tokens in one launch
-TC5_MAX_CTAS = int(_os.environ.get("QD_TC5_CTAS", "148"))   # the tcgen05 kernel runs one persistent CTA per SM
+
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of the (current) CUDA device: what grids of persistent CTAs and the splits of the
+    attention kernels are sized by."""
+    index = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return n
+
+
+def stream_max_ctas() -> int:
+    """Two persistent CTAs of the weight streamer on every multiprocessor."""
+    return 2 * sm_count()
+
+
+def tc5_max_ctas() -> int:
+    """The tcgen05 product runs one persistent CTA per multiprocessor."""
+    return sm_count()
 
 
 def tile_weight(w: torch.Tensor, halves: int = 1) -> torch.Tensor:
@@ -321,11 +345,11 @@ def _skinny_call(x, w, bias, out, part, T, N, K, splits, epi, what, w_tiled=Fals
     if impl == "tc5":
         _check(library("gemm_tc5").qd_gemm_tc5(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
-            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(TC5_MAX_CTAS), _I(1 if w_tiled else 0), _stream()), what)
+            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(tc5_max_ctas()), _I(1 if w_tiled else 0), _stream()), what)
     elif impl == "stream":
         _check(library("gemm_stream").qd_gemm_stream(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
-            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(STREAM_MAX_CTAS), _stream()), what)
+            _I(T), _I(N), _I(K), _I(splits), _I(epi), _I(stream_max_ctas()), _stream()), what)
     else:
         _check(library("gemm_skinny").qd_gemm_skinny(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),
@@ -390,7 +414,7 @@ def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, b
     part = torch.empty((splits, T, D), dtype=torch.float32, device=x.device)
     _check(library("gemm_stream").qd_ffn_stream(
         _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(h), _LL(h.stride(0)), _ptr(w_down), _ptr(part), _I(T), _I(D),
-        _I(F), _I(splits), _ptr(barrier), _I(STREAM_MAX_CTAS), _stream()), "ffn_stream")
+        _I(F), _I(splits), _ptr(barrier), _I(stream_max_ctas()), _stream()), "ffn_stream")
     return part
 
 

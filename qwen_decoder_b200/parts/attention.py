@@ -124,25 +124,25 @@ class GQAttention(Mixer):
 
 
 import os as _os
-_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ATTN_CTAS", "148"))
 _DECODE_ROPE = _os.environ.get("QD_DECODE_ROPE", "1") != "0"
 _PREFILL_TC5 = _os.environ.get("QD_PREFILL_TC5", "1") != "0"      # prompt portions on tcgen05 where its sizes allow
-_ROPE_TARGET_CTAS = int(_os.environ.get("QD_DECODE_ROPE_CTAS", "148"))
 
 
 def decode_rope_splits(ctas_without_split: int, max_keys: int) -> int:
     """CTAs (of 8 warps) per (request, kv head) in the kernel that also rotates and writes the cache: one
-    CTA for each of the 148 SMs (two were slower in whole decode steps at batch 4 and 8, equal at 1 and 2),
+    CTA for each multiprocessor (two were slower in whole decode steps at batch 4 and 8, equal at 1 and 2),
     never more than that, and none with fewer than eight 16-key chunks, one per warp."""
-    by_fill = max(1, _ROPE_TARGET_CTAS // max(1, ctas_without_split))      # never a second wave
+    by_fill = max(1, kernels.sm_count() // max(1, ctas_without_split))      # never a second wave
     by_work = max(1, (max_keys + 127) // 128)
     return max(1, min(by_fill, by_work, 64))
 
 
-def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: int = _TARGET_CTAS) -> int:
+def decode_splits(ctas_without_split: int, max_keys: int, target_ctas: Optional[int] = None) -> int:
     """How many CTAs share one (request, kv head) in decode attention: enough for one CTA on each of
-    the 148 SMs (more splits cost more in the combine than they gain: measured in whole decode steps at
+    the multiprocessors (more splits cost more in the combine than they gain: measured in whole decode steps at
     batch 1, 8 and 64), but no CTA with fewer than four 16-key chunks."""
+    if target_ctas is None:
+        target_ctas = kernels.sm_count()
     by_fill = max(1, -(-target_ctas // max(1, ctas_without_split)))
     by_work = max(1, (max_keys + 63) // 64)
     return max(1, min(by_fill, by_work, 64))

@@ -30,7 +30,7 @@ from .. import kernels
 from . import matmul_backend
 
 _ENABLED = os.environ.get("QD_NATIVE_PROMPT", "1") != "0"
-_MIN_TOKENS = int(os.environ.get("QD_NATIVE_PROMPT_MIN", "1"))   # measured faster at every length: 4 tokens 3.2 against 4.4 ms
+_MIN_TOKENS = 1       # measured faster at every length: 4 tokens 3.2 against 4.4 ms
 # the one arrangement of parts whose order of kernels csrc/prompt_exec.cu restates: a block that answers
 # ``native_params()`` with any other ``composition`` (another order, another part) keeps the parts' own path
 COMPOSITION = "pre_norm/gq_attention/swiglu/rmsnorm/rmsnorm"

@@ -92,3 +92,58 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
             P(tr.data_ptr()), P(pos.data_ptr()), I(8), I(H), I(G), I(100), I(page_size), F(scale), I(0), I(2),
             P(torch.cuda.current_stream().cuda_stream))
     assert rc == 20002
+
+
+def test_no_alloc_entry_point_against_the_plain_formulas_at_the_edges():
+    """The second kernel of this entry point (the one that adds the shares up, where the ordinary entry point
+    lets the last CTA do it) with what makes shares uneven or empty: a window whose first visible key lies inside
+    a 16-key chunk, pages before the window given back (-1 in the block table), more shares than the shortest
+    request has chunks.  Compared with the plain formulas, not with the other entry point."""
+    import plain_model
+    from qwen_decoder_b200.csrc.build import library
+    lib = library("decode_attention_noalloc")
+    fn = lib.qd_decode_attention_noalloc
+    fn.restype = ctypes.c_int
+    lib.qd_decode_attention_noalloc_strerror.restype = ctypes.c_char_p
+    H, G, d, page_size, window = 6, 2, 64, 16, 75
+    scale = 1.0 / math.sqrt(d)
+    P, I, LL, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    lens = [300, 20, 76, 131, 1]                    # keys lens[i] - window .. lens[i] - 1 are visible
+    g = torch.Generator().manual_seed(41)
+    ks = [torch.randn(n, G, d, generator=g).to(torch.bfloat16) for n in lens]
+    vs = [torch.randn(n, G, d, generator=g).to(torch.bfloat16) for n in lens]
+    n_pages = sum((n + page_size - 1) // page_size for n in lens) + 1
+    kv = torch.zeros(n_pages, 2, G, page_size, d, dtype=torch.bfloat16)
+    mb = max((n + page_size - 1) // page_size for n in lens)
+    bt = torch.full((len(lens), mb), -1, dtype=torch.int32)
+    page = 0
+    for i, n in enumerate(lens):
+        first_needed = max(0, n - window) // page_size      # pages below it were given back when the window passed
+        for lp in range((n + page_size - 1) // page_size):
+            if lp < first_needed:
+                continue
+            bt[i, lp] = page
+            lo, hi = lp * page_size, min(n, (lp + 1) * page_size)
+            kv[page, 0, :, :hi - lo, :] = ks[i][lo:hi].transpose(0, 1)
+            kv[page, 1, :, :hi - lo, :] = vs[i][lo:hi].transpose(0, 1)
+            page += 1
+    q = torch.randn(len(lens), H * d, generator=g).to(torch.bfloat16)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    tr = torch.arange(len(lens), dtype=torch.int32)
+    want = []
+    for i, n in enumerate(lens):
+        qq = torch.zeros(n, H * d, dtype=torch.float64)
+        qq[n - 1] = q[i].double()
+        want.append(plain_model.attention(qq, ks[i].double().reshape(n, G * d), vs[i].double().reshape(n, G * d),
+                                          H, G, d, window)[n - 1])
+    want = torch.stack(want)
+    dq, dkv, dbt, dtr, dpos = (t.to(DEV) for t in (q, kv, bt, tr, pos))
+    for splits in (1, 3, 7, 24):                    # 24 shares: more than any of these requests has chunks in its window
+        got = torch.full((len(lens), H * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        rc = fn(P(dq.data_ptr()), LL(dq.stride(0)), P(got.data_ptr()), P(dkv.data_ptr()), P(dbt.data_ptr()),
+                I(dbt.shape[1]), P(dtr.data_ptr()), P(dpos.data_ptr()), I(len(lens)), I(H), I(G), I(d), I(page_size),
+                F(scale), I(window), I(splits), P(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert rc == 0, lib.qd_decode_attention_noalloc_strerror(rc)
+        err = float((got.double().cpu() - want).abs().max())
+        assert err <= 1e-2 * float(max(v.abs().max() for v in vs)), (splits, err)
