@@ -8,7 +8,8 @@ import torch
 
 import plain_model
 
-pytestmark = pytest.mark.gpu
+# every device buffer these tests and the code under test allocate lies between guard regions (conftest.py)
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("guard_regions")]
 DEV = "cuda:0"
 DTYPES = [torch.float32, torch.bfloat16]
 
@@ -640,3 +641,15 @@ def test_generate_raises_when_a_wait_ran_out(tmp_path):
     with pytest.raises(kernels.KernelError):
         eng.generate([[4, 5, 6]], SamplingParams(max_new_tokens=4, ignore_eos=True))
     kernels.check_status()
+
+
+def test_guard_regions_catch_a_stray_write(guard_regions):
+    """The guard regions themselves: a write one element past a buffer, as an off-by-one index in a kernel would
+    make it, changes the margin that the end of every test in this file checks."""
+    t = torch.empty(8, 16, dtype=torch.bfloat16, device=DEV)
+    raw, nbytes, shape, dtype = guard_regions[-1]
+    assert shape == (8, 16) and nbytes == 8 * 16 * 2 and t.data_ptr() == raw.data_ptr() + 1024
+    flat = t.view(-1)
+    torch.as_strided(flat, (1,), (1,), flat.storage_offset() + flat.numel()).fill_(1.0)
+    assert not bool((raw[1024 + nbytes:] == 0xA5).all())
+    raw[1024 + nbytes:].fill_(0xA5)                   # put it back: the check at the end of this test must pass

@@ -14,7 +14,8 @@ from qwen_decoder_b200.engine.batch import StepEntry, build_context
 from qwen_decoder_b200.parts.base import PagedCacheView, ResidualStream
 from qwen_decoder_b200.weights.loader import TensorSource
 
-pytestmark = pytest.mark.gpu
+# every device buffer these tests and the code under test allocate lies between guard regions (conftest.py)
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("guard_regions")]
 DEV = torch.device("cuda:0")
 DTYPES = [torch.float32, torch.bfloat16]
 TOL = {torch.float32: 1e-5, torch.bfloat16: 3e-2}
