@@ -183,10 +183,54 @@ def serve(args):
     return 0
 
 
+def mixed_step(args):
+    """One step of a busy server: ``--batch`` decoding requests at ``--context`` cached tokens each beside one
+    prompt portion of ``--prefill-tokens`` tokens that follows ``--history`` cached tokens, at ``--shape`` with
+    ``--layers`` layers; device time by CUDA events (for launch lists: a few layers are enough)."""
+    import torch
+    from qwen_decoder_b200.config import Qwen2Config
+    from qwen_decoder_b200.engine import ModelRunner, StepEntry
+    cfg = Qwen2Config.from_dict(dict(SHAPES[args.shape], num_hidden_layers=args.layers))
+    B, C, P, hist, page = args.batch, args.context, args.prefill_tokens, args.history, args.page_size
+    pages = (B * (C + 64) + 16 * (P + hist + 64)) // page + 64
+    runner = ModelRunner.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", num_pages=pages, page_size=page,
+                                     max_requests=B + 4, max_positions=max(C, P + hist) + 128)
+    for kv in runner.cache.kv:
+        kv.normal_(0.0, 1.0)
+    dec = []
+    for i in range(B):
+        rc = runner.open(f"d{i}")
+        runner.cache.ensure(rc, C)
+        runner.cache.commit(rc, C)
+        dec.append(rc)
+    times = []
+    for i in range(max(3, args.warmup) + args.steps):
+        rc = runner.open(f"p{i}")
+        runner.cache.ensure(rc, hist)
+        runner.cache.commit(rc, hist)
+        entries = [StepEntry(rc, list(range(P)), [P - 1])] + [StepEntry(d, [7], [0]) for d in dec]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step(entries)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+        runner.close(rc)
+        for d in dec:                     # the decoding requests stay where they were
+            d.num_tokens -= 1
+    ts = sorted(times[max(3, args.warmup):])
+    print(json.dumps({"micro": "mixed_step", "shape": args.shape, "layers": args.layers, "decoding_requests": B,
+                      "context": C, "prompt_tokens": P, "history": hist, "ms": round(ts[len(ts) // 2], 3)}))
+    return 0
+
+
 def micro(args):
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
     if args.micro == "serve":
         return serve(args)
+    if args.micro == "mixed_step":
+        return mixed_step(args)
     import math
     import torch
     from qwen_decoder_b200 import kernels
@@ -198,6 +242,41 @@ def micro(args):
         N, K = {"qkv": (2560, 2048), "o": (2048, 2048), "gate_up": (22016, 2048), "down": (2048, 11008),
                 "lm_head": (151936, 2048)}[args.micro_shape]
         x = torch.randn(T, K, device=dev).bfloat16()
+        if args.micro_graph:
+            # launch latency left out: a graph of launches on so many copies of the weights that L2 cannot hold
+            # them, replayed; with --micro-splits the product leaves float32 partial sums of that many shares of K
+            copies = max(4, int(400e6 // (N * K * 2)) + 1)
+            ws = [(torch.randn(N, K, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+            out = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
+            sp = args.micro_splits
+            part = torch.empty(sp, T, N, device=dev, dtype=torch.float32) if sp > 1 else None
+            if args.micro_impl == "cublas":
+                one = lambda w: torch.mm(x, w.t(), out=out)
+            else:
+                kernels.skinny_impl = args.micro_impl
+                kernels.TC5_POLICY_TOKENS = kernels.SKINNY_POLICY_TOKENS = 64
+                one = (lambda w: kernels._skinny_call(x, w, None, out, None, T, N, K, 1, kernels.EPI_STORE, "micro")) \
+                    if sp <= 1 else (lambda w: kernels._skinny_call(x, w, None, None, part, T, N, K, sp, kernels.EPI_PARTIAL, "micro"))
+            for w in ws:
+                one(w)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for w in ws:
+                    one(w)
+            g.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(4):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (4 * copies)
+            print(json.dumps({"micro": "gemm", "impl": args.micro_impl, "shape": args.micro_shape, "tokens": T,
+                              "splits": sp, "us": round(us, 2), "GB/s": round(N * K * 2 / us / 1e3, 1),
+                              "note": f"mean of {copies} launches on different weights inside a replayed graph"}))
+            return 0
         w = (torch.randn(N, K, device=dev) * 0.02).bfloat16()
         out = torch.empty(T, N, device=dev, dtype=torch.bfloat16)
         if args.micro_impl == "cublas":
@@ -361,7 +440,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (a multiple of 16)")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")
@@ -371,6 +450,9 @@ def main():
     ap.add_argument("--micro-impl", default="stream", choices=["stream", "regs", "tc5", "cublas"])
     ap.add_argument("--micro-shape", default="lm_head", choices=["qkv", "o", "gate_up", "down", "lm_head"])
     ap.add_argument("--tokens", type=int, default=8)
+    ap.add_argument("--micro-graph", action="store_true", help="gemm: time inside a replayed graph, cold weights")
+    ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
+    ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
     args = ap.parse_args()
     shape = SHAPES[args.shape]
     if args.layers is None:
