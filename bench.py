@@ -328,6 +328,20 @@ def micro(args):
         fn = kernels.prefill_attention if args.micro_impl == "regs" else kernels.prefill_attention_tc5
         run = lambda: fn(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0)
         work = {"bytes": T * (H + 2 * G) * d * 2 * 2, "flops": 4 * d * H * (T * (T + 1) // 2)}
+        if args.timeline and args.micro_impl != "regs" and T >= 2048:
+            # nanosecond stamps of the CTA whose rows end at key 2047 (16 key tiles), written by the kernel itself:
+            # row 0's softmax thread (8 per tile) and the MMA thread (4 per tile); printed relative to the first
+            tl = torch.zeros(16 * 8 + 16 * 4, dtype=torch.int64, device=dev)
+            for _ in range(3):
+                fn(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0, tl)
+            torch.cuda.synchronize()
+            sm, mm = tl[:128].view(16, 8).cpu(), tl[128:].view(16, 4).cpu()
+            t0 = int(sm[0][0])
+            names_s = ["top", "S ready", "S loaded", "maximum shared", "exponentials", "P stored", "O' added"]
+            names_m = ["top", "K ready", "P and V ready", "MMAs issued"]
+            for j in range(16):
+                print(f"tile {j:2d}  softmax: " + "  ".join(f"{n} {(int(sm[j][i]) - t0) / 1e3:.2f}" for i, n in enumerate(names_s)) +
+                      "  ||  mma: " + "  ".join(f"{n} {(int(mm[j][i]) - t0) / 1e3:.2f}" for i, n in enumerate(names_m)), file=sys.stderr)
     for _ in range(3):
         run()
     torch.cuda.synchronize()
@@ -440,6 +454,8 @@ def main():
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (a multiple of 16)")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --micro prefill_attention: print the kernel's own time stamps of one CTA (microseconds) to stderr")
     ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "

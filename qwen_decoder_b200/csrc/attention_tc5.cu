@@ -3,29 +3,37 @@
 // (128-byte swizzle), float32 online softmax by one thread per row.
 //
 // A CTA takes 128 rows = (128 / gs) tokens x the gs query heads of one KV head (as attention_flash.cu
-// does with 64 or 128 rows), and walks key tiles of 128 through the request's block table.  Warps:
-//   8        producer: per key tile, 16-key boxes of K and of V (two 64-column halves each) from the pages
-//   9        issues the MMAs (one thread): S = Q K^T (both operands K-major; S has two buffers in tensor
-//            memory, so the next tile's scores are computed while this tile's softmax runs), O' = P V (V is
-//            MN-major: its rows are keys, the contraction dimension)
-//   0..7     softmax: two threads per row (= TMEM lane), one for keys 0..63 and output columns 0..d/2-1,
-//            one for the rest: each loads its half of S from tensor memory in one go, scales, masks, shares
-//            the row maximum through shared memory, writes P as bfloat16 into shared memory in the layout
-//            the MMA reads, then adds its half of O' into its output columns (held in registers, rescaled
-//            when the maximum moves).
+// does with 64 or 128 rows), and walks key tiles of 128 through the request's block table.  With TPR softmax
+// threads per row (2 here; 4 was measured 4 % slower at head size 128) the warps are:
+//   0..4 TPR-1  softmax: TPR threads per row (= TMEM lane), each for 128 / TPR keys and d / TPR output columns:
+//            each loads its share of S from tensor memory in one go, scales, masks, shares the row maximum
+//            through shared memory, writes P as bfloat16 back into tensor memory over the scores it has just
+//            read (two bfloat16 per column), then adds its share of O' of the tile before into its output
+//            columns (held in registers, rescaled when the maximum moves) and arrives once for both
+//   4 TPR    producer of K, 4 TPR + 1 producer of V: per key tile, 16-key boxes (two 64-column halves each)
+//            from the pages; each reads the page numbers of the next tile while this one's copies fly
+//   4 TPR+2  issues the MMAs (one thread): S = Q K^T (both operands K-major in shared memory; S has three
+//            buffers in tensor memory and the scores of tile j + 2 are issued between the product steps of
+//            tile j), O' = P V with P as the A operand from tensor memory and V MN-major in shared memory
+//            (its rows are keys, the contraction dimension)
+// Tensor memory: columns 0..383 the three S/P buffers, 384..511 O'.  Shared memory: Q, 2 stages of K, 3 of V.
 // Formulas: gpu_kernels.cu:223-311 of the reference (scores q.k / sqrt(d), causal, softmax, weighted sum).
 // Keys past a row's position are masked on the scores; their V rows are whatever finite values the
 // pages hold (the cache starts as zeros and is only ever written with finite numbers), times zero.
 //
 // Every wait on an mbarrier is bounded in polls and in time; a wait that runs out marks the CTA dead:
-// nobody waits again, all roles run to their end, tensor memory is freed, and the host reads a status.
+// nobody waits again, all roles run to their end, tensor memory is freed, and the host reads a status
+// (the number of the wait that gave up first).
 #include "common.cuh"
 #include "entry_points.h"
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
-#define AT_THREADS 320
-#define AT_SOFTMAX_THREADS 256
+// softmax threads per row (TPR): 2 or 4; the softmax warps come first, then the two producers and the MMA warp
+#define AT_SOFTMAX_THREADS_OF(TPR) ((TPR) * 128)
+#define AT_THREADS_OF(TPR) ((TPR) * 128 + 96)
+#define AT_K_STAGES 2      // K of tile j + 2 is asked for when the scores of tile j are done: two tiles ahead of its use
+#define AT_V_STAGES 3      // V of tile j is asked for when the product of tile j - 3 is done
 #define AT_ROWS 128
 #define AT_KEYS 128
 #define AT_SPIN_LIMIT (1u << 24)
@@ -78,6 +86,34 @@ __device__ __forceinline__ void at_umma(unsigned tmem_d, unsigned long long desc
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
+// The same with the A operand in tensor memory: rows = lanes, the contraction index along the columns, two
+// bfloat16 per 32-bit column (element 2c in the low half of column c).
+__device__ __forceinline__ void at_umma_ta(unsigned tmem_d, unsigned tmem_a, unsigned long long desc_b, unsigned idesc,
+                                           unsigned accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// N consecutive 32-bit columns of this thread's TMEM lane from registers (N = 16 or 32)
+template <int N>
+__device__ __forceinline__ void at_tmem_st(unsigned taddr, const unsigned (&r)[N]) {
+  static_assert(N == 16 || N == 32, "16 or 32 columns");
+  if (N == 16) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+  } else {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+  }
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void at_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(bar)) : "memory");
 }
@@ -94,9 +130,14 @@ __device__ __forceinline__ void at_tmem_ld16(unsigned taddr, float (&v)[16]) {
 // N consecutive columns of this thread's TMEM lane (N = 32 or 64) in one request
 template <int N>
 __device__ __forceinline__ void at_tmem_ld(unsigned taddr, float (&v)[N]) {
-  static_assert(N == 32 || N == 64, "32 or 64 columns");
+  static_assert(N == 16 || N == 32 || N == 64, "16, 32 or 64 columns");
   unsigned r[N];
-  if (N == 32) {
+  if (N == 16) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+  } else if (N == 32) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
         "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
@@ -159,38 +200,42 @@ struct AtParams {
                            // CTA with 16 key tiles (for measurements)
 };
 
-template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+template <int HD, int TPR>
+__global__ void __launch_bounds__(AT_THREADS_OF(TPR), 1)
 prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const AtParams p) {
+  constexpr int AT_SOFTMAX_THREADS = AT_SOFTMAX_THREADS_OF(TPR);
+  constexpr int W_PRODUCER = TPR * 4, W_MMA = TPR * 4 + 2;      // warps of the two producers (K, V) and of the MMA issuer
+  constexpr int KQ = AT_KEYS / TPR;                 // keys of a tile per softmax thread
+  constexpr int NKS = AT_K_STAGES, NVS = AT_V_STAGES;
   constexpr int NB = HD / 64;                       // 64-column blocks of a row
-  constexpr int DH = HD / 2;                        // output columns per softmax thread
+  constexpr int DH = HD / TPR;                      // output columns per softmax thread
   constexpr int TILE_BYTES = AT_ROWS * HD * 2;      // one [128][HD] bfloat16 tile
   constexpr unsigned TMEM_COLS = 512;               // three S buffers of 128 columns, then O': 384..384+HD-1
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* base = smem_raw + ((1024 - (at_smem(smem_raw) & 1023)) & 1023);
   unsigned char* q_s = base;                        // Q tile, K-major
-  unsigned char* p_s = q_s + TILE_BYTES;            // P tile [128 rows][128 keys], K-major
-  unsigned char* k_s = p_s + AT_ROWS * AT_KEYS * 2; // 2 stages of K [128 keys][HD], K-major
-  unsigned char* v_s = k_s + 2 * TILE_BYTES;        // 2 stages of V [128 keys][HD], MN-major for the product
-  __shared__ unsigned long long k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[3], p_full, o_full, o_free, q_full;
-  __shared__ float mx_s[2][2][AT_ROWS];             // [tile parity][half][row]: the halves' maxima
-  __shared__ float l_s[2][AT_ROWS];                 // the halves' sums, at the end
+  unsigned char* k_s = q_s + TILE_BYTES;            // NKS stages of K [128 keys][HD], K-major
+  unsigned char* v_s = k_s + NKS * TILE_BYTES;      // NVS stages of V [128 keys][HD], MN-major for the product
+  __shared__ unsigned long long k_full[NKS], v_full[NVS], k_empty[NKS], v_empty[NVS], s_full[3], p_full[2], o_full, q_full;
+  __shared__ float mx_s[2][TPR][AT_ROWS];           // [tile parity][share of the keys][row]: the shares' maxima
+  __shared__ float l_s[TPR][AT_ROWS];               // the shares' sums, at the end
   __shared__ unsigned tmem_slot;
   __shared__ int dead;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     dead = 0;
-    for (int s = 0; s < 2; s++) {
-      at_mbar_init(&k_full[s], 1); at_mbar_init(&v_full[s], 1); at_mbar_init(&k_empty[s], 1); at_mbar_init(&v_empty[s], 1);
-    }
+    for (int s = 0; s < NKS; s++) { at_mbar_init(&k_full[s], 1); at_mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < NVS; s++) { at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1); }
     for (int s = 0; s < 3; s++) at_mbar_init(&s_full[s], 1);
     at_mbar_init(&o_full, 1);
-    at_mbar_init(&p_full, AT_SOFTMAX_THREADS); at_mbar_init(&o_free, AT_SOFTMAX_THREADS);
+    // P of tile j + 1 may be ready before the MMA thread has looked at tile j's barrier (the softmax threads
+    // hand P over before they wait for the product of the tile before): two barriers, used in turn
+    at_mbar_init(&p_full[0], AT_SOFTMAX_THREADS); at_mbar_init(&p_full[1], AT_SOFTMAX_THREADS);
     at_mbar_init(&q_full, AT_SOFTMAX_THREADS);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == W_MMA) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(&tmem_slot)),
                  "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -224,45 +269,48 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   const int kt_lo = key_lo_tile / AT_KEYS, kt_hi = idle ? kt_lo : (key_hi + AT_KEYS - 1) / AT_KEYS;
   const int n_kt = kt_hi - kt_lo;
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ producer
-    // K and V tiles are asked for in the order the tensor cores take them: K(0), K(1), V(0), K(2), V(1), K(3), ...
-    // (the scores of tile j + 2 are computed together with the product of tile j), so that a K stage is
-    // refilled as soon as its scores are done and does not wait for the V stage beside it.
+  if (warp == W_PRODUCER || warp == W_PRODUCER + 1) {
+    // ------------------------------------------------------------------ producers: one warp for K, one for V
+    // Each walks its own tiles and is held back only by its own stages' barriers, so a K stage is refilled as
+    // soon as its scores are done and a V stage as soon as its product is.  A tile is eight 16-key boxes (two
+    // 64-column halves each) from eight pages; the page numbers of the next tile are read from the block
+    // table while this tile's stage is waited for, so no copy waits for a load of its own address.
     if (!idle) {
+      const int which = warp - W_PRODUCER;            // 0 = K, 1 = V
+      const int ns = which ? NVS : NKS;
       const int* bt = p.block_table + (size_t)r * p.max_blocks;
-      auto load = [&](int j, int which) {             // which: 0 = K, 1 = V
-        const int s = j & 1;
-        const unsigned ph = (j >> 1) & 1;
+      auto page_of = [&](int j) {                     // page of this lane's box row of tile j (lanes 0..7)
+        const int key0 = (kt_lo + j) * AT_KEYS + lane * 16;
+        return (lane < AT_KEYS / 16 && j < n_kt && key0 < key_hi) ? bt[key0 / p.page_size] : -1;
+      };
+      int page_next = page_of(0);
+      for (int j = 0; j < n_kt; j++) {
+        int page = page_next;
+        page_next = page_of(j + 1);
+        const int s = j % ns;
+        const unsigned ph = (j / ns) & 1;
         unsigned long long* empty = which ? &v_empty[s] : &k_empty[s];
         unsigned long long* full = which ? &v_full[s] : &k_full[s];
-        if (!at_mbar_wait(empty, ph ^ 1, &dead) && lane == 0) atomicExch(p.status, 1);
+        if (!at_mbar_wait(empty, ph ^ 1, &dead) && lane == 0) atomicCAS(p.status, 0, 1);
         if (lane == 0) at_mbar_expect_tx(full, TILE_BYTES);
         __syncwarp();
         if (lane < AT_KEYS / 16) {                    // one 16-key box row per lane
           const int key0 = (kt_lo + j) * AT_KEYS + lane * 16;
-          int page = key0 < key_hi ? bt[key0 / p.page_size] : -1;
           if (page < 0) page = 0;                     // no such keys: any page will do, the scores are masked
           const int row0 = ((page * 2 + which) * p.G + g) * p.page_size + key0 % p.page_size;
           unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES + lane * 2048;     // 16 keys = two groups of 8 rows
 #pragma unroll
           for (int cb = 0; cb < NB; cb++) at_tma_2d(dst + cb * (AT_KEYS * 128), &kv_map, cb * 64, row0, full);
         }
-      };
-      for (int j = 0; j < 2 && j < n_kt; j++) load(j, 0);
-      for (int j = 0; j < n_kt; j++) {
-        load(j, 1);
-        if (j + 2 < n_kt) load(j + 2, 0);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == W_MMA) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && !idle) {
       const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_KEYS >> 3) << 17) | ((unsigned)(AT_ROWS >> 4) << 24);
       const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
                                 ((unsigned)(AT_ROWS >> 4) << 24);
       const unsigned long long dq = at_desc_kmajor(at_smem(q_s));
-      const unsigned long long dp = at_desc_kmajor(at_smem(p_s));
       // MMAs into one accumulator wait for each other (some 200 cycles each), MMAs into different
       // accumulators overlap: the product of tile j is issued step by step together with the scores of tile
       // j + 2, which go to the third S buffer -- the scores of tile j + 1 are complete by then, so the
@@ -273,17 +321,17 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
         at_umma(tmem + (unsigned)(j % 3) * AT_KEYS, dq + adv, dk + adv, idesc_qk, k ? 1u : 0u);
       };
       auto k_ready = [&](int j) -> unsigned long long {
-        const int s = j & 1;
-        if (!at_mbar_wait(&k_full[s], (j >> 1) & 1, &dead)) atomicExch(p.status, 2);
+        const int s = j % NKS;
+        if (!at_mbar_wait(&k_full[s], (j / NKS) & 1, &dead)) atomicCAS(p.status, 0, 2);
         at_fence_after();
         return at_desc_kmajor(at_smem(k_s + s * TILE_BYTES));
       };
       auto qk_done = [&](int j) {
-        at_commit(&k_empty[j & 1]);
+        at_commit(&k_empty[j % NKS]);
         at_commit(&s_full[j % 3]);
       };
       const bool mstamp = p.timeline && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
-      if (!at_mbar_wait(&q_full, 0, &dead)) atomicExch(p.status, 3);
+      if (!at_mbar_wait(&q_full, 0, &dead)) atomicCAS(p.status, 0, 3);
       at_fence_after();
       for (int j = 0; j < 2 && j < n_kt; j++) {         // the first two tiles' scores, alone
         const unsigned long long dk = k_ready(j);
@@ -292,24 +340,23 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
         qk_done(j);
       }
       for (int j = 0; j < n_kt; j++) {
-        const int s = j & 1;
+        const int s = j % NVS;
         if (mstamp) p.timeline[128 + j * 4 + 0] = at_now();
         const bool ahead = j + 2 < n_kt;
         unsigned long long dk = 0;
         if (ahead) dk = k_ready(j + 2);
         if (mstamp) p.timeline[128 + j * 4 + 1] = at_now();
-        if (!at_mbar_wait(&p_full, j & 1, &dead)) atomicExch(p.status, 4);
-        if (!at_mbar_wait(&v_full[s], (j >> 1) & 1, &dead)) atomicExch(p.status, 5);
-        if (j > 0 && !at_mbar_wait(&o_free, (j - 1) & 1, &dead)) atomicExch(p.status, 6);
+        if (!at_mbar_wait(&p_full[j & 1], (j >> 1) & 1, &dead)) atomicCAS(p.status, 0, 4);
+        if (!at_mbar_wait(&v_full[s], (j / NVS) & 1, &dead)) atomicCAS(p.status, 0, 5);
         at_fence_after();
         if (mstamp) p.timeline[128 + j * 4 + 2] = at_now();
         const unsigned v_addr = at_smem(v_s + s * TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < AT_KEYS / 16; k++) {
-          const unsigned long long adv_p = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
           // 16 keys = two groups of 8 rows of V; the d columns 64.. lie one [128 keys][128 bytes] block further
           const unsigned long long dv = at_desc_mnmajor(v_addr + k * 2048, AT_KEYS * 128);
-          at_umma(tmem + 3 * AT_KEYS, dp + adv_p, dv, idesc_pv, k ? 1u : 0u);
+          // P of this tile lies where its scores were: 16 keys = 8 columns of bfloat16 pairs per step
+          at_umma_ta(tmem + 3 * AT_KEYS, tmem + (unsigned)(j % 3) * AT_KEYS + (unsigned)k * 8, dv, idesc_pv, k ? 1u : 0u);
           if (ahead && k < HD / 16) qk_step(j + 2, k, dk);
         }
         at_commit(&v_empty[s]);
@@ -319,18 +366,18 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax: two threads per row
+    // ------------------------------------------------------------------ softmax: TPR threads per row
     const int row = (warp & 3) * 32 + lane;                        // 0..127, also the TMEM lane
-    const int h = warp >> 2;                                       // which half of the keys and of the columns
+    const int h = warp >> 2;                                       // which share of the keys and of the columns
     const int t = row / gs, hh = row - t * gs;
     const bool ok = !idle && t < n_tok;
     const int pos = pos0 + t;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    // this thread's half of the Q row into shared memory, in the layout the MMA reads
+    // this thread's share of the Q row into shared memory, in the layout the MMA reads
     {
       const bf16* qr = p.q + (size_t)(tok0 + t) * p.q_stride + (size_t)(g * gs + hh) * HD;
 #pragma unroll
-      for (int c = h * (HD / 16); c < (h + 1) * (HD / 16); c++) {
+      for (int c = h * (HD / 8 / TPR); c < (h + 1) * (HD / 8 / TPR); c++) {
         uint4 v = make_uint4(0, 0, 0, 0);
         if (ok) v = *reinterpret_cast<const uint4*>(qr + c * 8);
         *reinterpret_cast<uint4*>(q_s + at_swz(row, c)) = v;
@@ -349,7 +396,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     const int free_hi = pos0 + 1;
     const int free_lo = (p.window > 0 && key_hi - p.window > 0) ? key_hi - p.window : 0;
     auto add_partial = [&](int j) {          // O += O' of tile j, once the tensor cores have made it
-      if (!at_mbar_wait(&o_full, j & 1, &dead) && lane == 0) atomicExch(p.status, 8);
+      if (!at_mbar_wait(&o_full, j & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 8);
       at_fence_after();
       float ov[DH];
       at_tmem_ld<DH>(t_lane + 3 * AT_KEYS + h * DH, ov);
@@ -359,23 +406,23 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     };
     for (int j = 0; j < n_kt; j++) {
       const int tile_base = (kt_lo + j) * AT_KEYS;
-      const int key_base = tile_base + h * 64;
+      const int key_base = tile_base + h * KQ;
       if (stamp) p.timeline[j * 8 + 0] = at_now();
-      if (!at_mbar_wait(&s_full[j % 3], (j / 3) & 1, &dead) && lane == 0) atomicExch(p.status, 7);
+      if (!at_mbar_wait(&s_full[j % 3], (j / 3) & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 7);
       at_fence_after();
       if (stamp) p.timeline[j * 8 + 1] = at_now();
-      float sv[64];
-      at_tmem_ld<64>(t_lane + (unsigned)(j % 3) * AT_KEYS + h * 64, sv);
+      float sv[KQ];
+      at_tmem_ld<KQ>(t_lane + (unsigned)(j % 3) * AT_KEYS + h * KQ, sv);
       if (stamp) p.timeline[j * 8 + 2] = at_now();
       const bool interior = tile_base >= free_lo && tile_base + AT_KEYS <= free_hi && p.scale_log2e > 0.f;
       float mx = -INFINITY;
       if (interior) {
 #pragma unroll
-        for (int i = 0; i < 64; i++) mx = fmaxf(mx, sv[i]);
+        for (int i = 0; i < KQ; i++) mx = fmaxf(mx, sv[i]);
         mx *= p.scale_log2e;
       } else {
 #pragma unroll
-        for (int i = 0; i < 64; i++) {
+        for (int i = 0; i < KQ; i++) {
           const int key = key_base + i;
           const bool vis = ok && key <= pos && key >= lo;
           sv[i] = vis ? sv[i] * p.scale_log2e : -INFINITY;
@@ -385,44 +432,48 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       mx_s[j & 1][h][row] = mx;
       asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_THREADS) : "memory");
       if (stamp) p.timeline[j * 8 + 3] = at_now();
-      const float m_new = fmaxf(m, fmaxf(mx, mx_s[j & 1][h ^ 1][row]));
+      float m_new = fmaxf(m, mx);
+#pragma unroll
+      for (int o2 = 1; o2 < TPR; o2++) m_new = fmaxf(m_new, mx_s[j & 1][(h + o2) % TPR][row]);
       const float ref = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = at_exp2(m - ref);
       m = m_new;
       // p = exp2(score - max) as bfloat16 pairs, kept in registers until the P tile is free
-      unsigned pk[32];
+      unsigned pk[KQ / 2];
       float sum = 0.f;
       const float mul = interior ? p.scale_log2e : 1.0f;
 #pragma unroll
-      for (int i = 0; i < 32; i++) {
+      for (int i = 0; i < KQ / 2; i++) {
         const float p0 = at_exp2(fmaf(sv[2 * i], mul, -ref)), p1 = at_exp2(fmaf(sv[2 * i + 1], mul, -ref));
         sum += p0 + p1;
         pk[i] = at_pack(p0, p1);
       }
       l = l * alpha + sum;
       if (stamp) p.timeline[j * 8 + 4] = at_now();
-      // the product of the tile before ran under all of the above; its result joins the output row, which
-      // then moves to the new maximum
-      if (j > 0) {
-        add_partial(j - 1);
-        at_mbar_arrive(&o_free);
-      }
+      // P goes into tensor memory, over the first half of this tile's own scores (every thread of the row has
+      // its scores in registers since the barrier above): the product reads it from there as its A operand,
+      // nothing passes through shared memory, and three tiles' P can be alive at once like their scores
+      at_tmem_st<KQ / 2>(t_lane + (unsigned)(j % 3) * AT_KEYS + h * (KQ / 2), pk);
       if (stamp) p.timeline[j * 8 + 5] = at_now();
+      // the product of the tile before ran under all of the above; its result joins the output row, which
+      // then moves to the new maximum.  One arrival tells the MMA thread both things it waits for: P of this
+      // tile is in tensor memory and O' of the tile before has been read (every wait of that one thread is time
+      // in which no MMA is issued)
+      if (j > 0) add_partial(j - 1);
+      at_fence_before();
+      at_mbar_arrive(&p_full[j & 1]);
 #pragma unroll
       for (int i = 0; i < DH; i++) o[i] *= alpha;
-#pragma unroll
-      for (int c = 0; c < 8; c++)
-        *reinterpret_cast<uint4*>(p_s + at_swz(row, h * 8 + c)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      at_fence_before();
-      at_fence_async_smem();
-      at_mbar_arrive(&p_full);
       if (stamp) p.timeline[j * 8 + 6] = at_now();
     }
     if (n_kt > 0) add_partial(n_kt - 1);
     l_s[h][row] = l;
     asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_THREADS) : "memory");
     if (ok) {
-      const float inv = 1.f / (l + l_s[h ^ 1][row]);
+      float l_all = l;
+#pragma unroll
+      for (int o2 = 1; o2 < TPR; o2++) l_all += l_s[(h + o2) % TPR][row];
+      const float inv = 1.f / l_all;
       bf16* d = p.out + (size_t)(tok0 + t) * p.H * HD + (size_t)(g * gs + hh) * HD + h * DH;
 #pragma unroll
       for (int c = 0; c < DH; c += 8) {
@@ -438,7 +489,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   pdl_launch_dependents();
   at_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == W_MMA) {
     at_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
@@ -474,15 +525,15 @@ static int* at_status_word() {
   return words[dev];
 }
 
-template <int HD>
+template <int HD, int TPR>
 static int at_launch(const CUtensorMap& map, const AtParams& p, int tiles, cudaStream_t stream) {
-  size_t smem = 1024 + (size_t)AT_ROWS * HD * 2 + (size_t)AT_ROWS * AT_KEYS * 2 + (size_t)4 * AT_ROWS * HD * 2;
-  auto kernel = prefill_attention_tc5_kernel<HD>;
+  size_t smem = 1024 + (size_t)(1 + AT_K_STAGES + AT_V_STAGES) * AT_ROWS * HD * 2;
+  auto kernel = prefill_attention_tc5_kernel<HD, TPR>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();
     return QD_ERR_UNSUPPORTED;
   }
-  qd_launch(kernel, dim3((unsigned)tiles, (unsigned)p.G), dim3(AT_THREADS), smem, stream, map, p);
+  qd_launch(kernel, dim3((unsigned)tiles, (unsigned)p.G), dim3(AT_THREADS_OF(TPR)), smem, stream, map, p);
   return (int)cudaGetLastError();
 }
 
@@ -521,7 +572,7 @@ extern "C" int qd_prefill_attention_tc5(const void* q, long long q_stride, void*
   p.status = status;
   p.timeline = timeline;
   const int tiles = (T + p.tok_tile - 1) / p.tok_tile + R;      // upper bound on the tiles of R requests
-  return d == 64 ? at_launch<64>(map, p, tiles, stream) : at_launch<128>(map, p, tiles, stream);
+  return d == 64 ? at_launch<64, 2>(map, p, tiles, stream) : at_launch<128, 2>(map, p, tiles, stream);
 }
 
 // 0 if no kernel of this library has recorded a bounded-wait expiry on the current device.  Synchronises.
