@@ -337,8 +337,8 @@ def micro(args):
             torch.cuda.synchronize()
             sm, mm = tl[:128].view(16, 8).cpu(), tl[128:].view(16, 4).cpu()
             t0 = int(sm[0][0])
-            names_s = ["top", "S ready", "S loaded", "maximum shared", "exponentials", "P stored", "O' added"]
-            names_m = ["top", "K ready", "P and V ready", "MMAs issued"]
+            names_s = ["top", "S ready", "S loaded", "maximum shared", "exponentials", "P stored"]
+            names_m = ["top", "P ready", "K, V ready and product issued", "scores of tile + 2 issued"]
             for j in range(16):
                 print(f"tile {j:2d}  softmax: " + "  ".join(f"{n} {(int(sm[j][i]) - t0) / 1e3:.2f}" for i, n in enumerate(names_s)) +
                       "  ||  mma: " + "  ".join(f"{n} {(int(mm[j][i]) - t0) / 1e3:.2f}" for i, n in enumerate(names_m)), file=sys.stderr)

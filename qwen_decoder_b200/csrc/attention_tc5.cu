@@ -6,17 +6,22 @@
 // does with 64 or 128 rows), and walks key tiles of 128 through the request's block table.  With TPR softmax
 // threads per row (2 here; 4 was measured 4 % slower at head size 128) the warps are:
 //   0..4 TPR-1  softmax: TPR threads per row (= TMEM lane), each for 128 / TPR keys and d / TPR output columns:
-//            each loads its share of S from tensor memory in one go, scales, masks, shares the row maximum
-//            through shared memory, writes P as bfloat16 back into tensor memory over the scores it has just
-//            read (two bfloat16 per column), then adds its share of O' of the tile before into its output
-//            columns (held in registers, rescaled when the maximum moves) and arrives once for both
+//            each writes its share of the Q row into tensor memory once, then per key tile loads its share of S
+//            from tensor memory in one go, scales, masks, shares the row maximum through shared memory and
+//            writes P as bfloat16 back into tensor memory over the scores it has just read (two bfloat16 per
+//            column).  The output rows stay in tensor memory, where the products accumulate; a row's sum and
+//            output are scaled down only when its maximum has grown by more than 2^8 since the reference of its
+//            exponentials (then the thread waits for the product in flight first), and once at the end by 1/sum
 //   4 TPR    producer of K, 4 TPR + 1 producer of V: per key tile, 16-key boxes (two 64-column halves each)
-//            from the pages; each reads the page numbers of the next tile while this one's copies fly
-//   4 TPR+2  issues the MMAs (one thread): S = Q K^T (both operands K-major in shared memory; S has three
-//            buffers in tensor memory and the scores of tile j + 2 are issued between the product steps of
-//            tile j), O' = P V with P as the A operand from tensor memory and V MN-major in shared memory
-//            (its rows are keys, the contraction dimension)
-// Tensor memory: columns 0..383 the three S/P buffers, 384..511 O'.  Shared memory: Q, 2 stages of K, 3 of V.
+//            from the pages; each reads the page numbers of the next tile while this one's copies fly.  A stage
+//            holds K of tile j + 2 and V of tile j under one barrier: what the MMA thread reads in its step j
+//   4 TPR+2  issues the MMAs (one thread): O += P V of tile j (P is the A operand from tensor memory, V MN-major
+//            in shared memory: its rows are keys, the contraction dimension), then S = Q K^T of tile j + 2 (Q the
+//            A operand from tensor memory, K K-major in shared memory) into the columns P of tile j was read
+//            from: the tensor cores run a thread's MMAs in the order it issued them.  The scores of tile j + 1
+//            are complete by then, so the softmax threads never wait for them.  With both A operands in tensor
+//            memory an MMA reads 4 KB of shared memory, not 8
+// Tensor memory: columns 0..255 the two S/P buffers, 256..383 O, 384..447 Q.  Shared memory: 3 stages of K and V.
 // Formulas: gpu_kernels.cu:223-311 of the reference (scores q.k / sqrt(d), causal, softmax, weighted sum).
 // Keys past a row's position are masked on the scores; their V rows are whatever finite values the
 // pages hold (the cache starts as zeros and is only ever written with finite numbers), times zero.
@@ -32,8 +37,7 @@
 // softmax threads per row (TPR): 2 or 4; the softmax warps come first, then the two producers and the MMA warp
 #define AT_SOFTMAX_THREADS_OF(TPR) ((TPR) * 128)
 #define AT_THREADS_OF(TPR) ((TPR) * 128 + 96)
-#define AT_K_STAGES 2      // K of tile j + 2 is asked for when the scores of tile j are done: two tiles ahead of its use
-#define AT_V_STAGES 3      // V of tile j is asked for when the product of tile j - 3 is done
+#define AT_STAGES 3        // a stage holds K of tile j + 2 and V of tile j: what the MMA thread's step j reads
 #define AT_ROWS 128
 #define AT_KEYS 128
 #define AT_SPIN_LIMIT (1u << 24)
@@ -57,43 +61,26 @@ __device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, int
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(at_smem(dst)), "l"(map), "r"(at_smem(bar)), "r"(x), "r"(y) : "memory");
 }
-// Shared-memory matrix descriptors, 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-// K-major (the contraction runs along a row): stride offset = 1024 (next 8 rows), leading offset unused.
-__device__ __forceinline__ unsigned long long at_desc_kmajor(unsigned addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
-  d |= (unsigned long long)1 << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= (unsigned long long)1 << 46;
-  d |= (unsigned long long)2 << 61;
-  return d;
+// Shared-memory matrix descriptors (64 bits), 128-byte swizzle, rows of 128 bytes, groups of 8 rows 1024 bytes
+// apart.  Low word: bits 0-13 the start address in 16-byte units, bits 16-29 the leading offset in 16-byte units.
+// High word: bits 0-13 the stride offset (1024 bytes: the next group of 8 rows) in 16-byte units, bit 14 the
+// descriptor version of this architecture, bits 29-31 the layout (2 = 128-byte swizzle).
+//   K-major (the contraction runs along a row; K tiles): leading offset unused (1).
+//   MN-major (a row holds 64 consecutive N elements of ONE contraction index, 8 contraction indices per group;
+//   V tiles): leading offset = distance to the next 64 N elements.
+// The high word is the same for all tiles, so a step along a tile is one 32-bit addition to the low word.
+#define AT_DESC_HI ((unsigned)(1024 >> 4) | (1u << 14) | (2u << 29))
+__device__ __forceinline__ unsigned at_desc_lo(unsigned smem_addr, unsigned leading_bytes) {
+  return ((smem_addr & 0x3FFFF) >> 4) | (leading_bytes ? ((leading_bytes >> 4) & 0x3FFF) << 16 : 1u << 16);
 }
-// MN-major (a row holds 64 consecutive N elements of ONE contraction index; 8 contraction indices per group):
-// stride offset = 1024 (next 8 contraction indices), leading offset = distance to the next 64 N elements.
-__device__ __forceinline__ unsigned long long at_desc_mnmajor(unsigned addr, unsigned lbo_bytes) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((addr & 0x3FFFF) >> 4);
-  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= (unsigned long long)1 << 46;
-  d |= (unsigned long long)2 << 61;
-  return d;
-}
-__device__ __forceinline__ void at_umma(unsigned tmem_d, unsigned long long desc_a, unsigned long long desc_b,
-                                        unsigned idesc, unsigned accumulate) {
+// D[128 x N] (+)= A[128 x 16] B[N x 16]^T with A in tensor memory: rows = lanes, the contraction index along the
+// columns, two bfloat16 per 32-bit column (element 2c in the low half of column c); B in shared memory.
+__device__ __forceinline__ void at_umma_ta(unsigned tmem_d, unsigned tmem_a, unsigned desc_lo, unsigned desc_hi,
+                                           unsigned idesc, unsigned accumulate) {
   asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// The same with the A operand in tensor memory: rows = lanes, the contraction index along the columns, two
-// bfloat16 per 32-bit column (element 2c in the low half of column c).
-__device__ __forceinline__ void at_umma_ta(unsigned tmem_d, unsigned tmem_a, unsigned long long desc_b, unsigned idesc,
-                                           unsigned accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+      "{\n .reg .pred p;\n .reg .b64 d;\n setp.ne.b32 p, %5, 0;\n mov.b64 d, {%2, %3};\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], d, %4, {%6, %6, %6, %6}, p;\n}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 // N consecutive 32-bit columns of this thread's TMEM lane from registers (N = 16 or 32)
 template <int N>
@@ -117,17 +104,7 @@ __device__ __forceinline__ void at_tmem_st(unsigned taddr, const unsigned (&r)[N
 __device__ __forceinline__ void at_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(bar)) : "memory");
 }
-__device__ __forceinline__ void at_tmem_ld16(unsigned taddr, float (&v)[16]) {
-  unsigned r[16];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
-}
-// N consecutive columns of this thread's TMEM lane (N = 32 or 64) in one request
+// N consecutive columns of this thread's TMEM lane (N = 16, 32 or 64) in one request
 template <int N>
 __device__ __forceinline__ void at_tmem_ld(unsigned taddr, float (&v)[N]) {
   static_assert(N == 16 || N == 32 || N == 64, "16, 32 or 64 columns");
@@ -167,7 +144,6 @@ __device__ __forceinline__ void at_tmem_ld(unsigned taddr, float (&v)[N]) {
 }
 __device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void at_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ float at_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -177,17 +153,16 @@ __device__ __forceinline__ unsigned at_pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
 }
-// Byte offset of the 16-byte piece `c` (of 64-column block c / 8) of row r in a [128 rows][HD] K-major tile
-// stored as HD / 64 blocks of [128 rows][128 bytes] with the 128-byte swizzle.
-__device__ __forceinline__ unsigned at_swz(int r, int c) {
-  return (unsigned)((c >> 3) * (AT_ROWS * 128) + (r >> 3) * 1024 + (r & 7) * 128 + (((c & 7) ^ (r & 7)) << 4));
-}
-
 __device__ __forceinline__ long long at_now() {
   long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
+
+// A row's sum and output are rescaled only when its maximum has grown by more than this (in powers of two) since
+// the value its exponentials refer to: P stays below 2^8, which loses nothing in bfloat16 or in the float32
+// sums, and the final division by the row sum, taken against the same reference, gives the same result.
+#define AT_RESCALE_STEP 8.0f
 
 struct AtParams {
   const bf16* q; long long q_stride; bf16* out;
@@ -206,17 +181,21 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   constexpr int AT_SOFTMAX_THREADS = AT_SOFTMAX_THREADS_OF(TPR);
   constexpr int W_PRODUCER = TPR * 4, W_MMA = TPR * 4 + 2;      // warps of the two producers (K, V) and of the MMA issuer
   constexpr int KQ = AT_KEYS / TPR;                 // keys of a tile per softmax thread
-  constexpr int NKS = AT_K_STAGES, NVS = AT_V_STAGES;
+  constexpr int NS = AT_STAGES;
   constexpr int NB = HD / 64;                       // 64-column blocks of a row
   constexpr int DH = HD / TPR;                      // output columns per softmax thread
   constexpr int TILE_BYTES = AT_ROWS * HD * 2;      // one [128][HD] bfloat16 tile
-  constexpr unsigned TMEM_COLS = 512;               // three S buffers of 128 columns, then O': 384..384+HD-1
+  // tensor memory: two S/P buffers of 128 columns, the output rows O (HD columns), the query rows Q (HD / 2
+  // columns of bfloat16 pairs)
+  constexpr unsigned TMEM_COLS = 512, T_O = 2 * AT_KEYS, T_Q = 3 * AT_KEYS;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned char* base = smem_raw + ((1024 - (at_smem(smem_raw) & 1023)) & 1023);
-  unsigned char* q_s = base;                        // Q tile, K-major
-  unsigned char* k_s = q_s + TILE_BYTES;            // NKS stages of K [128 keys][HD], K-major
-  unsigned char* v_s = k_s + NKS * TILE_BYTES;      // NVS stages of V [128 keys][HD], MN-major for the product
-  __shared__ unsigned long long k_full[NKS], v_full[NVS], k_empty[NKS], v_empty[NVS], s_full[3], p_full[2], o_full, q_full;
+  unsigned char* k_s = base;                        // NS stages of K [128 keys][HD], K-major
+  unsigned char* v_s = k_s + NS * TILE_BYTES;       // NS stages of V [128 keys][HD], MN-major for the product
+  // Slot i (i = -2 .. n_kt - 1, stage (i + 2) % NS) holds K of tile i + 2 and V of tile i, the two tiles the MMA
+  // thread reads in its step i, under one pair of barriers: each wait of that one thread is time in which no
+  // MMA is issued.  Both producers arrive at kv_full (with their bytes, or bare where a slot lacks their tile).
+  __shared__ unsigned long long kv_full[NS], kv_empty[NS], s_full[2], p_full[2], o_done, q_full;
   __shared__ float mx_s[2][TPR][AT_ROWS];           // [tile parity][share of the keys][row]: the shares' maxima
   __shared__ float l_s[TPR][AT_ROWS];               // the shares' sums, at the end
   __shared__ unsigned tmem_slot;
@@ -225,10 +204,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
 
   if (threadIdx.x == 0) {
     dead = 0;
-    for (int s = 0; s < NKS; s++) { at_mbar_init(&k_full[s], 1); at_mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < NVS; s++) { at_mbar_init(&v_full[s], 1); at_mbar_init(&v_empty[s], 1); }
-    for (int s = 0; s < 3; s++) at_mbar_init(&s_full[s], 1);
-    at_mbar_init(&o_full, 1);
+    for (int s = 0; s < NS; s++) { at_mbar_init(&kv_full[s], 2); at_mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < 2; s++) at_mbar_init(&s_full[s], 1);
+    at_mbar_init(&o_done, 1);
     // P of tile j + 1 may be ready before the MMA thread has looked at tile j's barrier (the softmax threads
     // hand P over before they wait for the product of the tile before): two barriers, used in turn
     at_mbar_init(&p_full[0], AT_SOFTMAX_THREADS); at_mbar_init(&p_full[1], AT_SOFTMAX_THREADS);
@@ -277,30 +255,33 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     // table while this tile's stage is waited for, so no copy waits for a load of its own address.
     if (!idle) {
       const int which = warp - W_PRODUCER;            // 0 = K, 1 = V
-      const int ns = which ? NVS : NKS;
+      const int shift = which ? 0 : 2;                // slot i holds this producer's tile i + shift
       const int* bt = p.block_table + (size_t)r * p.max_blocks;
       auto page_of = [&](int j) {                     // page of this lane's box row of tile j (lanes 0..7)
         const int key0 = (kt_lo + j) * AT_KEYS + lane * 16;
-        return (lane < AT_KEYS / 16 && j < n_kt && key0 < key_hi) ? bt[key0 / p.page_size] : -1;
+        return (lane < AT_KEYS / 16 && j >= 0 && j < n_kt && key0 < key_hi) ? bt[key0 / p.page_size] : -1;
       };
-      int page_next = page_of(0);
-      for (int j = 0; j < n_kt; j++) {
+      int page_next = page_of(-2 + shift);
+      for (int i = -2; i < n_kt; i++) {
+        const int j = i + shift;                      // this producer's tile of the slot, if 0 <= j < n_kt
         int page = page_next;
         page_next = page_of(j + 1);
-        const int s = j % ns;
-        const unsigned ph = (j / ns) & 1;
-        unsigned long long* empty = which ? &v_empty[s] : &k_empty[s];
-        unsigned long long* full = which ? &v_full[s] : &k_full[s];
-        if (!at_mbar_wait(empty, ph ^ 1, &dead) && lane == 0) atomicCAS(p.status, 0, 1);
-        if (lane == 0) at_mbar_expect_tx(full, TILE_BYTES);
+        const int s = (i + 2) % NS;
+        const unsigned ph = ((i + 2) / NS) & 1;
+        if (!at_mbar_wait(&kv_empty[s], ph ^ 1, &dead) && lane == 0) atomicCAS(p.status, 0, 1);
+        const bool have = j >= 0 && j < n_kt;
+        if (lane == 0) {
+          if (have) at_mbar_expect_tx(&kv_full[s], TILE_BYTES);
+          else at_mbar_arrive(&kv_full[s]);
+        }
         __syncwarp();
-        if (lane < AT_KEYS / 16) {                    // one 16-key box row per lane
+        if (have && lane < AT_KEYS / 16) {            // one 16-key box row per lane
           const int key0 = (kt_lo + j) * AT_KEYS + lane * 16;
           if (page < 0) page = 0;                     // no such keys: any page will do, the scores are masked
           const int row0 = ((page * 2 + which) * p.G + g) * p.page_size + key0 % p.page_size;
           unsigned char* dst = (which ? v_s : k_s) + s * TILE_BYTES + lane * 2048;     // 16 keys = two groups of 8 rows
 #pragma unroll
-          for (int cb = 0; cb < NB; cb++) at_tma_2d(dst + cb * (AT_KEYS * 128), &kv_map, cb * 64, row0, full);
+          for (int cb = 0; cb < NB; cb++) at_tma_2d(dst + cb * (AT_KEYS * 128), &kv_map, cb * 64, row0, &kv_full[s]);
         }
       }
     }
@@ -310,58 +291,56 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       const unsigned idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_KEYS >> 3) << 17) | ((unsigned)(AT_ROWS >> 4) << 24);
       const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) |
                                 ((unsigned)(AT_ROWS >> 4) << 24);
-      const unsigned long long dq = at_desc_kmajor(at_smem(q_s));
-      // MMAs into one accumulator wait for each other (some 200 cycles each), MMAs into different
-      // accumulators overlap: the product of tile j is issued step by step together with the scores of tile
-      // j + 2, which go to the third S buffer -- the scores of tile j + 1 are complete by then, so the
-      // softmax threads never wait for them.
-      auto qk_step = [&](int j, int k, unsigned long long dk) {
-        // 16 columns = 32 bytes inside a 64-column block; the next block is 128 rows x 128 bytes further
-        const unsigned long long adv = (unsigned long long)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
-        at_umma(tmem + (unsigned)(j % 3) * AT_KEYS, dq + adv, dk + adv, idesc_qk, k ? 1u : 0u);
+      // Q is the A operand from tensor memory (16 columns of the contraction = 8 columns of bfloat16 pairs per
+      // step), so the scores read only K from shared memory; P likewise for the product, which reads only V.
+      // Scores of tile j + 2 go where P of tile j lies and are issued after the product of tile j (the tensor
+      // cores run a thread's MMAs in the order it issued them); the scores of tile j + 1 are complete by then,
+      // so the softmax threads never wait for them.
+      const unsigned desc_hi = AT_DESC_HI;
+      const unsigned k_lo0 = at_desc_lo(at_smem(k_s), 0);                  // K-major
+      const unsigned v_lo0 = at_desc_lo(at_smem(v_s), AT_KEYS * 128);      // MN-major: the d columns 64.. lie one
+                                                                           // [128 keys][128 bytes] block further
+      auto slot_ready = [&](int i) {                    // K of tile i + 2 and V of tile i are in shared memory
+        if (!at_mbar_wait(&kv_full[(i + 2) % NS], ((i + 2) / NS) & 1, &dead)) atomicCAS(p.status, 0, 2);
       };
-      auto k_ready = [&](int j) -> unsigned long long {
-        const int s = j % NKS;
-        if (!at_mbar_wait(&k_full[s], (j / NKS) & 1, &dead)) atomicCAS(p.status, 0, 2);
-        at_fence_after();
-        return at_desc_kmajor(at_smem(k_s + s * TILE_BYTES));
-      };
-      auto qk_done = [&](int j) {
-        at_commit(&k_empty[j % NKS]);
-        at_commit(&s_full[j % 3]);
+      auto scores = [&](int j) {                        // S of tile j from the stage of slot j - 2
+        const unsigned k_lo = k_lo0 + (unsigned)(j % NS) * (TILE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < HD / 16; k++) {
+          // 16 columns = 32 bytes inside a 64-column block; the next block is 128 rows x 128 bytes further
+          const unsigned adv = (unsigned)(((k >> 2) * (AT_ROWS * 128) + (k & 3) * 32) >> 4);
+          at_umma_ta(tmem + (unsigned)(j & 1) * AT_KEYS, tmem + T_Q + (unsigned)k * 8, k_lo + adv, desc_hi, idesc_qk, k ? 1u : 0u);
+        }
       };
       const bool mstamp = p.timeline && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
       if (!at_mbar_wait(&q_full, 0, &dead)) atomicCAS(p.status, 0, 3);
-      at_fence_after();
-      for (int j = 0; j < 2 && j < n_kt; j++) {         // the first two tiles' scores, alone
-        const unsigned long long dk = k_ready(j);
-#pragma unroll
-        for (int k = 0; k < HD / 16; k++) qk_step(j, k, dk);
-        qk_done(j);
+      for (int j = 0; j < 2; j++) {                     // slots -2 and -1: the first two tiles' scores
+        slot_ready(j - 2);
+        at_fence_after();
+        if (j < n_kt) scores(j);
+        at_commit(&kv_empty[j % NS]);
+        if (j < n_kt) at_commit(&s_full[j & 1]);
       }
       for (int j = 0; j < n_kt; j++) {
-        const int s = j % NVS;
+        const int s = (j + 2) % NS;
         if (mstamp) p.timeline[128 + j * 4 + 0] = at_now();
-        const bool ahead = j + 2 < n_kt;
-        unsigned long long dk = 0;
-        if (ahead) dk = k_ready(j + 2);
-        if (mstamp) p.timeline[128 + j * 4 + 1] = at_now();
         if (!at_mbar_wait(&p_full[j & 1], (j >> 1) & 1, &dead)) atomicCAS(p.status, 0, 4);
-        if (!at_mbar_wait(&v_full[s], (j / NVS) & 1, &dead)) atomicCAS(p.status, 0, 5);
+        if (mstamp) p.timeline[128 + j * 4 + 1] = at_now();
+        slot_ready(j);
         at_fence_after();
-        if (mstamp) p.timeline[128 + j * 4 + 2] = at_now();
-        const unsigned v_addr = at_smem(v_s + s * TILE_BYTES);
+        const unsigned v_lo = v_lo0 + (unsigned)s * (TILE_BYTES >> 4);
 #pragma unroll
         for (int k = 0; k < AT_KEYS / 16; k++) {
-          // 16 keys = two groups of 8 rows of V; the d columns 64.. lie one [128 keys][128 bytes] block further
-          const unsigned long long dv = at_desc_mnmajor(v_addr + k * 2048, AT_KEYS * 128);
-          // P of this tile lies where its scores were: 16 keys = 8 columns of bfloat16 pairs per step
-          at_umma_ta(tmem + 3 * AT_KEYS, tmem + (unsigned)(j % 3) * AT_KEYS + (unsigned)k * 8, dv, idesc_pv, k ? 1u : 0u);
-          if (ahead && k < HD / 16) qk_step(j + 2, k, dk);
+          // 16 keys = two groups of 8 rows of V (2,048 bytes); P of this tile lies where its scores were: 16 keys
+          // = 8 columns of bfloat16 pairs per step
+          at_umma_ta(tmem + T_O, tmem + (unsigned)(j & 1) * AT_KEYS + (unsigned)k * 8, v_lo + (unsigned)k * (2048 >> 4), desc_hi,
+                      idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
         }
-        at_commit(&v_empty[s]);
-        at_commit(&o_full);
-        if (ahead) qk_done(j + 2);
+        if (mstamp) p.timeline[128 + j * 4 + 2] = at_now();
+        at_commit(&o_done);
+        if (j + 2 < n_kt) scores(j + 2);
+        at_commit(&kv_empty[s]);
+        if (j + 2 < n_kt) at_commit(&s_full[j & 1]);
         if (mstamp) p.timeline[128 + j * 4 + 3] = at_now();
       }
     }
@@ -373,46 +352,38 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     const bool ok = !idle && t < n_tok;
     const int pos = pos0 + t;
     const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
-    // this thread's share of the Q row into shared memory, in the layout the MMA reads
+    const unsigned t_lane = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
+    // this thread's share of the Q row into tensor memory: bfloat16 pairs as they lie in memory, a pair a column
     {
-      const bf16* qr = p.q + (size_t)(tok0 + t) * p.q_stride + (size_t)(g * gs + hh) * HD;
+      constexpr int QC = HD / 2 / TPR;                               // columns of this share
+      static_assert(QC == 16 || QC == 32, "a share of Q is 16 or 32 columns");
+      const bf16* qr = p.q + (size_t)(tok0 + t) * p.q_stride + (size_t)(g * gs + hh) * HD + h * (HD / TPR);
+      unsigned qv[QC];
 #pragma unroll
-      for (int c = h * (HD / 8 / TPR); c < (h + 1) * (HD / 8 / TPR); c++) {
+      for (int c = 0; c < QC / 4; c++) {
         uint4 v = make_uint4(0, 0, 0, 0);
         if (ok) v = *reinterpret_cast<const uint4*>(qr + c * 8);
-        *reinterpret_cast<uint4*>(q_s + at_swz(row, c)) = v;
+        qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
       }
-      at_fence_async_smem();
+      at_tmem_st<QC>(t_lane + T_Q + h * QC, qv);
+      at_fence_before();
       at_mbar_arrive(&q_full);
     }
-    float o[DH];
-#pragma unroll
-    for (int i = 0; i < DH; i++) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    const unsigned t_lane = tmem + ((unsigned)((warp & 3) * 32) << 16);      // this warp's 32 lanes
+    float m = -INFINITY, l = 0.f;        // m: the maximum that this row's exponentials, sum and output refer to
     const bool stamp = p.timeline && threadIdx.x == 0 && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
     // keys every valid row of the tile sees need no test: all up to the first row's position and, with a
     // window, from the last row's first visible key on
     const int free_hi = pos0 + 1;
     const int free_lo = (p.window > 0 && key_hi - p.window > 0) ? key_hi - p.window : 0;
-    auto add_partial = [&](int j) {          // O += O' of tile j, once the tensor cores have made it
-      if (!at_mbar_wait(&o_full, j & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 8);
-      at_fence_after();
-      float ov[DH];
-      at_tmem_ld<DH>(t_lane + 3 * AT_KEYS + h * DH, ov);
-#pragma unroll
-      for (int i = 0; i < DH; i++) o[i] += ov[i];
-      at_fence_before();
-    };
     for (int j = 0; j < n_kt; j++) {
       const int tile_base = (kt_lo + j) * AT_KEYS;
       const int key_base = tile_base + h * KQ;
       if (stamp) p.timeline[j * 8 + 0] = at_now();
-      if (!at_mbar_wait(&s_full[j % 3], (j / 3) & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 7);
+      if (!at_mbar_wait(&s_full[j & 1], (j >> 1) & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 7);
       at_fence_after();
       if (stamp) p.timeline[j * 8 + 1] = at_now();
       float sv[KQ];
-      at_tmem_ld<KQ>(t_lane + (unsigned)(j % 3) * AT_KEYS + h * KQ, sv);
+      at_tmem_ld<KQ>(t_lane + (unsigned)(j & 1) * AT_KEYS + h * KQ, sv);
       if (stamp) p.timeline[j * 8 + 2] = at_now();
       const bool interior = tile_base >= free_lo && tile_base + AT_KEYS <= free_hi && p.scale_log2e > 0.f;
       float mx = -INFINITY;
@@ -432,12 +403,33 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       mx_s[j & 1][h][row] = mx;
       asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_THREADS) : "memory");
       if (stamp) p.timeline[j * 8 + 3] = at_now();
-      float m_new = fmaxf(m, mx);
+      float m_tile = mx;
 #pragma unroll
-      for (int o2 = 1; o2 < TPR; o2++) m_new = fmaxf(m_new, mx_s[j & 1][(h + o2) % TPR][row]);
-      const float ref = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = at_exp2(m - ref);
-      m = m_new;
+      for (int o2 = 1; o2 < TPR; o2++) m_tile = fmaxf(m_tile, mx_s[j & 1][(h + o2) % TPR][row]);
+      // The row moves to a new reference only when its maximum has grown by more than AT_RESCALE_STEP (always
+      // from "no key yet"): then its sum and its output in tensor memory are scaled down, once the product of
+      // the tile before is complete.  All threads of a row decide alike; the warp acts together, since the
+      // tensor-memory accesses are the warp's.
+      const bool grow = m_tile > m + AT_RESCALE_STEP;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = grow ? at_exp2(m - m_tile) : 1.0f;     // m = -inf: 0, and sum and output are 0 so far
+        if (grow) m = m_tile;
+        l *= alpha;
+        if (j > 0) {
+          if (!at_mbar_wait(&o_done, (j - 1) & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 8);
+          at_fence_after();
+#pragma unroll
+          for (int c = 0; c < DH; c += 32) {
+            float ov[32];
+            at_tmem_ld<32>(t_lane + T_O + h * DH + c, ov);
+            unsigned ob[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) ob[i] = __float_as_uint(ov[i] * alpha);
+            at_tmem_st<32>(t_lane + T_O + h * DH + c, ob);
+          }
+        }
+      }
+      const float ref = m == -INFINITY ? 0.f : m;
       // p = exp2(score - max) as bfloat16 pairs, kept in registers until the P tile is free
       unsigned pk[KQ / 2];
       float sum = 0.f;
@@ -448,42 +440,45 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
         sum += p0 + p1;
         pk[i] = at_pack(p0, p1);
       }
-      l = l * alpha + sum;
+      l += sum;
       if (stamp) p.timeline[j * 8 + 4] = at_now();
       // P goes into tensor memory, over the first half of this tile's own scores (every thread of the row has
-      // its scores in registers since the barrier above): the product reads it from there as its A operand,
-      // nothing passes through shared memory, and three tiles' P can be alive at once like their scores
-      at_tmem_st<KQ / 2>(t_lane + (unsigned)(j % 3) * AT_KEYS + h * (KQ / 2), pk);
-      if (stamp) p.timeline[j * 8 + 5] = at_now();
-      // the product of the tile before ran under all of the above; its result joins the output row, which
-      // then moves to the new maximum.  One arrival tells the MMA thread both things it waits for: P of this
-      // tile is in tensor memory and O' of the tile before has been read (every wait of that one thread is time
-      // in which no MMA is issued)
-      if (j > 0) add_partial(j - 1);
+      // its scores in registers since the barrier above): the product reads it from there as its A operand and
+      // nothing passes through shared memory
+      at_tmem_st<KQ / 2>(t_lane + (unsigned)(j & 1) * AT_KEYS + h * (KQ / 2), pk);
       at_fence_before();
       at_mbar_arrive(&p_full[j & 1]);
-#pragma unroll
-      for (int i = 0; i < DH; i++) o[i] *= alpha;
-      if (stamp) p.timeline[j * 8 + 6] = at_now();
+      if (stamp) p.timeline[j * 8 + 5] = at_now();
     }
-    if (n_kt > 0) add_partial(n_kt - 1);
+    if (n_kt > 0) {
+      if (!at_mbar_wait(&o_done, (n_kt - 1) & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 9);
+      at_fence_after();
+    }
     l_s[h][row] = l;
     asm volatile("bar.sync 1, %0;" ::"n"(AT_SOFTMAX_THREADS) : "memory");
-    if (ok) {
+    if (n_kt > 0) {
       float l_all = l;
 #pragma unroll
       for (int o2 = 1; o2 < TPR; o2++) l_all += l_s[(h + o2) % TPR][row];
-      const float inv = 1.f / l_all;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
       bf16* d = p.out + (size_t)(tok0 + t) * p.H * HD + (size_t)(g * gs + hh) * HD + h * DH;
 #pragma unroll
-      for (int c = 0; c < DH; c += 8) {
-        uint4 v;
-        v.x = at_pack(o[c] * inv, o[c + 1] * inv);
-        v.y = at_pack(o[c + 2] * inv, o[c + 3] * inv);
-        v.z = at_pack(o[c + 4] * inv, o[c + 5] * inv);
-        v.w = at_pack(o[c + 6] * inv, o[c + 7] * inv);
-        *reinterpret_cast<uint4*>(d + c) = v;
+      for (int c = 0; c < DH; c += 32) {
+        float ov[32];
+        at_tmem_ld<32>(t_lane + T_O + h * DH + c, ov);      // the warp's access: rows without a token take part too
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = at_pack(ov[i] * inv, ov[i + 1] * inv);
+            v.y = at_pack(ov[i + 2] * inv, ov[i + 3] * inv);
+            v.z = at_pack(ov[i + 4] * inv, ov[i + 5] * inv);
+            v.w = at_pack(ov[i + 6] * inv, ov[i + 7] * inv);
+            *reinterpret_cast<uint4*>(d + c + i) = v;
+          }
+        }
       }
+      if (stamp) p.timeline[(n_kt - 1) * 8 + 6] = at_now();
     }
   }
   pdl_launch_dependents();
@@ -527,7 +522,7 @@ static int* at_status_word() {
 
 template <int HD, int TPR>
 static int at_launch(const CUtensorMap& map, const AtParams& p, int tiles, cudaStream_t stream) {
-  size_t smem = 1024 + (size_t)(1 + AT_K_STAGES + AT_V_STAGES) * AT_ROWS * HD * 2;
+  size_t smem = 1024 + (size_t)(2 * AT_STAGES) * AT_ROWS * HD * 2;
   auto kernel = prefill_attention_tc5_kernel<HD, TPR>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     cudaGetLastError();

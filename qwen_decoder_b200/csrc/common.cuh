@@ -98,7 +98,6 @@ static inline void qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 __device__ __forceinline__ bool qd_mbar_wait_bounded(unsigned bar_smem_addr, unsigned parity, volatile int* dead,
                                                      unsigned poll_limit, unsigned long long time_limit_ns,
                                                      unsigned backoff_ns = 0) {
-  if (*dead) return false;
   unsigned long long start = 0;
   for (unsigned spin = 0; spin < poll_limit; spin++) {
     if (backoff_ns && spin) __nanosleep(backoff_ns);     // long waits of many threads: leave the issue slots alone
@@ -106,7 +105,8 @@ __device__ __forceinline__ bool qd_mbar_wait_bounded(unsigned bar_smem_addr, uns
     asm volatile(
         "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok) : "r"(bar_smem_addr), "r"(parity) : "memory");
-    if (ok) return true;
+    if (ok) return true;                                 // a phase that is complete costs one instruction
+    if (*dead) return false;
     if ((spin & 255) == 255) {
       unsigned long long now;
       asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));

@@ -359,6 +359,54 @@ def test_prefill_attention_tcgen05(cfg):
         close(outc[int(cu[r]):int(cu[r + 1])], want, dt, scale=float(vs[r].abs().max()))
 
 
+@pytest.mark.parametrize("cfg", [(16, 2, 128, 16), (4, 1, 64, 32), (28, 4, 128, 16)])
+def test_prefill_attention_tcgen05_with_a_maximum_that_grows(cfg):
+    """The tcgen05 kernel keeps a row's output in tensor memory and rescales it only when the row's maximum has
+    grown by more than 2^8 since the reference of its exponentials.  Keys are placed so that rows see both: a
+    maximum that creeps up tile by tile (key norms grow along the sequence) and two far keys, in the second
+    and in the fourth key tile, whose scores for the last tokens of one head exceed everything before by far
+    more than that step; one early key that dominates another head from the first tile on."""
+    from qwen_decoder_b200 import kernels
+    H, G, d, page_size = cfg
+    dt = torch.bfloat16
+    plan = [(0, 700), (300, 340)]
+    lens = [a + b for a, b in plan]
+    kv, bt, ks, vs = _paged_setup(dt, lens, G, d, page_size, seed=31)
+    g = torch.Generator().manual_seed(32)
+    T = sum(b for _, b in plan)
+    q = torch.randn(T, H * d, generator=g).to(dt)
+    cu = [0, plan[0][1], T]
+
+    def put(r, key, kv_head, value):              # K of one key of request r, in the list and in its page
+        ks[r][key, kv_head] = value.to(dt)
+        kv[int(bt[r, key // page_size]), 0, kv_head, key % page_size] = ks[r][key, kv_head]
+
+    for r, (a, b) in enumerate(plan):
+        n = a + b
+        for key in range(n):                      # norms grow by a factor of three along the sequence
+            for kh in range(G):
+                put(r, key, kh, ks[r][key, kh].float() * (1.0 + 2.0 * key / n))
+        last = q[cu[r + 1] - 1].float()           # the request's last token
+        put(r, 140, 0, last[:d] * 1.0)            # head 0: score about sqrt(d) at key 140 ...
+        put(r, 400, 0, last[:d] * 2.5)            # ... and 2.5 sqrt(d) at key 400
+        put(r, 5, G - 1, last[(H - 1) * d:] * 3.0)     # the last head: its maximum is in the first tile
+    out = torch.full((T, H * d), float("nan"), dtype=dt, device=DEV)
+    kernels.prefill_attention_tc5(q.to(DEV), H * d, out, kv.to(DEV), bt.to(DEV), torch.tensor(cu, dtype=torch.int32, device=DEV),
+                                  torch.tensor([a for a, _ in plan], dtype=torch.int32, device=DEV), len(plan), T, H, G, d,
+                                  page_size, 1.0 / math.sqrt(d), 0)
+    assert kernels.prefill_attention_tc5_status() == 0
+    outc = out.cpu()
+    for r, (a, b) in enumerate(plan):
+        n = a + b
+        qq = torch.zeros(n, H * d, dtype=torch.float64)
+        qq[a:] = q[cu[r]:cu[r + 1]].double()
+        want = plain_model.attention(qq, ks[r].double().reshape(n, G * d), vs[r].double().reshape(n, G * d), H, G, d, None)[a:]
+        close(outc[cu[r]:cu[r + 1]], want, dt, scale=float(vs[r].abs().max()))
+        # the far key takes all of head 0 of the last token, the early key all of the last head
+        assert float((outc[cu[r + 1] - 1, :d].float() - vs[r][400, 0].float()).abs().max()) < 0.05
+        assert float((outc[cu[r + 1] - 1, (H - 1) * d:].float() - vs[r][5, G - 1].float()).abs().max()) < 0.05
+
+
 @pytest.mark.parametrize("shape", [(1, 48, 64), (7, 130, 72), (8, 2048, 2048), (9, 100, 136), (16, 64, 1000),
                                    (33, 257, 264), (64, 96, 512)])
 def test_gemm_skinny(shape):
