@@ -329,19 +329,38 @@ def micro(args):
         run = lambda: fn(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0)
         work = {"bytes": T * (H + 2 * G) * d * 2 * 2, "flops": 4 * d * H * (T * (T + 1) // 2)}
         if args.timeline and args.micro_impl != "regs" and T >= 2048:
-            # nanosecond stamps of the CTA whose rows end at key 2047 (16 key tiles), written by the kernel itself:
-            # row 0's softmax thread (8 per tile) and the MMA thread (4 per tile); printed relative to the first
-            tl = torch.zeros(16 * 8 + 16 * 4, dtype=torch.int64, device=dev)
+            # nanosecond stamps written by the kernel itself (layout: AtParams::timeline in csrc/attention_tc5.cu): of
+            # the CTA whose rows end at key 2047 (16 key tiles) the softmax thread of row 0 and the MMA thread, tile
+            # by tile, and that CTA's phases; of every CTA its start, end, SM and number of key tiles.  Each launch is
+            # synchronised, so that no CTA starts under the launch before it.
+            n_cta = (T // (128 // (H // G)) + 2) * G
+            tl = torch.zeros(192 + 4 * n_cta, dtype=torch.int64, device=dev)
             for _ in range(3):
                 fn(q, q.stride(0), out, kv, bt, cu, st, 1, T, H, G, d, ps, 1 / math.sqrt(d), 0, tl)
-            torch.cuda.synchronize()
-            sm, mm = tl[:128].view(16, 8).cpu(), tl[128:].view(16, 4).cpu()
-            t0 = int(sm[0][0])
+                torch.cuda.synchronize()
+            sm, mm = tl[:128].view(16, 8).cpu(), tl[128:192].view(16, 4).cpu()
+            t0 = int(sm[0][7])
+            us = lambda x: (int(x) - t0) / 1e3
             names_s = ["top", "S ready", "S loaded", "maximum shared", "exponentials", "P stored"]
             names_m = ["top", "P ready", "K, V ready and product issued", "scores of tile + 2 issued"]
             for j in range(16):
-                print(f"tile {j:2d}  softmax: " + "  ".join(f"{n} {(int(sm[j][i]) - t0) / 1e3:.2f}" for i, n in enumerate(names_s)) +
-                      "  ||  mma: " + "  ".join(f"{n} {(int(mm[j][i]) - t0) / 1e3:.2f}" for i, n in enumerate(names_m)), file=sys.stderr)
+                print(f"tile {j:2d}  softmax: " + "  ".join(f"{n} {us(sm[j][i]):.2f}" for i, n in enumerate(names_s)) +
+                      "  ||  mma: " + "  ".join(f"{n} {us(mm[j][i]):.2f}" for i, n in enumerate(names_m)), file=sys.stderr)
+            phases = ["start", "tensor memory allocated", "request found", "Q stored", "last P stored",
+                      "last product complete", "end"]
+            print("that CTA: " + "  ".join(f"{n} {us(sm[i][7]):.2f}" for i, n in enumerate(phases)) +
+                  f"  output written {us(sm[15][6]):.2f}", file=sys.stderr)
+            rec = tl[192:].view(n_cta, 4).cpu()
+            rec = rec[rec[:, 0] > 0]
+            first = int(rec[:, 0].min())
+            fixed = sorted((int(e) - int(s0)) / 1e3 - 1.2 * int(n) for s0, e, _, n in rec.tolist())
+            per_sm = {}
+            for s0, e, smid, n in rec.tolist():
+                per_sm.setdefault(smid, []).append(((s0 - first) / 1e3, (e - first) / 1e3, n))
+            last = max(per_sm.values(), key=lambda v: max(x[1] for x in v))
+            print(f"{len(rec)} CTAs on {len(per_sm)} SMs; last end {(int(rec[:, 1].max()) - first) / 1e3:.1f} us; "
+                  f"a CTA's time minus 1.2 us per key tile: median {fixed[len(fixed) // 2]:.1f} us; "
+                  f"the SM that ends last ran (start, end, key tiles): {sorted(last)}", file=sys.stderr)
     for _ in range(3):
         run()
     torch.cuda.synchronize()

@@ -171,8 +171,11 @@ struct AtParams {
   int R, H, G, page_size, window, tok_tile;
   float scale_log2e;
   int* status;
-  long long* timeline;     // null, or 16 x 8 nanosecond stamps of row 0's softmax thread and 16 x 4 of the MMA thread of one
-                           // CTA with 16 key tiles (for measurements)
+  // null, or nanosecond stamps for measurements: [0, 128) 16 x 8 of row 0's softmax thread and [128, 192) 16 x 4
+  // of the MMA thread of the CTA of KV head 0 whose rows end at key 2047 (16 key tiles; slot 7 of the first seven
+  // tiles holds the CTA's own phases: start, tensor memory allocated, request found, Q stored, last P stored, last
+  // product complete, end); from 192 on four words per CTA: start, end, SM, key tiles
+  long long* timeline;
 };
 
 template <int HD, int TPR>
@@ -201,6 +204,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   __shared__ unsigned tmem_slot;
   __shared__ int dead;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long cta_t0 = p.timeline ? at_now() : 0;
 
   if (threadIdx.x == 0) {
     dead = 0;
@@ -222,6 +226,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   __syncthreads();
   at_fence_after();
   const unsigned tmem = tmem_slot;
+  const long long cta_t1 = p.timeline ? at_now() : 0;
   pdl_wait();
 
   // ---- which request and which tokens (tiles numbered request by request, the longest histories first)
@@ -236,6 +241,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     before += nt;
   }
   const bool idle = r == p.R;
+  const long long cta_t2 = p.timeline ? at_now() : 0;
   int tok0 = 0, n_tok = 0, pos0 = 0;
   if (!idle) {
     tok0 = p.cu_tokens[r] + (b - before) * p.tok_tile;
@@ -371,6 +377,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
     }
     float m = -INFINITY, l = 0.f;        // m: the maximum that this row's exponentials, sum and output refer to
     const bool stamp = p.timeline && threadIdx.x == 0 && blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS;
+    if (stamp) { p.timeline[7] = cta_t0; p.timeline[8 + 7] = cta_t1; p.timeline[16 + 7] = cta_t2; p.timeline[24 + 7] = at_now(); }
     // keys every valid row of the tile sees need no test: all up to the first row's position and, with a
     // window, from the last row's first visible key on
     const int free_hi = pos0 + 1;
@@ -451,7 +458,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
       if (stamp) p.timeline[j * 8 + 5] = at_now();
     }
     if (n_kt > 0) {
+      if (stamp) p.timeline[32 + 7] = at_now();
       if (!at_mbar_wait(&o_done, (n_kt - 1) & 1, &dead) && lane == 0) atomicCAS(p.status, 0, 9);
+      if (stamp) p.timeline[40 + 7] = at_now();
       at_fence_after();
     }
     l_s[h][row] = l;
@@ -484,6 +493,13 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   pdl_launch_dependents();
   at_fence_before();
   __syncthreads();
+  if (p.timeline && threadIdx.x == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    long long* e = p.timeline + 192 + (size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 4;
+    e[0] = cta_t0; e[1] = at_now(); e[2] = smid; e[3] = n_kt;
+    if (blockIdx.y == 0 && n_kt >= 16 && pos0 + n_tok == n_kt * AT_KEYS) p.timeline[48 + 7] = e[1];
+  }
   if (warp == W_MMA) {
     at_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
