@@ -488,6 +488,9 @@ def main():
     ap.add_argument("--micro-graph", action="store_true", help="gemm: time inside a replayed graph, cold weights")
     ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
+    ap.add_argument("--without", default=None, metavar="KINDS",
+                    help="for profiles/: time the decode step with the kernels of these kinds left out (comma list of "
+                         "ffn, attention, projections, norms); the step's results are void, only its time is printed")
     args = ap.parse_args()
     shape = SHAPES[args.shape]
     if args.layers is None:
@@ -556,6 +559,32 @@ def main():
             runner.close(rc)
         return ms, launches, ctx_mean
 
+    if args.without:
+        # What does each kind of kernel add to the step?  Their launchers are replaced by nothing (outputs keep
+        # whatever they held), the step is captured and replayed as usual, and only the time is reported.
+        kinds = [k for k in args.without.split(",") if k]
+        unknown = set(kinds) - {"ffn", "attention", "projections", "norms"}
+        if unknown:
+            print(f"bench.py: --without takes ffn, attention, projections, norms; not {sorted(unknown)}")
+            return 2
+        held = {}
+
+        def buffer(shape, dtype):
+            return held.setdefault((tuple(shape), dtype), torch.zeros(shape, dtype=dtype, device=dev))
+        if "ffn" in kinds:
+            kernels.ffn_stream = lambda x, wgu, wd, barrier: buffer(
+                (kernels.skinny_splits(x.shape[1], wd.shape[1], x.shape[0]), x.shape[0], x.shape[1]), torch.float32)
+        if "attention" in kinds:
+            kernels.decode_attention_rope = lambda *a, **k: None
+        if "projections" in kinds:
+            kernels.gemm_skinny_partial = lambda x, w, splits: buffer((splits, x.shape[0], w.shape[0]), torch.float32)
+        if "norms" in kinds:
+            kernels.add_rmsnorm = lambda *a, **k: None
+        ms, launches, _ = time_decode(args.batch, K, W)
+        print(json.dumps({"micro": "decode_step_without", "without": kinds, "batch": args.batch, "context": args.context,
+                          "layers": args.layers, "steps": K, "ms_per_step": round(ms / K, 4), "launches_per_step": launches // K,
+                          "note": "the step's results are void: a measurement of what each kind of kernel adds"}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     ms, launches, ctx_mean = time_decode(args.batch, K, W)
