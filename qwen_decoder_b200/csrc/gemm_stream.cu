@@ -404,21 +404,24 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
 
 // ---------------------------------------------------------------------------------------------
 // The feed-forward of a few tokens as ONE launch of the resident-token streamer: gate/up with the SwiGLU
-// epilogue, a grid barrier, then the down projection as split-K partial sums.  The down projection needs
-// all of h, so every CTA waits for every other one -- but its producer warp does not: it goes on filling
-// the stages with the down projection's first weights while the barrier is waited for, so the second
-// product starts with its pipeline full and the first one's tail costs nothing.  All CTAs are resident
-// (the host launches no more than fit); the barrier's spin is bounded like every other wait.
+// epilogue, then the down projection as split-K partial sums.  A CTA's share of the down projection's K needs
+// those columns of h, so it waits until the row tiles that write them are counted (a counter per chunk of
+// ST_KC columns) -- but its producer warp does not: it goes on filling the stages with the down projection's
+// first weights meanwhile, so the second product starts with its pipeline full.  All CTAs are resident (the
+// host launches no more than fit); the wait's spin is bounded like every other wait.
+#define FFN_SYNC_WORDS 64
 struct FfnArgs {
   const bf16* w1; const bf16* x1; long long ldx1; int N1, K1, n_tiles1;        // [2F, D], tokens [T, D]
   bf16* h; long long ldh;                                                       // [T, F]
   const bf16* w2; int N2, K2, n_tiles2, splits2; float* part;                   // [D, F] -> [splits2, T, D]
   int T;
-  unsigned* gbar;            // two words, zero before first use: arrivals, generation
+  unsigned* gbar;            // FFN_SYNC_WORDS words, zero before first use: per chunk of ST_KC columns of h the
+                             // row tiles of the first product that are written; last word: CTAs past their wait
   int* status;
 };
 
-__global__ void __launch_bounds__(ST_THREADS)
+#define FFN_THREADS (ST_THREADS + 32)       // consumers, the producer warp, and a warp that tells and waits
+__global__ void __launch_bounds__(FFN_THREADS)
 ffn_stream_kernel(const FfnArgs a) {
   constexpr int NST = XR_STAGES;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -427,12 +430,14 @@ ffn_stream_kernel(const FfnArgs a) {
   float* red = reinterpret_cast<float*>(xres + 8 * XR_ROW_BYTES);
   __shared__ unsigned long long full_bar[NST], empty_bar[NST], x_bar, go_bar;
   __shared__ int dead;
+  __shared__ unsigned tiles_written;       // row tiles of the first product whose columns of h this CTA has written
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     dead = 0;
     for (int s = 0; s < NST; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ST_CONSUMERS); }
     mbar_init(&x_bar, 1);
     mbar_init(&go_bar, 1);
+    tiles_written = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -514,6 +519,56 @@ ffn_stream_kernel(const FfnArgs a) {
     return;
   }
 
+  if (warp == ST_CONSUMERS + 1) {
+    // ------------------------------------------------------------ the warp that tells and waits
+    // After each row tile of the first product it counts the tile for the chunk of ST_KC columns of h it lies in
+    // (a fence, then a reduction: no consumer waits for either).  The second product needs columns [k2_begin,
+    // k2_end) of h: the warp waits until every tile that writes into them is counted -- not for the whole grid:
+    // tiles are walked in the order of h's columns, so all but the last chunks are complete while some CTAs still
+    // work on their last tile -- and lets the producer fetch them.
+    if (lane != 0) return;
+    unsigned n = 0;
+    for (int tile = blockIdx.x; tile < a.n_tiles1; tile += gridDim.x, n++) {
+      // wait for the consumers' count in shared memory (it may be several tiles ahead); bounded like every wait
+      bool seen = false;
+      for (unsigned spin = 0; spin < (1u << 24) && !dead; spin++) {
+        if (*(volatile unsigned*)&tiles_written > n) { seen = true; break; }
+        __nanosleep(64);
+      }
+      if (!seen && !dead) { dead = 1; atomicExch(a.status, 5); }
+      __threadfence();
+      asm volatile("red.relaxed.gpu.global.add.u32 [%0], 1;" ::"l"(a.gbar + (tile * 8) / ST_KC) : "memory");
+    }
+    if (!idle2 && !dead) {
+      unsigned long long start = 0;
+      for (int c = cb2; c < ce2 && !dead; c++) {
+        const unsigned target = (unsigned)(min(ST_KC, a.K2 - c * ST_KC) / 8);
+        bool ok = false;
+        for (unsigned spin = 0; spin < (1u << 26); spin++) {
+          unsigned v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.gbar + c) : "memory");
+          if (v == target) { ok = true; break; }
+          if ((spin & 1023) == 1023) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            if (start == 0) start = now;
+            else if (now - start > 2000000000ull) break;
+          }
+        }
+        if (!ok) { dead = 1; atomicExch(a.status, 4); }
+      }
+    }
+    __threadfence();
+    mbar_arrive(&go_bar);
+    // the last CTA past its wait puts the words back to zero for the next launch: every CTA has counted its
+    // tiles before it waited, and counts itself here after a fence
+    if (atomicAdd(a.gbar + FFN_SYNC_WORDS - 1, 1u) == gridDim.x - 1) {
+      __threadfence();
+      for (int c = 0; c < FFN_SYNC_WORDS; c++) a.gbar[c] = 0;
+    }
+    return;
+  }
+
   // -------------------------------------------------------------- consumers
   const int j = lane & 3, r = lane >> 2;
   unsigned it = 0;
@@ -573,34 +628,9 @@ ffn_stream_kernel(const FfnArgs a) {
       a.h[(size_t)tok * a.ldh + f] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
     }
     asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
-  }
-  // ---- every CTA's part of h is written: meet the others
-  asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
-  if (threadIdx.x == 0) {
-    volatile unsigned* gen_p = a.gbar + 1;
-    const unsigned gen = *gen_p;
-    __threadfence();
-    const unsigned arrived = atomicAdd(a.gbar, 1u);
-    if (arrived == gridDim.x - 1) {
-      a.gbar[0] = 0;
-      __threadfence();
-      atomicAdd(a.gbar + 1, 1u);
-    } else if (!dead) {
-      unsigned long long start = 0;
-      bool ok = false;
-      for (unsigned spin = 0; spin < (1u << 26); spin++) {
-        if (*gen_p != gen) { ok = true; break; }
-        if ((spin & 1023) == 1023) {
-          unsigned long long now;
-          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-          if (start == 0) start = now;
-          else if (now - start > 2000000000ull) break;
-        }
-      }
-      if (!ok) { dead = 1; atomicExch(a.status, 4); }
-    }
-    __threadfence();
-    mbar_arrive(&go_bar);
+    // this tile's 8 columns of h are written (by the threads that met at the barrier above): the telling warp
+    // makes that known to the other CTAs, so that no consumer waits for a fence
+    if (threadIdx.x == 0) { __threadfence_block(); *(volatile unsigned*)&tiles_written = tiles_written + 1; }
   }
   // ---- phase 2: down projection, partial sums of this CTA's share of K
   if (!idle2) {
@@ -737,15 +767,15 @@ extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const
 }
 
 // The feed-forward of up to 8 tokens in one launch: h = silu(x Wg^T) * (x Wu^T) (w1 = [Wg; Wu], [2F, D]) and
-// part[s] = partial sums of h W2^T over `splits2` shares of F.  `gbar`: two zeroed words of device memory that
-// stay with the caller (the kernel leaves them ready for the next launch).  Refuses what it cannot take
+// part[s] = partial sums of h W2^T over `splits2` shares of F.  `gbar`: 64 zeroed words of device memory that
+// stay with the caller (the kernel leaves them zero for the next launch).  Refuses what it cannot take
 // (more than 8 tokens, D above 2,048, a share of F wider than 2,048, more CTAs than fit on the device at once).
 extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void* h, long long ldh, const void* w2,
                              float* part, int T, int D, int F, int splits2, unsigned* gbar, int max_ctas,
                              cudaStream_t stream) {
   if (T <= 0) return 0;
   if (T > 8 || D <= 0 || F <= 0 || D % 8 != 0 || F % 8 != 0 || ldx % 8 != 0 || ldh % 8 != 0 || D > XR_KMAX ||
-      splits2 < 1 || !gbar || !part)
+      splits2 < 1 || !gbar || !part || (F + ST_KC - 1) / ST_KC > FFN_SYNC_WORDS - 1)
     return QD_ERR_UNSUPPORTED;
   if (((uintptr_t)w1 & 15) || ((uintptr_t)w2 & 15) || ((uintptr_t)x & 15) || ((uintptr_t)h & 15)) return QD_ERR_UNSUPPORTED;
   if (!xres_fits(T, F, splits2, max_ctas)) return QD_ERR_UNSUPPORTED;
@@ -760,7 +790,7 @@ extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void*
   int per_sm = 0, dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ffn_stream_kernel, ST_THREADS, smem) != cudaSuccess || per_sm < 1) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ffn_stream_kernel, FFN_THREADS, smem) != cudaSuccess || per_sm < 1) {
     cudaGetLastError();
     return QD_ERR_UNSUPPORTED;
   }
@@ -773,7 +803,7 @@ extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void*
   if (grid > max_ctas) grid = max_ctas;
   if (grid > a.n_tiles1) grid = a.n_tiles1;
   if (grid < splits2) return QD_ERR_UNSUPPORTED;
-  qd_launch(ffn_stream_kernel, dim3(grid), dim3(ST_THREADS), smem, stream, a);
+  qd_launch(ffn_stream_kernel, dim3(grid), dim3(FFN_THREADS), smem, stream, a);
   return qd_last_error();
 }
 

@@ -399,13 +399,16 @@ def ffn_stream_supported(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch
             and w_down.shape[0] == D)
 
 
+FFN_SYNC_WORDS = 64      # words of device memory a layer's one-launch feed-forward synchronises through
+
+
 def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, barrier: torch.Tensor) -> torch.Tensor:
     """float32 partial sums [splits, T, D] of (silu(x Wg^T) * (x Wu^T)) Wd^T for up to 8 tokens, in one
     launch of the weight streamer: every CTA waits for all the others between the two products, its
-    producer warp meanwhile fetches the second product's first weights.  ``barrier``: two int32 words
+    producer warp meanwhile fetches the second product's first weights.  ``barrier``: ``FFN_SYNC_WORDS`` int32 words
     on the device, zero before their first use, that belong to the caller (no two launches that may run
     at the same time share them); every launch leaves them ready for the next."""
-    assert barrier.dtype == torch.int32 and barrier.numel() >= 2 and barrier.is_cuda
+    assert barrier.dtype == torch.int32 and barrier.numel() >= FFN_SYNC_WORDS and barrier.is_cuda
     T, D = x.shape
     F = w_down.shape[1]
     _contig(w_gate_up, "w_gate_up"); _contig(w_down, "w_down")

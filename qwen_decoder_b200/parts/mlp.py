@@ -45,8 +45,8 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         if matmul_backend.mode == "auto" and kernels.ffn_stream_supported(x, self.gate_up.weight, self.down.weight):
             matmul_backend.counters["own"] += 1
-            if self._barrier is None:       # this layer's own grid barrier words (zero once; each launch resets them)
-                self._barrier = torch.zeros(2, dtype=torch.int32, device=x.device)
+            if self._barrier is None:       # this layer's own synchronisation words (zero once; each launch leaves them zero)
+                self._barrier = torch.zeros(kernels.FFN_SYNC_WORDS, dtype=torch.int32, device=x.device)
             return kernels.ffn_stream(x, self.gate_up.weight, self.down.weight, self._barrier)   # one launch
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if matmul_backend.use_skinny(x, self.gate_up.weight):

@@ -596,8 +596,9 @@ def test_decode_attention_from_partial_sums(cfg):
 
 @pytest.mark.parametrize("shape", [(8, 2048, 11008), (5, 96, 264), (1, 64, 176), (7, 1024, 2816), (3, 128, 1400)])
 def test_feed_forward_in_one_launch(shape):
-    """Gate/up with SwiGLU, a grid barrier, the down projection: against the two separate launches and
-    against float64; several times in a row (the barrier must be left ready for the next launch)."""
+    """Gate/up with SwiGLU, the wait for the columns of h a CTA's share of the down projection reads, the down
+    projection: against the two separate launches and against float64; several times in a row (the
+    synchronisation words must be left ready for the next launch)."""
     from qwen_decoder_b200 import kernels
     T, D, F = shape
     g = torch.Generator().manual_seed(31)
@@ -610,7 +611,7 @@ def test_feed_forward_in_one_launch(shape):
     want = h_ref.double().cpu() @ w2.double().cpu().t()
     gate_up = x.double().cpu() @ w1.double().cpu().t()
     h64 = torch.nn.functional.silu(gate_up[:, :F]) * gate_up[:, F:]
-    barrier = torch.zeros(2, dtype=torch.int32, device=DEV)
+    barrier = torch.zeros(kernels.FFN_SYNC_WORDS, dtype=torch.int32, device=DEV)
     for _ in range(3):
         part = kernels.ffn_stream(x, w1, w2, barrier)
         got = part.sum(0).double().cpu()
@@ -642,10 +643,10 @@ def test_a_wait_that_runs_out_ends_the_kernel_and_is_reported_once(name):
 
 @pytest.mark.gpu
 def test_a_grid_barrier_that_runs_out_is_reported_and_repaired(tmp_path):
-    """The one-launch feed-forward meets all its CTAs at a grid barrier whose spin is bounded.  With a
-    barrier word that no arrival count can satisfy the spin runs out (two seconds), the step's results are
-    void, the runner's look at the status raises and puts the barrier words back; the steps after it are
-    right again."""
+    """The CTAs of the one-launch feed-forward wait for each other's columns of h through counters, with a
+    bounded spin.  With a counter that no count of tiles can bring to its target the spin runs out (two
+    seconds), the step's results are void, the runner's look at the status raises and puts the words back; the
+    steps after it are right again."""
     import plain_model
     from tiny_configs import make_folder
     from qwen_decoder_b200 import kernels
@@ -661,11 +662,11 @@ def test_a_grid_barrier_that_runs_out_is_reported_and_repaired(tmp_path):
     ff = runner.model.layers[0].feed_forward
     assert ff._barrier is not None, "the decode step did not run the one-launch feed-forward"
     runner.check_status()
-    ff._barrier[0] = 1 << 30                    # arrivals counted from here never reach the grid's size
+    ff._barrier[0] = 1 << 30                    # tiles counted from here never reach the chunk's number
     runner.step([StepEntry(rc, seq[8:9], [0])])
     with pytest.raises(kernels.KernelError, match="gemm_stream"):
         runner.check_status()
-    assert ff._barrier.tolist() == [0, 0]
+    assert ff._barrier.tolist() == [0] * kernels.FFN_SYNC_WORDS
     logits = runner.step([StepEntry(rc, seq[9:10], [0])])
     runner.check_status()
     # position 8 was computed by the void step: its cache entries are suspect, so compare a fresh request
