@@ -163,7 +163,7 @@ class ModelRunner:
         steps since then returned is void.  Synchronises the device.  Callers look before they hand
         results out: ``Engine`` whenever requests finish, trace replay after every step that writes
         logits, and every ``STATUS_EVERY`` steps in between.  After a fault the parts put the words their
-        kernels share between launches (a grid barrier's arrival count) back to their starting values."""
+        kernels share between launches (the feed-forward's counts of written tiles) back to their starting values."""
         from .. import kernels
         try:
             kernels.check_status()

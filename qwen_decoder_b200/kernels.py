@@ -391,7 +391,7 @@ def gemm_skinny_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
 
 
 def ffn_stream_supported(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> bool:
-    """Whether the one-launch feed-forward (gate/up + SwiGLU, grid barrier, down) takes these sizes."""
+    """Whether the one-launch feed-forward (gate/up + SwiGLU, a wait between CTAs, down) takes these sizes."""
     T, D = x.shape
     F = w_down.shape[1]
     return (_FFN_FUSED and T <= 8 and D <= 2048 and few_token_impl(T) == "stream" and skinny_supported(x, w_gate_up)
@@ -404,8 +404,8 @@ FFN_SYNC_WORDS = 64      # words of device memory a layer's one-launch feed-forw
 
 def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, barrier: torch.Tensor) -> torch.Tensor:
     """float32 partial sums [splits, T, D] of (silu(x Wg^T) * (x Wu^T)) Wd^T for up to 8 tokens, in one
-    launch of the weight streamer: every CTA waits for all the others between the two products, its
-    producer warp meanwhile fetches the second product's first weights.  ``barrier``: ``FFN_SYNC_WORDS`` int32 words
+    launch of the weight streamer: between the two products a CTA waits for the others' columns of h that its
+    share of the second product reads, its producer warp meanwhile fetches the second product's first weights.  ``barrier``: ``FFN_SYNC_WORDS`` int32 words
     on the device, zero before their first use, that belong to the caller (no two launches that may run
     at the same time share them); every launch leaves them ready for the next."""
     assert barrier.dtype == torch.int32 and barrier.numel() >= FFN_SYNC_WORDS and barrier.is_cuda

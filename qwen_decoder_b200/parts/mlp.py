@@ -38,7 +38,7 @@ class SwiGLU(FeedForward):
                 "wd": self.down.weight}
 
     def reset_after_fault(self) -> None:
-        """A launch whose grid barrier ran out may have left arrivals counted: start from zero again."""
+        """A launch whose wait for the other CTAs ran out may have left tiles counted: start from zero again."""
         if self._barrier is not None:
             self._barrier.zero_()
 
