@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
 
   {
     ar_stamp(p, 0);
+    pdl_launch_dependents();      // the next kernel's CTAs may start beside these and fetch their weights; they wait for this grid's end
     const int item = blockIdx.x;
     const int s = item % p.splits, g = (item / p.splits) % G, t = item / (p.splits * G);
     const int pos = p.positions[t];

@@ -275,6 +275,7 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
   }
   __syncthreads();
 
+  pdl_launch_dependents();      // the next kernel's CTAs may start where there is room; they wait for this grid's end
   const int n_chunks = (K + ST_KC - 1) / ST_KC;
   const int stride = (int)gridDim.x / splits;                 // CTAs per share of K (the host made it >= 1)
   const int sp = (int)blockIdx.x % splits;
