@@ -419,7 +419,17 @@ struct FfnArgs {
   unsigned* gbar;            // FFN_SYNC_WORDS words, zero before first use: per chunk of ST_KC columns of h the
                              // row tiles of the first product that are written; last word: CTAs past their wait
   int* status;
+  long long* timeline;       // null, or 8 nanosecond stamps per CTA (for measurements): start, tokens there, first tile
+                             // done, first product done, wait for h over, h there, second product done
 };
+
+__device__ __forceinline__ void ffn_stamp(const FfnArgs& a, int i) {
+  if (a.timeline) {
+    long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+    a.timeline[(size_t)blockIdx.x * 8 + i] = now;
+  }
+}
 
 #define FFN_THREADS (ST_THREADS + 32)       // consumers, the producer warp, and a warp that tells and waits
 __global__ void __launch_bounds__(FFN_THREADS)
@@ -442,6 +452,7 @@ ffn_stream_kernel(const FfnArgs a) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (threadIdx.x == 0) ffn_stamp(a, 0);
 
   const int T = a.T;
   const int F = a.N1 >> 1;
@@ -559,6 +570,7 @@ ffn_stream_kernel(const FfnArgs a) {
         if (!ok) { dead = 1; atomicExch(a.status, 4); }
       }
     }
+    ffn_stamp(a, 4);
     __threadfence();
     mbar_arrive(&go_bar);
     // the last CTA past its wait puts the words back to zero for the next launch: every CTA has counted its
@@ -612,6 +624,7 @@ ffn_stream_kernel(const FfnArgs a) {
       if (!have_x) {
         if (!mbar_wait(&x_bar, 0, &dead) && lane == 0) atomicExch(a.status, 2);
         have_x = true;
+        if (threadIdx.x == 0) ffn_stamp(a, 1);
       }
       stage_mma(acc, a.K1, c, 0);
     }
@@ -631,11 +644,17 @@ ffn_stream_kernel(const FfnArgs a) {
     asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
     // this tile's 8 columns of h are written (by the threads that met at the barrier above): the telling warp
     // makes that known to the other CTAs, so that no consumer waits for a fence
-    if (threadIdx.x == 0) { __threadfence_block(); *(volatile unsigned*)&tiles_written = tiles_written + 1; }
+    if (threadIdx.x == 0) {
+      __threadfence_block();
+      *(volatile unsigned*)&tiles_written = tiles_written + 1;
+      if (tile == (int)blockIdx.x) ffn_stamp(a, 2);
+    }
   }
+  if (threadIdx.x == 0) ffn_stamp(a, 3);
   // ---- phase 2: down projection, partial sums of this CTA's share of K
   if (!idle2) {
     if (!mbar_wait(&x_bar, 1, &dead) && lane == 0) atomicExch(a.status, 2);
+    if (threadIdx.x == 0) ffn_stamp(a, 5);
     for (int tile = first2; tile < a.n_tiles2; tile += stride2) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       for (int c = cb2; c < ce2; c++) stage_mma(acc, a.K2, c, cb2);
@@ -652,6 +671,7 @@ ffn_stream_kernel(const FfnArgs a) {
       asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
     }
   }
+  if (threadIdx.x == 0) ffn_stamp(a, 6);
   pdl_launch_dependents();
 }
 
@@ -773,7 +793,7 @@ extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const
 // (more than 8 tokens, D above 2,048, a share of F wider than 2,048, more CTAs than fit on the device at once).
 extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void* h, long long ldh, const void* w2,
                              float* part, int T, int D, int F, int splits2, unsigned* gbar, int max_ctas,
-                             cudaStream_t stream) {
+                             long long* timeline, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (T > 8 || D <= 0 || F <= 0 || D % 8 != 0 || F % 8 != 0 || ldx % 8 != 0 || ldh % 8 != 0 || D > XR_KMAX ||
       splits2 < 1 || !gbar || !part || (F + ST_KC - 1) / ST_KC > FFN_SYNC_WORDS - 1)
@@ -799,7 +819,7 @@ extern "C" int qd_ffn_stream(const void* w1, const void* x, long long ldx, void*
   a.w1 = (const bf16*)w1; a.x1 = (const bf16*)x; a.ldx1 = ldx; a.N1 = 2 * F; a.K1 = D; a.n_tiles1 = (F + 7) / 8;
   a.h = (bf16*)h; a.ldh = ldh;
   a.w2 = (const bf16*)w2; a.N2 = D; a.K2 = F; a.n_tiles2 = (D + 15) / 16; a.splits2 = splits2; a.part = part;
-  a.T = T; a.gbar = gbar; a.status = status;
+  a.T = T; a.gbar = gbar; a.status = status; a.timeline = timeline;
   int grid = per_sm * sms;
   if (grid > max_ctas) grid = max_ctas;
   if (grid > a.n_tiles1) grid = a.n_tiles1;

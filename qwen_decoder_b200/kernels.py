@@ -402,12 +402,14 @@ def ffn_stream_supported(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch
 FFN_SYNC_WORDS = 64      # words of device memory a layer's one-launch feed-forward synchronises through
 
 
-def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, barrier: torch.Tensor) -> torch.Tensor:
+def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, barrier: torch.Tensor,
+               timeline: Optional[torch.Tensor] = None) -> torch.Tensor:
     """float32 partial sums [splits, T, D] of (silu(x Wg^T) * (x Wu^T)) Wd^T for up to 8 tokens, in one
     launch of the weight streamer: between the two products a CTA waits for the others' columns of h that its
     share of the second product reads, its producer warp meanwhile fetches the second product's first weights.  ``barrier``: ``FFN_SYNC_WORDS`` int32 words
     on the device, zero before their first use, that belong to the caller (no two launches that may run
-    at the same time share them); every launch leaves them ready for the next."""
+    at the same time share them); every launch leaves them ready for the next.  ``timeline``: for measurements,
+    int64 [CTAs, 8] that takes the kernel's own nanosecond stamps."""
     assert barrier.dtype == torch.int32 and barrier.numel() >= FFN_SYNC_WORDS and barrier.is_cuda
     T, D = x.shape
     F = w_down.shape[1]
@@ -417,7 +419,7 @@ def ffn_stream(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, b
     part = torch.empty((splits, T, D), dtype=torch.float32, device=x.device)
     _check(library("gemm_stream").qd_ffn_stream(
         _ptr(w_gate_up), _ptr(x), _LL(x.stride(0)), _ptr(h), _LL(h.stride(0)), _ptr(w_down), _ptr(part), _I(T), _I(D),
-        _I(F), _I(splits), _ptr(barrier), _I(stream_max_ctas()), _stream()), "ffn_stream")
+        _I(F), _I(splits), _ptr(barrier), _I(stream_max_ctas()), _ptr(timeline), _stream()), "ffn_stream")
     return part
 
 
