@@ -490,7 +490,8 @@ def main():
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
     ap.add_argument("--without", default=None, metavar="KINDS",
                     help="for profiles/: time the decode step with the kernels of these kinds left out (comma list of "
-                         "ffn, attention, projections, norms); the step's results are void, only its time is printed")
+                         "ffn, attention, projections, norms for up to 8 requests; attention, products, norms, rope, swiglu "
+                         "for more than 16); the step's results are void, only its time is printed")
     args = ap.parse_args()
     shape = SHAPES[args.shape]
     if args.layers is None:
@@ -563,9 +564,9 @@ def main():
         # What does each kind of kernel add to the step?  Their launchers are replaced by nothing (outputs keep
         # whatever they held), the step is captured and replayed as usual, and only the time is reported.
         kinds = [k for k in args.without.split(",") if k]
-        unknown = set(kinds) - {"ffn", "attention", "projections", "norms"}
+        unknown = set(kinds) - {"ffn", "attention", "projections", "norms", "products", "rope", "swiglu"}
         if unknown:
-            print(f"bench.py: --without takes ffn, attention, projections, norms; not {sorted(unknown)}")
+            print(f"bench.py: --without takes ffn, attention, projections, norms, products, rope, swiglu; not {sorted(unknown)}")
             return 2
         held = {}
 
@@ -576,6 +577,13 @@ def main():
                 (kernels.skinny_splits(x.shape[1], wd.shape[1], x.shape[0]), x.shape[0], x.shape[1]), torch.float32)
         if "attention" in kinds:
             kernels.decode_attention_rope = lambda *a, **k: None
+            kernels.decode_attention = lambda *a, **k: None
+        if "products" in kinds:                    # the library products of more than 16 tokens
+            matmul_backend._cublas = lambda x, w, bias, out: None
+        if "rope" in kinds:
+            kernels.rope_kv_write = lambda *a, **k: None
+        if "swiglu" in kinds:
+            kernels.swiglu = lambda *a, **k: None
         if "projections" in kinds:
             kernels.gemm_skinny_partial = lambda x, w, splits: buffer((splits, x.shape[0], w.shape[0]), torch.float32)
         if "norms" in kinds:
