@@ -160,8 +160,10 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
       reinterpret_cast<unsigned*>(qs + (size_t)gs * LD)[(w / (HD / 2)) * (LD / 2) + (w % (HD / 2))] = 0u;
     const int n_tasks = (gs + (owns_new ? 2 : 0)) * (HD / 2);
     constexpr int NB = 4;
+    constexpr int NP = 4;          // shares of the sums whose loads are all in flight before any is used
     for (int base = threadIdx.x; base < n_tasks; base += AR_THREADS * NB) {
       float a[NB], b[NB], cv[NB], sv[NB];
+      float pa[NB][NP], pb[NB][NP];
       int i0[NB], i1[NB], row[NB];
 #pragma unroll
       for (int u = 0; u < NB; u++) {
@@ -180,9 +182,29 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
           if (p.bias) { a[u] = p.bias[e + i0[u]]; b[u] = p.bias[e + i1[u]]; }
           if (rot && p.cos_t) { cv[u] = p.cos_t[(size_t)pos * half + pp]; sv[u] = p.sin_t[(size_t)pos * half + pp]; }
           const float* src = acc + e;
-          for (int q = 0; q < p.n_parts; q++) {
-            a[u] += __ldcg(src + q * part_stride + i0[u]);
-            b[u] += __ldcg(src + q * part_stride + i1[u]);
+#pragma unroll
+          for (int q = 0; q < NP; q++) {
+            pa[u][q] = q < p.n_parts ? __ldcg(src + q * part_stride + i0[u]) : 0.f;
+            pb[u][q] = q < p.n_parts ? __ldcg(src + q * part_stride + i1[u]) : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < NP; q++) pa[u][q] = pb[u][q] = 0.f;
+        }
+      }
+      // The loads of all shares (up to NP) are out before any is used: a loop over a number of shares known only
+      // at run time would wait for each share's loads in turn.  The sums keep the order of the shares; more than
+      // NP shares: the rest one after the other.
+#pragma unroll
+      for (int u = 0; u < NB; u++) {
+        if (row[u] < 0) continue;
+#pragma unroll
+        for (int q = 0; q < NP; q++) { a[u] += pa[u][q]; b[u] += pb[u][q]; }
+        if (p.n_parts > NP) {
+          const int e = (row[u] < gs ? g * gs + row[u] : (row[u] == gs ? H + g : H + G + g)) * HD;
+          for (int q = NP; q < p.n_parts; q++) {
+            a[u] += __ldcg(acc + e + q * part_stride + i0[u]);
+            b[u] += __ldcg(acc + e + q * part_stride + i1[u]);
           }
         }
       }

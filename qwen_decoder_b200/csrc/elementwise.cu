@@ -81,12 +81,19 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, cons
                        TO* __restrict__ out, const int* __restrict__ rows, int D, float eps, int write_back,
                        int n_parts, size_t part_stride) {
   pdl_launch_dependents();
+  // the norm's weight does not come from the kernel before: it travels while that kernel is waited for, and is
+  // no round trip of its own after the sum of squares
+  const int n4 = D >> 2;
+  float4 v[VPT], wv[VPT];
+#pragma unroll
+  for (int q = 0; q < VPT; q++) {
+    const int i4 = threadIdx.x + q * blockDim.x;
+    wv[q] = i4 < n4 ? reinterpret_cast<const float4*>(w)[i4] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   pdl_wait();
   __shared__ float scratch[40];
   int r = blockIdx.x;
   size_t s = rows ? (size_t)rows[r] : (size_t)r;
-  int n4 = D >> 2;
-  float4 v[VPT];
   float ss = 0.f;
 #pragma unroll
   for (int q = 0; q < VPT; q++) {
@@ -129,7 +136,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, cons
   for (int q = 0; q < VPT; q++) {
     int i4 = threadIdx.x + q * blockDim.x;
     if (i4 < n4) {
-      float4 ww = reinterpret_cast<const float4*>(w)[i4];
+      const float4 ww = wv[q];
       float o0 = v[q].x * inv * ww.x, o1 = v[q].y * inv * ww.y, o2 = v[q].z * inv * ww.z, o3 = v[q].w * inv * ww.w;
       if (sizeof(TO) == 4) {
         reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)r * D)[i4] = make_float4(o0, o1, o2, o3);
