@@ -78,8 +78,7 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
   constexpr int STAGE = 2 * 16 * LD;                                  // elements of a stage: K chunk, V chunk
   float* mm = reinterpret_cast<float*>(kvs + (size_t)AR_WARPS * NS * STAGE);     // merge: [warps][16]
   float* ml = mm + AR_WARPS * 16;                                     // [warps][16]
-  float* fac = ml + AR_WARPS * 16;                                    // combine: [16][64] x 3
-  bf16* newkv = reinterpret_cast<bf16*>(fac + 3 * 16 * 64);          // the token's own k and v: [2][HD]
+  bf16* newkv = reinterpret_cast<bf16*>(ml + AR_WARPS * 16);         // the token's own k and v: [2][HD]
   __shared__ unsigned s_ticket;
   const size_t page_elems = (size_t)2 * G * p.page_size * HD;
   const int half = p.rotary_dim >> 1;
@@ -346,76 +345,61 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
     }
     ar_stamp(p, 5);
     if (p.splits > 1) {
-      __threadfence();
+      // The CTA's partial results are written by all its threads; they meet, then one thread takes the ticket
+      // with release and acquire at GPU scope: the barrier before it puts the others' writes before the release,
+      // the barrier after it puts the others' reads after the acquire.  One fence inside the atomic instead of
+      // one per thread before it and another after it.
       __syncthreads();
-      if (threadIdx.x == 0) s_ticket = atomicAdd(&p.tickets[(size_t)t * G + g], 1u);
+      if (threadIdx.x == 0) {
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.tickets + (size_t)t * G + g) : "memory");
+        s_ticket = old;
+      }
       __syncthreads();
       ar_stamp(p, 6);
       if (s_ticket == (unsigned)p.splits - 1) {          // the last item of this (t, g) combines
-        __threadfence();
-        float* pm = fac + 16 * 64;
-        float* pl = pm + 16 * 64;
-        // the partial outputs of the first 16 splits are requested first, so that they travel while the
-        // maxima and sums are read and the factors made
+        // A thread takes four output columns of one head (a warp: one head when HD = 128).  It asks for the
+        // maxima and sums of all splits of its head and for its columns of the first 16 partial outputs in one
+        // go, makes the factors itself (the lanes of a warp read the same maxima and sums: one access) and adds
+        // up: one trip through L2, no exchange through shared memory, no barrier.
         constexpr int PB = 16;
         const int n_out = gs * (HD / 4);
-        float4 pv[PB];
-        {
-          const int idx = threadIdx.x;
-          const int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
-          const size_t base = ((size_t)t * H + (size_t)g * gs + row) * p.splits;
-#pragma unroll
-          for (int u = 0; u < PB; u++)
-            pv[u] = (idx < n_out && u < p.splits)
-                        ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + u) * HD) + d4)
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        for (int idx = threadIdx.x; idx < gs * p.splits; idx += AR_THREADS) {
-          int row = idx / p.splits, sp = idx - row * p.splits;
-          size_t pi = ((size_t)t * H + (size_t)g * gs + row) * p.splits + sp;
-          float2 v = __ldcg(reinterpret_cast<const float2*>(p.part_ml) + pi);
-          pm[row * 64 + sp] = v.x;
-          pl[row * 64 + sp] = v.y;
-        }
-        __syncthreads();
-        for (int row = warp; row < gs; row += AR_WARPS) {        // a warp per row; a lane takes splits lane, lane + 32
-          const float ma = lane < p.splits ? pm[row * 64 + lane] : -INFINITY;
-          const float mb = lane + 32 < p.splits ? pm[row * 64 + lane + 32] : -INFINITY;
-          float M = fmaxf(ma, mb);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-          const float ea = lane < p.splits ? ar_exp2(ma - M) : 0.f;
-          const float eb = lane + 32 < p.splits ? ar_exp2(mb - M) : 0.f;
-          float Lsum = (lane < p.splits ? pl[row * 64 + lane] * ea : 0.f) +
-                       (lane + 32 < p.splits ? pl[row * 64 + lane + 32] * eb : 0.f);
-          Lsum = warp_sum(Lsum);
-          const float inv = 1.f / Lsum;
-          if (lane < p.splits) fac[row * 64 + lane] = ea * inv;
-          if (lane + 32 < p.splits) fac[row * 64 + lane + 32] = eb * inv;
-        }
-        __syncthreads();
         for (int idx = threadIdx.x; idx < n_out; idx += AR_THREADS) {
           const int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
           const size_t base = ((size_t)t * H + (size_t)g * gs + row) * p.splits;
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int s0 = 0; s0 < p.splits; s0 += PB) {
-            if (idx != (int)threadIdx.x || s0 > 0) {
+          const float2* ml_g = reinterpret_cast<const float2*>(p.part_ml) + base;
+          float2 mlv[PB];
+          float4 pv[PB];
 #pragma unroll
-              for (int u = 0; u < PB; u++)
-                pv[u] = s0 + u < p.splits
-                            ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + s0 + u) * HD) + d4)
-                            : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < PB; u++) {
-              const float f = s0 + u < p.splits ? fac[row * 64 + s0 + u] : 0.f;
-              a.x += pv[u].x * f; a.y += pv[u].y * f; a.z += pv[u].z * f; a.w += pv[u].w * f;
-            }
+          for (int u = 0; u < PB; u++) {
+            mlv[u] = u < p.splits ? __ldcg(ml_g + u) : make_float2(-INFINITY, 0.f);
+            pv[u] = u < p.splits ? __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + u) * HD) + d4)
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
           }
+          float M = -INFINITY;
+#pragma unroll
+          for (int u = 0; u < PB; u++) M = fmaxf(M, mlv[u].x);
+          for (int s0 = PB; s0 < p.splits; s0++) M = fmaxf(M, __ldcg(ml_g + s0).x);      // more than 16 splits
+          float Lsum = 0.f;
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < PB; u++) {
+            const float f = u < p.splits ? ar_exp2(mlv[u].x - M) : 0.f;
+            Lsum += mlv[u].y * f;
+            a.x += pv[u].x * f; a.y += pv[u].y * f; a.z += pv[u].z * f; a.w += pv[u].w * f;
+          }
+          for (int s0 = PB; s0 < p.splits; s0++) {
+            const float2 v = __ldcg(ml_g + s0);
+            const float4 o4 = __ldcg(reinterpret_cast<const float4*>(p.part_o + (base + s0) * HD) + d4);
+            const float f = ar_exp2(v.x - M);
+            Lsum += v.y * f;
+            a.x += o4.x * f; a.y += o4.y * f; a.z += o4.z * f; a.w += o4.w * f;
+          }
+          const float inv = 1.f / Lsum;
           bf16* dst = p.out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
           uint2 raw;
-          raw.x = ar_pack(a.x, a.y);
-          raw.y = ar_pack(a.z, a.w);
+          raw.x = ar_pack(a.x * inv, a.y * inv);
+          raw.y = ar_pack(a.z * inv, a.w * inv);
           *reinterpret_cast<uint2*>(dst) = raw;
         }
         if (threadIdx.x == 0) p.tickets[(size_t)t * G + g] = 0;
@@ -430,7 +414,7 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
 template <int HD, int NS>
 static int ar_launch_ns(const ArParams& p, cudaStream_t stream) {
   size_t smem = (size_t)16 * (HD + AR_PAD) * sizeof(bf16) + (size_t)AR_WARPS * NS * 2 * 16 * (HD + AR_PAD) * sizeof(bf16) +
-                (size_t)AR_WARPS * 16 * 2 * sizeof(float) + (size_t)3 * 16 * 64 * sizeof(float) +
+                (size_t)AR_WARPS * 16 * 2 * sizeof(float) +
                 (size_t)2 * HD * sizeof(bf16);
   auto kernel = decode_attention_rope_kernel<HD, NS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {

@@ -124,51 +124,60 @@ __device__ __forceinline__ void dec_finish(float (&o)[HD / 8][4], float m0, floa
     }
   }
   if (splits == 1 || tickets == nullptr) return;   // without tickets a combine kernel follows
-  // the CTA that finishes last for this (token, kv head) adds up all partial results
+  // The CTA that finishes last for this (token, kv head) adds up all partial results.  The partial results are
+  // written by all threads; they meet, then one thread takes the ticket with release and acquire at GPU scope:
+  // the barrier before it puts the others' writes before the release, the barrier after it the others' reads
+  // after the acquire.
   __shared__ unsigned s_ticket;
-  __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[(size_t)t * G + g], 1u);
+  if (threadIdx.x == 0) {
+    unsigned old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(tickets + (size_t)t * G + g) : "memory");
+    s_ticket = old;
+  }
   __syncthreads();
   if (s_ticket != (unsigned)splits - 1) return;
-  __threadfence();
-  // weights of the partial results: f[row][sp] = 2^(m_sp - M) / sum_sp l_sp 2^(m_sp - M), in smem
-  // (reusing the merge area: [16 rows][splits] after the (m, l) pairs have been read)
-  float* fac = reinterpret_cast<float*>(smem_raw);                 // [gs][splits]
-  float* pm = fac + 16 * 64;                                       // [gs][splits] maxima
-  float* pl = pm + 16 * 64;                                        // [gs][splits] denominators
-  for (int idx = threadIdx.x; idx < gs * splits; idx += DEC_WARPS * 32) {
-    int row = idx / splits, sp = idx - row * splits;
-    size_t pi = ((size_t)t * H + (size_t)g * gs + row) * splits + sp;
-    float2 ml2 = __ldcg(reinterpret_cast<const float2*>(part_ml) + pi);
-    pm[row * 64 + sp] = ml2.x;
-    pl[row * 64 + sp] = ml2.y;
-  }
-  __syncthreads();
-  if (threadIdx.x < gs) {
-    int row = threadIdx.x;
-    float M = -INFINITY;
-    for (int sp = 0; sp < splits; sp++) M = fmaxf(M, pm[row * 64 + sp]);
-    float L = 0.f;
-    for (int sp = 0; sp < splits; sp++) L += pl[row * 64 + sp] * exp2f(pm[row * 64 + sp] - M);
-    float invL = 1.f / L;
-    for (int sp = 0; sp < splits; sp++) fac[row * 64 + sp] = exp2f(pm[row * 64 + sp] - M) * invL;
-  }
-  __syncthreads();
+  // A thread takes four output columns of one head.  It asks for the maxima and sums of all splits of its head
+  // and for its columns of the first 16 partial outputs in one go, makes the weights 2^(m_sp - M) itself (the
+  // lanes of a warp that share a head read the same words: one access) and adds up: one trip through L2, no
+  // exchange through shared memory, no barrier.
+  constexpr int PB = 16;
   for (int idx = threadIdx.x; idx < gs * (HD / 4); idx += DEC_WARPS * 32) {
-    int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
-    size_t base = ((size_t)t * H + (size_t)g * gs + row) * splits;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int sp = 0; sp < splits; sp++) {
-      float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + sp) * HD) + d4);
-      float f = fac[row * 64 + sp];
-      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+    const int row = idx / (HD / 4), d4 = idx - row * (HD / 4);
+    const size_t base = ((size_t)t * H + (size_t)g * gs + row) * splits;
+    const float2* ml_g = reinterpret_cast<const float2*>(part_ml) + base;
+    float2 mlv[PB];
+    float4 pv[PB];
+#pragma unroll
+    for (int u = 0; u < PB; u++) {
+      mlv[u] = u < splits ? __ldcg(ml_g + u) : make_float2(-INFINITY, 0.f);
+      pv[u] = u < splits ? __ldcg(reinterpret_cast<const float4*>(part_o + (base + u) * HD) + d4)
+                         : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    float M = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < PB; u++) M = fmaxf(M, mlv[u].x);
+    for (int sp = PB; sp < splits; sp++) M = fmaxf(M, __ldcg(ml_g + sp).x);      // more than 16 splits
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < PB; u++) {
+      const float f = u < splits ? exp2f(mlv[u].x - M) : 0.f;
+      L += mlv[u].y * f;
+      acc.x += pv[u].x * f; acc.y += pv[u].y * f; acc.z += pv[u].z * f; acc.w += pv[u].w * f;
+    }
+    for (int sp = PB; sp < splits; sp++) {
+      const float2 v = __ldcg(ml_g + sp);
+      const float4 o4 = __ldcg(reinterpret_cast<const float4*>(part_o + (base + sp) * HD) + d4);
+      const float f = exp2f(v.x - M);
+      L += v.y * f;
+      acc.x += o4.x * f; acc.y += o4.y * f; acc.z += o4.z * f; acc.w += o4.w * f;
+    }
+    const float invL = 1.f / L;
     bf16* dst = out + (size_t)t * H * HD + ((size_t)g * gs + row) * HD + 4 * d4;
     uint2 raw;
-    raw.x = pack_bf16(acc.x, acc.y);
-    raw.y = pack_bf16(acc.z, acc.w);
+    raw.x = pack_bf16(acc.x * invL, acc.y * invL);
+    raw.y = pack_bf16(acc.z * invL, acc.w * invL);
     *reinterpret_cast<uint2*>(dst) = raw;
   }
   if (threadIdx.x == 0) tickets[(size_t)t * G + g] = 0;   // ready for the next launch
