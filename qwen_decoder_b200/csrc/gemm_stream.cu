@@ -253,6 +253,38 @@ gemm_stream_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long 
 #define XR_STAGES 2
 #define XR_STAGE_BYTES (16 * ST_ROW_BYTES)
 
+// One stage of the resident-token kernels for one consumer warp: its quarter of the stage's k (ST_KC / 4), in
+// steps of 32.  All loads from shared memory are issued before the first MMA, and the MMAs run as two chains
+// that are added at the end: a warp that has its data already (the first stage of a launch, a small product)
+// spends its time on latencies, not on arithmetic.  k-steps past K feed zeros.
+__device__ __forceinline__ void xr_stage_mma(float (&acc)[4], const unsigned char* st, const unsigned char* xs,
+                                             int k_stage, int K, int warp, int j, int r) {
+  constexpr int NU = ST_KC / 32 / ST_CONSUMERS;
+  uint4 lo[NU], hi[NU], b[NU];
+#pragma unroll
+  for (int u = 0; u < NU; u++) {
+    const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
+    const bool in = k_stage + kq + 8 * j < K;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const size_t col = (size_t)(kq + 8 * j) * 2;
+    lo[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
+    hi[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
+    // token rows past T were never copied: whatever is there only reaches columns that are not stored
+    b[u] = in ? *reinterpret_cast<const uint4*>(xs + (size_t)r * XR_ROW_BYTES + col) : zero;
+  }
+  float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int u = 0; u < NU; u += 2) {
+    mma16816(acc, lo[u].x, hi[u].x, lo[u].y, hi[u].y, b[u].x, b[u].y);
+    mma16816(acc2, lo[u + 1].x, hi[u + 1].x, lo[u + 1].y, hi[u + 1].y, b[u + 1].x, b[u + 1].y);
+    mma16816(acc, lo[u].z, hi[u].z, lo[u].w, hi[u].w, b[u].z, b[u].w);
+    mma16816(acc2, lo[u + 1].z, hi[u + 1].z, lo[u + 1].w, hi[u + 1].w, b[u + 1].z, b[u + 1].w);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) acc[i] += acc2[i];
+}
+
+
 template <int EPI, typename TO>
 __global__ void __launch_bounds__(ST_THREADS)
 gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long long ldx,
@@ -345,20 +377,7 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
       }
       const unsigned char* st = stages + (size_t)s * XR_STAGE_BYTES;
       const unsigned char* xs = xres + (size_t)(c - c_begin) * ST_KC * 2;
-#pragma unroll
-      for (int u = 0; u < ST_KC / 32 / ST_CONSUMERS; u++) {
-        const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
-        if (c * ST_KC + kq >= K) break;                 // the whole k-step lies past K (same for all lanes)
-        const bool in = c * ST_KC + kq + 8 * j < K;     // lanes past K feed zeros; every lane runs the MMAs
-        const uint4 zero = make_uint4(0, 0, 0, 0);
-        const size_t col = (size_t)(kq + 8 * j) * 2;
-        uint4 lo = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
-        uint4 hi = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
-        // token rows past T were never copied: whatever is there only reaches columns that are not stored
-        uint4 b = in ? *reinterpret_cast<const uint4*>(xs + (size_t)r * XR_ROW_BYTES + col) : zero;
-        mma16816(acc, lo.x, hi.x, lo.y, hi.y, b.x, b.y);
-        mma16816(acc, lo.z, hi.z, lo.w, hi.w, b.z, b.w);
-      }
+      xr_stage_mma(acc, st, xs, c * ST_KC, K, warp, j, r);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
@@ -591,19 +610,7 @@ ffn_stream_kernel(const FfnArgs a) {
     if (!mbar_wait(&full_bar[s], ph, &dead) && lane == 0) atomicExch(a.status, 2);
     const unsigned char* st = stages + (size_t)s * XR_STAGE_BYTES;
     const unsigned char* xs = xres + (size_t)(c - c_first) * ST_KC * 2;
-#pragma unroll
-    for (int u = 0; u < ST_KC / 32 / ST_CONSUMERS; u++) {
-      const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
-      if (c * ST_KC + kq >= K) break;
-      const bool in = c * ST_KC + kq + 8 * j < K;
-      const uint4 zero = make_uint4(0, 0, 0, 0);
-      const size_t col = (size_t)(kq + 8 * j) * 2;
-      uint4 lo = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
-      uint4 hi = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
-      uint4 b = in ? *reinterpret_cast<const uint4*>(xs + (size_t)r * XR_ROW_BYTES + col) : zero;
-      mma16816(acc, lo.x, hi.x, lo.y, hi.y, b.x, b.y);
-      mma16816(acc, lo.z, hi.z, lo.w, hi.w, b.z, b.w);
-    }
+    xr_stage_mma(acc, st, xs, c * ST_KC, K, warp, j, r);
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
     it++;
