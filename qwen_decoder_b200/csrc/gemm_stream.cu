@@ -176,6 +176,32 @@ gemm_stream_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long 
       if (!mbar_wait(&full_bar[s], ph, &dead) && lane == 0) atomicExch(status, 2);
       const unsigned char* st = stages + (size_t)s * STAGE_BYTES;
       // this warp's quarter of the stage: k-steps of 32 at kq = warp * (ST_KC / 4) + u * 32
+      if (TN == 1) {
+        // one tile of tokens: every load from shared memory before the first MMA, two chains of MMAs (as
+        // xr_stage_mma does it; the token rows lie below the 16 weight rows of the stage)
+        constexpr int NU = ST_KC / 32 / ST_CONSUMERS;
+        uint4 lo[NU], hi[NU], b[NU];
+#pragma unroll
+        for (int u = 0; u < NU; u++) {
+          const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
+          const bool in = c * ST_KC + kq + 8 * j < K;
+          const uint4 zero = make_uint4(0, 0, 0, 0);
+          const size_t col = (size_t)(kq + 8 * j) * 2;
+          lo[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
+          hi[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
+          b[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)(16 + r) * ST_ROW_BYTES + col) : zero;
+        }
+        float acc2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int u = 0; u < NU; u += 2) {
+          mma16816(acc[0], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b[u].x, b[u].y);
+          mma16816(acc2, lo[u + 1].x, hi[u + 1].x, lo[u + 1].y, hi[u + 1].y, b[u + 1].x, b[u + 1].y);
+          mma16816(acc[0], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b[u].z, b[u].w);
+          mma16816(acc2, lo[u + 1].z, hi[u + 1].z, lo[u + 1].w, hi[u + 1].w, b[u + 1].z, b[u + 1].w);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[0][i] += acc2[i];
+      } else
 #pragma unroll
       for (int u = 0; u < ST_KC / 32 / ST_CONSUMERS; u++) {
         const int kq = warp * (ST_KC / ST_CONSUMERS) + u * 32;
