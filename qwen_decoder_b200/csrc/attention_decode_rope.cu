@@ -229,6 +229,11 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    // q as MMA fragments, once for all chunks: matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15) in the order a0..a3
+    unsigned qa[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++)
+      ar_ldmatrix_x4(qa[kk], qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
     int it = 0;
     for (int c = c_first; c < c1; c += AR_WARPS, it++) {
       const int key0 = c * 16;
@@ -247,18 +252,29 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
         }
         __syncwarp();
       }
-      float sc[2][4];
+      // the chunk's K fragments are all loaded before the first MMA; four chains of MMAs (keys 0-7 and 8-15,
+      // even and odd k-steps) that are added at the end
+      float sc[2][4], sd[2][4];
 #pragma unroll
-      for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+      for (int n = 0; n < 2; n++) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = sd[n][0] = sd[n][1] = sd[n][2] = sd[n][3] = 0.f;
+      unsigned kb[HD / 16][4];
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; kk++)
+        ar_ldmatrix_x4(kb[kk], ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
 #pragma unroll
       for (int kk = 0; kk < HD / 16; kk++) {
-        unsigned qa[4], b[4];
-        // q fragment: matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15) in the order a0..a3 of the mma
-        ar_ldmatrix_x4(qa, qs + ((lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
-        ar_ldmatrix_x4(b, ks + ((lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
-        ar_mma(sc[0], qa[0], qa[1], qa[2], qa[3], b[0], b[1]);
-        ar_mma(sc[1], qa[0], qa[1], qa[2], qa[3], b[2], b[3]);
+        if (kk & 1) {
+          ar_mma(sd[0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kb[kk][0], kb[kk][1]);
+          ar_mma(sd[1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kb[kk][2], kb[kk][3]);
+        } else {
+          ar_mma(sc[0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kb[kk][0], kb[kk][1]);
+          ar_mma(sc[1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kb[kk][2], kb[kk][3]);
+        }
       }
+#pragma unroll
+      for (int n = 0; n < 2; n++)
+#pragma unroll
+        for (int jx = 0; jx < 4; jx++) sc[n][jx] += sd[n][jx];
 #pragma unroll
       for (int n = 0; n < 2; n++)
 #pragma unroll
@@ -303,16 +319,17 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
     pdl_launch_dependents();
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    // ---- merge the 8 warps; a warp's partial output [16][HD] float32 lies over its own K/V chunk buffers
-    // (a stage is 2 * 16 * LD bfloat16 = 16 * (HD + 8) floats), which it no longer reads
+    // ---- merge the 8 warps; a warp's partial output [16][HD + 8] float32 lies over its own K/V chunk buffers
+    // (a stage is 2 * 16 * LD bfloat16 = 16 * (HD + 8) floats), which it no longer reads.  Rows HD + 8 floats
+    // apart: the eight rows a store instruction touches fall on different banks (two by two)
+    constexpr int OLD = HD + 8;
     {
       const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
       __syncwarp();
 #pragma unroll
       for (int n = 0; n < HD / 8; n++) {
-        float* d0 = reinterpret_cast<float*>(wbuf) + (size_t)r0 * HD + n * 8 + cq;
-        float* d1 = reinterpret_cast<float*>(wbuf) + (size_t)r1 * HD + n * 8 + cq;
-        d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(wbuf) + (size_t)r0 * OLD + n * 8 + cq) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(reinterpret_cast<float*>(wbuf) + (size_t)r1 * OLD + n * 8 + cq) = make_float2(o[n][2], o[n][3]);
       }
       if ((lane & 3) == 0) {
         mm[warp * 16 + r0] = m0; mm[warp * 16 + r1] = m1;
@@ -320,26 +337,34 @@ __global__ void __launch_bounds__(AR_THREADS, NS == 1 ? 2 : 1) decode_attention_
       }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < gs * HD; idx += AR_THREADS) {
-      int row = idx / HD, dim = idx - row * HD;
+    // a thread takes four columns of a head: the factors of the eight warps once, the sums as float4
+    for (int idx = threadIdx.x; idx < gs * (HD / 4); idx += AR_THREADS) {
+      const int row = idx / (HD / 4), dim = (idx - row * (HD / 4)) * 4;
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < AR_WARPS; w++) M = fmaxf(M, mm[w * 16 + row]);
-      float Lsum = 0.f, O = 0.f;
+      float Lsum = 0.f;
+      float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
       if (M != -INFINITY) {
 #pragma unroll
         for (int w = 0; w < AR_WARPS; w++) {
-          float f = ar_exp2(mm[w * 16 + row] - M);
+          const float f = ar_exp2(mm[w * 16 + row] - M);
           Lsum += ml[w * 16 + row] * f;
-          O += reinterpret_cast<const float*>(kvs + (size_t)w * NS * STAGE)[(size_t)row * HD + dim] * f;
+          const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(kvs + (size_t)w * NS * STAGE) +
+                                                            (size_t)row * OLD + dim);
+          O.x += v.x * f; O.y += v.y * f; O.z += v.z * f; O.w += v.w * f;
         }
       }
-      int hd = g * gs + row;
+      const int hd = g * gs + row;
       if (p.splits == 1) {
-        p.out[(size_t)t * H * HD + (size_t)hd * HD + dim] = __float2bfloat16_rn(O / Lsum);
+        const float inv = 1.f / Lsum;
+        uint2 raw;
+        raw.x = ar_pack(O.x * inv, O.y * inv);
+        raw.y = ar_pack(O.z * inv, O.w * inv);
+        *reinterpret_cast<uint2*>(p.out + (size_t)t * H * HD + (size_t)hd * HD + dim) = raw;
       } else {
-        size_t pi = ((size_t)t * H + hd) * p.splits + s;
-        p.part_o[pi * HD + dim] = O;
+        const size_t pi = ((size_t)t * H + hd) * p.splits + s;
+        *reinterpret_cast<float4*>(p.part_o + pi * HD + dim) = O;
         if (dim == 0) { p.part_ml[pi * 2] = M; p.part_ml[pi * 2 + 1] = Lsum; }
       }
     }
