@@ -83,16 +83,17 @@ __device__ __forceinline__ void dec_finish(float (&o)[HD / 8][4], float m0, floa
   l1 = quad_sum(l1);
   __syncthreads();  // every warp is done with its stage buffers: reuse them for the merge
 
-  float* mo = reinterpret_cast<float*>(smem_raw);             // [warps][16][HD]
-  float* mm = mo + DEC_WARPS * 16 * HD;                       // [warps][16]
+  // rows HD + 8 floats apart: the eight rows a store instruction touches fall on different banks (two by two)
+  constexpr int OLD = HD + 8;
+  float* mo = reinterpret_cast<float*>(smem_raw);             // [warps][16][HD + 8]
+  float* mm = mo + DEC_WARPS * 16 * OLD;                      // [warps][16]
   float* ml = mm + DEC_WARPS * 16;                            // [warps][16]
   {
     const int r0 = lane >> 2, r1 = r0 + 8, cq = (lane & 3) * 2;
 #pragma unroll
     for (int n = 0; n < HD / 8; n++) {
-      float* d0 = mo + ((size_t)warp * 16 + r0) * HD + n * 8 + cq;
-      float* d1 = mo + ((size_t)warp * 16 + r1) * HD + n * 8 + cq;
-      d0[0] = o[n][0]; d0[1] = o[n][1]; d1[0] = o[n][2]; d1[1] = o[n][3];
+      *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + r0) * OLD + n * 8 + cq) = make_float2(o[n][0], o[n][1]);
+      *reinterpret_cast<float2*>(mo + ((size_t)warp * 16 + r1) * OLD + n * 8 + cq) = make_float2(o[n][2], o[n][3]);
     }
     if ((lane & 3) == 0) {
       mm[warp * 16 + r0] = m0; mm[warp * 16 + r1] = m1;
@@ -100,26 +101,33 @@ __device__ __forceinline__ void dec_finish(float (&o)[HD / 8][4], float m0, floa
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < gs * HD; idx += DEC_WARPS * 32) {
-    int row = idx / HD, dim = idx - row * HD;
+  // a thread takes four columns of a head: the warps' factors once, the sums as float4
+  for (int idx = threadIdx.x; idx < gs * (HD / 4); idx += DEC_WARPS * 32) {
+    const int row = idx / (HD / 4), dim = (idx - row * (HD / 4)) * 4;
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mm[w * 16 + row]);
-    float L = 0.f, O = 0.f;
+    float L = 0.f;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
     if (M != -INFINITY) {
 #pragma unroll
       for (int w = 0; w < DEC_WARPS; w++) {
-        float f = exp2f(mm[w * 16 + row] - M);
+        const float f = exp2f(mm[w * 16 + row] - M);
         L += ml[w * 16 + row] * f;
-        O += mo[((size_t)w * 16 + row) * HD + dim] * f;
+        const float4 v = *reinterpret_cast<const float4*>(mo + ((size_t)w * 16 + row) * OLD + dim);
+        O.x += v.x * f; O.y += v.y * f; O.z += v.z * f; O.w += v.w * f;
       }
     }
-    int h = g * gs + row;
+    const int h = g * gs + row;
     if (splits == 1) {
-      out[(size_t)t * H * HD + (size_t)h * HD + dim] = __float2bfloat16_rn(O / L);
+      const float inv = 1.f / L;
+      uint2 raw;
+      raw.x = pack_bf16(O.x * inv, O.y * inv);
+      raw.y = pack_bf16(O.z * inv, O.w * inv);
+      *reinterpret_cast<uint2*>(out + (size_t)t * H * HD + (size_t)h * HD + dim) = raw;
     } else {
-      size_t pi = ((size_t)t * H + h) * splits + s;
-      part_o[pi * HD + dim] = O;
+      const size_t pi = ((size_t)t * H + h) * splits + s;
+      *reinterpret_cast<float4*>(part_o + pi * HD + dim) = O;
       if (dim == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
     }
   }
@@ -544,9 +552,8 @@ static int launch_decode(const bf16* q, long long q_stride, bf16* out, const bf1
                          unsigned* tickets, cudaStream_t stream) {
   constexpr int LD = HD + FA_PAD;
   size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_CHUNK * LD * sizeof(bf16);
-  size_t merge = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
+  size_t merge = (size_t)DEC_WARPS * 16 * (HD + 8 + 2) * sizeof(float);         // the warps' outputs, maxima and sums
   if (merge > smem) smem = merge;
-  if (smem < 3 * 16 * 64 * sizeof(float)) smem = 3 * 16 * 64 * sizeof(float);   // the last CTA's combine
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(decode_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid(splits, G, T);
