@@ -484,7 +484,7 @@ ffn_stream_kernel(const FfnArgs a) {
   unsigned char* stages = smem_raw;
   unsigned char* xres = smem_raw + NST * XR_STAGE_BYTES;
   float* red = reinterpret_cast<float*>(xres + 8 * XR_ROW_BYTES);
-  __shared__ unsigned long long full_bar[NST], empty_bar[NST], x_bar, go_bar;
+  __shared__ unsigned long long full_bar[NST], empty_bar[NST], x_bar;
   __shared__ int dead;
   __shared__ unsigned tiles_written;       // row tiles of the first product whose columns of h this CTA has written
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -492,7 +492,6 @@ ffn_stream_kernel(const FfnArgs a) {
     dead = 0;
     for (int s = 0; s < NST; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ST_CONSUMERS); }
     mbar_init(&x_bar, 1);
-    mbar_init(&go_bar, 1);
     tiles_written = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -547,32 +546,15 @@ ffn_stream_kernel(const FfnArgs a) {
       }
     }
     if (!waited) tokens1();
-    // the down projection's weights follow at once; its tokens (h) only when every CTA has written its part
-    unsigned issued2 = 0;
-    bool have_h = false;
-    auto tokens2 = [&]() {
-      have_h = true;
-      if (!mbar_wait(&go_bar, 0, &dead) && lane == 0) atomicExch(a.status, 3);
-      asm volatile("fence.proxy.async;" ::: "memory");        // h was written by ordinary stores of other CTAs
-      if (idle2) return;
-      const unsigned xb = (unsigned)((k2_end - k2_begin) * 2);
-      if (lane == 0) mbar_expect_tx(&x_bar, xb * T);
-      __syncwarp();
-      for (int t = lane; t < T; t += 32)
-        bulk_copy(xres + (size_t)t * XR_ROW_BYTES, a.h + (size_t)t * a.ldh + k2_begin, xb, &x_bar);
-    };
+    // the down projection's weights follow at once (the stages fill while the consumers wait for its tokens, h:
+    // the warp below fetches those as soon as they are written)
     if (!idle2) {
       for (int tile = first2; tile < a.n_tiles2; tile += stride2) {
         long long row = (long long)tile * 16 + (lane & 15);
         if (row >= a.N2) row = a.N2 - 1;
-        for (int c = cb2; c < ce2; c++) {
-          if (issued2 >= (unsigned)NST && !have_h) tokens2();
-          weights(a.w2, row, a.K2, c);
-          issued2++;
-        }
+        for (int c = cb2; c < ce2; c++) weights(a.w2, row, a.K2, c);
       }
     }
-    if (!have_h) tokens2();
     return;
   }
 
@@ -616,8 +598,16 @@ ffn_stream_kernel(const FfnArgs a) {
       }
     }
     ffn_stamp(a, 4);
+    if (!idle2) {
+      // this CTA's consumers are done with the first product's tokens (their last tile is counted above): h takes
+      // their place.  h was written by ordinary stores of other CTAs, the copy reads it through the async proxy
+      asm volatile("fence.proxy.async;" ::: "memory");
+      const unsigned xb = (unsigned)((k2_end - k2_begin) * 2);
+      mbar_expect_tx(&x_bar, xb * T);
+      for (int t = 0; t < T; t++)
+        bulk_copy(xres + (size_t)t * XR_ROW_BYTES, a.h + (size_t)t * a.ldh + k2_begin, xb, &x_bar);
+    }
     __threadfence();
-    mbar_arrive(&go_bar);
     // the last CTA past its wait puts the words back to zero for the next launch: every CTA has counted its
     // tiles before it waited, and counts itself here after a fence
     if (atomicAdd(a.gbar + FFN_SYNC_WORDS - 1, 1u) == gridDim.x - 1) {
