@@ -157,11 +157,12 @@ def serve(args):
         torch.cuda.synchronize()
         r0 = len(engine.step_records())
         s0, l0, t0 = engine.runner.steps, kernels.launches(), time.perf_counter()
+        g0 = len(engine.runner._graphs)
         outs = engine.generate(prompts, sp)
         torch.cuda.synchronize()
         rounds.append((time.perf_counter() - t0, engine.runner.steps - s0, kernels.launches() - l0,
-                       sum(len(o) for o in outs), engine.step_records()[r0:]))
-    sec, steps, launches, made, recs = rounds[-1]
+                       sum(len(o) for o in outs), engine.step_records()[r0:], len(engine.runner._graphs) - g0))
+    sec, steps, launches, made, recs, new_graphs = rounds[-1]
     n_prompt = sum(lengths[1])
     pct = lambda xs, q: round(sorted(xs)[min(len(xs) - 1, int(q * len(xs)))], 3) if xs else None
     mixed = [r["ms"] for r in recs if r["prompt_tokens"] and r["decode_tokens"]]
@@ -179,7 +180,10 @@ def serve(args):
                                   "prompt_only": {"n": len(prompt_only), "p50": pct(prompt_only, 0.5)},
                                   "decode_only": {"n": len(decode_only), "p50": pct(decode_only, 0.5), "p90": pct(decode_only, 0.9)}},
                       "device_seconds_of_steps": round(sum(r["ms"] for r in recs) / 1e3, 4),
-                      "first_round_seconds": round(rounds[0][0], 3)}))
+                      "first_round_seconds": round(rounds[0][0], 3),
+                      # decode-step shapes (padded batch, block-table width) met for the first time in the timed
+                      # round: each is run once eagerly and captured, which is what the slowest steps are
+                      "graphs_captured_in_the_timed_round": new_graphs}))
     return 0
 
 
