@@ -38,6 +38,7 @@
 #define AT_SOFTMAX_THREADS_OF(TPR) ((TPR) * 128)
 #define AT_THREADS_OF(TPR) ((TPR) * 128 + 96)
 #define AT_STAGES 3        // a stage holds K of tile j + 2 and V of tile j: what the MMA thread's step j reads
+#define AT_META 256        // requests whose token ranges are staged in shared memory
 #define AT_ROWS 128
 #define AT_KEYS 128
 #define AT_SPIN_LIMIT (1u << 24)
@@ -203,6 +204,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   __shared__ float l_s[TPR][AT_ROWS];               // the shares' sums, at the end
   __shared__ unsigned tmem_slot;
   __shared__ int dead;
+  __shared__ int cu_s[AT_META + 1], sp_s[AT_META + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long cta_t0 = p.timeline ? at_now() : 0;
 
@@ -222,20 +224,30 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
                  "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // the requests' token ranges and start positions (the step's metadata, not the work of the kernel before) go to
+  // shared memory in one trip: the search below would otherwise wait for a load per request it passes
+  const bool meta_staged = p.R < AT_META;
+  if (meta_staged) {
+    for (int i = threadIdx.x; i <= p.R; i += AT_THREADS_OF(TPR)) {
+      cu_s[i] = p.cu_tokens[i];
+      sp_s[i] = i < p.R ? p.start_pos[i] : 0;
+    }
+  }
   at_fence_before();
   __syncthreads();
   at_fence_after();
   const unsigned tmem = tmem_slot;
   const long long cta_t1 = p.timeline ? at_now() : 0;
-  pdl_wait();
 
   // ---- which request and which tokens (tiles numbered request by request, the longest histories first)
   const int g = blockIdx.y;
   const int gs = p.H / p.G;
+  const int* cu = meta_staged ? cu_s : p.cu_tokens;
+  const int* sp = meta_staged ? sp_s : p.start_pos;
   int b = gridDim.x - 1 - blockIdx.x;
   int r = 0, before = 0;
   for (; r < p.R; r++) {
-    int n = p.cu_tokens[r + 1] - p.cu_tokens[r];
+    int n = cu[r + 1] - cu[r];
     int nt = (n + p.tok_tile - 1) / p.tok_tile;
     if (b < before + nt) break;
     before += nt;
@@ -244,10 +256,11 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap kv_map, const A
   const long long cta_t2 = p.timeline ? at_now() : 0;
   int tok0 = 0, n_tok = 0, pos0 = 0;
   if (!idle) {
-    tok0 = p.cu_tokens[r] + (b - before) * p.tok_tile;
-    n_tok = min(p.tok_tile, p.cu_tokens[r + 1] - tok0);
-    pos0 = p.start_pos[r] + (tok0 - p.cu_tokens[r]);
+    tok0 = cu[r] + (b - before) * p.tok_tile;
+    n_tok = min(p.tok_tile, cu[r + 1] - tok0);
+    pos0 = sp[r] + (tok0 - cu[r]);
   }
+  pdl_wait();
   const int key_hi = pos0 + n_tok;
   const int key_lo_tile = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
   const int kt_lo = key_lo_tile / AT_KEYS, kt_hi = idle ? kt_lo : (key_hi + AT_KEYS - 1) / AT_KEYS;
