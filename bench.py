@@ -492,6 +492,9 @@ def main():
     ap.add_argument("--micro-graph", action="store_true", help="gemm: time inside a replayed graph, cold weights")
     ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
+    ap.add_argument("--stamps", action="store_true",
+                    help="for profiles/: run the decode step (up to 8 requests) with the attention and feed-forward "
+                         "kernels writing their own time stamps, and print where a launch of each spends its time")
     ap.add_argument("--without", default=None, metavar="KINDS",
                     help="for profiles/: time the decode step with the kernels of these kinds left out (comma list of "
                          "ffn, attention, projections, norms for up to 8 requests; attention, products, norms, rope, swiglu "
@@ -564,6 +567,37 @@ def main():
             runner.close(rc)
         return ms, launches, ctx_mean
 
+    if args.stamps:
+        # The kernels' own nanosecond stamps (%globaltimer) inside real, replayed steps: the buffers belong to the last
+        # layer's launches of the last step.  Medians over the CTAs, microseconds from the first CTA's start.
+        tl_a = torch.zeros(1024 * 16, dtype=torch.int64, device=dev)
+        tl_f = torch.zeros(1024 * 8, dtype=torch.int64, device=dev)
+        attn, ffn = kernels.decode_attention_rope, kernels.ffn_stream
+        kernels.decode_attention_rope = lambda *a, **k: attn(*a, timeline=tl_a, **k)
+        kernels.ffn_stream = lambda x, wgu, wd, barrier: ffn(x, wgu, wd, barrier, timeline=tl_f)
+        ms, _, _ = time_decode(args.batch, K, W)
+        torch.cuda.synchronize(dev)
+
+        def table(tl, width, names):
+            rows = [r for r in tl.view(-1, width).cpu().tolist() if r[0] > 0]
+            if not rows:
+                return ["  (this kernel did not run in the step)"]
+            t0 = min(r[0] for r in rows)
+            out = [f"  {len(rows)} CTAs"]
+            for i, name in enumerate(names):
+                v = sorted((r[i] - t0) / 1e3 for r in rows if r[i] > r[0] or i == 0)
+                if v:
+                    out.append(f"  {name:34s} min {v[0]:6.2f}  median {v[len(v) // 2]:6.2f}  max {v[-1]:6.2f}  (n={len(v)})")
+            return out
+        print(f"decode step, batch {args.batch}, context {args.context}: {ms / K:.4f} ms a step", file=sys.stderr)
+        print("decode attention from partial sums:", file=sys.stderr)
+        print("\n".join(table(tl_a, 16, ["start", "first chunks of keys asked for", "kernel before it done", "q built",
+                                         "keys done", "warps merged, partial sums written", "ticket taken",
+                                         "splits combined (one CTA per token and KV head)"])), file=sys.stderr)
+        print("feed-forward in one launch:", file=sys.stderr)
+        print("\n".join(table(tl_f, 8, ["start", "tokens there", "first tile written", "first product done",
+                                        "its columns of h counted", "h there", "second product done"])), file=sys.stderr)
+        return 0
     if args.without:
         # What does each kind of kernel add to the step?  Their launchers are replaced by nothing (outputs keep
         # whatever they held), the step is captured and replayed as usual, and only the time is reported.
