@@ -560,6 +560,51 @@ __global__ void swiglu_vec_kernel(const bf16* __restrict__ gate_up, bf16* __rest
   if (two) reinterpret_cast<uint4*>(out)[i1] = swiglu8(g1, u1);
 }
 
+// The same from the float32 partial sums of a split-K product: part [n_parts, T, 2F]; the shares are added
+// first, exactly (float32), and the result is rounded to bfloat16 once.  Four features per thread with 16-byte
+// loads, all shares of a thread's gate and up values asked for before any is used (in groups of four shares).
+__global__ void swiglu_partial_kernel(const float* __restrict__ part, int n_parts, bf16* __restrict__ out, int F4,
+                                      size_t n4, size_t part_stride4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const size_t t = i / F4;
+  const int a = (int)(i - t * F4);
+  const float4* base = reinterpret_cast<const float4*>(part) + t * 2 * F4 + a;
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+  for (int p0 = 0; p0 < n_parts; p0 += 4) {
+    float4 gv[4], uv[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const bool in = p0 + q < n_parts;
+      gv[q] = in ? __ldcg(base + (size_t)(p0 + q) * part_stride4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      uv[q] = in ? __ldcg(base + (size_t)(p0 + q) * part_stride4 + F4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      g.x += gv[q].x; g.y += gv[q].y; g.z += gv[q].z; g.w += gv[q].w;
+      u.x += uv[q].x; u.y += uv[q].y; u.z += uv[q].z; u.w += uv[q].w;
+    }
+  }
+  __nv_bfloat162 o0 = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+  __nv_bfloat162 o1 = __floats2bfloat162_rn(g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+  uint2 o;
+  o.x = *reinterpret_cast<unsigned*>(&o0);
+  o.y = *reinterpret_cast<unsigned*>(&o1);
+  reinterpret_cast<uint2*>(out)[i] = o;
+}
+
+// out [T, F] bfloat16 = silu(sum_p part[p, t, f]) * (sum_p part[p, t, F + f]); F a multiple of 4, 16-byte aligned.
+extern "C" int qd_swiglu_partial(const float* part, int n_parts, void* out, int T, int F, cudaStream_t stream) {
+  if (T <= 0 || F <= 0) return 0;
+  if (n_parts < 1 || F % 4 != 0 || (((uintptr_t)part) & 15) || (((uintptr_t)out) & 7)) return QD_ERR_UNSUPPORTED;
+  const size_t n4 = (size_t)T * F / 4;
+  qd_launch(swiglu_partial_kernel, dim3((unsigned)((n4 + 127) / 128)), dim3(128), 0, stream, part, n_parts, (bf16*)out,
+            F / 4, n4, (size_t)T * 2 * F / 4);
+  return qd_last_error();
+}
+
 extern "C" int qd_swiglu(const void* gate_up, void* out, int dtype, int T, int F, cudaStream_t stream) {
   size_t n = (size_t)T * F;
   if (n == 0) return 0;

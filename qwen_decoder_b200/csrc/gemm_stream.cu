@@ -269,7 +269,7 @@ gemm_stream_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long 
 
 // ---------------------------------------------------------------------------------------------
 // The same streamer with the tokens RESIDENT in shared memory: for up to 8 tokens and a k range per
-// CTA of at most XR_KMAX.  Above, every stage carries the tokens' rows for its k beside the 16 rows
+// CTA of at most XR_KMAX, or 9 to 16 tokens and a k range of at most XR_KMAX / 2 (TN = 2).  Above, every stage carries the tokens' rows for its k beside the 16 rows
 // of W -- half as many bytes again through the copy engine, which is what bounds the stream.  Here a
 // CTA keeps ONE share of K for the whole launch (CTA b: share b % splits, tiles b / splits,
 // b / splits + grid / splits, ...), copies the tokens' rows for that share once, and its stages
@@ -311,8 +311,48 @@ __device__ __forceinline__ void xr_stage_mma(float (&acc)[4], const unsigned cha
 }
 
 
-template <int EPI, typename TO>
-__global__ void __launch_bounds__(ST_THREADS)
+// The same for 9 to 16 tokens (two token tiles of the MMA): the resident rows are half as long (a share of K of
+// at most XR_KMAX / 2), so that the tokens take the same shared memory and two CTAs still fit on an SM.  The
+// loads go out in two halves of the warp's k range (registers); each half feeds two chains per token tile.
+#define XR_ROW_BYTES2 (XR_KMAX / 2 * 2 + 64)
+__device__ __forceinline__ void xr_stage_mma2(float (&acc)[2][4], const unsigned char* st, const unsigned char* xs,
+                                              int k_stage, int K, int warp, int j, int r) {
+  constexpr int NU = ST_KC / 32 / ST_CONSUMERS, NH = NU / 2;
+  float acc2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    uint4 lo[NH], hi[NH], b0[NH], b1[NH];
+#pragma unroll
+    for (int u = 0; u < NH; u++) {
+      const int kq = warp * (ST_KC / ST_CONSUMERS) + (h * NH + u) * 32;
+      const bool in = k_stage + kq + 8 * j < K;
+      const uint4 zero = make_uint4(0, 0, 0, 0);
+      const size_t col = (size_t)(kq + 8 * j) * 2;
+      lo[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)r * ST_ROW_BYTES + col) : zero;
+      hi[u] = in ? *reinterpret_cast<const uint4*>(st + (size_t)(r + 8) * ST_ROW_BYTES + col) : zero;
+      b0[u] = in ? *reinterpret_cast<const uint4*>(xs + (size_t)r * XR_ROW_BYTES2 + col) : zero;
+      b1[u] = in ? *reinterpret_cast<const uint4*>(xs + (size_t)(r + 8) * XR_ROW_BYTES2 + col) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < NH; u += 2) {
+      mma16816(acc[0], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b0[u].x, b0[u].y);
+      mma16816(acc[1], lo[u].x, hi[u].x, lo[u].y, hi[u].y, b1[u].x, b1[u].y);
+      mma16816(acc2[0], lo[u + 1].x, hi[u + 1].x, lo[u + 1].y, hi[u + 1].y, b0[u + 1].x, b0[u + 1].y);
+      mma16816(acc2[1], lo[u + 1].x, hi[u + 1].x, lo[u + 1].y, hi[u + 1].y, b1[u + 1].x, b1[u + 1].y);
+      mma16816(acc[0], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b0[u].z, b0[u].w);
+      mma16816(acc[1], lo[u].z, hi[u].z, lo[u].w, hi[u].w, b1[u].z, b1[u].w);
+      mma16816(acc2[0], lo[u + 1].z, hi[u + 1].z, lo[u + 1].w, hi[u + 1].w, b0[u + 1].z, b0[u + 1].w);
+      mma16816(acc2[1], lo[u + 1].z, hi[u + 1].z, lo[u + 1].w, hi[u + 1].w, b1[u + 1].z, b1[u + 1].w);
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 2; n++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) acc[n][i] += acc2[n][i];
+}
+
+template <int TN, int EPI, typename TO>
+__global__ void __launch_bounds__(ST_THREADS, 2)
 gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, long long ldx,
                         const float* __restrict__ bias, TO* __restrict__ out, long long ldo,
                         float* __restrict__ part, int T, int N, int K, int splits, int n_tiles,
@@ -320,8 +360,9 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
   constexpr int NST = XR_STAGES;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* stages = smem_raw;                                               // NST x 16 rows of W
-  unsigned char* xres = smem_raw + NST * XR_STAGE_BYTES;                          // 8 token rows
-  float* red = reinterpret_cast<float*>(xres + 8 * XR_ROW_BYTES);                 // [4][16][9]
+  constexpr int XROW = TN == 1 ? XR_ROW_BYTES : XR_ROW_BYTES2;
+  unsigned char* xres = smem_raw + NST * XR_STAGE_BYTES;                          // TN * 8 token rows
+  float* red = reinterpret_cast<float*>(xres + TN * 8 * XROW);                    // [4][16][TN * 8 + 1]
   __shared__ unsigned long long full_bar[NST], empty_bar[NST], x_bar;
   __shared__ int dead;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -341,7 +382,7 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
   const bool idle = first >= stride;
   const int c_begin = (int)((long long)n_chunks * sp / splits), c_end = (int)((long long)n_chunks * (sp + 1) / splits);
   const int k_begin = c_begin * ST_KC, k_end = min(K, c_end * ST_KC);
-  constexpr int RED_LD = 9;
+  constexpr int RED_LD = TN * 8 + 1;
 
   if (warp == ST_CONSUMERS) {
     // ------------------------------------------------------------ producer
@@ -356,7 +397,7 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
       if (lane == 0) mbar_expect_tx(&x_bar, xb * T);
       __syncwarp();
       for (int t = lane; t < T; t += 32)
-        bulk_copy(xres + (size_t)t * XR_ROW_BYTES, X + (size_t)t * ldx + k_begin, xb, &x_bar);
+        bulk_copy(xres + (size_t)t * XROW, X + (size_t)t * ldx + k_begin, xb, &x_bar);
     };
     for (int tile = first; tile < n_tiles; tile += stride) {
       long long row;                      // the row of W this lane copies (lanes 0..15)
@@ -392,7 +433,9 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
   unsigned it = 0;
   bool have_x = false;
   for (int tile = first; tile < n_tiles; tile += stride) {
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[TN][4];
+#pragma unroll
+    for (int n = 0; n < TN; n++) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
     for (int c = c_begin; c < c_end; c++, it++) {
       const int s = it % NST;
       const unsigned ph = (it / NST) & 1;
@@ -403,19 +446,23 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
       }
       const unsigned char* st = stages + (size_t)s * XR_STAGE_BYTES;
       const unsigned char* xs = xres + (size_t)(c - c_begin) * ST_KC * 2;
-      xr_stage_mma(acc, st, xs, c * ST_KC, K, warp, j, r);
+      if constexpr (TN == 1) xr_stage_mma(acc[0], st, xs, c * ST_KC, K, warp, j, r);
+      else xr_stage_mma2(acc, st, xs, c * ST_KC, K, warp, j, r);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
     float* base = red + (size_t)warp * 16 * RED_LD;
-    base[r * RED_LD + 2 * j] = acc[0];
-    base[r * RED_LD + 2 * j + 1] = acc[1];
-    base[(r + 8) * RED_LD + 2 * j] = acc[2];
-    base[(r + 8) * RED_LD + 2 * j + 1] = acc[3];
+#pragma unroll
+    for (int n = 0; n < TN; n++) {
+      base[r * RED_LD + n * 8 + 2 * j] = acc[n][0];
+      base[r * RED_LD + n * 8 + 2 * j + 1] = acc[n][1];
+      base[(r + 8) * RED_LD + n * 8 + 2 * j] = acc[n][2];
+      base[(r + 8) * RED_LD + n * 8 + 2 * j + 1] = acc[n][3];
+    }
     asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory");
     if (EPI == EPI_SWIGLU) {
       const int F = N >> 1;
-      for (int idx = threadIdx.x; idx < 8 * 8; idx += ST_CONSUMERS * 32) {
+      for (int idx = threadIdx.x; idx < 8 * TN * 8; idx += ST_CONSUMERS * 32) {
         int row = idx & 7, tok = idx >> 3;
         int f = tile * 8 + row;
         if (tok >= T || f >= F) continue;
@@ -428,7 +475,7 @@ gemm_stream_xres_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, 
         out[(size_t)tok * ldo + f] = from_float<TO>(gate / (1.0f + expf(-gate)) * up);
       }
     } else {
-      for (int idx = threadIdx.x; idx < 16 * 8; idx += ST_CONSUMERS * 32) {
+      for (int idx = threadIdx.x; idx < 16 * TN * 8; idx += ST_CONSUMERS * 32) {
         int row = idx & 15, tok = idx >> 4;
         int n = tile * 16 + row;
         if (tok >= T || n >= N) continue;
@@ -712,17 +759,20 @@ static int* status_word() {
   return g_status[dev];
 }
 
-// The resident-token form: up to 8 tokens, every share of K at most XR_KMAX wide, at least one CTA per share.
+// The resident-token form: up to 8 tokens with every share of K at most XR_KMAX wide, or 9 to 16 tokens with
+// shares of at most XR_KMAX / 2; at least one CTA per share.
 static bool xres_fits(int T, int K, int splits, int max_ctas) {
-  if (T > 8 || splits > max_ctas) return false;
+  if (T > 16 || splits > max_ctas) return false;
+  const int widest = T <= 8 ? XR_KMAX : XR_KMAX / 2;
   const int n_chunks = (K + ST_KC - 1) / ST_KC;
   for (int sp = 0; sp < splits; sp++) {
     int cb = (int)((long long)n_chunks * sp / splits), ce = (int)((long long)n_chunks * (sp + 1) / splits);
-    if ((ce - cb) * ST_KC > XR_KMAX) return false;
+    if ((ce - cb) * ST_KC > widest) return false;
   }
   return true;
 }
 
+template <int TN>
 static int launch_stream_xres(const bf16* W, const bf16* X, long long ldx, const float* bias, void* out, int out_dtype,
                               long long ldo, float* part, int T, int N, int K, int splits, int epi, int max_ctas,
                               cudaStream_t stream) {
@@ -733,11 +783,12 @@ static int launch_stream_xres(const bf16* W, const bf16* X, long long ldx, const
   int per_share = max_ctas / splits;
   if (per_share > n_tiles) per_share = n_tiles;
   int grid = per_share * splits;
-  size_t smem = (size_t)XR_STAGES * XR_STAGE_BYTES + (size_t)8 * XR_ROW_BYTES + (size_t)ST_CONSUMERS * 16 * 9 * sizeof(float);
+  size_t smem = (size_t)XR_STAGES * XR_STAGE_BYTES + (size_t)TN * 8 * (TN == 1 ? XR_ROW_BYTES : XR_ROW_BYTES2) +
+                (size_t)ST_CONSUMERS * 16 * (TN * 8 + 1) * sizeof(float);
 #define LAUNCH(E, TO)                                                                                            \
   do {                                                                                                           \
-    cudaFuncSetAttribute(gemm_stream_xres_kernel<E, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    qd_launch(gemm_stream_xres_kernel<E, TO>, dim3(grid), dim3(ST_THREADS), smem, stream, W, X, ldx, bias,       \
+    cudaFuncSetAttribute(gemm_stream_xres_kernel<TN, E, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    qd_launch(gemm_stream_xres_kernel<TN, E, TO>, dim3(grid), dim3(ST_THREADS), smem, stream, W, X, ldx, bias,       \
               (TO*)out, ldo, part, T, N, K, splits, n_tiles, status);                                            \
   } while (0)
   if (epi == EPI_SWIGLU) {
@@ -803,7 +854,8 @@ extern "C" int qd_gemm_stream(const void* W, const void* X, long long ldx, const
   const bf16* w = (const bf16*)W;
   const bf16* x = (const bf16*)X;
   if (xres_fits(T, K, splits, max_ctas))
-    return launch_stream_xres(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
+    return T <= 8 ? launch_stream_xres<1>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream)
+                  : launch_stream_xres<2>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 8) return launch_stream<1>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 16) return launch_stream<2>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);
   if (T <= 32) return launch_stream<4>(w, x, ldx, bias, out, out_dtype, ldo, part, T, N, K, splits, epi, max_ctas, stream);

@@ -195,6 +195,17 @@ def rope_kv_write_biased(qkv: torch.Tensor, bias: Optional[torch.Tensor], H: int
         "rope_kv_write_biased")
 
 
+def swiglu_partial(part: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, f] = silu(sum_p part[p, t, f]) * (sum_p part[p, t, F + f]) from the float32 partial sums
+    [n_parts, T, 2F] of a split-K gate/up product; out bfloat16."""
+    T, F = out.shape
+    assert part.dim() == 3 and tuple(part.shape[1:]) == (T, 2 * F) and part.dtype == torch.float32
+    assert out.dtype == torch.bfloat16 and F % 4 == 0
+    _contig(part, "part"); _contig(out, "out")
+    _check(library("elementwise").qd_swiglu_partial(_ptr(part), _I(part.shape[0]), _ptr(out), _I(T), _I(F), _stream()),
+           "swiglu_partial")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
     T, F = out.shape
@@ -226,6 +237,11 @@ SKINNY_POLICY_TOKENS = 16      # up to here the few-token kernels are the faster
 STREAM_POLICY_TOKENS = 8       # the streaming kernel up to here
 TC5_POLICY_TOKENS = 16         # from there up to here the tcgen05 kernel; 16 = never:
 # on row-major weights it reads 128-byte pieces of 128 rows per copy and stays below the library product
+STREAM_RESIDENT_TOKENS = 16    # ... except that from 9 tokens up to here the streaming kernel still takes a product
+# whose result is partial sums over shares of K of one stage (1,024) each: the tokens' rows for such a share stay in
+# shared memory as they do for up to 8 tokens (a decode step at batch 16: 2.47 -> 2.13 ms at the 3B sizes,
+# 5.33 -> 3.56 ms at the 7B sizes)
+STREAM_RESIDENT_MAX_SHARES = 32
 EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
 
 
@@ -239,6 +255,43 @@ def few_token_impl(T: int) -> str:
         # tiles its stages shrink and the register-load kernel wins clearly (measured in whole decode steps)
         return "regs" if skinny_impl == "stream" and T > STREAM_POLICY_TOKENS else skinny_impl
     return "tc5" if T <= TC5_POLICY_TOKENS else ""
+
+
+def stream_resident_shares(T: int, K: int) -> int:
+    """For 9 to ``STREAM_RESIDENT_TOKENS`` tokens: the number of shares of K (one stage of the streamer each) with
+    which the streaming kernel keeps the tokens resident, or 0 if this product is not taken that way."""
+    if skinny_impl != "stream" or not (STREAM_POLICY_TOKENS < T <= min(16, STREAM_RESIDENT_TOKENS)):
+        return 0
+    chunks = (K + 1023) // 1024
+    return chunks if chunks <= STREAM_RESIDENT_MAX_SHARES else 0
+
+
+SWIGLU_FROM_SHARES_WIDE = True     # up to 8 tokens and a hidden size above two stages: gate/up as partial sums
+
+
+def swiglu_shares(T: int, K: int, N: int) -> int:
+    """The shares of K over which the stacked gate/up product [N, K] of T tokens leaves partial sums for
+    ``swiglu_partial``, or 0 where the product's own SwiGLU epilogue is the better choice.  Partial sums pay
+    where they keep the tokens' rows resident in the streamer: for 9 to 16 tokens, and for up to 8 tokens when
+    K is wider than the rows the streamer keeps (the one-kernel form then copies the tokens with every stage)."""
+    shares = stream_resident_shares(T, K)
+    if shares:
+        return shares
+    chunks = (K + 1023) // 1024
+    if SWIGLU_FROM_SHARES_WIDE and few_token_impl(T) == "stream" and T <= STREAM_POLICY_TOKENS and chunks > 2:
+        sp = skinny_splits(N, K, T)
+        if max(chunks * (i + 1) // sp - chunks * i // sp for i in range(sp)) <= 2:
+            return sp
+    return 0
+
+
+def _impl_for(T: int, K: int, splits: int, epi: int) -> str:
+    """The kernel one product runs on: ``few_token_impl`` by the number of tokens, and the streaming kernel for
+    partial sums of 9 to 16 tokens over shares that keep the tokens resident."""
+    impl = few_token_impl(T) or "tc5"
+    if impl == "regs" and epi == EPI_PARTIAL and splits == stream_resident_shares(T, K):
+        return "stream"
+    return impl
 
 
 def skinny_supported(x: torch.Tensor, w: torch.Tensor, limit: Optional[int] = None) -> bool:
@@ -255,6 +308,8 @@ def skinny_splits(N: int, K: int, T: int = 1, target_ctas: Optional[int] = None)
     """Shares of K over the grid: enough CTAs (16 rows of W each) for four per SM, every warp at
     least one group of 128 k.  The tcgen05 kernel has tiles of 128 rows and one CTA per SM."""
     impl = few_token_impl(T) or "tc5"
+    if impl == "regs" and stream_resident_shares(T, K):
+        return stream_resident_shares(T, K)
     if target_ctas is None:
         target_ctas = 4 * sm_count()
     if impl == "tc5":
@@ -341,7 +396,7 @@ def gemm_tc5_status() -> int:
 def _skinny_call(x, w, bias, out, part, T, N, K, splits, epi, what, w_tiled=False):
     out_code = dtype_code(out.dtype) if out is not None else F32
     ldo = out.stride(0) if out is not None else 0
-    impl = few_token_impl(T) or "tc5"
+    impl = _impl_for(T, K, splits, epi)
     if impl == "tc5":
         _check(library("gemm_tc5").qd_gemm_tc5(
             _ptr(w), _ptr(x), _LL(x.stride(0)), _ptr(bias), _ptr(out), _I(out_code), _LL(ldo), _ptr(part),

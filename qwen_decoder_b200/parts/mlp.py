@@ -50,7 +50,12 @@ class SwiGLU(FeedForward):
             return kernels.ffn_stream(x, self.gate_up.weight, self.down.weight, self._barrier)   # one launch
         h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         if matmul_backend.use_skinny(x, self.gate_up.weight):
-            kernels.gemm_skinny_swiglu(x, self.gate_up.weight, h)       # gate, up and SwiGLU in one kernel
+            shares = kernels.swiglu_shares(x.shape[0], self.hidden_size, 2 * self.intermediate_size)
+            if shares and self.intermediate_size % 4 == 0:
+                # where the streamer keeps the tokens resident only for a share of K: partial sums, then SwiGLU
+                kernels.swiglu_partial(kernels.gemm_skinny_partial(x, self.gate_up.weight, shares), h)
+            else:
+                kernels.gemm_skinny_swiglu(x, self.gate_up.weight, h)       # gate, up and SwiGLU in one kernel
             matmul_backend.counters["own"] += 1
         else:
             kernels.swiglu(self.gate_up.forward(x), h)

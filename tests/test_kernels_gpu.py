@@ -447,6 +447,48 @@ def test_gemm_skinny(shape):
         close(h, plain_model.silu(want[:, :F]) * want[:, F:], dt)
 
 
+@pytest.mark.parametrize("shape", [(9, 100, 136), (12, 2560, 2048), (16, 50, 1000), (16, 2048, 11008), (13, 264, 3080),
+                                   (16, 33, 1032)])
+def test_gemm_stream_with_sixteen_tokens_resident(shape):
+    """9 to 16 tokens through the streaming kernel with the tokens' rows resident: partial sums over shares of one
+    stage of K each; a K that is no multiple of a stage, an N that is no multiple of a tile, token rows 8..15 with
+    values of their own (a kernel that read rows 0..7 twice would fail), and the feed-forward's SwiGLU from the sums."""
+    from qwen_decoder_b200 import kernels
+    T, N, K = shape
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(23)
+    x = torch.randn(T, K, generator=g)
+    x[8:] *= 3.0                                  # the second token tile is not a copy of the first
+    x = x.to(dt)
+    w = (0.05 * torch.randn(N, K, generator=g)).to(dt)
+    want = plain_model.linear(x.double(), w.double())
+    shares = kernels.stream_resident_shares(T, K)
+    assert shares == (K + 1023) // 1024 and kernels._impl_for(T, K, shares, kernels.EPI_PARTIAL) == "stream"
+    assert kernels.skinny_splits(N, K, T) == shares
+    wide = torch.zeros(T, K + 64, dtype=dt)       # rows further apart than K
+    wide[:, 32:32 + K] = x
+    for xin in (x.to(DEV), wide.to(DEV)[:, 32:32 + K]):
+        part = kernels.gemm_skinny_partial(xin, w.to(DEV), shares)
+        assert kernels.gemm_stream_status() == 0 and part.shape == (shares, T, N)
+        close(part.sum(0), want, TENSOR_F32, scale=float(want.abs().max()))
+    if N % 8 == 0:
+        F = N // 2
+        h = torch.full((T, F), float("nan"), dtype=dt, device=DEV)
+        kernels.swiglu_partial(part, h)
+        close(h, plain_model.silu(want[:, :F]) * want[:, F:], dt)
+
+
+def test_swiglu_from_partial_sums():
+    from qwen_decoder_b200 import kernels
+    g = torch.Generator().manual_seed(24)
+    for n_parts, T, F in ((1, 3, 8), (2, 16, 1004), (5, 11, 260), (9, 1, 12)):
+        part = 2 * torch.randn(n_parts, T, 2 * F, generator=g)
+        out = torch.full((T, F), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.swiglu_partial(part.to(DEV), out)
+        v = part.double().sum(0)
+        close(out, plain_model.silu(v[:, :F]) * v[:, F:], torch.bfloat16)
+
+
 def test_partial_sums_are_added_by_the_consumers():
     """add_rmsnorm and rope_kv_write_partial take float32 partial sums [parts, T, width]."""
     from qwen_decoder_b200 import kernels
