@@ -95,6 +95,24 @@ def test_swiglu_part(dtype, T):
     close(got, want, dtype)
 
 
+@pytest.mark.parametrize("T,D,F", [(1, 3080, 264), (8, 2056, 520), (8, 1032, 1100), (9, 1032, 520), (13, 3080, 260),
+                                   (16, 192, 2200), (17, 264, 520)])
+def test_swiglu_part_at_every_few_token_form(T, D, F):
+    """bfloat16 at the token counts and widths where the feed-forward changes its kernels: one launch (up to 8
+    tokens, hidden size up to 2,048), gate/up as partial sums with a SwiGLU kernel of its own (up to 8 tokens and
+    a wider hidden size; 9 to 16 tokens), the library product from 17 tokens on.  Tokens 8.. differ in scale from
+    tokens 0..7."""
+    dtype = torch.bfloat16
+    ff = create_part("feed_forward", "swiglu", hidden_size=D, intermediate_size=F, prefix="m.")
+    w = bind(ff, dtype, 5, scale=0.04)
+    x = torch.randn(T, D, generator=torch.Generator().manual_seed(6))
+    x[8:] *= 2.0
+    x = x.to(dtype)
+    got = total(ff.forward(x.to(DEV), FakeContext(T)))
+    want = plain_model.swiglu_ffn(x.double(), w["m.gate_proj.weight"], w["m.up_proj.weight"], w["m.down_proj.weight"])
+    close(got, want, dtype)
+
+
 def attention_setup(dtype, H, G, d, D, window, page_size=16):
     rot = create_part("position", "rotary", head_dim=d, rotary_dim=d, base=30000.0, pairing="adjacent")
     rot.prepare(600, DEV)
