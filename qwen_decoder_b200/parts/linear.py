@@ -61,4 +61,8 @@ class Linear:
         if self.bias is None and matmul_backend.use_skinny(x, self.weight):
             matmul_backend.counters["own"] += 1
             return kernels.gemm_skinny_partial(x, self.weight, kernels.skinny_splits(self.out_features, self.in_features, x.shape[0]))
+        if self.bias is None and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous():
+            shares = matmul_backend.library_shares(x.shape[0], self.out_features, self.in_features)
+            if shares:
+                return matmul_backend.linear_partial_library(x, self.weight, shares)
         return self.forward(x)
