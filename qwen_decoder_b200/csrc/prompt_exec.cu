@@ -34,6 +34,12 @@ typedef cublasStatus_t (*PeGemmEx)(cublasHandle_t, cublasOperation_t, cublasOper
                                    const void*, cudaDataType, int, const void*, cudaDataType, int, const void*, void*,
                                    cudaDataType, int, cublasComputeType_t, cublasGemmAlgo_t);
 
+// cublasGemmStridedBatchedEx (32-bit form)
+typedef cublasStatus_t (*PeGemmBatched)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*,
+                                        const void*, cudaDataType, int, long long, const void*, cudaDataType, int,
+                                        long long, const void*, void*, cudaDataType, int, long long, int,
+                                        cublasComputeType_t, cublasGemmAlgo_t);
+
 struct PeFns {
   decltype(&qd_add_rmsnorm) add_rmsnorm;
   decltype(&qd_rope_kv_write_biased) rope_kv_write;
@@ -43,6 +49,7 @@ struct PeFns {
   decltype(&qd_decode_attention) attention_decode;      // split-KV, for the single tokens of a mixed step
   PeGemmEx gemm_ex;
   cublasHandle_t blas;             // the caller's handle, bound to ``stream``
+  PeGemmBatched gemm_batched;
 };
 
 struct PeParams {
@@ -61,6 +68,10 @@ struct PeParams {
   // a mixed step: requests and tokens 0 .. n_decode-1 are single tokens and go to the decode kernel
   int n_decode, decode_splits;
   const int* token_req; float* part_o; float* part_ml; unsigned* tickets;
+  // the down projection over ``down_shares`` equal shares of F as one batched product that leaves float32 partial
+  // sums [down_shares, T, D] in ``down_part`` for the next norm's kernel (0: the plain product into ``delta``).
+  // With few tokens, a long K and few output features the plain product fills the GPU with too few CTAs.
+  float* down_part; int down_shares, pad2;
 };
 
 extern "C" int qd_prompt_exec_struct_sizes(int* layer_bytes, int* params_bytes) {
@@ -77,6 +88,16 @@ static int product(const PeParams& p, const void* W, const void* X, void* Y, int
   return st == CUBLAS_STATUS_SUCCESS ? 0 : 20000 + (int)st;
 }
 
+// part[s][T, N] = X[T, share s of K] W[N, share s of K]^T in float32, for `shares` equal shares of K
+static int product_shares(const PeParams& p, const void* W, const void* X, float* part, int T, int N, int K, int shares) {
+  const float one = 1.f, zero = 0.f;
+  const int kc = K / shares;
+  cublasStatus_t st = p.fn.gemm_batched(p.fn.blas, CUBLAS_OP_T, CUBLAS_OP_N, N, T, kc, &one, W, CUDA_R_16BF, K, kc, X,
+                                        CUDA_R_16BF, K, kc, &zero, part, CUDA_R_32F, N, (long long)T * N, shares,
+                                        CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  return st == CUBLAS_STATUS_SUCCESS ? 0 : 20000 + (int)st;
+}
+
 #define PE_TRY(call)            \
   do {                          \
     int rc_ = (call);           \
@@ -86,14 +107,18 @@ static int product(const PeParams& p, const void* W, const void* X, void* Y, int
 extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
   const PeParams& p = *pp;
   if (p.T <= 0 || p.n_layers < 0 || p.n_decode < 0 || p.n_decode >= p.R) return QD_ERR_UNSUPPORTED;
+  const int shares = p.down_shares;
+  if (shares < 0 || shares == 1 || (shares > 1 && (!p.down_part || !p.fn.gemm_batched || p.F % (8 * shares))))
+    return QD_ERR_UNSUPPORTED;
   const int T = p.T, D = p.D, H = p.H, G = p.G, d = p.d, F = p.F;
   const int n_qkv = (H + 2 * G) * d;
   const long long xn = (long long)T * D;
   const void* delta = p.delta0;
+  int delta_dtype = QD_BF16, delta_parts = 1;          // what the previous layer's down projection left
   for (int l = 0; l < p.n_layers; l++) {
     const PeLayer& L = p.layers[l];
-    PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? QD_BF16 : -1, L.norm1_w, p.h, QD_BF16, nullptr, T, D, L.eps1, 1, 1, xn,
-                            stream));
+    PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? delta_dtype : -1, L.norm1_w, p.h, QD_BF16, nullptr, T, D, L.eps1, 1,
+                            delta_parts, xn, stream));
     PE_TRY(product(p, L.wqkv, p.h, p.qkv, T, n_qkv, D));
     PE_TRY(p.fn.rope_kv_write(p.qkv, L.bqkv, T, H, G, d, p.rotary_dim, p.pairing, p.cos_t, p.sin_t, p.positions, L.kv,
                               p.slot_map, p.page_size, L.write_kv, stream));
@@ -114,11 +139,16 @@ extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
     PE_TRY(p.fn.add_rmsnorm(p.x, p.delta, QD_BF16, L.norm2_w, p.h, QD_BF16, nullptr, T, D, L.eps2, 1, 1, xn, stream));
     PE_TRY(product(p, L.wgu, p.h, p.gu, T, 2 * F, D));
     PE_TRY(p.fn.swiglu(p.gu, p.act, QD_BF16, T, F, stream));
-    PE_TRY(product(p, L.wd, p.act, p.delta, T, D, F));
-    delta = p.delta;
+    if (shares > 1) {
+      PE_TRY(product_shares(p, L.wd, p.act, p.down_part, T, D, F, shares));
+      delta = p.down_part; delta_dtype = QD_F32; delta_parts = shares;
+    } else {
+      PE_TRY(product(p, L.wd, p.act, p.delta, T, D, F));
+      delta = p.delta;
+    }
   }
   if (p.n_wanted > 0)
-    PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? QD_BF16 : -1, p.final_w, p.hrows, QD_BF16, p.logit_rows, p.n_wanted, D,
-                            p.final_eps, 0, 1, xn, stream));       // only the wanted rows: x itself stays as it is
+    PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? delta_dtype : -1, p.final_w, p.hrows, QD_BF16, p.logit_rows, p.n_wanted,
+                            D, p.final_eps, 0, delta_parts, xn, stream));     // only the wanted rows: x itself stays as it is
   return 0;
 }

@@ -682,7 +682,8 @@ class PromptLayer(ctypes.Structure):
 class PromptFns(ctypes.Structure):
     """Addresses of the launchers and of the library product that the native prompt step calls."""
     _fields_ = [(n, ctypes.c_void_p) for n in ("add_rmsnorm", "rope_kv_write", "swiglu", "attention_regs",
-                                               "attention_tc5", "attention_decode", "gemm_ex", "blas")]
+                                               "attention_tc5", "attention_decode", "gemm_ex", "blas",
+                                               "gemm_batched")]
 
 
 class PromptParams(ctypes.Structure):
@@ -695,7 +696,8 @@ class PromptParams(ctypes.Structure):
                                         "logit_rows", "cos_t", "sin_t", "final_w", "x", "delta0", "h", "qkv",
                                         "attn", "delta", "gu", "act", "hrows")] + \
         [("n_decode", ctypes.c_int), ("decode_splits", ctypes.c_int)] + \
-        [(n, ctypes.c_void_p) for n in ("token_req", "part_o", "part_ml", "tickets")]
+        [(n, ctypes.c_void_p) for n in ("token_req", "part_o", "part_ml", "tickets", "down_part")] + \
+        [("down_shares", ctypes.c_int), ("pad2", ctypes.c_int)]
 
 
 def prompt_exec_struct_sizes_match() -> bool:
@@ -737,6 +739,7 @@ def prompt_fns(use_tc5: bool, with_decode: bool = False) -> PromptFns:
         if with_decode:
             fns.attention_decode = addr(library("attention_flash").qd_decode_attention)
         fns.gemm_ex = addr(_loaded_cublas().cublasGemmEx)
+        fns.gemm_batched = addr(_loaded_cublas().cublasGemmStridedBatchedEx)
         _prompt_fns[(use_tc5, with_decode)] = fns
     return fns
 

@@ -73,21 +73,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         counters["own"] += 1
 
 
-# A library product of few tokens with a long K and few output features (the down projection at 17 to 64 tokens)
+# A library product of few tokens with a long K and few output features (the down projection of 17 to 512 tokens)
 # fills the GPU with too few CTAs: it is given as a batch over shares of K, and leaves float32 partial sums.
 # Decode steps at the 3B sizes: batch 64 3.11 -> 2.92 ms, batch 32 2.60 -> 2.44 (2 and 8 shares: 2.95); at the 7B
-# sizes batch 32 3.81 -> 3.69; with 5,120 output features (the 32B sizes) nothing is gained.
+# sizes batch 32 3.81 -> 3.69; with 5,120 output features (the 32B sizes) nothing is gained.  The product alone on
+# cold weights at the 3B sizes: 17.5 -> 12.0 us at 128 tokens, 18.8 -> 13.5 at 256, 24.7 -> 20.0 at 512 with two
+# shares (21.1 with four); nothing at 1,024, and nothing at 512 tokens with the 3,584 features of the 7B sizes: above
+# 256 tokens two shares while tokens x features stay below 1.4 million.
 library_split_k = 4
 LIBRARY_SPLIT_MAX_FEATURES = 4096
+LIBRARY_SPLIT_MAX_OUTPUTS = 1_400_000
 
 
 def library_shares(T: int, N: int, K: int) -> int:
-    """Shares of K for ``linear_partial_library``, or 0 where the plain library product stands."""
-    s = library_split_k
-    if (mode != "auto" or s < 2 or not (16 < T <= 64) or N > LIBRARY_SPLIT_MAX_FEATURES or K < 2 * N or K < 4096
-            or K % (8 * s)):
+    """Shares of K for ``linear_partial_library`` and for the native prompt loop's down projection, or 0 where
+    the plain library product stands."""
+    if (mode != "auto" or library_split_k < 2 or T <= 16 or (T > 256 and T * N > LIBRARY_SPLIT_MAX_OUTPUTS)
+            or N > LIBRARY_SPLIT_MAX_FEATURES or K < 2 * N or K < 4096):
         return 0
-    return s
+    s = library_split_k if T <= 256 else 2
+    return s if K % (8 * s) == 0 else 0
 
 
 def linear_partial_library(x: torch.Tensor, w: torch.Tensor, shares: int) -> torch.Tensor:

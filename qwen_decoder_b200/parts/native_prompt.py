@@ -172,6 +172,10 @@ class NativePrompt:
         p.x, p.delta0 = x.data_ptr(), None
         p.h, p.qkv, p.attn, p.delta, p.gu, p.act = (base + 2 * o for o in offs)
         p.hrows = hrows.data_ptr() if hrows is not None else None
+        shares = matmul_backend.library_shares(T, D, F)
+        down_part = torch.empty((shares, T, D), dtype=torch.float32, device=dev) if shares else None
+        p.down_shares = shares
+        p.down_part = down_part.data_ptr() if shares else None
         n_launches = len(self.entries) * (OWN_LAUNCHES_PER_LAYER + (1 if nd else 0)) + (1 if ctx.num_wanted else 0)
         kernels.prompt_exec(p, n_launches)
         self.steps += 1

@@ -113,10 +113,12 @@ def test_swiglu_part_at_every_few_token_form(T, D, F):
     close(got, want, dtype)
 
 
-@pytest.mark.parametrize("T,N,K", [(17, 136, 4096), (40, 2048, 4128), (64, 520, 11008), (64, 136, 4104), (65, 136, 4096)])
+@pytest.mark.parametrize("T,N,K", [(17, 136, 4096), (40, 2048, 4128), (64, 520, 11008), (64, 136, 4104), (300, 136, 4112),
+                                   (700, 2048, 4096)])
 def test_linear_part_as_partial_sums_of_a_batched_library_product(T, N, K):
-    """17 to 64 tokens, a long K and few output features: shares of K as one batched product; a K that does not
-    divide into shares of whole 16-byte pieces, and 65 tokens, take the plain product."""
+    """From 17 tokens, a long K and few output features: shares of K as one batched product (four shares, two
+    above 256 tokens); a K that does not divide into shares of whole 16-byte pieces, and more than 1.4 million
+    outputs, take the plain product."""
     from qwen_decoder_b200.parts.linear import Linear
     from qwen_decoder_b200.parts import matmul_backend
     lin = Linear(K, [("p", N)], bias=False)
@@ -126,7 +128,8 @@ def test_linear_part_as_partial_sums_of_a_batched_library_product(T, N, K):
     x = x.to(torch.bfloat16)
     got = lin.forward_partial(x.to(DEV))
     shares = matmul_backend.library_shares(T, N, K)
-    assert shares == (4 if T <= 64 and K % 32 == 0 else 0)
+    per = 4 if T <= 256 else 2
+    assert shares == (0 if T * N > 1_400_000 or K % (8 * per) else per)
     assert (got.dim() == 3 and got.shape[0] == shares and got.dtype == torch.float32) if shares else got.dim() == 2
     close(total(got), plain_model.linear(x.double(), w["p.weight"]), torch.bfloat16)
 
