@@ -234,14 +234,15 @@ SKINNY_MAX_TOKENS = 64      # what the mma.sync few-token kernels take
 # Who takes a product of T tokens was settled by measurement in whole decode steps (profiles/); the numbers are
 # module attributes so that a measurement can move them, not switches of the environment.
 SKINNY_POLICY_TOKENS = 16      # up to here the few-token kernels are the faster choice
-STREAM_POLICY_TOKENS = 8       # the streaming kernel up to here
-TC5_POLICY_TOKENS = 16         # from there up to here the tcgen05 kernel; 16 = never:
-# on row-major weights it reads 128-byte pieces of 128 rows per copy and stays below the library product
-STREAM_RESIDENT_TOKENS = 16    # ... except that from 9 tokens up to here the streaming kernel still takes a product
-# whose result is partial sums over shares of K of one stage (1,024) each: the tokens' rows for such a share stay in
-# shared memory as they do for up to 8 tokens (a decode step at batch 16: 2.47 -> 2.13 ms at the 3B sizes,
-# 5.33 -> 3.56 ms at the 7B sizes)
+STREAM_POLICY_TOKENS = 8       # up to here the streaming kernel takes every product
+STREAM_RESIDENT_TOKENS = 16    # from there up to here it still takes a product whose result is partial sums over
+# shares of K of one stage (1,024) each: the tokens' rows for such a share stay in shared memory as whole rows do
+# for up to 8 tokens (a decode step at batch 16: 2.47 -> 2.13 ms at the 3B sizes, 5.33 -> 3.56 ms at the 7B sizes);
+# the other products of 9 to 16 tokens (whole sums: the output projection over the vocabulary) take the
+# register-load kernel
 STREAM_RESIDENT_MAX_SHARES = 32
+TC5_POLICY_TOKENS = 16         # from SKINNY_POLICY_TOKENS up to here the tcgen05 kernel; 16 = never:
+# on row-major weights it reads 128-byte pieces of 128 rows per copy and stays below the library product
 EPI_STORE, EPI_PARTIAL, EPI_SWIGLU = 0, 1, 2
 
 
