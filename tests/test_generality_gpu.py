@@ -393,4 +393,5 @@ def test_another_order_of_the_same_parts_keeps_the_parts_path(tmp_path):
     assert type(usual.model.layers[0]).__name__ == "ToyParallelBlock"
     plain_cfg = ToyConfig("ToyLM", kinds=("full", "full"))
     folder = write_random_model(plain_cfg, str(tmp_path / "prenorm"), seed=11)
-    assert ModelRunner.from_folder(folder, dtype="bfloat16", device="cuda:0", num_pages=8).model.native_prompt is not None
+    if os.environ.get("QD_NATIVE_PROMPT", "1") != "0":          # the switch takes the native loop away from every model
+        assert ModelRunner.from_folder(folder, dtype="bfloat16", device="cuda:0", num_pages=8).model.native_prompt is not None
