@@ -74,6 +74,11 @@ static inline bool qd_pdl_enabled() {
   return v == 1;
 }
 
+// Set by a library's ``plain_next`` entry point: its next launch goes without the attribute, that is with the
+// stream's full ordering after everything before it.  For a kernel that reads what a library kernel wrote whose
+// inner workings (several kernels? dependencies of their own among them?) this code cannot see.
+static bool qd_plain_next_launch = false;
+
 template <typename... KArgs, typename... Args>
 static inline void qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                              Args... args) {
@@ -86,7 +91,8 @@ static inline void qd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = qd_pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (qd_pdl_enabled() && !qd_plain_next_launch) ? 1 : 0;
+  qd_plain_next_launch = false;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

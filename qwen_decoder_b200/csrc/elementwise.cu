@@ -151,6 +151,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, cons
   }
 }
 
+// The next launch of this library is ordered after all earlier work of its stream (no programmatic dependent launch).
+extern "C" void qd_elementwise_plain_next() { qd_plain_next_launch = true; }
+
 extern "C" int qd_add_rmsnorm(float* x, const void* delta, int delta_dtype, const float* w, void* out,
                               int out_dtype, const int* rows, int n_rows, int D, float eps,
                               int write_back, int n_parts, long long part_stride, cudaStream_t stream) {

@@ -12,6 +12,7 @@ int qd_rope_kv_write_biased(void* qkv, const float* bias, int T, int H, int G, i
                             const float* cos_t, const float* sin_t, const int* positions, void* kv,
                             const int* slot_map, int page_size, int write_kv, cudaStream_t stream);
 int qd_swiglu(const void* gate_up, void* out, int dtype, int T, int F, cudaStream_t stream);
+void qd_elementwise_plain_next();
 int qd_decode_attention(const void* q, long long q_stride, void* out, const void* kv, const int* block_table,
                         int max_blocks, const int* token_req, const int* positions, int T, int H, int G, int d,
                         int page_size, float scale, int window, int splits, float* part_o, float* part_ml,

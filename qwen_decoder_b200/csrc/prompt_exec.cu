@@ -50,6 +50,7 @@ struct PeFns {
   PeGemmEx gemm_ex;
   cublasHandle_t blas;             // the caller's handle, bound to ``stream``
   PeGemmBatched gemm_batched;
+  decltype(&qd_elementwise_plain_next) plain_next;      // the elementwise library's next launch without the attribute
 };
 
 struct PeParams {
@@ -108,7 +109,8 @@ extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
   const PeParams& p = *pp;
   if (p.T <= 0 || p.n_layers < 0 || p.n_decode < 0 || p.n_decode >= p.R) return QD_ERR_UNSUPPORTED;
   const int shares = p.down_shares;
-  if (shares < 0 || shares == 1 || (shares > 1 && (!p.down_part || !p.fn.gemm_batched || p.F % (8 * shares))))
+  if (shares < 0 || shares == 1 ||
+      (shares > 1 && (!p.down_part || !p.fn.gemm_batched || !p.fn.plain_next || p.F % (8 * shares))))
     return QD_ERR_UNSUPPORTED;
   const int T = p.T, D = p.D, H = p.H, G = p.G, d = p.d, F = p.F;
   const int n_qkv = (H + 2 * G) * d;
@@ -117,6 +119,7 @@ extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
   int delta_dtype = QD_BF16, delta_parts = 1;          // what the previous layer's down projection left
   for (int l = 0; l < p.n_layers; l++) {
     const PeLayer& L = p.layers[l];
+    if (delta_parts > 1) p.fn.plain_next();            // the norm that reads the batched product waits for all of it
     PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? delta_dtype : -1, L.norm1_w, p.h, QD_BF16, nullptr, T, D, L.eps1, 1,
                             delta_parts, xn, stream));
     PE_TRY(product(p, L.wqkv, p.h, p.qkv, T, n_qkv, D));
@@ -147,6 +150,7 @@ extern "C" int qd_prompt_exec(const PeParams* pp, cudaStream_t stream) {
       delta = p.delta;
     }
   }
+  if (p.n_wanted > 0 && delta_parts > 1) p.fn.plain_next();
   if (p.n_wanted > 0)
     PE_TRY(p.fn.add_rmsnorm(p.x, delta, delta ? delta_dtype : -1, p.final_w, p.hrows, QD_BF16, p.logit_rows, p.n_wanted,
                             D, p.final_eps, 0, delta_parts, xn, stream));     // only the wanted rows: x itself stays as it is

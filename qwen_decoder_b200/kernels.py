@@ -195,6 +195,15 @@ def rope_kv_write_biased(qkv: torch.Tensor, bias: Optional[torch.Tensor], H: int
         "rope_kv_write_biased")
 
 
+def elementwise_plain_next() -> None:
+    """The next launch of the elementwise library (the norm or the addition that takes a branch's output) is
+    ordered after all earlier work of the stream, without programmatic dependent launch: for the reader of a
+    batched library product."""
+    fn = library("elementwise").qd_elementwise_plain_next
+    fn.restype = None
+    fn()
+
+
 def swiglu_partial(part: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, f] = silu(sum_p part[p, t, f]) * (sum_p part[p, t, F + f]) from the float32 partial sums
     [n_parts, T, 2F] of a split-K gate/up product; out bfloat16."""
@@ -684,7 +693,7 @@ class PromptFns(ctypes.Structure):
     """Addresses of the launchers and of the library product that the native prompt step calls."""
     _fields_ = [(n, ctypes.c_void_p) for n in ("add_rmsnorm", "rope_kv_write", "swiglu", "attention_regs",
                                                "attention_tc5", "attention_decode", "gemm_ex", "blas",
-                                               "gemm_batched")]
+                                               "gemm_batched", "plain_next")]
 
 
 class PromptParams(ctypes.Structure):
@@ -741,6 +750,7 @@ def prompt_fns(use_tc5: bool, with_decode: bool = False) -> PromptFns:
             fns.attention_decode = addr(library("attention_flash").qd_decode_attention)
         fns.gemm_ex = addr(_loaded_cublas().cublasGemmEx)
         fns.gemm_batched = addr(_loaded_cublas().cublasGemmStridedBatchedEx)
+        fns.plain_next = addr(ew.qd_elementwise_plain_next)
         _prompt_fns[(use_tc5, with_decode)] = fns
     return fns
 
