@@ -518,7 +518,7 @@ extern "C" int qd_rope_kv_write_partial(const float* part, int n_parts, const fl
 // (the reference's swiglu_kernel, gpu_kernels.cu:157-158).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int F, size_t n) {
-  pdl_launch_dependents();
+  // no early start for the successor: it is a library product (the down projection), which gains nothing from it
   pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
@@ -547,8 +547,7 @@ __device__ __forceinline__ uint4 swiglu8(const uint4& g, const uint4& u) {
 }
 
 __global__ void swiglu_vec_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int F8, size_t n8) {
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait();        // as above: the successor is a library product
   const size_t half = (n8 + 1) / 2;
   const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x, i1 = i0 + half;
   if (i0 >= half) return;
