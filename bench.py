@@ -32,7 +32,7 @@ SHAPE_3B = dict(
     architectures=["Qwen2ForCausalLM"], hidden_size=2048, intermediate_size=11008, num_hidden_layers=36,
     num_attention_heads=16, num_key_value_heads=2, vocab_size=151936, max_position_embeddings=32768,
     rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
-# the two other GPU-sized shapes of the survey's measurement table (their own workloads: see --workload)
+# the two other GPU-sized shapes (their own workloads: --micro serve, and --batch/--context for long contexts)
 SHAPE_7B = dict(
     architectures=["Qwen2ForCausalLM"], hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
     num_attention_heads=28, num_key_value_heads=4, vocab_size=152064, max_position_embeddings=32768,
