@@ -73,25 +73,28 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         counters["own"] += 1
 
 
-# A library product of few tokens with a long K and few output features (the down projection of 17 to 512 tokens)
-# fills the GPU with too few CTAs: it is given as a batch over shares of K, and leaves float32 partial sums.
-# Decode steps at the 3B sizes: batch 64 3.11 -> 2.92 ms, batch 32 2.60 -> 2.44 (2 and 8 shares: 2.95); at the 7B
-# sizes batch 32 3.81 -> 3.69; with 5,120 output features (the 32B sizes) nothing is gained.  The product alone on
-# cold weights at the 3B sizes: 17.5 -> 12.0 us at 128 tokens, 18.8 -> 13.5 at 256, 24.7 -> 20.0 at 512 with two
-# shares (21.1 with four); nothing at 1,024, and nothing at 512 tokens with the 3,584 features of the 7B sizes: above
-# 256 tokens two shares while tokens x features stay below 1.4 million.
-library_split_k = 4
+# A library product of few tokens with a long K and few output features (the down projection of 17 to 256 tokens)
+# fills the GPU with too few CTAs.  Given as a batch over four shares of K that leaves float32 partial sums it is
+# faster: decode steps at the 3B sizes 3.11 -> 2.92 ms at batch 64 and 2.60 -> 2.44 at batch 32 (2 and 8 shares:
+# 2.95), at the 7B sizes 3.81 -> 3.69 at batch 32, nothing with 5,120 output features; the product alone on cold
+# weights 17.5 -> 12.0 us at 128 tokens and 18.8 -> 13.5 at 256.
+# It is OFF (``library_split_k = 0``; 4 turns it on).  With it on, tests at the 3B and 7B sizes saw, in about one
+# run of ten, one row tile of a LATER prompt step's logits wrong (a 268- or 291-token portion, always the rows from
+# 128 on), also when that step's own products were plain ones and with the batched product's reader and writer
+# ordered by plain launches; five runs with it off showed none, as did all runs before it existed.  The cause was
+# not found (what the library's kernels keep between calls cannot be seen from here), so the plain product stands.
+library_split_k = 0
 LIBRARY_SPLIT_MAX_FEATURES = 4096
-LIBRARY_SPLIT_MAX_OUTPUTS = 1_400_000
+LIBRARY_SPLIT_MAX_TOKENS = 256
 
 
 def library_shares(T: int, N: int, K: int) -> int:
     """Shares of K for ``linear_partial_library`` and for the native prompt loop's down projection, or 0 where
     the plain library product stands."""
-    if (mode != "auto" or library_split_k < 2 or T <= 16 or (T > 256 and T * N > LIBRARY_SPLIT_MAX_OUTPUTS)
+    if (mode != "auto" or library_split_k < 2 or not (16 < T <= LIBRARY_SPLIT_MAX_TOKENS)
             or N > LIBRARY_SPLIT_MAX_FEATURES or K < 2 * N or K < 4096):
         return 0
-    s = library_split_k if T <= 256 else 2
+    s = library_split_k
     return s if K % (8 * s) == 0 else 0
 
 

@@ -67,34 +67,6 @@ def test_native_prompt_steps_match_the_parts(name, tmp_path):
     native.cache.check()
 
 
-def test_native_prompt_with_the_down_projection_in_shares(tmp_path):
-    """An intermediate size of 4,128 with a hidden size of 96: the native loop gives the down projection to the
-    library as a batch over shares of K (four shares up to 256 tokens, two above) and the next norm adds the
-    float32 partial sums -- also the final norm, which gathers rows."""
-    from qwen_decoder_b200.config import Qwen2Config
-    from qwen_decoder_b200.weights import write_random_model
-    from qwen_decoder_b200.parts import matmul_backend
-    cfg_dict = dict(TINY["D"], intermediate_size=4128, max_position_embeddings=1024)
-    assert matmul_backend.library_shares(70, 96, 4128) == 4 and matmul_backend.library_shares(300, 96, 4128) == 2
-    folder = write_random_model(Qwen2Config.from_dict(cfg_dict), str(tmp_path), 17, dtype=torch.bfloat16)
-    cfg, w = plain_model.read_folder(folder)
-    rng = random.Random(12)
-    seqs = [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in (420, 97, 40)]
-    cuts = [70, 300, 50]
-    native, parts = runner_for(folder, True), runner_for(folder, False)
-    a = run_portions(native, seqs, cuts)
-    b = run_portions(parts, seqs, cuts)
-    assert native.model.native_prompt.steps == 3
-    want = [plain_model.forward(cfg, w, s).numpy() for s in seqs]
-    scale = max(float(np.abs(x).max()) for x in want)
-    assert a.keys() == b.keys() and len(a) == 6
-    for (i, pos), row in a.items():
-        assert np.isfinite(row).all()
-        assert np.abs(row - b[(i, pos)]).max() <= 2e-2 * scale
-        assert np.abs(row - want[i][pos]).max() <= 3e-2 * scale
-    native.cache.check()
-
-
 def test_native_prompt_declines_float32(tmp_path):
     """The native loop is for bfloat16; the float32 path keeps the parts' own launches."""
     from qwen_decoder_b200.engine import ModelRunner

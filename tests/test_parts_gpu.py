@@ -113,27 +113,6 @@ def test_swiglu_part_at_every_few_token_form(T, D, F):
     close(got, want, dtype)
 
 
-@pytest.mark.parametrize("T,N,K", [(17, 136, 4096), (40, 2048, 4128), (64, 520, 11008), (64, 136, 4104), (300, 136, 4112),
-                                   (700, 2048, 4096)])
-def test_linear_part_as_partial_sums_of_a_batched_library_product(T, N, K):
-    """From 17 tokens, a long K and few output features: shares of K as one batched product (four shares, two
-    above 256 tokens); a K that does not divide into shares of whole 16-byte pieces, and more than 1.4 million
-    outputs, take the plain product."""
-    from qwen_decoder_b200.parts.linear import Linear
-    from qwen_decoder_b200.parts import matmul_backend
-    lin = Linear(K, [("p", N)], bias=False)
-    w = bind(lin, torch.bfloat16, 8, scale=0.03)
-    x = torch.randn(T, K, generator=torch.Generator().manual_seed(9))
-    x[:, K // 2:] *= 3.0                       # the shares of K differ in weight
-    x = x.to(torch.bfloat16)
-    got = lin.forward_partial(x.to(DEV))
-    shares = matmul_backend.library_shares(T, N, K)
-    per = 4 if T <= 256 else 2
-    assert shares == (0 if T * N > 1_400_000 or K % (8 * per) else per)
-    assert (got.dim() == 3 and got.shape[0] == shares and got.dtype == torch.float32) if shares else got.dim() == 2
-    close(total(got), plain_model.linear(x.double(), w["p.weight"]), torch.bfloat16)
-
-
 def attention_setup(dtype, H, G, d, D, window, page_size=16):
     rot = create_part("position", "rotary", head_dim=d, rotary_dim=d, base=30000.0, pairing="adjacent")
     rot.prepare(600, DEV)

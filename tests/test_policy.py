@@ -9,21 +9,24 @@ from qwen_decoder_b200.parts import matmul_backend
 @pytest.mark.parametrize("T,N,K,want", [
     (16, 2048, 11008, 0),        # up to 16 tokens the few-token kernels take the product
     (17, 2048, 11008, 4), (64, 2048, 11008, 4), (256, 2048, 11008, 4),
-    (257, 2048, 11008, 2), (576, 2048, 11008, 2),       # 512 prompt tokens beside 64 decoding requests
-    (700, 2048, 11008, 0),       # more than 1.4 million outputs
-    (64, 3584, 18944, 4), (384, 3584, 18944, 2), (512, 3584, 18944, 0),
+    (257, 2048, 11008, 0), (576, 2048, 11008, 0),       # above 256 tokens the plain product stands
+    (64, 3584, 18944, 4), (384, 3584, 18944, 0),
     (64, 5120, 27648, 0),        # too many output features to leave the GPU idle
     (64, 2048, 2048, 0),         # K no longer than the output is wide
     (64, 2560, 2048, 0),
     (64, 520, 4104, 0),          # shares of 1,026 columns would not start on 16-byte boundaries
-    (300, 136, 4112, 2), (200, 136, 4112, 0),
+    (300, 136, 4128, 0), (200, 136, 4112, 0), (200, 136, 4128, 4),
 ])
-def test_library_shares(T, N, K, want):
+def test_library_shares(T, N, K, want, monkeypatch):
     assert matmul_backend.mode == "auto"
+    assert matmul_backend.library_shares(T, N, K) == 0          # off unless a number of shares is set
+    monkeypatch.setattr(matmul_backend, "library_split_k", 4)
     assert matmul_backend.library_shares(T, N, K) == want
 
 
 def test_library_shares_follow_the_mode(monkeypatch):
+    monkeypatch.setattr(matmul_backend, "library_split_k", 4)
+    assert matmul_backend.library_shares(64, 2048, 11008) == 4
     monkeypatch.setattr(matmul_backend, "mode", "cublas")
     assert matmul_backend.library_shares(64, 2048, 11008) == 0
     monkeypatch.setattr(matmul_backend, "mode", "auto")
